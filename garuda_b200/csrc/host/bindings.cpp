@@ -1,0 +1,166 @@
+// Python bindings of the host runtime: cache manager, scheduler, generator.
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "cache_manager.hpp"
+#include "scheduler.hpp"
+
+namespace py = pybind11;
+using namespace garuda;
+
+PYBIND11_MODULE(_garuda_host, m) {
+  m.doc() = "garuda_b200 host runtime: paged-cache bookkeeping, scheduler, splitmix64";
+
+  py::register_exception<CacheError>(m, "CacheError");
+  py::register_exception<OutOfPages>(m, "OutOfPages", m.attr("CacheError").ptr());
+  py::register_exception<SchedulerError>(m, "SchedulerError");
+  py::register_exception<Busy>(m, "Busy", m.attr("SchedulerError").ptr());
+
+  py::class_<GroupConfig>(m, "GroupConfig")
+      .def(py::init([](int num_pages, int window) {
+             GroupConfig g;
+             g.num_pages = num_pages;
+             g.window = window;
+             return g;
+           }),
+           py::arg("num_pages"), py::arg("window") = 0)
+      .def_readwrite("num_pages", &GroupConfig::num_pages)
+      .def_readwrite("window", &GroupConfig::window);
+
+  py::class_<CacheManager>(m, "CacheManager")
+      .def(py::init<std::vector<GroupConfig>, int, int, int>(), py::arg("groups"), py::arg("page_size"),
+           py::arg("max_requests"), py::arg("max_positions"))
+      .def("acquire", &CacheManager::acquire)
+      .def("pages_needed", &CacheManager::pages_needed)
+      .def("can_reserve", &CacheManager::can_reserve)
+      .def("reserve", &CacheManager::reserve)
+      .def("commit", &CacheManager::commit)
+      .def("release", &CacheManager::release)
+      .def("known", &CacheManager::known)
+      .def("length", &CacheManager::length)
+      .def("slot", &CacheManager::slot)
+      .def("reserved_length", &CacheManager::reserved_length)
+      .def("block_table_row",
+           [](const CacheManager& c, int64_t request, int group) {
+             py::array_t<int32_t> out(c.max_pages_per_request());
+             c.block_table_row(request, group, out.mutable_data(), c.max_pages_per_request());
+             return out;
+           })
+      .def("fill_block_tables",
+           // out: int32 [groups, rows, width]; row i is request ids[i]
+           [](const CacheManager& c, const std::vector<int64_t>& ids,
+              py::array_t<int32_t, py::array::c_style> out) {
+             auto buf = out.mutable_unchecked<3>();
+             if (buf.shape(0) != c.num_groups() || buf.shape(1) < static_cast<py::ssize_t>(ids.size()))
+               throw CacheError("fill_block_tables: output has the wrong shape");
+             const int width = static_cast<int>(buf.shape(2));
+             for (int g = 0; g < c.num_groups(); ++g)
+               for (size_t i = 0; i < ids.size(); ++i)
+                 c.block_table_row(ids[i], g, &buf(g, i, 0), width);
+           })
+      .def_property_readonly("num_groups", &CacheManager::num_groups)
+      .def_property_readonly("page_size", &CacheManager::page_size)
+      .def_property_readonly("max_pages_per_request", &CacheManager::max_pages_per_request)
+      .def_property_readonly("max_positions", &CacheManager::max_positions)
+      .def_property_readonly("max_requests", &CacheManager::max_requests)
+      .def("free_pages", &CacheManager::free_pages)
+      .def("total_pages", &CacheManager::total_pages)
+      .def("window", [](const CacheManager& c, int g) { return c.group(g).window; })
+      .def_property_readonly("free_slots", &CacheManager::free_slots)
+      .def_property_readonly("live_requests", &CacheManager::live_requests)
+      .def("first_live_position", &CacheManager::first_live_position)
+      .def("check_invariants", &CacheManager::check_invariants)
+      .def_property_readonly("pages_handed_out", &CacheManager::pages_handed_out)
+      .def_property_readonly("pages_reused", &CacheManager::pages_reused);
+
+  py::class_<Rng>(m, "Rng")
+      .def(py::init<uint64_t>(), py::arg("seed") = 0)
+      .def("next_u64", &Rng::next_u64)
+      .def("next_f32", &Rng::next_f32)
+      .def_property_readonly("state", &Rng::state);
+
+  py::class_<SamplingParams>(m, "SamplingParams")
+      .def(py::init([](float temperature, float top_p, int top_k, int max_tokens, py::object seed) {
+             SamplingParams p;
+             p.temperature = temperature;
+             p.top_p = top_p;
+             p.top_k = top_k;
+             p.max_tokens = max_tokens;
+             p.has_seed = !seed.is_none();
+             p.seed = seed.is_none() ? 0 : seed.cast<uint64_t>();
+             return p;
+           }),
+           py::arg("temperature") = 0.8f, py::arg("top_p") = 0.95f, py::arg("top_k") = 40,
+           py::arg("max_tokens") = 128, py::arg("seed") = py::none())
+      .def_readwrite("temperature", &SamplingParams::temperature)
+      .def_readwrite("top_p", &SamplingParams::top_p)
+      .def_readwrite("top_k", &SamplingParams::top_k)
+      .def_readwrite("max_tokens", &SamplingParams::max_tokens)
+      .def_readwrite("has_seed", &SamplingParams::has_seed)
+      .def_readwrite("seed", &SamplingParams::seed)
+      .def("problem", &SamplingParams::problem);
+
+  py::class_<SchedulerConfig>(m, "SchedulerConfig")
+      .def(py::init<>())
+      .def_readwrite("max_concurrent", &SchedulerConfig::max_concurrent)
+      .def_readwrite("queue_capacity", &SchedulerConfig::queue_capacity)
+      .def_readwrite("max_batch_tokens", &SchedulerConfig::max_batch_tokens)
+      .def_readwrite("prefill_chunk", &SchedulerConfig::prefill_chunk)
+      .def_readwrite("max_context", &SchedulerConfig::max_context)
+      .def_readwrite("eos_token_id", &SchedulerConfig::eos_token_id)
+      .def_readwrite("vocab_size", &SchedulerConfig::vocab_size)
+      .def_readwrite("ignore_eos", &SchedulerConfig::ignore_eos);
+
+  py::class_<PlanEntry>(m, "PlanEntry")
+      .def_readonly("id", &PlanEntry::id)
+      .def_readonly("slot", &PlanEntry::slot)
+      .def_readonly("start", &PlanEntry::start)
+      .def_readonly("tokens", &PlanEntry::tokens)
+      .def_readonly("sample", &PlanEntry::sample)
+      .def_readonly("temperature", &PlanEntry::temperature)
+      .def_readonly("top_p", &PlanEntry::top_p)
+      .def_readonly("top_k", &PlanEntry::top_k)
+      .def_readonly("u", &PlanEntry::u);
+
+  py::enum_<EventKind>(m, "EventKind")
+      .value("Token", EventKind::Token)
+      .value("Done", EventKind::Done)
+      .value("Error", EventKind::Error);
+
+  py::class_<Event>(m, "Event")
+      .def_readonly("id", &Event::id)
+      .def_readonly("kind", &Event::kind)
+      .def_readonly("token", &Event::token)
+      .def_readonly("detail", &Event::detail);
+
+  py::class_<StepPlan>(m, "StepPlan")
+      .def_readonly("entries", &StepPlan::entries)
+      .def_readonly("preempted", &StepPlan::preempted)
+      .def_readonly("events", &StepPlan::events)
+      .def_property_readonly("num_tokens", &StepPlan::num_tokens);
+
+  py::class_<SchedulerStats>(m, "SchedulerStats")
+      .def_readonly("submitted", &SchedulerStats::submitted)
+      .def_readonly("completed", &SchedulerStats::completed)
+      .def_readonly("cancelled", &SchedulerStats::cancelled)
+      .def_readonly("failed", &SchedulerStats::failed)
+      .def_readonly("rejected_busy", &SchedulerStats::rejected_busy)
+      .def_readonly("preemptions", &SchedulerStats::preemptions)
+      .def_readonly("steps", &SchedulerStats::steps)
+      .def_readonly("tokens_fed", &SchedulerStats::tokens_fed)
+      .def_readonly("tokens_generated", &SchedulerStats::tokens_generated)
+      .def_readonly("running", &SchedulerStats::running)
+      .def_readonly("queued", &SchedulerStats::queued);
+
+  py::class_<Scheduler>(m, "Scheduler")
+      .def(py::init<SchedulerConfig, CacheManager*>(), py::arg("config"), py::arg("cache"),
+           py::keep_alive<1, 3>())
+      .def("submit", &Scheduler::submit, py::arg("prompt"), py::arg("params"), py::arg("priority") = 0)
+      .def("cancel", &Scheduler::cancel)
+      .def("plan", &Scheduler::plan)
+      .def("complete", &Scheduler::complete)
+      .def("fail", &Scheduler::fail)
+      .def("idle", &Scheduler::idle)
+      .def("stats", &Scheduler::stats);
+}

@@ -1,0 +1,240 @@
+// Turning logits into tokens. garuda/src/runtime/mod.rs:87-175.
+#include "common.cuh"
+
+namespace {
+
+// Greedy: the first maximum wins (a strict `>` scan from index 0, :99-107), so
+// among equal values the lowest index is kept, and NaN never wins.
+__device__ int block_argmax(const float* __restrict__ row, int V) {
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) { best = v; best_i = i; }  // ascending i within a thread: first maximum
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ int result;
+  auto better = [](float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { sv[warp] = best; si[warp] = best_i; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    best_i = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) result = best_i == 0x7fffffff ? 0 : best_i;
+  }
+  __syncthreads();
+  return result;
+}
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V) {
+  const int tok = block_argmax(logits + (size_t)blockIdx.x * V, V);
+  if (threadIdx.x == 0) out[blockIdx.x] = tok;
+}
+
+// ------------------------------------------------------------------ sampling
+// Temperature, softmax over the whole vocabulary, top-k, top-p, then a draw
+// (garuda/src/runtime/mod.rs:109-175). The reference sorts the candidates by
+// (probability descending, token id ascending), keeps the first k, of those the
+// shortest prefix whose probabilities sum to top_p, and walks that list
+// subtracting probabilities from u * total until it reaches zero. Survivors are
+// not renormalised.
+//
+// Nothing is sorted here. "The j-th candidate" is found by bisecting on the bit
+// pattern of the probability (non-negative floats order like their bits): for a
+// threshold tau one pass gives how many probabilities exceed it, how many equal
+// it, and the sum of those that exceed it. Sums are taken in 64-bit so that
+// their order does not matter.
+
+struct Tally {
+  int gt;      // how many p > tau
+  int eq;      // how many p == tau
+  double sgt;  // sum of those > tau
+  float tau;
+  __device__ int ge() const { return gt + eq; }
+  __device__ double sge() const { return sgt + (double)eq * (double)tau; }
+};
+
+__device__ Tally block_tally(const float* __restrict__ p, int V, uint32_t tau_bits, double* sh_d, int* sh_i) {
+  int gt = 0, eq = 0;
+  double sgt = 0.0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = p[i];
+    const uint32_t b = __float_as_uint(v);
+    if (b > tau_bits) { ++gt; sgt += (double)v; }
+    else if (b == tau_bits) ++eq;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    gt += __shfl_xor_sync(0xffffffffu, gt, o);
+    eq += __shfl_xor_sync(0xffffffffu, eq, o);
+    sgt += __shfl_xor_sync(0xffffffffu, sgt, o);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();  // everyone has read the previous result
+  if (lane == 0) { sh_i[warp] = gt; sh_i[32 + warp] = eq; sh_d[warp] = sgt; }
+  __syncthreads();
+  Tally t{0, 0, 0.0, __uint_as_float(tau_bits)};
+  for (int w = 0; w < nw; ++w) { t.gt += sh_i[w]; t.eq += sh_i[32 + w]; t.sgt += sh_d[w]; }
+  return t;
+}
+
+// The largest tau for which pred(tally(tau)) holds. pred must hold for small
+// tau and fail for large ones. Returns false if it does not even hold at 0.
+template <typename Pred>
+__device__ bool bisect(const float* p, int V, double* sh_d, int* sh_i, Pred pred, Tally* found) {
+  Tally best = block_tally(p, V, 0u, sh_d, sh_i);
+  if (!pred(best)) return false;
+  uint32_t cur = 0;
+  for (int bit = 30; bit >= 0; --bit) {  // probabilities lie in [0, 1]: the sign bit is never set
+    const uint32_t cand = cur | (1u << bit);
+    if (cand > 0x3f800000u) continue;    // above 1.0 nothing is left
+    const Tally t = block_tally(p, V, cand, sh_d, sh_i);
+    if (pred(t)) { cur = cand; best = t; }
+  }
+  *found = best;
+  return true;
+}
+
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ u, int32_t* __restrict__ out, float* __restrict__ scratch, int V) {
+  __shared__ double sh_d[32];
+  __shared__ int sh_i[64];
+  __shared__ float sh_f[32];
+  __shared__ int sh_cnt[1024];
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * V;
+  float* p = scratch + (size_t)r * V;
+  const float temp = temperature[r];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (temp == 0.f) {  // greedy (:99-107)
+    const int tok = block_argmax(row, V);
+    if (threadIdx.x == 0) out[r] = tok;
+    return;
+  }
+
+  // softmax(logits / temperature), with the reference's uniform fallbacks
+  // (garuda/src/simd/mod.rs:132-158)
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, row[i] / temp);
+  m = gb::warp_max(m);
+  if (lane == 0) sh_f[warp] = m;
+  __syncthreads();
+  m = -INFINITY;
+  for (int w = 0; w < nw; ++w) m = fmaxf(m, sh_f[w]);
+  const bool finite_max = (m - m) == 0.f;  // neither infinite nor NaN
+  double sum = 0.0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float e = finite_max ? expf(row[i] / temp - m) : 1.0f;
+    p[i] = e;
+    sum += (double)e;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) sh_d[warp] = sum;
+  __syncthreads();
+  sum = 0.0;
+  for (int w = 0; w < nw; ++w) sum += sh_d[w];
+  const float fsum = (float)sum;
+  const bool good = finite_max && (fsum - fsum) == 0.f && fsum > 0.f;  // a NaN among the inputs fails here
+  const float inv = good ? 1.0f / fsum : 0.f;
+  const float uniform = 1.0f / (float)V;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) p[i] = good ? p[i] * inv : uniform;
+  __syncthreads();
+
+  // n: how many candidates survive top-k (:144-158) and top-p (:161-172)
+  int n = V;
+  Tally t;
+  const float tp = top_p[r];
+  if (tp < 1.0f) {
+    const double want = (double)tp;
+    if (bisect(p, V, sh_d, sh_i, [&](const Tally& a) { return a.ge() >= 1 && a.sge() >= want; }, &t)) {
+      // candidates above tau, then as many of those equal to tau as it takes to reach top_p
+      int ties = t.tau > 0.f ? (int)ceil((want - t.sgt) / (double)t.tau) : t.eq;
+      ties = max(1, min(ties, t.eq));
+      n = t.gt + ties;
+    }
+  }
+  const int k = top_k[r];
+  if (k > 0 && k < n) n = k;
+
+  // total mass of the first n (:109), and the point the walk has to reach (:117)
+  bisect(p, V, sh_d, sh_i, [&](const Tally& a) { return a.ge() >= n; }, &t);
+  const float total = (float)(t.sgt + (double)(n - t.gt) * (double)t.tau);
+  int j = 1;  // 1-based rank of the chosen candidate; zero mass: the most likely one (:111-115)
+  if (total > 0.f) {
+    const double point = (double)(u[r] * total);
+    Tally x;
+    if (bisect(p, V, sh_d, sh_i, [&](const Tally& a) { return a.ge() >= 1 && a.sge() >= point; }, &x)) {
+      int ties = x.tau > 0.f ? (int)ceil((point - x.sgt) / (double)x.tau) : 1;
+      ties = max(1, min(ties, x.eq));
+      j = x.gt + ties;
+    } else {
+      j = n;
+    }
+    j = max(1, min(j, n));
+  }
+
+  // the j-th candidate: value of the j-th largest, then by token id among equals
+  bisect(p, V, sh_d, sh_i, [&](const Tally& a) { return a.ge() >= j; }, &t);
+  const int want_tie = j - t.gt;  // 1-based among p == tau, ascending id
+  const uint32_t tau_bits = __float_as_uint(t.tau);
+  const int chunk = (V + blockDim.x - 1) / blockDim.x;
+  const int lo = threadIdx.x * chunk, hi = min(V, lo + chunk);
+  int mine = 0;
+  for (int i = lo; i < hi; ++i) mine += (__float_as_uint(p[i]) == tau_bits);
+  sh_cnt[threadIdx.x] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int seen = 0, owner = -1, skip = 0;
+    for (int th = 0; th < (int)blockDim.x; ++th) {
+      if (seen + sh_cnt[th] >= want_tie) { owner = th; skip = want_tie - seen; break; }
+      seen += sh_cnt[th];
+    }
+    sh_i[0] = owner;
+    sh_i[1] = skip;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x == sh_i[0]) {
+    int left = sh_i[1];
+    for (int i = lo; i < hi; ++i) {
+      if (__float_as_uint(p[i]) == tau_bits && --left == 0) { out[r] = i; break; }
+    }
+  }
+}
+
+}  // namespace
+
+GB_EXPORT int gb_argmax(const float* logits, int32_t* out, int R, int V, cudaStream_t stream) {
+  if (R <= 0) return GB_OK;
+  if (V <= 0) return gb::fail(GB_BAD_ARGUMENT, "cannot sample from empty logits");
+  argmax_kernel<<<R, 1024, 0, stream>>>(logits, out, V);
+  return gb::check_launch("argmax");
+}
+
+// One token per row of logits [R, V]. Rows with temperature 0 are greedy.
+// scratch: R * V floats of work space (the probabilities).
+GB_EXPORT int gb_sample(const float* logits, const float* temperature, const int32_t* top_k,
+                        const float* top_p, const float* u, int32_t* out, float* scratch, int R, int V,
+                        cudaStream_t stream) {
+  if (R <= 0) return GB_OK;
+  if (V <= 0) return gb::fail(GB_BAD_ARGUMENT, "cannot sample from empty logits");
+  sample_kernel<<<R, 1024, 0, stream>>>(logits, temperature, top_k, top_p, u, out, scratch, V);
+  return gb::check_launch("sample");
+}

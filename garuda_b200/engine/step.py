@@ -1,0 +1,179 @@
+"""The step function: one batch of (request, its next tokens) in, logits at the
+wanted places out.
+
+The reference's contract for a forward call (garuda/src/core/mod.rs:232-261):
+consume only positions not seen yet, advance every layer by one position per
+token, fail with an error and not a panic, be deterministic; and nothing is
+half-applied: a batch is checked before any cache is touched
+(garuda/src/llama/mod.rs:1160-1172, :1061-1067). The same holds here, for a
+batch that may mix portions of prompts with single decoded tokens, cut anywhere.
+A step runs only the tokens it is given; everything earlier comes from the cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import PagedCache
+from .batch import StepBatch, StepContext, Workspace
+
+
+class StepError(ValueError):
+    """A batch that was refused; no request and no page has changed."""
+
+
+@dataclass
+class StepEntry:
+    request: int                      # the caller's id of the request
+    tokens: Sequence[int]             # its next tokens, in order
+    want: Sequence[int] = field(default_factory=tuple)   # places among them whose logits are wanted
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+class StepRunner:
+    def __init__(self, model, cache: PagedCache, ops, dtype: torch.dtype, device):
+        self.model, self.cache, self.ops, self.dtype = model, cache, ops, dtype
+        self.device = torch.device(device)
+        self.ws = Workspace(self.device)
+        self.vocab = model.spec.vocab_size
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------------ checks
+    def _validate_and_reserve(self, entries: Sequence[StepEntry]):
+        mgr = self.cache.manager
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        wants = []
+        fresh = []
+        for e in entries:
+            if e.request in seen:
+                raise StepError(f"request {e.request} appears twice in one step")
+            seen.add(e.request)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.request} brings no tokens")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab:
+                    raise StepError(f"token {t} of request {e.request} is outside the vocabulary of {self.vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"request {e.request} wants logits at place {w} of {n} tokens")
+            known = mgr.known(e.request)
+            old = mgr.length(e.request) if known else 0
+            if old + n > mgr.max_positions:
+                raise StepError(f"{n} tokens do not fit the {mgr.max_positions}-position context "
+                                f"({old} used) of request {e.request}")
+            if not known:
+                fresh.append(e.request)
+            wants.append((e.request, old + n))
+        if len(fresh) > mgr.free_slots:
+            raise StepError(f"{len(fresh)} new requests but only {mgr.free_slots} request slots are free")
+        for r in fresh:
+            self.cache.acquire(r)
+        try:
+            if not mgr.can_reserve(wants):
+                need = [mgr.pages_needed(r, n) for r, n in wants]
+                total = [sum(x[g] for x in need) for g in range(mgr.num_groups)]
+                free = [mgr.free_pages(g) for g in range(mgr.num_groups)]
+                raise self.cache.host_module.OutOfPages(
+                    f"the step needs {total} pages per group but only {free} are free")
+            for r, n in wants:
+                mgr.reserve(r, n)
+        except Exception:
+            for r in fresh:
+                mgr.release(r)
+            raise
+        return wants
+
+    # ------------------------------------------------------------------ batch
+    def build_batch(self, entries: Sequence[StepEntry], new_lens) -> StepBatch:
+        mgr = self.cache.manager
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        W = sum(len(e.want) for e in entries)
+        G, width = mgr.num_groups, self.cache.table_width
+        offs = {}
+        cursor = 0
+        for name, n in (("token_ids", T), ("positions", T), ("token_req", T), ("cu_q", R + 1),
+                        ("kv_lens", R), ("slots", R), ("logit_rows", max(W, 1)),
+                        ("tables", G * R * width)):
+            offs[name] = (cursor, n)
+            cursor += _align(n)
+        host = np.empty(cursor, dtype=np.int32)
+
+        def view(name):
+            o, n = offs[name]
+            return host[o:o + n]
+
+        token_ids, positions, token_req = view("token_ids"), view("positions"), view("token_req")
+        cu_q, kv_lens, slots, logit_rows = view("cu_q"), view("kv_lens"), view("slots"), view("logit_rows")
+        logit_rows[:] = 0
+        t = w = 0
+        cu_q[0] = 0
+        max_q = max_kv = 0
+        for i, (e, (_, new_len)) in enumerate(zip(entries, new_lens)):
+            n = len(e.tokens)
+            start = new_len - n
+            token_ids[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
+            positions[t:t + n] = np.arange(start, new_len, dtype=np.int32)
+            token_req[t:t + n] = i
+            for place in e.want:
+                logit_rows[w] = t + int(place)
+                w += 1
+            t += n
+            cu_q[i + 1] = t
+            kv_lens[i] = new_len
+            slots[i] = mgr.slot(e.request)
+            max_q, max_kv = max(max_q, n), max(max_kv, new_len)
+        tables = view("tables").reshape(G, R, width) if G else None
+        if G:
+            mgr.fill_block_tables([e.request for e in entries], tables)
+
+        cpu = torch.from_numpy(host)
+        if self.device.type == "cuda":
+            dev = cpu.pin_memory().to(self.device, non_blocking=True)
+        else:
+            dev = cpu.clone()
+
+        def dview(name):
+            o, n = offs[name]
+            return dev[o:o + n]
+
+        dtables = [dview("tables").view(G, R, width)[g] for g in range(G)] if G else []
+        return StepBatch(
+            num_tokens=T, num_requests=R, token_ids=dview("token_ids"), positions=dview("positions"),
+            token_req=dview("token_req"), cu_q=dview("cu_q"), kv_lens=dview("kv_lens"),
+            slots=dview("slots"), block_tables=dtables, logit_rows=dview("logit_rows")[:W],
+            num_logit_rows=W, max_q_len=max_q, max_kv_len=max_kv,
+            host={"token_ids": token_ids, "positions": positions, "token_req": token_req, "cu_q": cu_q,
+                  "kv_lens": kv_lens, "slots": slots, "logit_rows": logit_rows[:W],
+                  "requests": [e.request for e in entries]},
+        )
+
+    # ------------------------------------------------------------------ run
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Logits ``[W, vocab]`` (float32, on the device) at the wanted places, in
+        the order of the entries and of their ``want``. Valid until the next step."""
+        new_lens = self._validate_and_reserve(entries)
+        batch = self.build_batch(entries, new_lens)
+        ctx = StepContext(batch=batch, ws=self.ws, ops=self.ops, dtype=self.dtype)
+        caches = self.cache.layer_caches(batch.block_tables)
+        logits = self.model.forward(ctx, caches)
+        mgr = self.cache.manager
+        for r, n in new_lens:
+            mgr.commit(r, n)
+        self.steps += 1
+        self.tokens_run += batch.num_tokens
+        return logits
+
+    def end(self, request: int) -> None:
+        """The request is finished: what it holds is given back."""
+        self.cache.release(request)

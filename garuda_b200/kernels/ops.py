@@ -1,0 +1,258 @@
+"""The kernel set of the product path: thin, checking wrappers around the CUDA
+entry points. There is no other implementation behind them: without a CUDA
+device or without the compiled library every call fails loudly.
+
+Each method takes torch tensors that live on the device, checks dtypes, shapes
+and contiguity, and launches on torch's current stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p, c_int, c_float, c_longlong
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..csrc.build import load_kernel_lib
+
+GB_F32, GB_BF16 = 0, 1
+_TAG = {torch.float32: GB_F32, torch.bfloat16: GB_BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _tag(t: torch.Tensor, what: str) -> int:
+    try:
+        return _TAG[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class CudaOps:
+    """Hand-written sm_100a kernels. ``tensor_cores=False`` keeps every matrix
+    product and the attention on the plain 32-bit-arithmetic kernels (the true
+    32-bit path uses them in any case)."""
+
+    name = "cuda"
+
+    def __init__(self, device="cuda:0", tensor_cores: bool = True):
+        if not torch.cuda.is_available():
+            raise KernelError("garuda_b200 needs a CUDA device: there is no CPU path")
+        self.device = torch.device(device)
+        self.core = load_kernel_lib("garuda_core")
+        self._declare_core()
+        self.tc = None
+        if tensor_cores:
+            from .tc import TensorCoreKernels
+            self.tc = TensorCoreKernels(self)
+        self._inv_freq = {}
+
+    # ------------------------------------------------------------------ plumbing
+    def _declare_core(self):
+        L = self.core
+        L.gb_last_error.restype = ctypes.c_char_p
+        sig = {
+            "gb_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+            "gb_rmsnorm": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+            "gb_rope_kv_append": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                  c_int, c_void_p],
+            "gb_rope_inplace": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+            "gb_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+            "gb_residual_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+            "gb_gemm_simple": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+            "gb_attention_simple": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                    c_void_p],
+            "gb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+            "gb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                          c_void_p],
+        }
+        for name, argtypes in sig.items():
+            fn = getattr(L, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _check(self, lib, code: int, what: str) -> None:
+        if code != 0:
+            raise KernelError(f"{what}: {lib.gb_last_error().decode()}")
+
+    def _on_device(self, *tensors):
+        for t in tensors:
+            if t is not None:
+                _need(t.is_cuda, "kernel operands must live on the CUDA device")
+
+    # ------------------------------------------------------------------ parts
+    def inv_freq(self, theta: float, head_dim: int) -> torch.Tensor:
+        """``1 / theta^(2i/head_dim)`` in 32-bit (garuda/src/simd/mod.rs:199), once per
+        (theta, head_dim)."""
+        key = (float(theta), int(head_dim))
+        if key not in self._inv_freq:
+            i = np.arange(head_dim // 2, dtype=np.float32)
+            f = np.float32(1.0) / np.power(np.float32(theta), np.float32(2.0) * i / np.float32(head_dim),
+                                           dtype=np.float32)
+            self._inv_freq[key] = torch.from_numpy(f).to(self.device)
+        return self._inv_freq[key]
+
+    def embedding(self, table, ids, out):
+        self._on_device(table, ids, out)
+        _need(out.dtype == torch.float32 and out.is_contiguous(), "embedding: out must be contiguous float32")
+        _need(ids.dtype == torch.int32, "embedding: ids must be int32")
+        _need(table.is_contiguous() and table.shape[1] == out.shape[1], "embedding: widths differ")
+        T = ids.shape[0]
+        _need(out.shape[0] >= T, "embedding: out has too few rows")
+        self._check(self.core, self.core.gb_embedding(
+            table.data_ptr(), _tag(table, "embedding table"), ids.data_ptr(), out.data_ptr(), T,
+            table.shape[1], table.shape[0], self._stream()), "embedding")
+
+    def rmsnorm(self, x, weight, eps, out, rows=None):
+        self._on_device(x, weight, out, rows)
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "rmsnorm: x must be contiguous float32")
+        d = x.shape[1]
+        _need(weight.numel() == d and out.shape[1] == d and out.is_contiguous(), "rmsnorm: widths differ")
+        n = x.shape[0] if rows is None else rows.shape[0]
+        _need(out.shape[0] == n, "rmsnorm: out has the wrong number of rows")
+        if rows is not None:
+            _need(rows.dtype == torch.int32, "rmsnorm: rows must be int32")
+        self._check(self.core, self.core.gb_rmsnorm(
+            x.data_ptr(), weight.data_ptr(), _tag(weight, "norm weight"), float(eps), out.data_ptr(),
+            _tag(out, "rmsnorm out"), _ptr(rows), n, d, self._stream()), "rmsnorm")
+
+    def linear(self, a, w, out, accumulate: bool = False):
+        """``out[M,N] (+)= a[M,K] @ w[N,K]^T``; accumulation is into a 32-bit ``out``."""
+        self._on_device(a, w, out)
+        _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "linear: operands must be matrices")
+        M, K = a.shape
+        N = w.shape[0]
+        _need(w.shape[1] == K and out.shape == (M, N), f"linear: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
+        _need(a.dtype == w.dtype, "linear: a and w must have one dtype")
+        _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
+        if self.tc is not None and a.dtype == torch.bfloat16 and self.tc.linear(a, w, out, accumulate):
+            return
+        self._check(self.core, self.core.gb_gemm_simple(
+            a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _tag(a, "linear input"),
+            _tag(out, "linear output"), int(accumulate), self._stream()), "linear")
+
+    def pack_gate_up(self, gate, up):
+        """The layout ``linear_swiglu`` wants: gate rows, then up rows."""
+        return torch.cat([gate, up], dim=0).contiguous()
+
+    def linear_swiglu(self, ctx, h, w_gate_up, act):
+        """``act[M,F] = silu(h @ gate^T) * (h @ up^T)``, the activation in 32-bit."""
+        M, F = act.shape
+        if self.tc is not None and h.dtype == torch.bfloat16 and self.tc.linear_swiglu(h, w_gate_up, act):
+            return
+        tmp = ctx.ws.get("gate_up", (M, 2 * F), torch.float32)
+        self.linear(h, w_gate_up, tmp)
+        self.silu_mul(tmp, act)
+
+    def silu_mul(self, gate_up, out):
+        self._on_device(gate_up, out)
+        M, F = out.shape
+        _need(gate_up.shape == (M, 2 * F) and gate_up.is_contiguous() and out.is_contiguous(),
+              "silu_mul: gate_up must be [M, 2F] for out [M, F]")
+        self._check(self.core, self.core.gb_silu_mul(
+            gate_up.data_ptr(), _tag(gate_up, "silu_mul in"), out.data_ptr(), _tag(out, "silu_mul out"),
+            M, F, self._stream()), "silu_mul")
+
+    def residual_add(self, x, y):
+        self._on_device(x, y)
+        _need(x.dtype == torch.float32 and x.shape == y.shape and x.is_contiguous() and y.is_contiguous(),
+              "residual_add: x must be contiguous float32 of y's shape")
+        self._check(self.core, self.core.gb_residual_add(
+            x.data_ptr(), y.data_ptr(), _tag(y, "residual_add y"), x.numel(), self._stream()), "residual_add")
+
+    def rope_kv_append(self, qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
+                       heads, kv_heads, head_dim, rotary, page_size):
+        """Split ``qkv [T, (heads + 2 kv_heads) head_dim]``, rotate queries and keys
+        (``rotary`` None: leave them), write queries to ``q_out [T, heads, head_dim]``
+        and keys and values into their pages."""
+        self._on_device(qkv, q_out, k_pool, v_pool, positions, token_req, block_table)
+        T = qkv.shape[0]
+        _need(qkv.stride(1) == 1 and qkv.shape[1] == (heads + 2 * kv_heads) * head_dim,
+              "rope_kv_append: qkv has the wrong width")
+        _need(q_out.is_contiguous() and q_out.shape == (T, heads, head_dim), "rope_kv_append: q_out shape")
+        _need(positions.dtype == torch.int32 and token_req.dtype == torch.int32, "rope_kv_append: int32 indices")
+        if kv_heads:
+            _need(k_pool.dtype == q_out.dtype and v_pool.dtype == q_out.dtype, "rope_kv_append: cache dtype")
+            _need(k_pool.is_contiguous() and v_pool.is_contiguous() and
+                  tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim), "rope_kv_append: pool shape")
+            _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "rope_kv_append: block table")
+        inv = None
+        inter = 0
+        if rotary is not None:
+            _need(rotary.head_dim == head_dim, "rope_kv_append: rotary is for another head_dim")
+            inv = self.inv_freq(rotary.theta, head_dim)
+            inter = int(rotary.interleaved)
+        self._check(self.core, self.core.gb_rope_kv_append(
+            qkv.data_ptr(), _tag(qkv, "qkv"), qkv.stride(0), q_out.data_ptr(), _ptr(k_pool), _ptr(v_pool),
+            _tag(q_out, "q_out"), positions.data_ptr(), token_req.data_ptr(), _ptr(block_table),
+            block_table.shape[1] if block_table is not None else 0, T, heads, kv_heads, head_dim,
+            _ptr(inv), inter, page_size, self._stream()), "rope_kv_append")
+
+    def rope_inplace(self, x, positions, theta, interleaved):
+        """Rotate ``x [T, H, head_dim]`` (float32, rows may be strided) in place."""
+        self._on_device(x, positions)
+        _need(x.dtype == torch.float32 and x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == x.shape[2],
+              "rope_inplace: x must be float32 [T, H, hd] with contiguous heads")
+        T, H, hd = x.shape
+        self._check(self.core, self.core.gb_rope_inplace(
+            x.data_ptr(), x.stride(0), T, H, hd, positions.data_ptr(),
+            self.inv_freq(theta, hd).data_ptr(), int(interleaved), self._stream()), "rope_inplace")
+
+    def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
+                        scale, window, page_size, num_requests, max_q_len, max_kv_len):
+        self._on_device(q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out)
+        T, Hq, hd = q.shape
+        Hkv = k_pool.shape[1]
+        _need(q.is_contiguous() and out.is_contiguous() and out.shape == (T, Hq * hd), "attention: q/out shape")
+        _need(q.dtype == k_pool.dtype == v_pool.dtype == out.dtype, "attention: one dtype for q, cache and out")
+        _need(tuple(k_pool.shape[1:]) == (Hkv, page_size, hd) and k_pool.shape == v_pool.shape,
+              "attention: pool shape")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: block table")
+        if self.tc is not None and q.dtype == torch.bfloat16 and self.tc.paged_attention(
+                q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
+                num_requests, max_q_len, max_kv_len):
+            return
+        self._check(self.core, self.core.gb_attention_simple(
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _tag(q, "attention q"),
+            block_table.data_ptr(), block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(),
+            token_req.data_ptr(), out.data_ptr(), T, Hq, Hkv, hd, float(scale), int(window),
+            int(page_size), self._stream()), "attention")
+
+    # ------------------------------------------------------------------ sampling
+    def argmax(self, logits, out):
+        self._on_device(logits, out)
+        _need(logits.dtype == torch.float32 and logits.is_contiguous() and out.dtype == torch.int32,
+              "argmax: float32 logits, int32 out")
+        R, V = logits.shape
+        self._check(self.core, self.core.gb_argmax(logits.data_ptr(), out.data_ptr(), R, V, self._stream()),
+                    "argmax")
+
+    def sample(self, logits, temperature, top_k, top_p, u, out, scratch):
+        """One token per row. ``temperature`` 0 is greedy; ``u`` is the row's uniform
+        draw. ``scratch``: float32 ``[R, V]`` work space."""
+        self._on_device(logits, temperature, top_k, top_p, u, out, scratch)
+        R, V = logits.shape
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: float32 logits")
+        _need(temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and u.dtype == torch.float32
+              and top_k.dtype == torch.int32 and out.dtype == torch.int32, "sample: parameter dtypes")
+        _need(scratch.dtype == torch.float32 and scratch.numel() >= R * V, "sample: scratch too small")
+        self._check(self.core, self.core.gb_sample(
+            logits.data_ptr(), temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), u.data_ptr(),
+            out.data_ptr(), scratch.data_ptr(), R, V, self._stream()), "sample")
