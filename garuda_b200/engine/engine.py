@@ -1,0 +1,209 @@
+"""The Python entry point: a model folder in, generated tokens out.
+
+The reference's programmatic surface is ``Engine::build`` (garuda/src/server/mod.rs:48-54,
+:343-479: read the configuration, open the checkpoint, dispatch on its
+architecture, size the cache, build the runtime) followed by
+``Scheduler::submit`` (garuda/src/scheduler/mod.rs:258-303) or
+``InferenceRuntime::start`` / ``next_token`` (garuda/src/runtime/mod.rs:560, :698).
+``Engine`` here does the first, ``generate`` the second: it submits every
+prompt to the scheduler and runs mixed steps until all have finished.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.manager import PagedCache, CacheConfig
+from ..config.engine_config import EngineConfig, parse_size
+from ..config.model_config import ConfigError, read_config_json
+from ..config.registry import build_model
+from ..csrc.build import load_host_module
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from ..weights.loader import load_weights
+from .step import StepRunner, StepEntry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[int] = field(default_factory=list)
+    finish_reason: str = ""          # "length" | "context_full" | "eos" | "error"
+    error: Optional[str] = None
+
+
+class Engine:
+    def __init__(self, model_dir: str, dtype="bfloat16", *, context: Optional[int] = None,
+                 sliding_window: int = 0, page_size: int = 32, kv_tokens: Optional[int] = None,
+                 kv_cache_bytes: Optional[int] = None, max_concurrent: int = 4,
+                 queue_capacity: int = 256, max_batch_tokens: int = 2048, prefill_chunk: int = 512,
+                 cuda_graphs: bool = True, device: int = 0, ignore_eos: bool = False,
+                 eos_token_id: Optional[int] = None, ops=None):
+        if dtype not in _DTYPES:
+            raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
+        self.dtype = _DTYPES[dtype]
+        self.model_dir = model_dir
+        config_dict = read_config_json(model_dir)
+        if sliding_window:
+            config_dict = dict(config_dict, sliding_window=int(sliding_window))
+        if ops is None:
+            from ..kernels.ops import CudaOps
+            self.device = torch.device(f"cuda:{device}")
+            torch.cuda.set_device(self.device)
+            # the 32-bit path never touches a tensor core: true 32-bit multiply-adds throughout
+            ops = CudaOps(self.device, tensor_cores=self.dtype == torch.bfloat16)
+        else:
+            self.device = torch.device(getattr(ops, "device", "cpu"))
+        self.ops = ops
+        self.config, self.model = build_model(config_dict)
+        load_weights(self.model, model_dir, ops, self.dtype, self.device)
+
+        spec = self.model.spec
+        self.max_context = min(int(context), spec.max_positions) if context else spec.max_positions
+        if self.max_context < 2:
+            raise ConfigError("the context must hold at least 2 tokens")
+        probe = PagedCache(self.model, CacheConfig(page_size=page_size, num_pages=0,
+                                                   max_requests=max_concurrent,
+                                                   max_positions=self.max_context),
+                           self.dtype, self.device, allocate=False)
+        if kv_tokens:
+            tokens = int(kv_tokens)
+        elif kv_cache_bytes:
+            per_position = max(probe.bytes_per_position(), 1)
+            tokens = int(kv_cache_bytes) // per_position
+        else:
+            tokens = max_concurrent * self.max_context
+        pages = max((tokens + page_size - 1) // page_size, 1)
+        self.cache = PagedCache(self.model, CacheConfig(page_size=page_size, num_pages=pages,
+                                                        max_requests=max_concurrent,
+                                                        max_positions=self.max_context),
+                                self.dtype, self.device)
+        self.runner = StepRunner(self.model, self.cache, ops, self.dtype, self.device)
+        self.sampler = Sampler(ops, self.device)
+        host = load_host_module()
+        self._host = host
+        sc = host.SchedulerConfig()
+        sc.max_concurrent = max_concurrent
+        sc.queue_capacity = queue_capacity
+        sc.max_batch_tokens = max_batch_tokens
+        sc.prefill_chunk = prefill_chunk
+        sc.max_context = self.max_context
+        sc.vocab_size = spec.vocab_size
+        eos = eos_token_id if eos_token_id is not None else spec.eos_token_id
+        sc.eos_token_id = -1 if eos is None else int(eos)
+        sc.ignore_eos = bool(ignore_eos)
+        self.scheduler = host.Scheduler(sc, self.cache.manager)
+        self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda"
+        if self.cuda_graphs:
+            from .graph import DecodeGraphs
+            self.runner.graphs = DecodeGraphs(self.runner, max_concurrent)
+
+    @classmethod
+    def from_config(cls, cfg: EngineConfig, **overrides) -> "Engine":
+        kv_bytes = parse_size(cfg.memory.kv_cache)
+        kwargs = dict(
+            dtype=cfg.model.dtype, context=cfg.model.context, sliding_window=cfg.model.sliding_window,
+            page_size=cfg.memory.page_size, kv_tokens=cfg.memory.kv_tokens or None,
+            kv_cache_bytes=kv_bytes or None, max_concurrent=cfg.server.max_concurrent,
+            queue_capacity=cfg.server.queue_capacity, max_batch_tokens=cfg.runtime.max_batch_tokens,
+            prefill_chunk=cfg.runtime.prefill_chunk, cuda_graphs=cfg.runtime.cuda_graphs,
+            device=cfg.runtime.device)
+        kwargs.update(overrides)
+        return cls(cfg.model.path, **kwargs)
+
+    # ------------------------------------------------------------------ raw step
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """One step of the step function; see ``StepRunner.run``."""
+        return self.runner.run(entries)
+
+    # ------------------------------------------------------------------ generate
+    def _host_params(self, p: SamplingParams):
+        p.validate()
+        return self._host.SamplingParams(temperature=p.temperature, top_p=p.top_p, top_k=p.top_k,
+                                         max_tokens=p.max_tokens, seed=p.seed)
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None,
+                 on_token=None) -> List[GenerationResult]:
+        """Generate for every prompt (lists of token ids), batching them
+        continuously. ``sampling``: one ``SamplingParams`` for all, or one per
+        prompt. ``on_token(index, token)`` is called as tokens arrive."""
+        if sampling is None:
+            sampling = SamplingParams()
+        if isinstance(sampling, SamplingParams):
+            sampling = [sampling] * len(prompts)
+        if len(sampling) != len(prompts):
+            raise ConfigError(f"{len(sampling)} sampling settings for {len(prompts)} prompts")
+        results = [GenerationResult() for _ in prompts]
+        index_of: Dict[int, int] = {}
+        pending = list(range(len(prompts)))
+        sched = self.scheduler
+        live = 0
+
+        def handle(events):
+            nonlocal live
+            for ev in events:
+                i = index_of.get(ev.id)
+                if i is None:
+                    continue
+                if ev.kind == self._host.EventKind.Token:
+                    results[i].tokens.append(ev.token)
+                    if on_token is not None:
+                        on_token(i, ev.token)
+                elif ev.kind == self._host.EventKind.Done:
+                    results[i].finish_reason = ev.detail
+                    live -= 1
+                else:
+                    results[i].finish_reason = "error"
+                    results[i].error = ev.detail
+                    live -= 1
+
+        while pending or live:
+            while pending:
+                i = pending[0]
+                try:
+                    rid = sched.submit(list(map(int, prompts[i])), self._host_params(sampling[i]))
+                except self._host.Busy:
+                    break      # the queue is full: run steps, then submit the rest
+                except (self._host.SchedulerError, ConfigError) as e:
+                    results[i].finish_reason, results[i].error = "error", str(e)
+                    pending.pop(0)
+                    continue
+                index_of[rid] = i
+                live += 1
+                pending.pop(0)
+            if not live:
+                continue
+            plan = sched.plan()
+            handle(plan.events)
+            if not plan.entries:
+                continue
+            entries = [StepEntry(e.id, e.tokens, (len(e.tokens) - 1,) if e.sample else ())
+                       for e in plan.entries]
+            try:
+                logits = self.runner.run(entries)
+                rows = [e for e in plan.entries if e.sample]
+                tokens = self.sampler.sample(logits, [e.temperature for e in rows], [e.top_k for e in rows],
+                                             [e.top_p for e in rows], [e.u for e in rows])
+            except Exception as exc:     # the step failed as a whole: its requests end with the error
+                handle(sched.fail(plan, f"{type(exc).__name__}: {exc}"))
+                continue
+            handle(sched.complete(plan, tokens))
+        return results
+
+    def stats(self) -> dict:
+        s = self.scheduler.stats()
+        m = self.cache.manager
+        out = {k: getattr(s, k) for k in ("submitted", "completed", "cancelled", "failed", "rejected_busy",
+                                          "preemptions", "steps", "tokens_fed", "tokens_generated",
+                                          "running", "queued")}
+        out["pages_free"] = [m.free_pages(g) for g in range(m.num_groups)]
+        out["pages_total"] = [m.total_pages(g) for g in range(m.num_groups)]
+        out["pages_reused"] = m.pages_reused
+        out["engine_steps"] = self.runner.steps
+        return out

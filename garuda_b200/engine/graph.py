@@ -1,0 +1,135 @@
+"""Decode steps replayed from captured CUDA graphs.
+
+A decode step is a few hundred short kernels; launched one by one from the
+host they cost more than they run. A step in which every request brings one
+token is therefore captured once per batch-size bucket and replayed: the
+kernels read the batch's token ids, positions, lengths and block tables from
+fixed device buffers that are refilled before every replay. Rows beyond the
+live requests are padding: a request of one token whose block table holds no
+page, which the kernels skip.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import numpy as np
+import torch
+
+from .batch import StepBatch, StepContext, Workspace
+
+
+def _bucket(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class _Captured:
+    def __init__(self, graph, logits, host, dev, offs):
+        self.graph, self.logits, self.host, self.dev, self.offs = graph, logits, host, dev, offs
+
+
+class DecodeGraphs:
+    def __init__(self, runner, max_requests: int):
+        self.runner = runner
+        self.max_bucket = _bucket(max_requests)
+        self.graphs: Dict[int, _Captured] = {}
+        self.replays = 0
+
+    def eligible(self, entries) -> bool:
+        return len(entries) <= self.max_bucket and all(len(e.tokens) == 1 for e in entries)
+
+    # ------------------------------------------------------------------ layout
+    def _layout(self, B: int):
+        mgr = self.runner.cache.manager
+        G, width = mgr.num_groups, self.runner.cache.table_width
+        offs, cursor = {}, 0
+        for name, n in (("token_ids", B), ("positions", B), ("token_req", B), ("cu_q", B + 1),
+                        ("kv_lens", B), ("slots", B), ("logit_rows", B), ("tables", G * B * width)):
+            offs[name] = (cursor, n)
+            cursor += (n + 3) // 4 * 4
+        return offs, cursor
+
+    def _fill(self, cap: _Captured, B: int, entries, new_lens) -> None:
+        mgr = self.runner.cache.manager
+        G, width = mgr.num_groups, self.runner.cache.table_width
+        h = cap.host
+
+        def view(name):
+            o, n = cap.offs[name]
+            return h[o:o + n]
+
+        R = len(entries)
+        token_ids, positions = view("token_ids"), view("positions")
+        kv_lens, slots = view("kv_lens"), view("slots")
+        token_ids[:] = 0
+        positions[:] = 0
+        kv_lens[:] = 1
+        slots[:] = -1          # padding rows have no state slot
+        view("token_req")[:] = np.arange(B, dtype=np.int32)
+        view("cu_q")[:] = np.arange(B + 1, dtype=np.int32)
+        view("logit_rows")[:] = np.arange(B, dtype=np.int32)
+        tables = view("tables").reshape(G, B, width) if G else None
+        if G:
+            tables[:] = -1
+        for i, (e, (_, new_len)) in enumerate(zip(entries, new_lens)):
+            token_ids[i] = int(e.tokens[0])
+            positions[i] = new_len - 1
+            kv_lens[i] = new_len
+            slots[i] = mgr.slot(e.request)
+        if G and R:
+            mgr.fill_block_tables([e.request for e in entries], tables)
+
+    def _batch(self, cap: _Captured, B: int) -> StepBatch:
+        mgr = self.runner.cache.manager
+        G, width = mgr.num_groups, self.runner.cache.table_width
+
+        def dview(name):
+            o, n = cap.offs[name]
+            return cap.dev[o:o + n]
+
+        tables = [dview("tables").view(G, B, width)[g] for g in range(G)] if G else []
+        return StepBatch(num_tokens=B, num_requests=B, token_ids=dview("token_ids"),
+                         positions=dview("positions"), token_req=dview("token_req"), cu_q=dview("cu_q"),
+                         kv_lens=dview("kv_lens"), slots=dview("slots"), block_tables=tables,
+                         logit_rows=dview("logit_rows"), num_logit_rows=B, max_q_len=1,
+                         max_kv_len=mgr.max_positions, host={})
+
+    # ------------------------------------------------------------------ capture
+    def _capture(self, B: int) -> _Captured:
+        r = self.runner
+        offs, size = self._layout(B)
+        host = torch.empty(size, dtype=torch.int32).pin_memory()
+        dev = torch.zeros(size, dtype=torch.int32, device=r.device)
+        cap = _Captured(None, None, host.numpy(), dev, offs)
+        cap.pinned = host
+        self._fill(cap, B, [], [])
+        dev.copy_(host, non_blocking=True)
+        batch = self._batch(cap, B)
+        ws = Workspace(r.device)
+        ctx = StepContext(batch=batch, ws=ws, ops=r.ops, dtype=r.dtype)
+        caches = r.cache.layer_caches(batch.block_tables)
+        # once outside the capture: tables and scratch that are made on first use
+        r.model.forward(ctx, caches)
+        torch.cuda.synchronize(r.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = r.model.forward(ctx, caches)
+        cap.graph, cap.logits, cap.ws = graph, logits, ws
+        return cap
+
+    # ------------------------------------------------------------------ run
+    def run(self, entries, new_lens) -> torch.Tensor:
+        B = _bucket(len(entries))
+        cap = self.graphs.get(B)
+        if cap is None:
+            cap = self.graphs[B] = self._capture(B)
+        self._fill(cap, B, entries, new_lens)
+        cap.dev.copy_(cap.pinned, non_blocking=True)
+        cap.graph.replay()
+        self.replays += 1
+        rows = [i for i, e in enumerate(entries) if len(e.want)]
+        if len(rows) == len(entries):
+            return cap.logits[:len(entries)]
+        return cap.logits[torch.tensor(rows, dtype=torch.long, device=cap.logits.device)]

@@ -44,6 +44,7 @@ class StepRunner:
         self.vocab = model.spec.vocab_size
         self.steps = 0
         self.tokens_run = 0
+        self.graphs = None        # DecodeGraphs, when decode steps are replayed from CUDA graphs
 
     # ------------------------------------------------------------------ checks
     def _validate_and_reserve(self, entries: Sequence[StepEntry]):
@@ -163,15 +164,20 @@ class StepRunner:
         """Logits ``[W, vocab]`` (float32, on the device) at the wanted places, in
         the order of the entries and of their ``want``. Valid until the next step."""
         new_lens = self._validate_and_reserve(entries)
-        batch = self.build_batch(entries, new_lens)
-        ctx = StepContext(batch=batch, ws=self.ws, ops=self.ops, dtype=self.dtype)
-        caches = self.cache.layer_caches(batch.block_tables)
-        logits = self.model.forward(ctx, caches)
+        if self.graphs is not None and self.graphs.eligible(entries):
+            logits = self.graphs.run(entries, new_lens)
+            tokens = len(entries)
+        else:
+            batch = self.build_batch(entries, new_lens)
+            ctx = StepContext(batch=batch, ws=self.ws, ops=self.ops, dtype=self.dtype)
+            caches = self.cache.layer_caches(batch.block_tables)
+            logits = self.model.forward(ctx, caches)
+            tokens = batch.num_tokens
         mgr = self.cache.manager
         for r, n in new_lens:
             mgr.commit(r, n)
         self.steps += 1
-        self.tokens_run += batch.num_tokens
+        self.tokens_run += tokens
         return logits
 
     def end(self, request: int) -> None:
