@@ -33,7 +33,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall"]
 #: kernel libraries: name -> sources under csrc/kernels
 KERNEL_LIBS: Dict[str, List[str]] = {
     "garuda_core": ["elementwise.cu", "gemm_simple.cu", "attention_simple.cu", "sampling.cu"],
-    "garuda_tc": ["gemm_tcgen05.cu", "attention_mma.cu"],
+    "garuda_tc": ["gemm_tcgen05.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "bindings.cpp"]
 

@@ -1,0 +1,351 @@
+// bfloat16 matrix products on the 5th-generation tensor cores:
+//   out[Mx, Nw] (+)= x[Mx, K] * w[Nw, K]^T        (garuda/src/simd/mod.rs:96-129)
+// and the fused gate/up product with the SiLU-gate of the feed-forward
+//   out[Mx, F] = silu(x * gate^T) * (x * up^T)     (garuda/src/llama/mod.rs:1013-1017)
+//
+// One CTA computes a 128 x BN tile: a producer thread streams 128x64 and BNx64
+// operand tiles into shared memory with TMA (128-byte swizzle), one thread
+// issues tcgen05.mma with the accumulator in tensor memory, and when the last
+// MMA has retired the four warps read the accumulator back with tcgen05.ld and
+// run the epilogue. Accumulation is 32-bit.
+//
+// Two orientations. With many tokens the 128 rows of the MMA are tokens and the
+// BN columns are output features. With few tokens (decode) the operands swap:
+// the 128 MMA rows are output features (weight rows) and the BN = 16..64 columns
+// are tokens, so that the weight stream fills the tensor core's rows and the
+// result is written transposed.
+//
+// Rows outside a matrix are zero-filled by TMA and masked in the epilogue; K
+// need not be a multiple of 64 (the tail is zero-filled) but must be a multiple
+// of 8, because a TMA row pitch is a multiple of 16 bytes.
+#include <mutex>
+#include <unordered_map>
+
+#include "tc_common.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;   // MMA rows per CTA
+constexpr int BK = 64;    // bf16 per 128-byte swizzled row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 128;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2 };
+
+__device__ int g_error_word;
+
+template <int BN, bool DUAL_M, bool DUAL_N>
+struct Geometry {
+  static constexpr int NUM_M = DUAL_M ? 2 : 1, NUM_N = DUAL_N ? 2 : 1;
+  static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = NUM_M * A_BYTES + NUM_N * B_BYTES;
+  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
+  static constexpr int ACCUMULATORS = NUM_M * NUM_N;
+  static constexpr int COLS_NEEDED = ACCUMULATORS * BN;
+  static constexpr int TMEM_COLS = COLS_NEEDED <= 32 ? 32 : COLS_NEEDED <= 64 ? 64 : COLS_NEEDED <= 128 ? 128
+                                   : COLS_NEEDED <= 256 ? 256 : 512;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the tiles to 1024 B
+  static_assert(STAGES >= 2, "tile too large for shared memory");
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
+};
+
+template <typename OT>
+__device__ __forceinline__ void store_value(OT* p, float v);
+template <>
+__device__ __forceinline__ void store_value<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float silu_gate(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
+// rows_m / rows_n: valid rows of the MMA-row operand and of the MMA-column operand.
+// TRANS: the MMA rows are output columns (swapped orientation).
+template <int BN, bool DUAL_M, bool DUAL_N, int EPI, bool TRANS, typename OT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_m2,
+               const __grid_constant__ CUtensorMap map_n, const __grid_constant__ CUtensorMap map_n2,
+               OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K) {
+  using G = Geometry<BN, DUAL_M, DUAL_N>;
+  constexpr int STAGES = G::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_kb = (K + BK - 1) / BK;
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&accum_bar), 1);
+    abort_s = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tensormap(&map_m);
+    prefetch_tensormap(&map_n);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), G::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer
+    int issued = 0;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t phase = (kb / STAGES) & 1;
+      if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1)) {
+        atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
+        abort_s = 1;
+        break;
+      }
+      if (*(volatile int*)&abort_s) break;
+      const uint32_t bar = smem_u32(&full_bar[s]);
+      const uint32_t base = tiles + s * G::STAGE_BYTES;
+      mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
+      tma_load_2d(base, &map_m, bar, kb * BK, m0);
+      if (DUAL_M) tma_load_2d(base + G::A_BYTES, &map_m2, bar, kb * BK, m0);
+      tma_load_2d(base + G::NUM_M * G::A_BYTES, &map_n, bar, kb * BK, n0);
+      if (DUAL_N) tma_load_2d(base + G::NUM_M * G::A_BYTES + G::B_BYTES, &map_n2, bar, kb * BK, n0);
+      issued = kb + 1;
+    }
+    if (*(volatile int*)&abort_s) {
+      // wind down: let the copies already in flight land before the CTA's shared memory is given up
+      for (int kb = issued > STAGES ? issued - STAGES : 0; kb < issued; ++kb) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (!mbar_try_wait(smem_u32(&full_bar[kb % STAGES]), (kb / STAGES) & 1)) {
+          if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
+            atomicCAS(&g_error_word, 0, ERR_WAIT_DRAIN);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t phase = (kb / STAGES) & 1;
+      if (!mbar_wait(smem_u32(&full_bar[s]), phase)) {
+        atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
+        abort_s = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t base = tiles + s * G::STAGE_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k) {
+        const uint32_t koff = k * UMMA_K * 2;  // bytes along the swizzled row
+        const bool acc = kb > 0 || k > 0;
+        const uint64_t da = smem_desc_sw128(base + koff);
+        const uint64_t db = smem_desc_sw128(base + G::NUM_M * G::A_BYTES + koff);
+        mma_bf16(tmem_base, da, db, idesc, acc);
+        if (DUAL_M) mma_bf16(tmem_base + BN, smem_desc_sw128(base + G::A_BYTES + koff), db, idesc, acc);
+        if (DUAL_N)
+          mma_bf16(tmem_base + BN, da, smem_desc_sw128(base + G::NUM_M * G::A_BYTES + G::B_BYTES + koff),
+                   idesc, acc);
+      }
+      mma_commit(smem_u32(&empty_bar[s]));  // the stage is free once these MMAs have read it
+    }
+    mma_commit(smem_u32(&accum_bar));       // fires when every MMA above has retired
+  }
+  __syncwarp();
+
+  // -------------------------------------------------------------------- epilogue
+  bool have = mbar_wait(smem_u32(&accum_bar), 0);
+  if (!have && lane == 0) atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+  have = have && !*(volatile int*)&abort_s;
+  tc_fence_after_sync();
+  if (have) {
+    const int row = m0 + warp * 32 + lane;           // this thread's MMA row
+    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 16) {
+      uint32_t r0[16], r1[16];
+      tmem_ld_16(taddr + c, r0);
+      if (EPI == EPI_SWIGLU) tmem_ld_16(taddr + BN + c, r1);
+      tmem_ld_wait();
+      if (row < rows_m) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int col = n0 + c + j;
+          if (col >= rows_n) continue;
+          float v = __uint_as_float(r0[j]);
+          if (EPI == EPI_SWIGLU) v = silu_gate(v, __uint_as_float(r1[j]));
+          OT* p = TRANS ? out + (size_t)col * ldo + row : out + (size_t)row * ldo + col;
+          if (EPI == EPI_ACCUMULATE) v += gb::to_float<OT>(*p);
+          store_value<OT>(p, v);
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, G::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, cols;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^
+           (std::hash<long long>()(k.cols) * 131) ^ (size_t)k.box_rows * 7919;
+  }
+};
+
+// A [rows, cols] bf16 row-major matrix seen through boxes of box_rows x 64, 128-byte swizzle.
+int tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{ptr, rows, cols, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return GB_OK;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return gb::fail(GB_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return gb::fail(GB_CUDA_ERROR, "cuTensorMapEncodeTiled failed with code %d for a %lld x %lld matrix", (int)r,
+                    rows, cols);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return GB_OK;
+}
+
+template <int BN, bool DUAL_M, bool DUAL_N, int EPI, bool TRANS, typename OT>
+int launch(const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn, const CUtensorMap& mn2, OT* out,
+           int ldo, int rows_m, int rows_n, int K, cudaStream_t stream) {
+  using G = Geometry<BN, DUAL_M, DUAL_N>;
+  auto kernel = gemm_tc_kernel<BN, DUAL_M, DUAL_N, EPI, TRANS, OT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
+    if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((rows_n + BN - 1) / BN, (rows_m + BM - 1) / BM);
+  kernel<<<grid, THREADS, G::SMEM_BYTES, stream>>>(mm, mm2, mn, mn2, out, ldo, rows_m, rows_n, K);
+  return gb::check_launch("gemm_tc");
+}
+
+template <int BN, bool TRANS>
+int dispatch(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn,
+             const CUtensorMap& mn2, void* out, int ldo, int rows_m, int rows_n, int K, cudaStream_t stream) {
+  constexpr bool DM = TRANS, DN = !TRANS;  // which side carries gate and up
+  if (epi == EPI_STORE) {
+    if (out_dtype == GB_F32)
+      return launch<BN, false, false, EPI_STORE, TRANS, float>(mm, mm2, mn, mn2, (float*)out, ldo, rows_m, rows_n, K, stream);
+    return launch<BN, false, false, EPI_STORE, TRANS, __nv_bfloat16>(mm, mm2, mn, mn2, (__nv_bfloat16*)out, ldo, rows_m, rows_n, K, stream);
+  }
+  if (epi == EPI_ACCUMULATE)
+    return launch<BN, false, false, EPI_ACCUMULATE, TRANS, float>(mm, mm2, mn, mn2, (float*)out, ldo, rows_m, rows_n, K, stream);
+  return launch<BN, DM, DN, EPI_SWIGLU, TRANS, __nv_bfloat16>(mm, mm2, mn, mn2, (__nv_bfloat16*)out, ldo, rows_m, rows_n, K, stream);
+}
+
+}  // namespace
+
+GB_DEFINE_LAST_ERROR()
+
+// Returns the device error word (0: none) and clears it. Synchronises the device.
+GB_EXPORT int gb_tc_error_check() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_error_word, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_error_word, &zero, sizeof(int));
+  }
+  return v;
+}
+
+// Whether gb_gemm_tc takes this problem (else the caller uses the plain kernel).
+GB_EXPORT int gb_gemm_tc_supported(const void* x, const void* w, int Mx, int Nw, int K) {
+  if (Mx < 1 || Nw < 1 || K < 8 || K % 8) return 0;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return 0;
+  return 1;
+}
+
+// epi 0: out[Mx,Nw] = x w^T (out_dtype f32 or bf16); 1: out (f32) += x w^T;
+// 2: w holds gate rows then up rows ([2*Nw, K]); out[Mx,Nw] (bf16) = silu(x gate^T) * (x up^T).
+GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw, int K, int out_dtype, int epi,
+                         cudaStream_t stream) {
+  if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc: needs K a multiple of 8 and 16-byte aligned operands (K = %d)", K);
+  if (epi == EPI_ACCUMULATE && out_dtype != GB_F32)
+    return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: accumulation needs a 32-bit output");
+  if (epi == EPI_SWIGLU && out_dtype != GB_BF16)
+    return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: the SiLU-gate epilogue writes bfloat16");
+  const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
+  const void* w2 = epi == EPI_SWIGLU ? (const void*)(wp + (size_t)Nw * K) : w;
+  if (epi == EPI_SWIGLU && ((uintptr_t)w2 & 15))
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc: the up rows do not start on a 16-byte boundary");
+  const bool swap = Mx <= 64;
+  const int bn = swap ? (Mx <= 16 ? 16 : Mx <= 32 ? 32 : 64) : 128;
+  CUtensorMap mm, mm2, mn, mn2;
+  int rc;
+  if (swap) {
+    if ((rc = tensor_map_2d(w, Nw, K, BM, &mm))) return rc;
+    if ((rc = tensor_map_2d(w2, Nw, K, BM, &mm2))) return rc;
+    if ((rc = tensor_map_2d(x, Mx, K, bn, &mn))) return rc;
+    mn2 = mn;
+    if (bn == 16) return dispatch<16, true>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Nw, Mx, K, stream);
+    if (bn == 32) return dispatch<32, true>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Nw, Mx, K, stream);
+    return dispatch<64, true>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Nw, Mx, K, stream);
+  }
+  if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
+  mm2 = mm;
+  if ((rc = tensor_map_2d(w, Nw, K, bn, &mn))) return rc;
+  if ((rc = tensor_map_2d(w2, Nw, K, bn, &mn2))) return rc;
+  return dispatch<128, false>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Mx, Nw, K, stream);
+}
