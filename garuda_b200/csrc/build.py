@@ -120,11 +120,23 @@ def nvcc_path() -> str:
                      "the CUDA kernels cannot be built")
 
 
+def attention_lib_name(head_dim: int) -> str:
+    """The tensor-core attention is compiled per head size, when a model first needs it."""
+    return f"garuda_attn_hd{int(head_dim)}"
+
+
+def _lib_recipe(name: str):
+    if name.startswith("garuda_attn_hd"):
+        return ["attention_mma.cu"], [f"-DGB_HEAD_DIM={int(name[len('garuda_attn_hd'):])}"]
+    return KERNEL_LIBS[name], []
+
+
 def kernel_lib_path(name: str) -> str:
     """Build (if needed) and return the path of a kernel library."""
     folder = os.path.join(HERE, "kernels")
-    sources = [os.path.join(folder, s) for s in KERNEL_LIBS[name]]
-    tag = _hash(sources + _headers(folder), NVCC_FLAGS)
+    names, defines = _lib_recipe(name)
+    sources = [os.path.join(folder, s) for s in names]
+    tag = _hash(sources + _headers(folder), NVCC_FLAGS + defines)
     out_dir = build_dir()
     target = os.path.join(out_dir, f"lib{name}.{tag}.so")
     if os.path.exists(target):
@@ -139,7 +151,7 @@ def kernel_lib_path(name: str) -> str:
 
         def one(src):
             obj = os.path.join(out_dir, f"{name}.{os.path.basename(src)}.{tag}.{os.getpid()}.o")
-            _run([nvcc, *NVCC_FLAGS, "-I", folder, "-c", src, "-o", obj], os.path.basename(src))
+            _run([nvcc, *NVCC_FLAGS, *defines, "-I", folder, "-c", src, "-o", obj], os.path.basename(src))
             return obj
 
         with ThreadPoolExecutor(max_workers=min(4, len(sources))) as pool:
@@ -217,8 +229,10 @@ def load_host_module():
     return _HOST
 
 
-def build_all() -> None:
+def build_all(head_dims=(16, 32, 48, 64, 128)) -> None:
     """Everything, for a build check."""
     host_module_path()
     for name in KERNEL_LIBS:
         kernel_lib_path(name)
+    for hd in head_dims:
+        kernel_lib_path(attention_lib_name(hd))

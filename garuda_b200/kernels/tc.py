@@ -7,11 +7,11 @@ case the caller uses the plain kernel instead.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_void_p, c_int
+from ctypes import c_void_p, c_int, c_float
 
 import torch
 
-from ..csrc.build import load_kernel_lib
+from ..csrc.build import load_kernel_lib, attention_lib_name
 
 _WAIT_NAMES = {1: "an operand tile never arrived (TMA)", 2: "a pipeline stage was never released",
                3: "the accumulator never completed", 4: "copies in flight did not land while winding down"}
@@ -28,6 +28,7 @@ class TensorCoreKernels:
         L.gb_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
         L.gb_gemm_tc_supported.restype = c_int
         L.gb_tc_error_check.restype = c_int
+        self._attn = {}
 
     def check_errors(self) -> None:
         """Synchronises, and raises if a kernel gave up on a wait since the last check."""
@@ -56,5 +57,51 @@ class TensorCoreKernels:
             return False
         return self._gemm(h, w_gate_up, act, act.shape[1], 2)
 
-    def paged_attention(self, *args) -> bool:
-        return False
+    # ------------------------------------------------------------------ attention
+    def _attention_lib(self, head_dim: int):
+        lib = self._attn.get(head_dim)
+        if lib is None:
+            lib = load_kernel_lib(attention_lib_name(head_dim))
+            lib.gb_last_error.restype = ctypes.c_char_p
+            lib.gb_attention_mma.argtypes = ([c_void_p] * 6 + [c_int] + [c_void_p] * 3 + [c_int] * 4 + [c_float]
+                                             + [c_int] * 4 + [c_void_p])
+            lib.gb_attention_mma.restype = c_int
+            lib.gb_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int]
+            lib.gb_attention_mma_scratch_floats.restype = ctypes.c_longlong
+            self._attn[head_dim] = lib
+        return lib
+
+    @staticmethod
+    def attention_splits(num_requests: int, kv_heads: int, max_kv_len: int) -> int:
+        """CTAs that share one decode request's keys: enough to fill the GPU twice
+        over, but no split shorter than one tile of 64 keys."""
+        tiles = max((max_kv_len + 63) // 64, 1)
+        want = -(-2 * 148 // max(num_requests * kv_heads, 1))
+        return max(1, min(want, tiles, 64))
+
+    def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale,
+                        window, page_size, num_requests, max_q_len, max_kv_len, ws=None) -> bool:
+        T, Hq, hd = q.shape
+        Hkv = k_pool.shape[1]
+        if hd % 16 or hd > 128 or Hq // Hkv > 64:
+            return False
+        lib = self._attention_lib(hd)
+        splits = self.attention_splits(num_requests, Hkv, max_kv_len)
+        scratch = None
+        if splits > 1:
+            n = lib.gb_attention_mma_scratch_floats(T, Hq, splits)
+            scratch = (ws or self.ops.private_ws).get("attention_partial", (n,), torch.float32)
+        code = self._call_attention(lib, q, k_pool, v_pool, out, scratch, block_table, cu_q, kv_lens,
+                                    token_req, T, num_requests, Hq, Hkv, scale, window, page_size,
+                                    max_q_len, splits)
+        self.ops._check(lib, code, "attention_mma")
+        return True
+
+    def _call_attention(self, lib, q, k_pool, v_pool, out, scratch, block_table, cu_q, kv_lens, token_req,
+                        T, R, Hq, Hkv, scale, window, page_size, max_q_len, splits) -> int:
+        return lib.gb_attention_mma(
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+            None if scratch is None else scratch.data_ptr(), block_table.data_ptr(),
+            block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), token_req.data_ptr(),
+            T, R, Hq, Hkv, float(scale), int(window), int(page_size), int(max_q_len), int(splits),
+            self.ops._stream())
