@@ -183,7 +183,7 @@ def host_module_path() -> str:
     folder = os.path.join(HERE, "host")
     sources = [os.path.join(folder, s) for s in HOST_SOURCES]
     includes = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", folder]
-    tag = _hash(sources + _headers(folder), CXX_FLAGS + [sys.version.split()[0]])
+    tag = _hash(sources + _headers(folder), CXX_FLAGS + [sys.version.split()[0], "system-g++"])
     out_dir = build_dir()
     target = os.path.join(out_dir, f"_garuda_host.{tag}.so")
     if os.path.exists(target):
@@ -191,7 +191,9 @@ def host_module_path() -> str:
     with _Lock(os.path.join(out_dir, ".host.lock")):
         if os.path.exists(target):
             return target
-        cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+        # The system g++: it links libstdc++ dynamically, which an extension that throws
+        # exceptions inside a Python process (next to numpy and torch) needs.
+        cxx = os.environ.get("GARUDA_B200_CXX") or shutil.which("g++") or "g++"
         _log("compiling the host runtime (first use only)")
         t0 = time.time()
 

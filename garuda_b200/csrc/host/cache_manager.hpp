@@ -23,12 +23,12 @@
 namespace garuda {
 
 struct CacheError : std::runtime_error {
-  using std::runtime_error::runtime_error;
+  explicit CacheError(const std::string& what) : std::runtime_error(what) {}
 };
 
 // Raised when a reservation cannot be met; nothing has changed when it is thrown.
 struct OutOfPages : CacheError {
-  using CacheError::CacheError;
+  explicit OutOfPages(const std::string& what) : CacheError(what) {}
 };
 
 struct GroupConfig {

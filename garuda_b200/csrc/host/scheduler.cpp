@@ -187,12 +187,18 @@ StepPlan Scheduler::plan() {
     }
 
     // admission (garuda/src/scheduler/mod.rs:450-462): a slot and the pages of a first portion
-    while (static_cast<int>(running_.size()) < config_.max_concurrent && !queue_.empty() && budget > 0 &&
-           cache_->free_slots() > 0) {
+    // A request that was sent back in this very plan waits for the next one, and
+    // comes back only when all it holds so far fits: otherwise it would take the
+    // pages it just gave up and be sent back again.
+    while (plan.preempted.empty() && static_cast<int>(running_.size()) < config_.max_concurrent &&
+           !queue_.empty() && budget > 0 && cache_->free_slots() > 0) {
       Request& q = queue_.front();
       const int want = std::min({static_cast<int>(q.tokens.size()), budget, chunk_cap});
       cache_->acquire(q.id);
-      const int got = largest_reservable(q, want);
+      int got = largest_reservable(q, want);
+      if (q.requeued && !running_.empty() &&
+          !cache_->can_reserve({{q.id, std::min(static_cast<int>(q.tokens.size()) + 1, config_.max_context)}}))
+        got = 0;
       if (got < want && !(running_.empty() && got > 0)) {
         cache_->release(q.id);
         if (running_.empty()) {

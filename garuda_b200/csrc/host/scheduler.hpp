@@ -67,10 +67,10 @@ struct SchedulerConfig {
 };
 
 struct SchedulerError : std::runtime_error {
-  using std::runtime_error::runtime_error;
+  explicit SchedulerError(const std::string& what) : std::runtime_error(what) {}
 };
 struct Busy : SchedulerError {  // garuda/src/scheduler/mod.rs:287-295
-  using SchedulerError::SchedulerError;
+  explicit Busy(const std::string& what) : SchedulerError(what) {}
 };
 
 struct PlanEntry {

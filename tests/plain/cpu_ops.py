@@ -21,6 +21,8 @@ import torch
 class CpuOps:
     name = "cpu-reference"
 
+    device = "cpu"
+
     def __init__(self):
         self.tc = None
 
@@ -129,3 +131,25 @@ class CpuOps:
     # garuda/src/runtime/mod.rs:99-107
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(torch.int32))
+
+    # garuda/src/runtime/mod.rs:109-175
+    def sample(self, logits, temperature, top_k, top_p, u, out, scratch):
+        from .sampling_plain import candidates
+        from .llama_plain import argmax_first
+        for r in range(logits.shape[0]):
+            row = logits[r].numpy()
+            if float(temperature[r]) == 0.0:
+                out[r] = argmax_first(row)
+                continue
+            cand = candidates(row, float(temperature[r]), int(top_k[r]), float(top_p[r]))
+            total = np.float32(sum(np.float32(p) for _, p in cand))
+            pick = cand[0][0]
+            if total > 0:
+                point = np.float32(np.float32(float(u[r])) * total)
+                pick = cand[-1][0]
+                for tok, p in cand:
+                    point = np.float32(point - p)
+                    if point <= 0:
+                        pick = tok
+                        break
+            out[r] = pick

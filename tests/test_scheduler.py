@@ -1,0 +1,256 @@
+"""The scheduler's decisions, without a model: what goes into a step, when a
+request finishes, and what happens when pages run out.
+(The reference's scheduler tests: garuda/src/scheduler/mod.rs:760-1112.)"""
+import pytest
+
+from garuda_b200.csrc.build import load_host_module
+
+host = load_host_module()
+Token, Done, Error = host.EventKind.Token, host.EventKind.Done, host.EventKind.Error
+
+
+def make(pages=64, page_size=4, max_concurrent=4, max_batch_tokens=32, prefill_chunk=16, max_context=64,
+         queue_capacity=8, eos=-1, windows=(0,), vocab=100):
+    cache = host.CacheManager([host.GroupConfig(pages, w) for w in windows], page_size, max_concurrent, max_context)
+    c = host.SchedulerConfig()
+    c.max_concurrent, c.queue_capacity, c.max_batch_tokens = max_concurrent, queue_capacity, max_batch_tokens
+    c.prefill_chunk, c.max_context, c.eos_token_id, c.vocab_size = prefill_chunk, max_context, eos, vocab
+    return host.Scheduler(c, cache), cache
+
+
+def greedy(max_tokens=4, seed=None, temperature=0.0):
+    return host.SamplingParams(temperature=temperature, top_p=1.0, top_k=0, max_tokens=max_tokens, seed=seed)
+
+
+def run_step(s, cache, token=7):
+    plan = s.plan()
+    sampled = [token] * sum(1 for e in plan.entries if e.sample)
+    return plan, s.complete(plan, sampled)
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    s, cache = make(max_batch_tokens=32, prefill_chunk=16)
+    a = s.submit(list(range(40)), greedy())
+    plan, ev = run_step(s, cache)
+    assert [(e.id, e.start, len(e.tokens), e.sample) for e in plan.entries] == [(a, 0, 16, False)] and not ev
+    plan, ev = run_step(s, cache)
+    assert [(e.start, len(e.tokens), e.sample) for e in plan.entries] == [(16, 16, False)]
+    plan, ev = run_step(s, cache)
+    assert [(e.start, len(e.tokens), e.sample) for e in plan.entries] == [(32, 8, True)]
+    assert plan.entries[0].tokens == list(range(32, 40))
+    assert [(e.kind, e.token) for e in ev] == [(Token, 7)]
+    plan, ev = run_step(s, cache)                       # now decoding: one token
+    assert [(e.start, e.tokens, e.sample) for e in plan.entries] == [(40, [7], True)]
+
+
+def test_decode_tokens_come_first_and_share_the_step_with_prompt_portions():
+    s, cache = make(max_batch_tokens=10, prefill_chunk=16)
+    a = s.submit([1, 2, 3], greedy(max_tokens=8))
+    run_step(s, cache)                                  # a's prompt; a is decoding from now on
+    b = s.submit(list(range(30)), greedy(max_tokens=8))
+    plan, _ = run_step(s, cache)
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(a, 1), (b, 9)]   # 10 tokens in all
+    assert plan.num_tokens == 10
+    plan, _ = run_step(s, cache)
+    assert [(e.id, e.start, len(e.tokens)) for e in plan.entries] == [(a, 4, 1), (b, 9, 9)]
+
+
+def test_admission_stops_at_max_concurrent_and_goes_on_when_one_finishes():
+    s, cache = make(max_concurrent=2)
+    ids = [s.submit([1, 2], greedy(max_tokens=2)) for _ in range(3)]
+    plan, ev = run_step(s, cache)
+    assert [e.id for e in plan.entries] == ids[:2] and s.stats().queued == 1
+    plan, ev = run_step(s, cache)                       # second token: both reach max_tokens
+    assert [(e.kind, e.detail) for e in ev if e.kind == Done] == [(Done, "length")] * 2
+    assert cache.live_requests == 0
+    plan, ev = run_step(s, cache)
+    assert [e.id for e in plan.entries] == ids[2:]
+    cache.check_invariants()
+
+
+def test_finish_reasons():
+    s, cache = make(eos=9, max_context=8)
+    a = s.submit([1, 2, 3], greedy(max_tokens=10))
+    plan = s.plan()
+    ev = s.complete(plan, [9])                          # the end-of-sequence token is not emitted
+    assert [(e.kind, e.detail) for e in ev] == [(Done, "eos")] and not cache.known(a)
+    b = s.submit([1, 2, 3, 4, 5, 6], greedy(max_tokens=10))
+    _, ev = run_step(s, cache)                          # 7 tokens in the context
+    assert [e.kind for e in ev] == [Token]
+    _, ev = run_step(s, cache)                          # 8 = max_context: full
+    assert [(e.kind, e.detail) for e in ev] == [(Token, ""), (Done, "context_full")]
+    c = s.submit([1], greedy(max_tokens=1))
+    _, ev = run_step(s, cache)
+    assert [(e.kind, e.detail) for e in ev] == [(Token, ""), (Done, "length")]
+    assert s.idle() and s.stats().completed == 3
+    cache.check_invariants()
+
+
+def test_submit_refuses_what_cannot_run():
+    s, cache = make(max_context=8, queue_capacity=2, vocab=50)
+    with pytest.raises(host.SchedulerError, match="empty"):
+        s.submit([], greedy())
+    with pytest.raises(host.SchedulerError, match="does not fit"):
+        s.submit(list(range(8)), greedy())
+    with pytest.raises(host.SchedulerError, match="vocabulary"):
+        s.submit([1, 50], greedy())
+    with pytest.raises(host.SchedulerError, match="temperature"):
+        s.submit([1], host.SamplingParams(temperature=-1.0))
+    with pytest.raises(host.SchedulerError, match="top_p"):
+        s.submit([1], host.SamplingParams(top_p=0.0))
+    with pytest.raises(host.SchedulerError, match="max_tokens"):
+        s.submit([1], host.SamplingParams(max_tokens=0))
+    s.submit([1], greedy())
+    s.submit([1], greedy())
+    with pytest.raises(host.Busy):
+        s.submit([1], greedy())
+    assert s.stats().rejected_busy == 1
+
+
+def test_priority_overtakes_and_fifo_within():
+    s, cache = make(max_concurrent=1)
+    low = s.submit([1], greedy(max_tokens=1), 0)
+    low2 = s.submit([1], greedy(max_tokens=1), 0)
+    high = s.submit([1], greedy(max_tokens=1), 5)
+    order = []
+    while not s.idle():
+        plan, _ = run_step(s, cache)
+        order += [e.id for e in plan.entries]
+    assert order == [high, low, low2]
+
+
+def test_cancel_frees_pages_between_steps():
+    s, cache = make()
+    a = s.submit(list(range(20)), greedy(max_tokens=50))
+    b = s.submit([1, 2], greedy(max_tokens=50))
+    run_step(s, cache)
+    s.cancel(a)
+    plan = s.plan()
+    assert [(e.id, e.kind, e.detail) for e in plan.events] == [(a, Error, "cancelled")]
+    assert [e.id for e in plan.entries] == [b] and not cache.known(a)
+    s.complete(plan, [3])
+    assert s.stats().cancelled == 1
+    cache.check_invariants()
+
+
+def test_when_pages_run_out_the_most_recent_request_goes_back_to_the_queue():
+    # 6 pages of 4 positions; two requests of 8 tokens fill 4 pages, then both decode
+    s, cache = make(pages=6, page_size=4, max_concurrent=2, prefill_chunk=8, max_batch_tokens=16)
+    a = s.submit(list(range(8)), greedy(max_tokens=12))
+    b = s.submit(list(range(10, 18)), greedy(max_tokens=12))
+    plan, _ = run_step(s, cache, token=1)
+    assert [e.id for e in plan.entries] == [a, b]
+    preempted_at = None
+    for step in range(12):
+        plan, ev = run_step(s, cache, token=1)
+        cache.check_invariants()
+        if plan.preempted:
+            preempted_at = step
+            assert plan.preempted == [b]                # the most recently admitted one
+            assert [e.id for e in plan.entries] == [a]
+            assert not cache.known(b) and s.stats().queued == 1
+            break
+    assert preempted_at is not None
+    assert s.stats().preemptions == 1
+    # a runs on to its limit; b comes back with its prompt and what it had generated, and finishes
+    done = {}
+    refed = []
+    for _ in range(200):
+        if s.idle():
+            break
+        plan, ev = run_step(s, cache, token=1)
+        for e in plan.entries:
+            if e.id == b:
+                assert e.start == len(refed)
+                refed += e.tokens
+        for e in ev:
+            if e.kind == Done:
+                done[e.id] = e.detail
+        cache.check_invariants()
+    assert done == {a: "length", b: "length"}
+    # b was recomputed from its prompt and the tokens it had generated before it was sent back
+    assert refed[:8] == list(range(10, 18)) and refed[8:12] == [1, 1, 1, 1] and len(refed) == 8 + 11
+    assert cache.live_requests == 0 and cache.free_pages(0) == 6
+
+
+def test_a_request_that_cannot_fit_alone_ends_with_an_error():
+    s, cache = make(pages=2, page_size=4, max_concurrent=2, max_context=64)
+    a = s.submit(list(range(6)), greedy(max_tokens=30))
+    errors = []
+    for _ in range(20):
+        if s.idle():
+            break
+        plan, ev = run_step(s, cache)
+        errors += [e for e in list(plan.events) + list(ev) if e.kind == Error]
+    assert len(errors) == 1 and errors[0].id == a and "more pages" in errors[0].detail
+    assert cache.free_pages(0) == 2 and s.stats().failed == 1
+    # and a prompt longer than the whole pool
+    b = s.submit(list(range(20)), greedy())
+    for _ in range(5):
+        plan, ev = run_step(s, cache)
+        errors += [e for e in list(plan.events) + list(ev) if e.kind == Error]
+        if s.idle():
+            break
+    assert errors[-1].id == b and s.idle()
+    cache.check_invariants()
+
+
+def test_admission_waits_for_the_pages_of_a_first_portion():
+    s, cache = make(pages=5, page_size=4, max_concurrent=2, prefill_chunk=16, max_batch_tokens=32)
+    a = s.submit(list(range(12)), greedy(max_tokens=2))     # 3 pages, a 4th with its first decoded token
+    run_step(s, cache)
+    b = s.submit(list(range(16)), greedy(max_tokens=2))     # wants 4 pages, 1 is free
+    plan, ev = run_step(s, cache)
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(a, 1)]      # b is not admitted yet
+    assert [e.detail for e in ev if e.kind == Done] == ["length"]         # a has its 2 tokens
+    plan, _ = run_step(s, cache)
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(b, 16)]
+    cache.check_invariants()
+
+
+def test_prefill_portion_is_cut_to_the_pages_there_are():
+    s, cache = make(pages=5, page_size=4, max_concurrent=2, prefill_chunk=8, max_batch_tokens=32)
+    a = s.submit([1, 2, 3, 4], greedy(max_tokens=20))        # 1 page, a 2nd as soon as it decodes
+    b = s.submit(list(range(16)), greedy(max_tokens=2))
+    plan, _ = run_step(s, cache)
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(a, 4), (b, 8)]     # 1 + 2 pages
+    plan, _ = run_step(s, cache)
+    # a takes its 2nd page; one page is left, so b's second portion is 4 tokens instead of 8
+    assert [(e.id, e.start, len(e.tokens)) for e in plan.entries] == [(a, 4, 1), (b, 8, 4)]
+    assert cache.free_pages(0) == 0
+    cache.check_invariants()
+
+
+def test_seeded_draws_are_reproducible_and_default_to_the_request_id():
+    s, cache = make()
+    a = s.submit([1], greedy(max_tokens=3, seed=42, temperature=0.8))
+    us = []
+    for _ in range(3):
+        plan = s.plan()
+        us.append(plan.entries[0].u)
+        s.complete(plan, [5])
+    r = host.Rng(42)
+    assert us == [r.next_f32() for _ in range(3)]
+    b = s.submit([1], greedy(max_tokens=1, temperature=0.8))
+    plan = s.plan()
+    assert plan.entries[0].u == host.Rng(b).next_f32()      # garuda/src/runtime/mod.rs:612
+    c = s.submit([1], greedy(max_tokens=1))
+    s.complete(plan, [5])
+    plan = s.plan()
+    assert plan.entries[0].u == 0.0                          # greedy draws nothing
+
+
+def test_windowed_group_lets_a_long_request_run_in_few_pages():
+    s, cache = make(pages=4, page_size=4, windows=(6,), max_context=64, prefill_chunk=4)
+    a = s.submit(list(range(30)), greedy(max_tokens=20))
+    done = None
+    for _ in range(100):
+        plan, ev = run_step(s, cache)
+        cache.check_invariants()
+        for e in ev:
+            if e.kind in (Done, Error):
+                done = e
+        if s.idle():
+            break
+    assert done is not None and done.kind == Done and done.detail == "length"
+    assert s.stats().preemptions == 0
