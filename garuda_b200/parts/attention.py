@@ -70,7 +70,8 @@ class PagedAttention(Mixer):
         writes = cache.writes and not self.reads_shared_cache
         cols = self.q_dim + (2 * self.kv_dim if writes else 0)
         qkv = ws.get("qkv", (T, cols), torch.float32)
-        ops.linear(h, self.w_qkv, qkv)
+        # a call that reads another call's cache projects queries only (the first rows)
+        ops.linear(h, self.w_qkv if self.w_qkv.shape[0] == cols else self.w_qkv[:cols], qkv)
         q = ws.get("q_heads", (T, self.heads, self.head_dim), self.dtype)
         rotary = self.position.rotary
         if rotary is None and self.position.changes_vectors:

@@ -1,0 +1,313 @@
+"""Each CUDA kernel alone against its plain reference (tests/plain/cpu_ops.py),
+at sizes other than the tiny models': widths and vocabularies that are no power
+of two, head sizes in steps of 16, odd numbers of heads and groups."""
+import numpy as np
+import pytest
+import torch
+
+from tests.plain.cpu_ops import CpuOps
+from tests.plain.sampling_plain import Rng
+
+pytestmark = pytest.mark.gpu
+cpu = CpuOps()
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from garuda_b200.kernels import CudaOps
+    return CudaOps("cuda:0", tensor_cores=True)
+
+
+def dev(t):
+    return t.cuda()
+
+
+def close(got, want, tol, what=""):
+    got, want = got.float().cpu(), want.float().cpu()
+    scale = max(float(want.abs().max()), 1e-6)
+    err = float((got - want).abs().max())
+    assert torch.isfinite(got).all(), what
+    assert err <= tol * scale, f"{what}: {err:.3e} > {tol * scale:.3e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding(ops, dtype):
+    table = torch.randn(331, 72).to(dtype)
+    ids = torch.tensor([0, 330, 5, 5, 17], dtype=torch.int32)
+    out = torch.zeros(5, 72, device="cuda")
+    ops.embedding(dev(table), dev(ids), out)
+    assert torch.equal(out.cpu(), table[ids.long()].float())
+
+
+@pytest.mark.parametrize("d,eps", [(72, 1e-5), (2048, 1e-6), (100, 1e-3)])
+@pytest.mark.parametrize("wdt,odt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                     (torch.bfloat16, torch.bfloat16)])
+def test_rmsnorm(ops, d, eps, wdt, odt):
+    x = torch.randn(9, d) * 3
+    w = (1 + 0.1 * torch.randn(d)).to(wdt)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    for r in (None, rows):
+        n = 9 if r is None else 3
+        ref = torch.zeros(n, d)
+        cpu.rmsnorm(x, w, eps, ref, r)
+        out = torch.zeros(n, d, dtype=odt, device="cuda")
+        ops.rmsnorm(dev(x), dev(w), eps, out, None if r is None else dev(r))
+        close(out, ref, 1e-6 if odt == torch.float32 else 8e-3, "rmsnorm")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 130, 72), (7, 331, 200), (70, 96, 176), (130, 250, 64)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_plain_matrix_product(ops, M, N, K, dtype):
+    from garuda_b200.kernels import CudaOps
+    plain = CudaOps("cuda:0", tensor_cores=False)
+    a, w = torch.randn(M, K).to(dtype), (torch.randn(N, K) * 0.1).to(dtype)
+    ref = a.float() @ w.float().t()
+    out = torch.zeros(M, N, device="cuda")
+    plain.linear(dev(a), dev(w), out)
+    close(out, ref, 2e-6, "store")
+    base = torch.randn(M, N)
+    acc = dev(base.clone())
+    plain.linear(dev(a), dev(w), acc, accumulate=True)
+    close(acc, base + ref, 2e-6, "accumulate")
+
+
+def test_plain_product_does_not_depend_on_the_batch(ops):
+    from garuda_b200.kernels import CudaOps
+    plain = CudaOps("cuda:0", tensor_cores=False)
+    a, w = torch.randn(77, 200), torch.randn(130, 200)
+    whole = torch.zeros(77, 130, device="cuda")
+    plain.linear(dev(a), dev(w), whole)
+    one = torch.zeros(1, 130, device="cuda")
+    plain.linear(dev(a[40:41].contiguous()), dev(w), one)
+    assert torch.equal(whole[40:41], one)
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 40, 64, 65, 130, 300])
+@pytest.mark.parametrize("N,K", [(250, 72), (331, 200), (1000, 1024)])
+def test_tensor_core_product(ops, M, N, K):
+    a, w = (torch.randn(M, K) * 0.5).bfloat16(), (torch.randn(N, K) * 0.1).bfloat16()
+    ref = a.float() @ w.float().t()
+    for odt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 8e-3)):
+        out = torch.full((M, N), 5.0, dtype=odt, device="cuda")
+        assert ops.tc.linear(dev(a), dev(w), out, False)
+        close(out, ref, tol, f"store {odt}")
+    base = torch.randn(M, N)
+    acc = dev(base.clone())
+    assert ops.tc.linear(dev(a), dev(w), acc, True)
+    close(acc, base + ref, 1e-5, "accumulate")
+    ops.tc.check_errors()
+
+
+@pytest.mark.parametrize("M", [1, 9, 33, 64, 100, 257])
+@pytest.mark.parametrize("F,K", [(176, 64), (200, 72), (1000, 256)])
+def test_tensor_core_gate_up(ops, M, F, K):
+    h = (torch.randn(M, K) * 0.5).bfloat16()
+    w = (torch.randn(2 * F, K) * 0.2).bfloat16()
+    ref = torch.zeros(M, F)
+    cpu.linear_swiglu(None, h, w, ref)
+    out = torch.full((M, F), 9.0, dtype=torch.bfloat16, device="cuda")
+    assert ops.tc.linear_swiglu(dev(h), dev(w), out)
+    close(out, ref, 8e-3, "swiglu")
+    ops.tc.check_errors()
+
+
+def test_row_pitch_that_tma_cannot_take_uses_the_plain_kernel(ops):
+    a, w = torch.randn(5, 20).bfloat16(), torch.randn(12, 20).bfloat16()     # K = 20: 40-byte rows
+    out = torch.zeros(5, 12, device="cuda")
+    assert not ops.tc.linear(dev(a), dev(w), out, False)
+    ops.linear(dev(a), dev(w), out)
+    close(out, a.float() @ w.float().t(), 2e-6)
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rotate_and_store(ops, interleaved, dtype):
+    from garuda_b200.parts.rotary import RotaryParams
+    Hq, Hkv, hd, page, T = 6, 3, 48, 8, 11
+    rot = RotaryParams(500000.0, hd, interleaved)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * hd)
+    positions = torch.tensor([0, 1, 2, 3, 40, 41, 7, 100, 101, 102, 103], dtype=torch.int32)
+    token_req = torch.tensor([0, 0, 0, 0, 1, 1, 2, 3, 3, 3, 3], dtype=torch.int32)
+    bt = torch.full((4, 14), -1, dtype=torch.int32)
+    bt[0, 0], bt[1, 5], bt[2, 0], bt[3, 12] = 3, 0, 5, 1
+    k_ref, v_ref = torch.zeros(6, Hkv, page, hd), torch.zeros(6, Hkv, page, hd)
+    q_ref = torch.zeros(T, Hq, hd)
+    cpu.rope_kv_append(qkv, q_ref, k_ref, v_ref, positions, token_req, bt, Hq, Hkv, hd, rot, page)
+    k, v = torch.zeros(6, Hkv, page, hd, dtype=dtype, device="cuda"), torch.zeros(6, Hkv, page, hd, dtype=dtype, device="cuda")
+    q = torch.zeros(T, Hq, hd, dtype=dtype, device="cuda")
+    ops.rope_kv_append(dev(qkv), q, k, v, dev(positions), dev(token_req), dev(bt), Hq, Hkv, hd, rot, page)
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    close(q, q_ref, tol, "q"), close(k, k_ref, tol, "k"), close(v, v_ref, tol, "v")
+    # rotation in place, for position encodings that are applied outside the fused kernel
+    x = torch.randn(T, Hq, hd)
+    ref = x.clone()
+    cpu.rope_inplace(ref, positions, 500000.0, interleaved)
+    xd = dev(x)
+    ops.rope_inplace(xd, dev(positions), 500000.0, interleaved)
+    close(xd, ref, 2e-6, "in place")
+
+
+def _attention_case(Hq, Hkv, hd, page, reqs, window, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    R, T = len(reqs), sum(q for _, q in reqs)
+    npages = sum((kv + page - 1) // page for kv, _ in reqs) + 2
+    perm = torch.randperm(npages, generator=g)
+    width = max((kv + page - 1) // page for kv, _ in reqs) + 1
+    bt = torch.full((R, width), -1, dtype=torch.int32)
+    c = 0
+    for i, (kv, _) in enumerate(reqs):
+        n = (kv + page - 1) // page
+        bt[i, :n] = perm[c:c + n].int()
+        c += n
+    k = torch.randn(npages, Hkv, page, hd, generator=g).to(dtype)
+    v = torch.randn(npages, Hkv, page, hd, generator=g).to(dtype)
+    q = torch.randn(T, Hq, hd, generator=g).to(dtype)
+    cu = torch.tensor([0] + list(np.cumsum([ql for _, ql in reqs])), dtype=torch.int32)
+    kvl = torch.tensor([kv for kv, _ in reqs], dtype=torch.int32)
+    treq = torch.cat([torch.full((ql,), i, dtype=torch.int32) for i, (_, ql) in enumerate(reqs)])
+    ref = torch.zeros(T, Hq * hd)
+    cpu.paged_attention(q.float(), k.float(), v.float(), bt, cu, kvl, treq, ref, hd ** -0.5, window, page, R, 0, 0)
+    return q, k, v, bt, cu, kvl, treq, ref
+
+
+ATTENTION_CASES = [
+    (4, 2, 16, 8, [(70, 70)], 0), (4, 2, 16, 8, [(70, 1)], 0),
+    (3, 1, 32, 16, [(96, 30), (50, 1), (33, 2), (200, 1)], 0),
+    (3, 1, 32, 16, [(96, 30), (50, 1), (33, 2), (200, 1)], 20),
+    (6, 3, 48, 16, [(130, 65), (64, 64), (65, 1)], 16),
+    (32, 4, 64, 32, [(700, 1)] * 5, 0), (32, 4, 64, 32, [(1500, 1), (300, 3)], 100),
+    (8, 8, 128, 64, [(257, 129), (300, 1)], 0), (5, 5, 80, 8, [(77, 77), (13, 1)], 0),
+    (7, 1, 112, 4, [(40, 9), (41, 1)], 0),
+]
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,reqs,window", ATTENTION_CASES)
+def test_attention_plain_kernel(ops, Hq, Hkv, hd, page, reqs, window):
+    from garuda_b200.kernels import CudaOps
+    plain = CudaOps("cuda:0", tensor_cores=False)
+    for dtype, tol in ((torch.float32, 3e-6), (torch.bfloat16, 8e-3)):
+        q, k, v, bt, cu, kvl, treq, ref = _attention_case(Hq, Hkv, hd, page, reqs, window, dtype)
+        out = torch.zeros(ref.shape, dtype=dtype, device="cuda")
+        plain.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5,
+                              window, page, len(reqs), max(x for _, x in reqs), max(x for x, _ in reqs))
+        close(out, ref, tol, f"plain attention {dtype}")
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,reqs,window", ATTENTION_CASES)
+def test_attention_tensor_core_kernel(ops, Hq, Hkv, hd, page, reqs, window):
+    q, k, v, bt, cu, kvl, treq, ref = _attention_case(Hq, Hkv, hd, page, reqs, window, torch.bfloat16)
+    out = torch.zeros(ref.shape, dtype=torch.bfloat16, device="cuda")
+    assert ops.tc.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5,
+                                  window, page, len(reqs), max(x for _, x in reqs), max(x for x, _ in reqs))
+    close(out, ref, 1e-2, "tensor-core attention")
+
+
+def test_attention_finds_one_far_key_among_hundreds(ops):
+    # random values hide a missed key: make one early key's score stand out for one query head
+    Hq, Hkv, hd, page = 4, 2, 64, 16
+    for dtype in (torch.float32, torch.bfloat16):
+        q, k, v, bt, cu, kvl, treq, _ = _attention_case(Hq, Hkv, hd, page, [(900, 1), (333, 5)], 0, dtype)
+        far = 3                                   # position 3 of request 0, in its first page
+        pg = int(bt[0, far // page])
+        k[pg, 1, far % page] = (q[0, 2].float() * 4).to(dtype)      # head 2 reads kv head 1
+        v[pg, 1, far % page] = 50.0
+        ref = torch.zeros(6, Hq * hd)
+        cpu.paged_attention(q.float(), k.float(), v.float(), bt, cu, kvl, treq, ref, hd ** -0.5, 0, page, 2, 0, 0)
+        assert ref[0, 2 * hd:3 * hd].mean() > 40              # the far key dominates that head
+        out = torch.zeros(ref.shape, dtype=dtype, device="cuda")
+        ops.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5, 0,
+                            page, 2, 5, 900)
+        close(out, ref, 3e-6 if dtype == torch.float32 else 1e-2, f"far key {dtype}")
+
+
+def test_attention_window_edge(ops):
+    # the key just outside the window must not be read, the one just inside must
+    Hq, Hkv, hd, page, window = 2, 1, 32, 8, 24
+    for dtype in (torch.float32, torch.bfloat16):
+        q, k, v, bt, cu, kvl, treq, _ = _attention_case(Hq, Hkv, hd, page, [(100, 1)], window, dtype)
+        pos = 99
+        inside, outside = pos + 1 - window, pos - window
+        for j, val in ((inside, 30.0), (outside, -70.0)):
+            pg = int(bt[0, j // page])
+            k[pg, 0, j % page] = (q[0, 0].float() * 4).to(dtype)
+            v[pg, 0, j % page] = val
+        out = torch.zeros(1, Hq * hd, dtype=dtype, device="cuda")
+        ops.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5,
+                            window, page, 1, 1, 100)
+        head0 = out[0, :hd].float().cpu()
+        assert head0.mean() > 25, "the key at the window's edge was not read"
+        ref = torch.zeros(1, Hq * hd)
+        cpu.paged_attention(q.float(), k.float(), v.float(), bt, cu, kvl, treq, ref, hd ** -0.5, window, page, 1, 0, 0)
+        close(out, ref, 3e-6 if dtype == torch.float32 else 1e-2, "window edge")
+
+
+def test_silu_gate_and_residual(ops):
+    gu = torch.randn(7, 2 * 200) * 3
+    ref = torch.zeros(7, 200)
+    cpu.silu_mul(gu, ref)
+    for odt, tol in ((torch.float32, 2e-6), (torch.bfloat16, 8e-3)):
+        out = torch.zeros(7, 200, dtype=odt, device="cuda")
+        ops.silu_mul(dev(gu), out)
+        close(out, ref, tol, "silu_mul")
+    x, y = torch.randn(5, 72), torch.randn(5, 72)
+    xd = dev(x.clone())
+    ops.residual_add(xd, dev(y.bfloat16()))
+    close(xd, x + y.bfloat16().float(), 1e-7, "residual")
+
+
+def test_argmax_first_maximum_wins(ops):
+    logits = torch.randn(6, 32003)
+    logits[1, 100] = logits[1, 31000] = 50.0          # a tie: the lower index
+    logits[2, :] = -float("inf")
+    logits[3, 0] = float("nan")
+    logits[3, 77] = 60.0
+    out = torch.zeros(6, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(logits), out)
+    want = [int(torch.argmax(logits[0])), 100, 0, 77, int(torch.argmax(logits[4])), int(torch.argmax(logits[5]))]
+    assert out.tolist() == want
+
+
+@pytest.mark.parametrize("V", [50, 331, 32000])
+def test_sampling_follows_the_plain_sampler(ops, V):
+    from tests.plain.sampling_plain import sample as plain_sample
+
+    class FixedU:
+        def __init__(self, u): self.u = u
+        def next_f32(self): return np.float32(self.u)
+
+    g = torch.Generator().manual_seed(V)
+    rows = []
+    for temp, k, p in ((0.8, 40, 0.95), (1.0, 0, 1.0), (0.5, 5, 1.0), (1.3, 0, 0.7), (0.0, 40, 0.95),
+                       (0.8, 1, 0.95), (2.0, 100, 0.5)):
+        for u in (0.0, 0.123, 0.5, 0.77, 0.999):
+            rows.append((temp, k, p, u))
+    R = len(rows)
+    logits = torch.randn(R, V, generator=g) * 2
+    logits[3, 5] = logits[3, 9] = logits[3].max() + 1          # ties among the most likely
+    out = torch.zeros(R, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(R * V, device="cuda")
+    f = lambda i, dt: dev(torch.tensor([r[i] for r in rows], dtype=dt))
+    ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32),
+               out, scratch)
+    got = out.tolist()
+    from tests.plain.sampling_plain import candidates
+    for i, (temp, k, p, u) in enumerate(rows):
+        want = plain_sample(logits[i].numpy(), temp, k, p, FixedU(u))
+        if got[i] == want:
+            continue
+        # The reference walks the sorted candidates subtracting 32-bit probabilities one by one; the
+        # kernel sums in another order. Over tens of thousands of terms the two running sums differ in
+        # their last bits, and a draw that lands within that rounding of a boundary between two
+        # candidates may fall on either side. Anything further from the boundary is a fault.
+        assert temp > 0
+        cand = candidates(logits[i].numpy(), temp, k, p)
+        ids = [t for t, _ in cand]
+        cum = np.cumsum(np.array([float(pr) for _, pr in cand], dtype=np.float64))
+        point = float(u) * cum[-1]
+        assert got[i] in ids, f"row {i}: token {got[i]} is not among the candidates"
+        j = ids.index(got[i])
+        lo = cum[j - 1] if j else 0.0
+        slack = 4 * len(cand) * np.finfo(np.float32).eps * cum[-1]
+        assert lo - slack <= point <= cum[j] + slack, (
+            f"row {i}: temperature {temp}, top_k {k}, top_p {p}, u {u}: token {got[i]} covers "
+            f"[{lo}, {cum[j]}], the draw is {point} (plain sampler: {want})")
