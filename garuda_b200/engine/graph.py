@@ -114,10 +114,19 @@ class DecodeGraphs:
         r.model.forward(ctx, caches)
         torch.cuda.synchronize(r.device)
         graph = torch.cuda.CUDAGraph()
+        before = getattr(r.ops, "launches", 0)
         with torch.cuda.graph(graph):
             logits = r.model.forward(ctx, caches)
+        cap.launches = getattr(r.ops, "launches", 0) - before      # kernels one replay runs
+        if hasattr(r.ops, "launches"):
+            r.ops.launches = before
         cap.graph, cap.logits, cap.ws = graph, logits, ws
         return cap
+
+    def launches_replayed(self, num_requests: int) -> int:
+        """Kernels that one replay for this many requests launches."""
+        cap = self.graphs.get(_bucket(num_requests))
+        return cap.launches if cap is not None else 0
 
     # ------------------------------------------------------------------ run
     def run(self, entries, new_lens) -> torch.Tensor:

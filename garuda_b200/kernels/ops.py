@@ -58,6 +58,7 @@ class CudaOps:
             from .tc import TensorCoreKernels
             self.tc = TensorCoreKernels(self)
         self._inv_freq = {}
+        self.launches = 0
         from ..engine.batch import Workspace
         self.private_ws = Workspace(self.device)   # scratch for calls made outside a step
 
@@ -90,9 +91,10 @@ class CudaOps:
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 
-    def _check(self, lib, code: int, what: str) -> None:
+    def _check(self, lib, code: int, what: str, kernels: int = 1) -> None:
         if code != 0:
             raise KernelError(f"{what}: {lib.gb_last_error().decode()}")
+        self.launches += kernels     # kernels of this library launched so far (not counting graph replays)
 
     def _on_device(self, *tensors):
         for t in tensors:

@@ -94,7 +94,9 @@ class TensorCoreKernels:
         code = self._call_attention(lib, q, k_pool, v_pool, out, scratch, block_table, cu_q, kv_lens,
                                     token_req, T, num_requests, Hq, Hkv, scale, window, page_size,
                                     max_q_len, splits)
-        self.ops._check(lib, code, "attention_mma")
+        g = Hq // Hkv
+        kernels = 1 + (1 if splits > 1 else 0) + (1 if max_q_len * g > 16 else 0)
+        self.ops._check(lib, code, "attention_mma", kernels)
         return True
 
     def _call_attention(self, lib, q, k_pool, v_pool, out, scratch, block_table, cu_q, kv_lens, token_req,
