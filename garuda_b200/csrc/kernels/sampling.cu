@@ -238,3 +238,49 @@ GB_EXPORT int gb_sample(const float* logits, const float* temperature, const int
   sample_kernel<<<R, 1024, 0, stream>>>(logits, temperature, top_k, top_p, u, out, scratch, V);
   return gb::check_launch("sample");
 }
+
+// ---------------------------------------------------------------------------
+// gb_sample_noalloc: the same kernel with work space that the library brings
+// itself, for callers that cannot allocate (see no_alloc.h for the contract).
+#include "no_alloc.h"
+
+namespace {
+
+// The work space. In host code this name is only a handle for the runtime's
+// symbol calls, never an address a kernel could use; the device address is
+// looked up once per device below.
+static __device__ __align__(256) float g_noalloc_scratch[GB_SAMPLE_NOALLOC_MAX_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_noalloc_ptr[MAX_DEVICES];   // device address of the array, per device; null until looked up
+
+}  // namespace
+
+GB_EXPORT int gb_sample_noalloc(const float* logits, const float* temperature, const int32_t* top_k,
+                                const float* top_p, const float* u, int32_t* out, int R, int V,
+                                cudaStream_t stream) {
+  if (R <= 0) return GB_OK;
+  if (V <= 0) return gb::fail(GB_BAD_ARGUMENT, "cannot sample from empty logits");
+  if ((long long)R * V > (long long)GB_SAMPLE_NOALLOC_MAX_FLOATS)
+    return gb::fail(GB_BAD_ARGUMENT,
+                    "gb_sample_noalloc: %d rows of %d logits need %lld floats of work space, the built-in "
+                    "array holds %d; use gb_sample with the caller's own scratch",
+                    R, V, (long long)R * V, (int)GB_SAMPLE_NOALLOC_MAX_FLOATS);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gb_sample_noalloc: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= MAX_DEVICES)
+    return gb::fail(GB_UNSUPPORTED, "gb_sample_noalloc: device %d is beyond the %d this table holds", device,
+                    MAX_DEVICES);
+  if (g_noalloc_ptr[device] == nullptr) {
+    // set-up, once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return gb::fail(GB_CUDA_ERROR, "gb_sample_noalloc: cannot find the work space on device %d: %s", device,
+                      cudaGetErrorString(e));
+    g_noalloc_ptr[device] = p;
+  }
+  sample_kernel<<<R, 1024, 0, stream>>>(logits, temperature, top_k, top_p, u, out, g_noalloc_ptr[device], V);
+  return gb::check_launch("sample (built-in work space)");
+}
