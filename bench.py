@@ -131,6 +131,9 @@ def run_ours(args) -> dict:
     V = cfg["vocab_size"]
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
+    if args.only:
+        return run_one_phase(args, engine, cfg, rng)
+
     # ---------------------------------------------------------------- prefill, 2048 tokens in one step
     toks = rng.integers(0, V, PREFILL_TOKENS).tolist()
     times = []
@@ -229,12 +232,53 @@ def run_ours(args) -> dict:
     }
 
 
+def run_one_phase(args, engine, cfg, rng) -> dict:
+    """One phase only, for profiling: `--only prefill` runs a 2,048-token prompt `steps` times,
+    `--only decode` prefills `--batch` requests and runs `steps` decode steps. Prints times, not the
+    benchmark record."""
+    import torch
+    from garuda_b200 import StepEntry
+    runner, V = engine.runner, cfg["vocab_size"]
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    times = []
+    if args.only == "prefill":
+        toks = rng.integers(0, V, PREFILL_TOKENS).tolist()
+        for i in range(args.warmup + args.steps):
+            s, e = ev(), ev()
+            torch.cuda.synchronize()
+            s.record()
+            runner.run([StepEntry(i, toks, [PREFILL_TOKENS - 1])])
+            e.record()
+            torch.cuda.synchronize()
+            runner.end(i)
+            if i >= args.warmup:
+                times.append(s.elapsed_time(e))
+    else:
+        ids = list(range(args.batch))
+        start_len = CONTEXT - args.steps - args.warmup
+        for r in ids:
+            runner.run([StepEntry(r, rng.integers(0, V, start_len).tolist(), [])])
+        for i in range(args.warmup + args.steps):
+            s, e = ev(), ev()
+            torch.cuda.synchronize()
+            s.record()
+            runner.run([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in ids])
+            e.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times.append(s.elapsed_time(e))
+    engine.ops.tc.check_errors()
+    return {"only": args.only, "batch": args.batch, "layers": args.layers, "ms": [round(t, 4) for t in times]}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", choices=["prefill", "decode"], help="run one phase only (for profiling)")
+    ap.add_argument("--batch", type=int, default=8, help="requests of the decode phase with --only decode")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS,
                     help="fewer layers than the configuration has (reported beside the full number)")
     args = ap.parse_args()
