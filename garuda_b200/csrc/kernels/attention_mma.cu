@@ -353,17 +353,20 @@ attention_mma_kernel(const Params p) {
   }
 }
 
-// One block per (token, query head) of a SPLIT request: combine the splits.
-__global__ void attention_merge_kernel(const Params p, const int32_t* __restrict__ token_req) {
+// One block per (request, kv head): combine the splits of a SPLIT request's rows.
+__global__ void __launch_bounds__(128)
+attention_merge_kernel(const Params p) {
   constexpr int RS = HD + 2;
-  const int t = blockIdx.x, h = blockIdx.y;
-  const int r = token_req[t];
-  const int q_len = p.cu_q[r + 1] - p.cu_q[r];
-  if (q_len * p.g > ROWS_SPLIT) return;   // a TILE request: its output is already final
-  const float* src = p.partial + ((size_t)t * p.Hq + h) * p.num_splits * RS;
-  float m = -INFINITY;
-  for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, src[s * RS + HD]);
-  for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+  const int r = blockIdx.x, kvh = blockIdx.y;
+  const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin;
+  const int nrows = q_len * p.g;
+  if (q_len <= 0 || nrows > ROWS_SPLIT) return;   // a TILE request: its output is already final
+  for (int idx = threadIdx.x; idx < nrows * HD; idx += blockDim.x) {
+    const int row = idx / HD, c = idx % HD;
+    const size_t orow = (size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g;
+    const float* src = p.partial + orow * p.num_splits * RS;
+    float m = -INFINITY;
+    for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, src[s * RS + HD]);
     float acc = 0.f, l = 0.f;
     for (int s = 0; s < p.num_splits; ++s) {
       const float ms = src[s * RS + HD];
@@ -371,7 +374,7 @@ __global__ void attention_merge_kernel(const Params p, const int32_t* __restrict
       acc += f * src[s * RS + c];
       l += f * src[s * RS + HD + 1];
     }
-    p.out[((size_t)t * p.Hq + h) * HD + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    p.out[orow * HD + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
   }
 }
 
@@ -393,12 +396,12 @@ GB_EXPORT long long gb_attention_mma_scratch_floats(int T, int Hq, int num_split
 
 // q [T, Hq, HD], pools [pages, Hkv, page_size, HD], out [T, Hq*HD], all bfloat16.
 // num_splits: CTAs that share the keys of a decode request (1: no scratch needed).
-// max_q_len decides which variants are launched.
+// max_q_len and min_q_len (over the batch's requests) decide which variants are launched.
 GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
                                const int32_t* block_table, int table_width, const int32_t* cu_q,
                                const int32_t* kv_lens, const int32_t* token_req, int T, int R, int Hq, int Hkv,
-                               float scale, int window, int page_size, int max_q_len, int num_splits,
-                               cudaStream_t stream) {
+                               float scale, int window, int page_size, int max_q_len, int min_q_len,
+                               int num_splits, cudaStream_t stream) {
   if (T <= 0 || R <= 0) return GB_OK;
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "attention: %d query heads for %d kv heads", Hq, Hkv);
   const int g = Hq / Hkv;
@@ -421,15 +424,15 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
       return gb::fail(GB_CUDA_ERROR, "attention_mma: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     configured = true;
   }
-  // SPLIT requests (a decode token's group, or a very short portion)
-  {
+  // SPLIT requests (a decode token's group, or a very short portion), if the batch can hold any
+  if (min_q_len * g <= ROWS_SPLIT) {
     dim3 grid(num_splits, Hkv, R);
     attention_mma_kernel<true><<<grid, THREADS, smem_bytes(true), stream>>>(p);
     int rc = gb::check_launch("attention_mma (split)");
     if (rc) return rc;
     if (num_splits > 1) {
-      dim3 mg(T, Hq);
-      attention_merge_kernel<<<mg, HD < 64 ? 32 : 64, 0, stream>>>(p, token_req);
+      dim3 mg(R, Hkv);
+      attention_merge_kernel<<<mg, 128, 0, stream>>>(p);
       rc = gb::check_launch("attention_merge");
       if (rc) return rc;
     }

@@ -58,48 +58,122 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict
     o[c] = gb::from_float<OT>((xr[c] * scale) * gb::to_float<WT>(w[c]));
 }
 
+template <typename OT>
+__device__ __forceinline__ void store4(OT* p, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<uint32_t*>(&lo);
+  v.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
+// Rows of up to 4096 values whose length is a multiple of 4: the row is read once, 16 bytes per
+// load, and kept in registers between the sum of squares and the scaling.
+template <typename WT, typename OT>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(const float* __restrict__ x, const WT* __restrict__ w, float eps, OT* __restrict__ out,
+                   const int32_t* __restrict__ rows, int d) {
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * d);
+  const int nvec = d >> 2;
+  float4 v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = threadIdx.x + i * 256;
+    v[i] = c < nvec ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  __shared__ float warp_part[8];
+  __shared__ float scale_s;
+  ss = gb::warp_sum(ss);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) warp_part[warp] = ss;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < 8 ? warp_part[lane] : 0.f;
+    t = gb::warp_sum(t);
+    if (lane == 0) scale_s = 1.0f / sqrtf(t / (float)d + eps);
+  }
+  __syncthreads();
+  const float scale = scale_s;
+  OT* o = out + (size_t)r * d;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c >= nvec) continue;
+    const float w0 = gb::to_float<WT>(w[4 * c]), w1 = gb::to_float<WT>(w[4 * c + 1]);
+    const float w2 = gb::to_float<WT>(w[4 * c + 2]), w3 = gb::to_float<WT>(w[4 * c + 3]);
+    store4<OT>(o + 4 * c, (v[i].x * scale) * w0, (v[i].y * scale) * w1, (v[i].z * scale) * w2,
+               (v[i].w * scale) * w3);
+  }
+}
+
 // ------------------------------------------------- rotary + cache write
-// One block per (token, head). Heads [0, Hq) are queries, [Hq, Hq+Hkv) keys,
-// [Hq+Hkv, Hq+2Hkv) values. Angle = (float)pos * inv_freq[i], in 32-bit.
+// One block per token. Heads [0, Hq) are queries, [Hq, Hq+Hkv) keys, [Hq+Hkv, Hq+2Hkv) values.
+// Angle = (float)pos * inv_freq[i], in 32-bit; sine and cosine are computed once per token and pair.
 template <typename IT, typename OT>
-__global__ void rope_kv_append_kernel(const IT* __restrict__ qkv, int row_stride, OT* __restrict__ q_out,
-                                      OT* __restrict__ k_pool, OT* __restrict__ v_pool,
-                                      const int32_t* __restrict__ positions,
-                                      const int32_t* __restrict__ token_req,
-                                      const int32_t* __restrict__ block_table, int table_width,
-                                      int Hq, int Hkv, int hd, const float* __restrict__ inv_freq,
-                                      int interleaved, int page_size) {
-  const int t = blockIdx.x, head = blockIdx.y;
+__global__ void __launch_bounds__(256)
+rope_kv_append_kernel(const IT* __restrict__ qkv, int row_stride, OT* __restrict__ q_out,
+                      OT* __restrict__ k_pool, OT* __restrict__ v_pool,
+                      const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
+                      const int32_t* __restrict__ block_table, int table_width, int Hq, int Hkv, int hd,
+                      const float* __restrict__ inv_freq, int interleaved, int page_size) {
+  __shared__ float sin_s[128], cos_s[128];   // head_dim / 2 <= 128
+  const int t = blockIdx.x;
   const int pos = positions[t];
-  const IT* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
-  OT* dst;
-  bool rotate = inv_freq != nullptr;
-  if (head < Hq) {
-    dst = q_out + ((size_t)t * Hq + head) * hd;
-  } else {
-    const int kvh = (head - Hq) % Hkv;
-    const bool is_v = head >= Hq + Hkv;
-    const int req = token_req[t];
-    const int page = block_table[(size_t)req * table_width + pos / page_size];
-    if (page < 0) return;  // no page behind this position: the host refuses such a step
-    OT* pool = is_v ? v_pool : k_pool;
-    dst = pool + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * hd;
-    if (is_v) rotate = false;
-  }
-  if (!rotate) {
-    for (int c = threadIdx.x; c < hd; c += blockDim.x) dst[c] = gb::from_float<OT>(gb::to_float<IT>(src[c]));
-    return;
-  }
   const int half = hd >> 1;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float ang = (float)pos * inv_freq[i];
-    float s, c;
-    sincosf(ang, &s, &c);
+  const bool rotate = inv_freq != nullptr;
+  if (rotate) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sin_s[i], &cos_s[i]);
+  }
+  long long cache_row = -1;   // row of this token in the pools, in units of one head's page_size * hd block
+  if (Hkv > 0) {
+    const int page = block_table[(size_t)token_req[t] * table_width + pos / page_size];
+    // no page behind this position: the host refuses such a step; nothing is stored
+    if (page >= 0) cache_row = (long long)page * Hkv;
+  }
+  __syncthreads();
+  const IT* src = qkv + (size_t)t * row_stride;
+  // queries and keys: pairs
+  const int rot_heads = Hq + Hkv;
+  for (int e = threadIdx.x; e < rot_heads * half; e += blockDim.x) {
+    const int head = e / half, i = e % half;
     const int ia = interleaved ? 2 * i : i;
     const int ib = interleaved ? 2 * i + 1 : i + half;
-    const float a = gb::to_float<IT>(src[ia]), b = gb::to_float<IT>(src[ib]);
-    dst[ia] = gb::from_float<OT>(a * c - b * s);
-    dst[ib] = gb::from_float<OT>(a * s + b * c);
+    const IT* s = src + (size_t)head * hd;
+    OT* dst;
+    if (head < Hq) {
+      dst = q_out + ((size_t)t * Hq + head) * hd;
+    } else {
+      if (cache_row < 0) continue;
+      dst = k_pool + ((cache_row + (head - Hq)) * page_size + (pos % page_size)) * hd;
+    }
+    const float a = gb::to_float<IT>(s[ia]), b = gb::to_float<IT>(s[ib]);
+    if (rotate) {
+      dst[ia] = gb::from_float<OT>(a * cos_s[i] - b * sin_s[i]);
+      dst[ib] = gb::from_float<OT>(a * sin_s[i] + b * cos_s[i]);
+    } else {
+      dst[ia] = gb::from_float<OT>(a);
+      dst[ib] = gb::from_float<OT>(b);
+    }
+  }
+  // values: a copy
+  if (cache_row >= 0) {
+    const IT* vs = src + (size_t)(Hq + Hkv) * hd;
+    for (int e = threadIdx.x; e < Hkv * hd; e += blockDim.x) {
+      const int head = e / hd, c = e % hd;
+      v_pool[((cache_row + head) * page_size + (pos % page_size)) * hd + c] =
+          gb::from_float<OT>(gb::to_float<IT>(vs[e]));
+    }
   }
 }
 
@@ -162,7 +236,10 @@ GB_EXPORT int gb_rmsnorm(const float* x, const void* w, int w_dtype, float eps, 
   const int block = d >= 1024 ? 256 : 128;
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
-      rmsnorm_kernel<WT, OT><<<n_rows, block, 0, stream>>>(x, (const WT*)w, eps, (OT*)out, rows, d);
+      if (d % 4 == 0 && d <= 4096 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0)
+        rmsnorm_vec_kernel<WT, OT><<<n_rows, 256, 0, stream>>>(x, (const WT*)w, eps, (OT*)out, rows, d);
+      else
+        rmsnorm_kernel<WT, OT><<<n_rows, block, 0, stream>>>(x, (const WT*)w, eps, (OT*)out, rows, d);
       return gb::check_launch("rmsnorm");
     });
   });
@@ -177,13 +254,14 @@ GB_EXPORT int gb_rope_kv_append(const void* qkv, int in_dtype, int row_stride, v
   if (hd % 2) return gb::fail(GB_UNSUPPORTED, "rope_kv_append: head_dim %d is odd", hd);
   if (Hkv > 0 && (!k_pool || !v_pool || !block_table || page_size < 1))
     return gb::fail(GB_BAD_ARGUMENT, "rope_kv_append: kv heads given without a cache to store them in");
-  dim3 grid(T, Hq + 2 * Hkv);
-  const int block = hd / 2 >= 64 ? 64 : 32;
+  if (hd > 256) return gb::fail(GB_UNSUPPORTED, "rope_kv_append: head_dim %d is larger than 256", hd);
+  const int work = (Hq + Hkv) * (hd / 2);
+  const int block = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
   return GB_DISPATCH_DTYPE(in_dtype, IT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
-      rope_kv_append_kernel<IT, OT><<<grid, block, 0, stream>>>(
+      rope_kv_append_kernel<IT, OT><<<T, block, 0, stream>>>(
           (const IT*)qkv, row_stride, (OT*)q_out, (OT*)k_pool, (OT*)v_pool, positions, token_req,
-          block_table, table_width, Hq, Hkv > 0 ? Hkv : 1, hd, inv_freq, interleaved, page_size);
+          block_table, table_width, Hq, Hkv, hd, inv_freq, interleaved, page_size);
       return gb::check_launch("rope_kv_append");
     });
   });

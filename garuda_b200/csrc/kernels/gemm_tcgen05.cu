@@ -15,6 +15,14 @@
 // are tokens, so that the weight stream fills the tensor core's rows and the
 // result is written transposed.
 //
+// In the swapped orientation a matrix has few 128-row tiles (16 to 44 for a
+// 2048-wide layer), too few CTAs to pull memory at full rate. There the K range
+// is split over the CTAs of a thread-block cluster: every CTA accumulates its
+// share of K in its own tensor memory, the others send their partial sums into
+// the leader's shared memory (distributed shared memory), and the leader adds
+// them in rank order and runs the epilogue. No scratch in global memory, no
+// atomics, and the same sum order every time.
+//
 // Rows outside a matrix are zero-filled by TMA and masked in the epilogue; K
 // need not be a multiple of 64 (the tail is zero-filled) but must be a multiple
 // of 8, because a TMA row pitch is a multiple of 16 bytes.
@@ -31,18 +39,24 @@ constexpr int BM = 128;   // MMA rows per CTA
 constexpr int BK = 64;    // bf16 per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 128;
-constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // one CTA per SM
+constexpr int SMEM_BUDGET_SMALL = 110 * 1024;   // two CTAs per SM: more CTAs of a cluster fit side by side
 
 enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2 };
 
 __device__ int g_error_word;
 
-template <int BN, bool DUAL_M, bool DUAL_N>
+template <int BN, bool DUAL_M, bool DUAL_N, bool TRANS = false>
 struct Geometry {
   static constexpr int NUM_M = DUAL_M ? 2 : 1, NUM_N = DUAL_N ? 2 : 1;
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = NUM_M * A_BYTES + NUM_N * B_BYTES;
+  static constexpr int SMEM_BUDGET = (TRANS && !DUAL_M) ? SMEM_BUDGET_SMALL : SMEM_BUDGET_LARGE;
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
+  // bytes one peer of a cluster sends to the leader, and how many peers the pipeline's memory holds
+  static constexpr int PARTIAL_BYTES = NUM_M * NUM_N * BN * BM * 4;
+  static constexpr int MAX_CLUSTER = 1 + (STAGES * STAGE_BYTES) / PARTIAL_BYTES < 8
+                                         ? 1 + (STAGES * STAGE_BYTES) / PARTIAL_BYTES : 8;
   static constexpr int ACCUMULATORS = NUM_M * NUM_N;
   static constexpr int COLS_NEEDED = ACCUMULATORS * BN;
   static constexpr int TMEM_COLS = COLS_NEEDED <= 32 ? 32 : COLS_NEEDED <= 64 ? 64 : COLS_NEEDED <= 128 ? 128
@@ -61,15 +75,32 @@ __device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, flo
 
 __device__ __forceinline__ float silu_gate(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 
+// ---- thread-block cluster helpers (split-K over distributed shared memory)
+__device__ __forceinline__ void cluster_arrive_wait() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address, in the cluster's shared window, of `local` in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
 // rows_m / rows_n: valid rows of the MMA-row operand and of the MMA-column operand.
 // TRANS: the MMA rows are output columns (swapped orientation).
-template <int BN, bool DUAL_M, bool DUAL_N, int EPI, bool TRANS, typename OT>
+// CLUSTER: the CTAs of a cluster (gridDim.z of them, along z) split the K blocks,
+// kb_per_rank each; rank 0 collects the partial sums and writes the result.
+template <int BN, bool DUAL_M, bool DUAL_N, int EPI, bool TRANS, bool CLUSTER, typename OT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_m2,
                const __grid_constant__ CUtensorMap map_n, const __grid_constant__ CUtensorMap map_n2,
-               OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K) {
-  using G = Geometry<BN, DUAL_M, DUAL_N>;
+               OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int kb_per_rank) {
+  using G = Geometry<BN, DUAL_M, DUAL_N, TRANS>;
   constexpr int STAGES = G::STAGES;
+  constexpr int ACC = G::ACCUMULATORS;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -79,7 +110,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int num_kb = (K + BK - 1) / BK;
+  const int total_kb = (K + BK - 1) / BK;
+  const int rank = CLUSTER ? (int)blockIdx.z : 0;
+  const int ranks = CLUSTER ? (int)gridDim.z : 1;
+  const int kb_begin = CLUSTER ? rank * kb_per_rank : 0;
+  const int kb_end = CLUSTER ? min(total_kb, kb_begin + kb_per_rank) : total_kb;
+  const int num_kb = max(kb_end - kb_begin, 0);
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
   if (threadIdx.x == 0) {
@@ -106,9 +142,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
     int issued = 0;
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t phase = (kb / STAGES) & 1;
+    for (int it = 0; it < num_kb; ++it) {
+      const int s = it % STAGES;
+      const uint32_t phase = (it / STAGES) & 1;
       if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1)) {
         atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
         abort_s = 1;
@@ -117,18 +153,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
       if (*(volatile int*)&abort_s) break;
       const uint32_t bar = smem_u32(&full_bar[s]);
       const uint32_t base = tiles + s * G::STAGE_BYTES;
+      const int k0 = (kb_begin + it) * BK;
       mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
-      tma_load_2d(base, &map_m, bar, kb * BK, m0);
-      if (DUAL_M) tma_load_2d(base + G::A_BYTES, &map_m2, bar, kb * BK, m0);
-      tma_load_2d(base + G::NUM_M * G::A_BYTES, &map_n, bar, kb * BK, n0);
-      if (DUAL_N) tma_load_2d(base + G::NUM_M * G::A_BYTES + G::B_BYTES, &map_n2, bar, kb * BK, n0);
-      issued = kb + 1;
+      tma_load_2d(base, &map_m, bar, k0, m0);
+      if (DUAL_M) tma_load_2d(base + G::A_BYTES, &map_m2, bar, k0, m0);
+      tma_load_2d(base + G::NUM_M * G::A_BYTES, &map_n, bar, k0, n0);
+      if (DUAL_N) tma_load_2d(base + G::NUM_M * G::A_BYTES + G::B_BYTES, &map_n2, bar, k0, n0);
+      issued = it + 1;
     }
     if (*(volatile int*)&abort_s) {
       // wind down: let the copies already in flight land before the CTA's shared memory is given up
-      for (int kb = issued > STAGES ? issued - STAGES : 0; kb < issued; ++kb) {
+      for (int it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it) {
         const unsigned long long t0 = globaltimer_ns();
-        while (!mbar_try_wait(smem_u32(&full_bar[kb % STAGES]), (kb / STAGES) & 1)) {
+        while (!mbar_try_wait(smem_u32(&full_bar[it % STAGES]), (it / STAGES) & 1)) {
           if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
             atomicCAS(&g_error_word, 0, ERR_WAIT_DRAIN);
             break;
@@ -139,14 +176,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
     constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
-    bool ok = true;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t phase = (kb / STAGES) & 1;
+    for (int it = 0; it < num_kb; ++it) {
+      const int s = it % STAGES;
+      const uint32_t phase = (it / STAGES) & 1;
       if (!mbar_wait(smem_u32(&full_bar[s]), phase)) {
         atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
         abort_s = 1;
-        ok = false;
         break;
       }
       tc_fence_after_sync();
@@ -154,7 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
 #pragma unroll
       for (int k = 0; k < BK / UMMA_K; ++k) {
         const uint32_t koff = k * UMMA_K * 2;  // bytes along the swizzled row
-        const bool acc = kb > 0 || k > 0;
+        const bool acc = it > 0 || k > 0;
         const uint64_t da = smem_desc_sw128(base + koff);
         const uint64_t db = smem_desc_sw128(base + G::NUM_M * G::A_BYTES + koff);
         mma_bf16(tmem_base, da, db, idesc, acc);
@@ -169,14 +204,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
   }
   __syncwarp();
 
-  // -------------------------------------------------------------------- epilogue
+  // ---------------------------------------------------------- the accumulator is complete
   bool have = mbar_wait(smem_u32(&accum_bar), 0);
   if (!have && lane == 0) atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
   have = have && !*(volatile int*)&abort_s;
   tc_fence_after_sync();
-  if (have) {
-    const int row = m0 + warp * 32 + lane;           // this thread's MMA row
-    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const int row_in_tile = warp * 32 + lane;
+
+  if (CLUSTER) {
+    // Every CTA of the cluster has finished its MMAs: the leader's pipeline memory is free
+    // to receive the partial sums. Both barriers are reached by every thread whatever happened
+    // before, so that no CTA waits for one that gave up.
+    cluster_arrive_wait();
+    if (rank != 0 && num_kb > 0) {
+      // partial[(rank - 1)][accumulator][column][row]: consecutive lanes write consecutive words
+      const uint32_t mine = tiles + (uint32_t)(rank - 1) * G::PARTIAL_BYTES + (uint32_t)row_in_tile * 4;
+      const uint32_t remote = map_to_rank(mine, 0);
+#pragma unroll 1
+      for (int a = 0; a < ACC; ++a) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          tmem_ld_16(taddr + a * BN + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            st_cluster_f32(remote + (uint32_t)((a * BN + c + j) * BM * 4), have ? __uint_as_float(r[j]) : 0.f);
+        }
+      }
+    }
+    cluster_arrive_wait();
+  }
+
+  // -------------------------------------------------------------------- epilogue
+  if (have && rank == 0) {
+    const int row = m0 + row_in_tile;           // this thread's MMA row
+    const float* partial = reinterpret_cast<const float*>(smem_raw + (tiles - smem_u32(smem_raw)));
 #pragma unroll 1
     for (int c = 0; c < BN; c += 16) {
       uint32_t r0[16], r1[16];
@@ -189,7 +253,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
           const int col = n0 + c + j;
           if (col >= rows_n) continue;
           float v = __uint_as_float(r0[j]);
-          if (EPI == EPI_SWIGLU) v = silu_gate(v, __uint_as_float(r1[j]));
+          float v1 = EPI == EPI_SWIGLU ? __uint_as_float(r1[j]) : 0.f;
+          if (CLUSTER) {
+            for (int p = 1; p < ranks; ++p) {       // rank order: the same sum every time
+              if (p * kb_per_rank >= total_kb) break;  // that rank had no K blocks
+              const float* src = partial + (size_t)(p - 1) * (G::PARTIAL_BYTES / 4);
+              v += src[(c + j) * BM + row_in_tile];
+              if (EPI == EPI_SWIGLU) v1 += src[(BN + c + j) * BM + row_in_tile];
+            }
+          }
+          if (EPI == EPI_SWIGLU) v = silu_gate(v, v1);
           OT* p = TRANS ? out + (size_t)col * ldo + row : out + (size_t)row * ldo + col;
           if (EPI == EPI_ACCUMULATE) v += gb::to_float<OT>(*p);
           store_value<OT>(p, v);
@@ -264,19 +337,76 @@ int tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows,
   return GB_OK;
 }
 
+// How many CTAs of a cluster share K: as many as fill the GPU in one wave, given how
+// many clusters of each size can run at once (asked of the runtime once per kernel).
+// `active[s]`: clusters of size s that can be resident at once (0: not asked yet), kept by the caller
+// per kernel.
+template <typename Kernel>
+int pick_cluster_size(Kernel kernel, int* active, int smem_bytes, int tiles, int total_kb, int max_cluster) {
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= max_cluster && s <= total_kb; ++s) {
+    if (active[s] == 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(1, 148, s);
+      cfg.blockDim = dim3(THREADS);
+      cfg.dynamicSmemBytes = smem_bytes;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = s;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        n = -1;
+      }
+      active[s] = n;
+    }
+    if (active[s] < 1) continue;
+    const int per = (total_kb + s - 1) / s;
+    const int waves = (tiles + active[s] - 1) / active[s];
+    const double cost = waves * (per + 6.0 + 0.5 * s);   // K blocks per CTA, plus fixed and gathering costs
+    if (cost < best_cost) { best_cost = cost; best = s; }
+  }
+  return best;
+}
+
 template <int BN, bool DUAL_M, bool DUAL_N, int EPI, bool TRANS, typename OT>
 int launch(const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn, const CUtensorMap& mn2, OT* out,
            int ldo, int rows_m, int rows_n, int K, cudaStream_t stream) {
-  using G = Geometry<BN, DUAL_M, DUAL_N>;
-  auto kernel = gemm_tc_kernel<BN, DUAL_M, DUAL_N, EPI, TRANS, OT>;
+  using G = Geometry<BN, DUAL_M, DUAL_N, TRANS>;
+  constexpr bool CLUSTER = TRANS;
+  auto kernel = gemm_tc_kernel<BN, DUAL_M, DUAL_N, EPI, TRANS, CLUSTER, OT>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((rows_n + BN - 1) / BN, (rows_m + BM - 1) / BM);
-  kernel<<<grid, THREADS, G::SMEM_BYTES, stream>>>(mm, mm2, mn, mn2, out, ldo, rows_m, rows_n, K);
+  const int tiles_n = (rows_n + BN - 1) / BN, tiles_m = (rows_m + BM - 1) / BM;
+  const int total_kb = (K + BK - 1) / BK;
+  if (!CLUSTER) {
+    dim3 grid(tiles_n, tiles_m);
+    kernel<<<grid, THREADS, G::SMEM_BYTES, stream>>>(mm, mm2, mn, mn2, out, ldo, rows_m, rows_n, K, total_kb);
+    return gb::check_launch("gemm_tc");
+  }
+  static int active[9] = {0};
+  int split = pick_cluster_size(kernel, active, G::SMEM_BYTES, tiles_n * tiles_m, total_kb, G::MAX_CLUSTER);
+  const int per = (total_kb + split - 1) / split;
+  split = (total_kb + per - 1) / per;            // no rank without K blocks
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles_n, tiles_m, split);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = G::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = split;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mm, mm2, mn, mn2, out, ldo, rows_m, rows_n, K, per);
+  if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc (cluster of %d): %s", split, cudaGetErrorString(e));
   return gb::check_launch("gemm_tc");
 }
 

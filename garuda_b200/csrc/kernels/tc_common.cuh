@@ -57,14 +57,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Waits for the phase with the given parity to complete. False after WAIT_LIMIT_NS.
+// The clock is read only once in a few thousand polls: reading it costs far more than a
+// poll, and a waiter that is busy reading the clock wakes up late.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-#pragma unroll 1
-  for (int i = 0; i < 128; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = 0;
+  uint32_t polls = 0;
 #pragma unroll 1
   while (!mbar_try_wait(bar, parity)) {
-    if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+    if ((++polls & 0xFFFu) == 0) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) return false;
+    }
   }
   return true;
 }

@@ -39,6 +39,7 @@ class StepBatch:
     num_logit_rows: int
     max_q_len: int
     max_kv_len: int
+    min_q_len: int = 1
     # host copies, for parts written in Python (toy mixers) and for checks
     host: Dict[str, list] = field(default_factory=dict)
 

@@ -120,6 +120,7 @@ class StepRunner:
         t = w = 0
         cu_q[0] = 0
         max_q = max_kv = 0
+        min_q = 1 << 30
         for i, (e, (_, new_len)) in enumerate(zip(entries, new_lens)):
             n = len(e.tokens)
             start = new_len - n
@@ -133,7 +134,7 @@ class StepRunner:
             cu_q[i + 1] = t
             kv_lens[i] = new_len
             slots[i] = mgr.slot(e.request)
-            max_q, max_kv = max(max_q, n), max(max_kv, new_len)
+            max_q, max_kv, min_q = max(max_q, n), max(max_kv, new_len), min(min_q, n)
         tables = view("tables").reshape(G, R, width) if G else None
         if G:
             mgr.fill_block_tables([e.request for e in entries], tables)
@@ -153,7 +154,7 @@ class StepRunner:
             num_tokens=T, num_requests=R, token_ids=dview("token_ids"), positions=dview("positions"),
             token_req=dview("token_req"), cu_q=dview("cu_q"), kv_lens=dview("kv_lens"),
             slots=dview("slots"), block_tables=dtables, logit_rows=dview("logit_rows")[:W],
-            num_logit_rows=W, max_q_len=max_q, max_kv_len=max_kv,
+            num_logit_rows=W, max_q_len=max_q, max_kv_len=max_kv, min_q_len=min_q,
             host={"token_ids": token_ids, "positions": positions, "token_req": token_req, "cu_q": cu_q,
                   "kv_lens": kv_lens, "slots": slots, "logit_rows": logit_rows[:W],
                   "requests": [e.request for e in entries]},

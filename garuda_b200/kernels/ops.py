@@ -220,7 +220,7 @@ class CudaOps:
             self.inv_freq(theta, hd).data_ptr(), int(interleaved), self._stream()), "rope_inplace")
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
-                        scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None):
+                        scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1):
         self._on_device(q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out)
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
@@ -231,7 +231,7 @@ class CudaOps:
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: block table")
         if self.tc is not None and q.dtype == torch.bfloat16 and self.tc.paged_attention(
                 q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
-                num_requests, max_q_len, max_kv_len, ws):
+                num_requests, max_q_len, max_kv_len, ws, min_q_len):
             return
         self._check(self.core, self.core.gb_attention_simple(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _tag(q, "attention q"),

@@ -64,7 +64,7 @@ class TensorCoreKernels:
             lib = load_kernel_lib(attention_lib_name(head_dim))
             lib.gb_last_error.restype = ctypes.c_char_p
             lib.gb_attention_mma.argtypes = ([c_void_p] * 6 + [c_int] + [c_void_p] * 3 + [c_int] * 4 + [c_float]
-                                             + [c_int] * 4 + [c_void_p])
+                                             + [c_int] * 5 + [c_void_p])
             lib.gb_attention_mma.restype = c_int
             lib.gb_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int]
             lib.gb_attention_mma_scratch_floats.restype = ctypes.c_longlong
@@ -80,30 +80,32 @@ class TensorCoreKernels:
         return max(1, min(want, tiles, 64))
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale,
-                        window, page_size, num_requests, max_q_len, max_kv_len, ws=None) -> bool:
+                        window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1) -> bool:
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
         if hd % 16 or hd > 128 or Hq // Hkv > 64:
             return False
         lib = self._attention_lib(hd)
-        splits = self.attention_splits(num_requests, Hkv, max_kv_len)
+        g = Hq // Hkv
+        has_split = min_q_len * g <= 16
+        splits = self.attention_splits(num_requests, Hkv, max_kv_len) if has_split else 1
         scratch = None
         if splits > 1:
             n = lib.gb_attention_mma_scratch_floats(T, Hq, splits)
             scratch = (ws or self.ops.private_ws).get("attention_partial", (n,), torch.float32)
         code = self._call_attention(lib, q, k_pool, v_pool, out, scratch, block_table, cu_q, kv_lens,
                                     token_req, T, num_requests, Hq, Hkv, scale, window, page_size,
-                                    max_q_len, splits)
-        g = Hq // Hkv
-        kernels = 1 + (1 if splits > 1 else 0) + (1 if max_q_len * g > 16 else 0)
+                                    max_q_len, min_q_len, splits)
+        kernels = (1 if has_split else 0) + (1 if splits > 1 else 0) + (1 if max_q_len * g > 16 else 0)
         self.ops._check(lib, code, "attention_mma", kernels)
         return True
 
     def _call_attention(self, lib, q, k_pool, v_pool, out, scratch, block_table, cu_q, kv_lens, token_req,
-                        T, R, Hq, Hkv, scale, window, page_size, max_q_len, splits) -> int:
+                        T, R, Hq, Hkv, scale, window, page_size, max_q_len, min_q_len, splits) -> int:
         return lib.gb_attention_mma(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
             None if scratch is None else scratch.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), token_req.data_ptr(),
-            T, R, Hq, Hkv, float(scale), int(window), int(page_size), int(max_q_len), int(splits),
+            T, R, Hq, Hkv, float(scale), int(window), int(page_size), int(max_q_len), int(min_q_len),
+            int(splits),
             self.ops._stream())

@@ -87,7 +87,7 @@ class PagedAttention(Mixer):
         out = ws.get("attn_ctx", (T, self.q_dim), self.dtype)
         ops.paged_attention(q, cache.k, cache.v, cache.block_table, b.cu_q, b.kv_lens, b.token_req, out,
                             self.scale, self.window or 0, cache.page_size,
-                            b.num_requests, b.max_q_len, b.max_kv_len, ws=ws)
+                            b.num_requests, b.max_q_len, b.max_kv_len, ws=ws, min_q_len=b.min_q_len)
         if residual is not None:
             ops.linear(out, self.w_o, residual, accumulate=True)
             return None

@@ -107,7 +107,7 @@ class CpuOps:
 
     # garuda/src/llama/mod.rs:793-818; garuda/src/cache/mod.rs:333-338
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
-                        scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None):
+                        scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1):
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
         g = Hq // Hkv
