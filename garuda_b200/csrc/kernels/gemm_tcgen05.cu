@@ -275,6 +275,235 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, G::TMEM_COLS);
 }
 
+// --------------------------------------------------------------------------
+// Many tokens: a persistent kernel. One CTA per SM walks a list of 128 x BN
+// tiles. Warp 0 feeds the shared-memory pipeline, warp 1 issues the MMAs into
+// one of two accumulator stages in tensor memory, warps 2-5 drain the other
+// stage (tcgen05.ld, epilogue arithmetic, 16-byte stores), so the epilogue of a
+// tile runs under the matrix product of the next.
+constexpr int P_THREADS = 192;
+
+template <typename OT>
+__device__ __forceinline__ void epilogue_store16(OT* p, const float (&v)[16], bool vec);
+template <>
+__device__ __forceinline__ void epilogue_store16<float>(float* p, const float (&v)[16], bool vec) {
+  if (vec) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) p[i] = v[i];
+  }
+}
+template <>
+__device__ __forceinline__ void epilogue_store16<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[16], bool vec) {
+  if (vec) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 u;
+      __nv_bfloat162 a = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]), b = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+      __nv_bfloat162 c = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]), d = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+      u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+      u.z = *reinterpret_cast<uint32_t*>(&c); u.w = *reinterpret_cast<uint32_t*>(&d);
+      reinterpret_cast<uint4*>(p)[i] = u;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) p[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+// The SiLU-gate of the fused epilogue. The exponential is the hardware's fast one: its error
+// (about 2 ulp of a float) is far below the rounding of the bfloat16 result.
+__device__ __forceinline__ float silu_gate_fast(float g, float u) {
+  return g * __frcp_rn(1.0f + __expf(-g)) * u;
+}
+
+template <int BN, bool DUAL, int EPI, typename OT>
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
+                          const __grid_constant__ CUtensorMap map_n2, OT* __restrict__ out, int ldo, int rows_m,
+                          int rows_n, int K, int tiles_m, int tiles_n) {
+  using G = Geometry<BN, false, DUAL, false>;
+  constexpr int STAGES = G::STAGES;
+  constexpr int ACC_COLS = G::ACCUMULATORS * BN;        // columns of one accumulator stage
+  constexpr int TMEM_COLS = 2 * ACC_COLS;               // two stages: 256 or 512
+  static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "two accumulator stages must fill a power of two");
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (K + BK - 1) / BK;
+  const int total_tiles = tiles_m * tiles_n;
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&acc_full[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), 4);      // one arrival per epilogue warp
+    }
+    abort_s = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tensormap(&map_m);
+    prefetch_tensormap(&map_n);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* aborted = &abort_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ producer
+      int it = 0, issued = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*aborted; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) & 1) ^ 1)) {
+            atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
+            *aborted = 1;
+          }
+          if (*aborted) break;
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          const uint32_t base = tiles + s * G::STAGE_BYTES;
+          mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
+          tma_load_2d(base, &map_m, bar, kb * BK, m0);
+          tma_load_2d(base + G::A_BYTES, &map_n, bar, kb * BK, n0);
+          if (DUAL) tma_load_2d(base + G::A_BYTES + G::B_BYTES, &map_n2, bar, kb * BK, n0);
+          issued = it + 1;
+        }
+      }
+      if (*aborted) {
+        for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
+          const unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(&full_bar[j % STAGES]), (j / STAGES) & 1)) {
+            if (globaltimer_ns() - t0 > 20000000ull) {
+              atomicCAS(&g_error_word, 0, ERR_WAIT_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+      int it = 0, t = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*aborted; tile += gridDim.x, ++t) {
+        const int as = t & 1;
+        if (!mbar_wait(smem_u32(&acc_empty[as]), ((t >> 1) & 1) ^ 1)) {   // the epilogue has drained this stage
+          atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+          *aborted = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t acc = tmem_base + as * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) {
+            atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
+            *aborted = 1;
+          }
+          if (*aborted) break;
+          tc_fence_after_sync();
+          const uint32_t base = tiles + s * G::STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t koff = k * UMMA_K * 2;
+            const bool accumulate = kb > 0 || k > 0;
+            const uint64_t da = smem_desc_sw128(base + koff);
+            mma_bf16(acc, da, smem_desc_sw128(base + G::A_BYTES + koff), idesc, accumulate);
+            if (DUAL)
+              mma_bf16(acc + BN, da, smem_desc_sw128(base + G::A_BYTES + G::B_BYTES + koff), idesc, accumulate);
+          }
+          mma_commit(smem_u32(&empty_bar[s]));
+        }
+        mma_commit(smem_u32(&acc_full[as]));
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue warps
+    const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4)
+    const bool vec = (((uintptr_t)out) & 15) == 0 && ((size_t)ldo * sizeof(OT)) % 16 == 0;
+    int t = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
+      const int as = t & 1;
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
+      if (!have && lane == 0) {
+        atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+        *aborted = 1;
+      }
+      if (!have || *aborted) break;
+      tc_fence_after_sync();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + as * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t r0[16], r1[16];
+        tmem_ld_16(taddr + c, r0);
+        if (EPI == EPI_SWIGLU) tmem_ld_16(taddr + BN + c, r1);
+        tmem_ld_wait();
+        const int col = n0 + c;
+        if (row >= rows_m || col >= rows_n) continue;
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          v[j] = __uint_as_float(r0[j]);
+          if (EPI == EPI_SWIGLU) v[j] = silu_gate_fast(v[j], __uint_as_float(r1[j]));
+        }
+        OT* p = out + (size_t)row * ldo + col;
+        if (col + 16 <= rows_n) {
+          if (EPI == EPI_ACCUMULATE) {
+            if (vec) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float4 old = reinterpret_cast<const float4*>(p)[i];
+                v[4 * i] += old.x; v[4 * i + 1] += old.y; v[4 * i + 2] += old.z; v[4 * i + 3] += old.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += gb::to_float<OT>(p[j]);
+            }
+          }
+          epilogue_store16<OT>(p, v, vec);
+        } else {
+          for (int j = 0; j < 16 && col + j < rows_n; ++j) {
+            float x = v[j];
+            if (EPI == EPI_ACCUMULATE) x += gb::to_float<OT>(p[j]);
+            store_value<OT>(p + j, x);
+          }
+        }
+      }
+      // every read of this accumulator stage has completed: hand it back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[as]));
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -410,6 +639,45 @@ int launch(const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn,
   return gb::check_launch("gemm_tc");
 }
 
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v;
+  }();
+  return n;
+}
+
+template <int BN, bool DUAL, int EPI, typename OT>
+int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, const CUtensorMap& mn2, OT* out, int ldo,
+                      int rows_m, int rows_n, int K, cudaStream_t stream) {
+  using G = Geometry<BN, false, DUAL, false>;
+  auto kernel = gemm_tc_persistent_kernel<BN, DUAL, EPI, OT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
+    if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tiles_m = (rows_m + BM - 1) / BM, tiles_n = (rows_n + BN - 1) / BN;
+  const int total = tiles_m * tiles_n;
+  const int grid = total < sm_count() ? total : sm_count();
+  kernel<<<grid, P_THREADS, G::SMEM_BYTES, stream>>>(mm, mn, mn2, out, ldo, rows_m, rows_n, K, tiles_m, tiles_n);
+  return gb::check_launch("gemm_tc (persistent)");
+}
+
+// Tile width for many tokens: the one that needs fewer rounds over the SMs (a 256-wide tile costs
+// two 128-wide ones but reads each operand half as often); ties go to the wide tile.
+int pick_tile_width(int rows_m, int rows_n) {
+  const int tiles_m = (rows_m + BM - 1) / BM, sms = sm_count();
+  auto cost = [&](int bn) {
+    const int tiles = tiles_m * ((rows_n + bn - 1) / bn);
+    return (long long)((tiles + sms - 1) / sms) * bn;
+  };
+  return cost(256) <= cost(128) ? 256 : 128;
+}
+
 template <int BN, bool TRANS>
 int dispatch(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn,
              const CUtensorMap& mn2, void* out, int ldo, int rows_m, int rows_n, int K, cudaStream_t stream) {
@@ -474,8 +742,24 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
     return dispatch<64, true>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Nw, Mx, K, stream);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
-  mm2 = mm;
-  if ((rc = tensor_map_2d(w, Nw, K, bn, &mn))) return rc;
-  if ((rc = tensor_map_2d(w2, Nw, K, bn, &mn2))) return rc;
-  return dispatch<128, false>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Mx, Nw, K, stream);
+  if (epi == EPI_SWIGLU) {
+    if ((rc = tensor_map_2d(w, Nw, K, 128, &mn))) return rc;
+    if ((rc = tensor_map_2d(w2, Nw, K, 128, &mn2))) return rc;
+    return launch_persistent<128, true, EPI_SWIGLU, __nv_bfloat16>(mm, mn, mn2, (__nv_bfloat16*)out, Nw, Mx, Nw, K, stream);
+  }
+  const int width = pick_tile_width(Mx, Nw);
+  if ((rc = tensor_map_2d(w, Nw, K, width, &mn))) return rc;
+  mn2 = mn;
+#define GB_PERSISTENT(BN_)                                                                                        \
+  do {                                                                                                            \
+    if (epi == EPI_ACCUMULATE)                                                                                    \
+      return launch_persistent<BN_, false, EPI_ACCUMULATE, float>(mm, mn, mn2, (float*)out, Nw, Mx, Nw, K, stream); \
+    if (out_dtype == GB_F32)                                                                                      \
+      return launch_persistent<BN_, false, EPI_STORE, float>(mm, mn, mn2, (float*)out, Nw, Mx, Nw, K, stream);   \
+    return launch_persistent<BN_, false, EPI_STORE, __nv_bfloat16>(mm, mn, mn2, (__nv_bfloat16*)out, Nw, Mx, Nw, \
+                                                                   K, stream);                                    \
+  } while (0)
+  if (width == 256) GB_PERSISTENT(256);
+  GB_PERSISTENT(128);
+#undef GB_PERSISTENT
 }
