@@ -18,7 +18,8 @@
 //  * SPLIT: at most 16 rows per CTA (a decode token's group); the four warps
 //    share the rows and split each key tile between them, and CTAs split a
 //    request's keys between them too. Partial results (unnormalised sum,
-//    maximum, denominator) go to scratch memory and a second kernel merges them.
+//    maximum, denominator) go to scratch memory; the CTA that finishes last
+//    (a ticket counter per request and kv head) merges them.
 // A request belongs to SPLIT if q_len * g <= 16, else to TILE; each kernel skips
 // the other's requests.
 //
@@ -39,6 +40,10 @@ constexpr int LD = HD + PAD;        // shared-memory row length in bf16
 constexpr int THREADS = 128;
 constexpr int ROWS_TILE = 64;
 constexpr int ROWS_SPLIT = 16;
+// Key tiles in flight per CTA. A decode CTA has little arithmetic per byte, so what matters is how
+// many bytes it has asked for at once: four tiles. A prompt CTA reuses each tile for 64 rows: two.
+constexpr int DEPTH_TILE = 2;
+constexpr int DEPTH_SPLIT = 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Params {
@@ -47,6 +52,7 @@ struct Params {
   const __nv_bfloat16* v_pool;
   __nv_bfloat16* out;            // [T, Hq * HD]
   float* partial;                // SPLIT with several splits: [T * Hq, splits, HD + 2]
+  int* counters;                 // SPLIT with several splits: [R * Hkv] tickets, zero between launches
   const int32_t* block_table;    // [R, table_width]
   const int32_t* cu_q;           // [R + 1]
   const int32_t* kv_lens;        // [R]
@@ -109,10 +115,13 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(THREADS)
 attention_mma_kernel(const Params p) {
   constexpr int ROWS = SPLIT ? ROWS_SPLIT : ROWS_TILE;
+  constexpr int DEPTH = SPLIT ? DEPTH_SPLIT : DEPTH_TILE;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [ROWS][LD]
-  __nv_bfloat16* kv = qs + ROWS * LD;                               // 2 stages x (K, V) x [KT][LD]
+  __nv_bfloat16* kv = qs + ROWS * LD;                               // DEPTH stages x (K, V) x [KT][LD]
 
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();     // queries and this step's keys and values come from the kernels in front
   const int r = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin;
   const int rows_total = q_len * p.g;
@@ -155,9 +164,14 @@ attention_mma_kernel(const Params p) {
       cp_async_16(qs + row * LD + ch * 8, src, valid);
     }
   }
-  if (tile_begin < tile_end)
-    load_kv_tile(kv, kv + KT * LD, p, table, kvh, tile_begin * KT, lo, hi);
-  cp_async_commit();
+  // the first DEPTH - 1 tiles are requested at once (one commit group per tile, empty if there is none)
+  for (int d = 0; d < DEPTH - 1; ++d) {
+    if (tile_begin + d < tile_end) {
+      __nv_bfloat16* kd = kv + d * 2 * KT * LD;
+      load_kv_tile(kd, kd + KT * LD, p, table, kvh, (tile_begin + d) * KT, lo, hi);
+    }
+    cp_async_commit();
+  }
 
   // this thread's two rows (lane / 4 and + 8) of the warp's 16
   const int wrow0 = SPLIT ? 0 : warp * 16;
@@ -188,15 +202,16 @@ attention_mma_kernel(const Params p) {
   const int key_off = SPLIT ? warp * 16 : 0;
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
-    const int stage = (tile - tile_begin) & 1;
+    const int stage = (tile - tile_begin) % DEPTH;
     __nv_bfloat16* ks = kv + stage * 2 * KT * LD;
     __nv_bfloat16* vs = ks + KT * LD;
-    if (tile + 1 < tile_end) {
-      __nv_bfloat16* kn = kv + (stage ^ 1) * 2 * KT * LD;
-      load_kv_tile(kn, kn + KT * LD, p, table, kvh, (tile + 1) * KT, lo, hi);
+    if (tile + DEPTH - 1 < tile_end) {
+      // into the stage that the previous iteration finished with
+      __nv_bfloat16* kn = kv + ((tile - tile_begin + DEPTH - 1) % DEPTH) * 2 * KT * LD;
+      load_kv_tile(kn, kn + KT * LD, p, table, kvh, (tile + DEPTH - 1) * KT, lo, hi);
     }
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<DEPTH - 1>();   // everything but the DEPTH - 1 newest groups: this tile has landed
     __syncthreads();
 
     if (!q_loaded) {
@@ -351,37 +366,57 @@ attention_mma_kernel(const Params p) {
       p.out[orow * HD + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     }
   }
-}
+  if (p.num_splits == 1) return;
 
-// One block per (request, kv head): combine the splits of a SPLIT request's rows.
-__global__ void __launch_bounds__(128)
-attention_merge_kernel(const Params p) {
-  constexpr int RS = HD + 2;
-  const int r = blockIdx.x, kvh = blockIdx.y;
-  const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin;
-  const int nrows = q_len * p.g;
-  if (q_len <= 0 || nrows > ROWS_SPLIT) return;   // a TILE request: its output is already final
-  for (int idx = threadIdx.x; idx < nrows * HD; idx += blockDim.x) {
+  // ---- the CTA that finishes last for this (request, kv head) merges the splits
+  __shared__ int ticket_s;
+  __threadfence();
+  __syncthreads();
+  int* counter = p.counters + (size_t)r * p.Hkv + kvh;
+  if (threadIdx.x == 0) ticket_s = atomicAdd(counter, 1);
+  __syncthreads();
+  if (ticket_s != p.num_splits - 1) return;
+  __threadfence();
+  const int S = p.num_splits;                           // at most 64
+  float* fac = red;                                     // [nrows][S]: weight of each split
+  float* inv = red + ROWS_SPLIT * 64;                   // [nrows]: 1 / denominator
+  for (int idx = threadIdx.x; idx < nrows * S; idx += THREADS) {
+    const int row = idx / S, sp = idx % S;
+    const size_t orow = (size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g;
+    fac[row * 64 + sp] = __ldcg(p.partial + (orow * S + sp) * RS + HD);      // its maximum, for now
+  }
+  __syncthreads();
+  if (threadIdx.x < nrows) {
+    const int row = threadIdx.x;
+    const size_t orow = (size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g;
+    float m = -INFINITY;
+    for (int sp = 0; sp < S; ++sp) m = fmaxf(m, fac[row * 64 + sp]);
+    float l = 0.f;
+    for (int sp = 0; sp < S; ++sp) {
+      const float ms = fac[row * 64 + sp];
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
+      fac[row * 64 + sp] = f;
+      l += f * __ldcg(p.partial + (orow * S + sp) * RS + HD + 1);
+    }
+    inv[row] = l > 0.f ? 1.0f / l : 0.f;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nrows * HD; idx += THREADS) {
     const int row = idx / HD, c = idx % HD;
     const size_t orow = (size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g;
-    const float* src = p.partial + orow * p.num_splits * RS;
-    float m = -INFINITY;
-    for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, src[s * RS + HD]);
-    float acc = 0.f, l = 0.f;
-    for (int s = 0; s < p.num_splits; ++s) {
-      const float ms = src[s * RS + HD];
-      const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
-      acc += f * src[s * RS + c];
-      l += f * src[s * RS + HD + 1];
-    }
-    p.out[orow * HD + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    const float* src = p.partial + orow * S * RS + c;
+    float acc = 0.f;
+    for (int sp = 0; sp < S; ++sp) acc += fac[row * 64 + sp] * __ldcg(src + (size_t)sp * RS);
+    p.out[orow * HD + c] = __float2bfloat16_rn(acc * inv[row]);
   }
+  if (threadIdx.x == 0) *counter = 0;     // ready for the next launch
 }
 
 constexpr int smem_bytes(bool split) {
-  return ((split ? ROWS_SPLIT : ROWS_TILE) * LD + 2 * 2 * KT * LD) * 2;
+  return ((split ? ROWS_SPLIT : ROWS_TILE) * LD + (split ? DEPTH_SPLIT : DEPTH_TILE) * 2 * KT * LD) * 2;
 }
 static_assert(4 * 16 * (HD + 2) * 4 <= 2 * 2 * KT * LD * 2, "merge buffer must fit in the K/V stages");
+static_assert((ROWS_SPLIT * 64 + ROWS_SPLIT) * 4 <= 2 * 2 * KT * LD * 2, "split weights must fit in the K/V stages");
 
 }  // namespace
 
@@ -389,7 +424,8 @@ GB_DEFINE_LAST_ERROR()
 
 GB_EXPORT int gb_attention_mma_head_dim() { return HD; }
 
-// Floats of scratch that gb_attention_mma needs for `num_splits` splits.
+// Floats of scratch that gb_attention_mma needs for `num_splits` splits (and R * Hkv ints of
+// ticket counters, zero before the first launch; every launch leaves them zero).
 GB_EXPORT long long gb_attention_mma_scratch_floats(int T, int Hq, int num_splits) {
   return num_splits > 1 ? (long long)T * Hq * num_splits * (HD + 2) : 0;
 }
@@ -398,7 +434,7 @@ GB_EXPORT long long gb_attention_mma_scratch_floats(int T, int Hq, int num_split
 // num_splits: CTAs that share the keys of a decode request (1: no scratch needed).
 // max_q_len and min_q_len (over the batch's requests) decide which variants are launched.
 GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
-                               const int32_t* block_table, int table_width, const int32_t* cu_q,
+                               int* counters, const int32_t* block_table, int table_width, const int32_t* cu_q,
                                const int32_t* kv_lens, const int32_t* token_req, int T, int R, int Hq, int Hkv,
                                float scale, int window, int page_size, int max_q_len, int min_q_len,
                                int num_splits, cudaStream_t stream) {
@@ -407,10 +443,12 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
   const int g = Hq / Hkv;
   if (g > ROWS_TILE) return gb::fail(GB_UNSUPPORTED, "attention_mma: a group of %d query heads per kv head", g);
   if (num_splits < 1) num_splits = 1;
-  if (num_splits > 1 && !scratch) return gb::fail(GB_BAD_ARGUMENT, "attention_mma: splits need scratch memory");
+  if (num_splits > 64) num_splits = 64;
+  if (num_splits > 1 && (!scratch || !counters))
+    return gb::fail(GB_BAD_ARGUMENT, "attention_mma: splits need scratch memory and ticket counters");
   Params p;
   p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
-  p.out = (__nv_bfloat16*)out; p.partial = scratch; p.block_table = block_table; p.cu_q = cu_q;
+  p.out = (__nv_bfloat16*)out; p.partial = scratch; p.counters = counters; p.block_table = block_table; p.cu_q = cu_q;
   p.kv_lens = kv_lens; p.table_width = table_width; p.Hq = Hq; p.Hkv = Hkv; p.g = g; p.window = window;
   p.page_size = page_size; p.num_splits = num_splits; p.scale_log2 = scale * LOG2E;
 
@@ -426,23 +464,18 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
   }
   // SPLIT requests (a decode token's group, or a very short portion), if the batch can hold any
   if (min_q_len * g <= ROWS_SPLIT) {
-    dim3 grid(num_splits, Hkv, R);
-    attention_mma_kernel<true><<<grid, THREADS, smem_bytes(true), stream>>>(p);
-    int rc = gb::check_launch("attention_mma (split)");
+    int rc = gb::check_pdl_launch(gb::launch_pdl(attention_mma_kernel<true>, dim3(num_splits, Hkv, R), dim3(THREADS),
+                                                 smem_bytes(true), stream, 1, p),
+                                  "attention_mma (split)");
     if (rc) return rc;
-    if (num_splits > 1) {
-      dim3 mg(R, Hkv);
-      attention_merge_kernel<<<mg, 128, 0, stream>>>(p);
-      rc = gb::check_launch("attention_merge");
-      if (rc) return rc;
-    }
   }
   // TILE requests
   if (max_q_len * g > ROWS_SPLIT) {
     const int tokens_per_tile = ROWS_TILE / g;
     dim3 grid((max_q_len + tokens_per_tile - 1) / tokens_per_tile, Hkv, R);
-    attention_mma_kernel<false><<<grid, THREADS, smem_bytes(false), stream>>>(p);
-    return gb::check_launch("attention_mma (tile)");
+    return gb::check_pdl_launch(gb::launch_pdl(attention_mma_kernel<false>, grid, dim3(THREADS), smem_bytes(false),
+                                               stream, 1, p),
+                                "attention_mma (tile)");
   }
   return GB_OK;
 }

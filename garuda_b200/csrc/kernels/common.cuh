@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #define GB_EXPORT extern "C" __attribute__((visibility("default")))
@@ -62,6 +63,59 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+
+// ---- programmatic dependent launch ----------------------------------------
+// A kernel launched with launch_pdl may start while the kernel before it in the
+// stream is still running. It must call pdl_wait() before it reads anything that
+// kernel wrote and before it writes anything that kernel may still read; what it
+// does before that (setting up barriers, fetching weights) overlaps the tail of
+// its predecessor. pdl_launch_dependents() lets the kernel after it start early
+// in the same way. Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("GARUDA_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+// Launch with the programmatic-serialization attribute (and a cluster shape along z, if cluster_z > 1).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              int cluster_z, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_z > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = 1;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = cluster_z;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+inline int check_pdl_launch(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) return fail(GB_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(e));
+  return check_launch(what);
 }
 
 }  // namespace gb

@@ -14,6 +14,8 @@ namespace {
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
                                  float* __restrict__ out, int d, int vocab) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * d;
@@ -32,6 +34,8 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __r
 template <typename WT, typename OT>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict__ w, float eps,
                                OT* __restrict__ out, const int32_t* __restrict__ rows, int d) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   const float* xr = x + (size_t)src * d;
@@ -79,6 +83,8 @@ template <typename WT, typename OT>
 __global__ void __launch_bounds__(256)
 rmsnorm_vec_kernel(const float* __restrict__ x, const WT* __restrict__ w, float eps, OT* __restrict__ out,
                    const int32_t* __restrict__ rows, int d) {
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * d);
@@ -128,6 +134,8 @@ rope_kv_append_kernel(const IT* __restrict__ qkv, int row_stride, OT* __restrict
                       const int32_t* __restrict__ block_table, int table_width, int Hq, int Hkv, int hd,
                       const float* __restrict__ inv_freq, int interleaved, int page_size) {
   __shared__ float sin_s[128], cos_s[128];   // head_dim / 2 <= 128
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = hd >> 1;
@@ -225,8 +233,8 @@ GB_EXPORT int gb_embedding(const void* table, int table_dtype, const int32_t* id
                            int d, int vocab, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   return GB_DISPATCH_DTYPE(table_dtype, TT, [&]() -> int {
-    embedding_kernel<TT><<<T, 256, 0, stream>>>((const TT*)table, ids, out, d, vocab);
-    return gb::check_launch("embedding");
+    return gb::check_pdl_launch(gb::launch_pdl(embedding_kernel<TT>, dim3(T), dim3(256), 0, stream, 1,
+                                               (const TT*)table, ids, out, d, vocab), "embedding");
   });
 }
 
@@ -237,10 +245,10 @@ GB_EXPORT int gb_rmsnorm(const float* x, const void* w, int w_dtype, float eps, 
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
       if (d % 4 == 0 && d <= 4096 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0)
-        rmsnorm_vec_kernel<WT, OT><<<n_rows, 256, 0, stream>>>(x, (const WT*)w, eps, (OT*)out, rows, d);
-      else
-        rmsnorm_kernel<WT, OT><<<n_rows, block, 0, stream>>>(x, (const WT*)w, eps, (OT*)out, rows, d);
-      return gb::check_launch("rmsnorm");
+        return gb::check_pdl_launch(gb::launch_pdl(rmsnorm_vec_kernel<WT, OT>, dim3(n_rows), dim3(256), 0, stream, 1,
+                                                   x, (const WT*)w, eps, (OT*)out, rows, d), "rmsnorm");
+      return gb::check_pdl_launch(gb::launch_pdl(rmsnorm_kernel<WT, OT>, dim3(n_rows), dim3(block), 0, stream, 1,
+                                                 x, (const WT*)w, eps, (OT*)out, rows, d), "rmsnorm");
     });
   });
 }
@@ -259,10 +267,11 @@ GB_EXPORT int gb_rope_kv_append(const void* qkv, int in_dtype, int row_stride, v
   const int block = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
   return GB_DISPATCH_DTYPE(in_dtype, IT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
-      rope_kv_append_kernel<IT, OT><<<T, block, 0, stream>>>(
-          (const IT*)qkv, row_stride, (OT*)q_out, (OT*)k_pool, (OT*)v_pool, positions, token_req,
-          block_table, table_width, Hq, Hkv, hd, inv_freq, interleaved, page_size);
-      return gb::check_launch("rope_kv_append");
+      return gb::check_pdl_launch(
+          gb::launch_pdl(rope_kv_append_kernel<IT, OT>, dim3(T), dim3(block), 0, stream, 1, (const IT*)qkv,
+                         row_stride, (OT*)q_out, (OT*)k_pool, (OT*)v_pool, positions, token_req, block_table,
+                         table_width, Hq, Hkv, hd, inv_freq, interleaved, page_size),
+          "rope_kv_append");
     });
   });
 }

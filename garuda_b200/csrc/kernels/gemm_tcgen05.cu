@@ -38,30 +38,59 @@ using namespace tc;
 constexpr int BM = 128;   // MMA rows per CTA
 constexpr int BK = 64;    // bf16 per 128-byte swizzled row
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 128;
-constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // one CTA per SM
-constexpr int SMEM_BUDGET_SMALL = 110 * 1024;   // two CTAs per SM: more CTAs of a cluster fit side by side
+constexpr int SMEM_LIMIT = 227 * 1024;          // most dynamic shared memory a CTA can have
+constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // many tokens: one CTA per SM, all of it pipeline
+constexpr int SMEM_BUDGET_SMALL = 110 * 1024;   // few tokens: pipeline of a CTA that may share its SM
+constexpr int SMEM_BUDGET_DUAL = 140 * 1024;    // few tokens, gate and up together
 
 enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2 };
 
 __device__ int g_error_word;
+
+// Compiled in with -DGB_TIMELINE only: eight time stamps per CTA of the cluster kernel, for finding
+// out where a short kernel spends its time. Slot = linear CTA index.
+#ifdef GB_TIMELINE
+__device__ unsigned long long g_timeline[8 * 4096];
+#define GB_STAMP(i)                                                                                   \
+  do {                                                                                                \
+    if (threadIdx.x == 0) {                                                                           \
+      const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
+      if (cta < 4096) g_timeline[8 * cta + (i)] = globaltimer_ns();                                   \
+    }                                                                                                 \
+  } while (0)
+#define GB_STAMP_E(i)                                                                                 \
+  do {                                                                                                \
+    if (threadIdx.x == 64) {                                                                          \
+      const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
+      if (cta < 4096) g_timeline[8 * cta + (i)] = globaltimer_ns();                                   \
+    }                                                                                                 \
+  } while (0)
+#else
+#define GB_STAMP(i) do {} while (0)
+#define GB_STAMP_E(i) do {} while (0)
+#endif
 
 template <int BN, bool DUAL_M, bool DUAL_N, bool TRANS = false>
 struct Geometry {
   static constexpr int NUM_M = DUAL_M ? 2 : 1, NUM_N = DUAL_N ? 2 : 1;
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = NUM_M * A_BYTES + NUM_N * B_BYTES;
-  static constexpr int SMEM_BUDGET = (TRANS && !DUAL_M) ? SMEM_BUDGET_SMALL : SMEM_BUDGET_LARGE;
-  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
-  // bytes one peer of a cluster sends to the leader, and how many peers the pipeline's memory holds
-  static constexpr int PARTIAL_BYTES = NUM_M * NUM_N * BN * BM * 4;
-  static constexpr int MAX_CLUSTER = 1 + (STAGES * STAGE_BYTES) / PARTIAL_BYTES < 8
-                                         ? 1 + (STAGES * STAGE_BYTES) / PARTIAL_BYTES : 8;
+  // shared memory for the operand pipeline; the swapped orientation leaves room for the partial sums
+  // that the other CTAs of a cluster send, and (without them) for a second CTA on the SM
+  static constexpr int PIPE_BUDGET = !TRANS ? SMEM_BUDGET_LARGE : (DUAL_M ? SMEM_BUDGET_DUAL : SMEM_BUDGET_SMALL);
+  static constexpr int STAGES = (PIPE_BUDGET / STAGE_BYTES) < 8 ? (PIPE_BUDGET / STAGE_BYTES) : 8;
   static constexpr int ACCUMULATORS = NUM_M * NUM_N;
   static constexpr int COLS_NEEDED = ACCUMULATORS * BN;
   static constexpr int TMEM_COLS = COLS_NEEDED <= 32 ? 32 : COLS_NEEDED <= 64 ? 64 : COLS_NEEDED <= 128 ? 128
                                    : COLS_NEEDED <= 256 ? 256 : 512;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the tiles to 1024 B
+  static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
+  // bytes one CTA of a cluster sends to the leader: its whole accumulator
+  static constexpr int PARTIAL_BYTES = ACCUMULATORS * BN * BM * 4;
+  static constexpr int MAX_CLUSTER_RAW = 1 + (SMEM_LIMIT - 1024 - PIPE_BYTES) / PARTIAL_BYTES;
+  static constexpr int MAX_CLUSTER = !TRANS ? 1 : (MAX_CLUSTER_RAW < 8 ? MAX_CLUSTER_RAW : 8);
+  // + slack to align the tiles to 1024 B
+  static constexpr int smem_bytes(int cluster) { return PIPE_BYTES + 1024 + (cluster - 1) * PARTIAL_BYTES; }
+  static constexpr int SMEM_BYTES = smem_bytes(1);
   static_assert(STAGES >= 2, "tile too large for shared memory");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
 };
@@ -73,7 +102,11 @@ __device__ __forceinline__ void store_value<float>(float* p, float v) { *p = v; 
 template <>
 __device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-__device__ __forceinline__ float silu_gate(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+// The SiLU-gate of the fused epilogues. The exponential is the hardware's fast one: its error
+// (about 2 ulp of a float) is far below the rounding of the bfloat16 result.
+__device__ __forceinline__ float silu_gate_fast(float g, float u) {
+  return g * __frcp_rn(1.0f + __expf(-g)) * u;
+}
 
 // ---- thread-block cluster helpers (split-K over distributed shared memory)
 __device__ __forceinline__ void cluster_arrive_wait() {
@@ -85,38 +118,57 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+
+// Four bytes into the shared memory of another CTA of the cluster; they are counted on that CTA's
+// mbarrier when they have landed.
+__device__ __forceinline__ void st_async_f32(uint32_t remote_addr, uint32_t remote_bar, float v) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %2, [%1];"
+               ::"r"(remote_addr), "r"(remote_bar), "r"(__float_as_uint(v))
+               : "memory");
 }
 
-// rows_m / rows_n: valid rows of the MMA-row operand and of the MMA-column operand.
-// TRANS: the MMA rows are output columns (swapped orientation).
-// CLUSTER: the CTAs of a cluster (gridDim.z of them, along z) split the K blocks,
-// kb_per_rank each; rank 0 collects the partial sums and writes the result.
-template <int BN, bool DUAL_M, bool DUAL_N, int EPI, bool TRANS, bool CLUSTER, typename OT>
-__global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_m2,
-               const __grid_constant__ CUtensorMap map_n, const __grid_constant__ CUtensorMap map_n2,
-               OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int kb_per_rank) {
-  using G = Geometry<BN, DUAL_M, DUAL_N, TRANS>;
+constexpr int C_THREADS = 192;   // warp 0: producer, warp 1: MMA issuer, warps 2-5: epilogue
+
+// Few tokens. rows_m / rows_n: valid rows of the MMA-row operand (the weights: output features)
+// and of the MMA-column operand (the tokens). The output is written transposed: out[token][feature].
+// The CTAs of a cluster (gridDim.z of them, along z) split the K blocks, kb_per_rank each. Every
+// CTA but rank 0 sends its accumulator to rank 0's shared memory with st.async, counted on rank
+// 0's mbarrier; rank 0 adds them in rank order and writes the result.
+template <int BN, bool DUAL_M, int EPI, typename OT>
+__global__ void __launch_bounds__(C_THREADS, 1)
+gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_m2,
+                       const __grid_constant__ CUtensorMap map_n, OT* __restrict__ out, int ldo, int rows_m,
+                       int rows_n, int K, int kb_per_rank) {
+  using G = Geometry<BN, DUAL_M, false, true>;
   constexpr int STAGES = G::STAGES;
   constexpr int ACC = G::ACCUMULATORS;
+  // With so few columns an MMA is over long before the next one that adds to the same accumulator
+  // may start. The four MMAs of a K block therefore go to four accumulators of their own (four
+  // independent chains); the epilogue adds the four.
+  constexpr int KSPLIT = BK / UMMA_K;
+  constexpr int ACC_COLS = ACC * BN;                     // columns of one of the four
+  constexpr int TMEM_COLS = KSPLIT * ACC_COLS <= 32 ? 32 : KSPLIT * ACC_COLS <= 64 ? 64
+                            : KSPLIT * ACC_COLS <= 128 ? 128 : KSPLIT * ACC_COLS <= 256 ? 256 : 512;
+  static_assert(KSPLIT * ACC_COLS <= 512, "accumulators exceed tensor memory");
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
   __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ __align__(8) uint64_t partial_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
+  GB_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int total_kb = (K + BK - 1) / BK;
-  const int rank = CLUSTER ? (int)blockIdx.z : 0;
-  const int ranks = CLUSTER ? (int)gridDim.z : 1;
-  const int kb_begin = CLUSTER ? rank * kb_per_rank : 0;
-  const int kb_end = CLUSTER ? min(total_kb, kb_begin + kb_per_rank) : total_kb;
-  const int num_kb = max(kb_end - kb_begin, 0);
+  const int rank = (int)blockIdx.z, ranks = (int)gridDim.z;
+  const int kb_begin = rank * kb_per_rank;
+  const int num_kb = max(min(total_kb, kb_begin + kb_per_rank) - kb_begin, 0);
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // [rank - 1][ACC * BN columns][128 rows] floats: the threads of a warp (consecutive rows) write and
+  // read consecutive words, so neither the remote stores nor the leader's loads collide on a bank
+  const uint32_t partials = tiles + G::PIPE_BYTES;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -124,155 +176,203 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant_
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
     mbar_init(smem_u32(&accum_bar), 1);
+    mbar_init(smem_u32(&partial_bar), 1);
     abort_s = 0;
     fence_barrier_init();
+    if (rank == 0 && ranks > 1) mbar_arrive_expect_tx(smem_u32(&partial_bar), (uint32_t)(ranks - 1) * G::PARTIAL_BYTES);
     fence_proxy_async();
     prefetch_tensormap(&map_m);
     prefetch_tensormap(&map_n);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_s), G::TMEM_COLS);
+    tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
+  // Rank 0's barrier is armed before anyone may send to it. This is the only cluster-wide
+  // barrier, and it is passed while the kernel in front is still running.
+  if (ranks > 1) cluster_arrive_wait();
+  GB_STAMP(1);
+  gb::pdl_launch_dependents();
 
-  if (warp == 0 && lane == 0) {
-    // ---------------------------------------------------------------- producer
-    int issued = 0;
-    for (int it = 0; it < num_kb; ++it) {
-      const int s = it % STAGES;
-      const uint32_t phase = (it / STAGES) & 1;
-      if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1)) {
-        atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
-        abort_s = 1;
-        break;
+  if (warp == 0) {
+    if (lane == 0) {
+      // -------------------------------------------------------------- producer
+      // The weights are written by no kernel: their first tiles are fetched before waiting for
+      // the kernel in front; the tokens' tiles after.
+      int issued = 0;
+      const int early = min(STAGES, num_kb);
+      for (int it = 0; it < early; ++it) {
+        const uint32_t bar = smem_u32(&full_bar[it]);
+        const uint32_t base = tiles + it * G::STAGE_BYTES;
+        const int k0 = (kb_begin + it) * BK;
+        mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
+        tma_load_2d(base, &map_m, bar, k0, m0);
+        if (DUAL_M) tma_load_2d(base + G::A_BYTES, &map_m2, bar, k0, m0);
       }
-      if (*(volatile int*)&abort_s) break;
-      const uint32_t bar = smem_u32(&full_bar[s]);
-      const uint32_t base = tiles + s * G::STAGE_BYTES;
-      const int k0 = (kb_begin + it) * BK;
-      mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
-      tma_load_2d(base, &map_m, bar, k0, m0);
-      if (DUAL_M) tma_load_2d(base + G::A_BYTES, &map_m2, bar, k0, m0);
-      tma_load_2d(base + G::NUM_M * G::A_BYTES, &map_n, bar, k0, n0);
-      if (DUAL_N) tma_load_2d(base + G::NUM_M * G::A_BYTES + G::B_BYTES, &map_n2, bar, k0, n0);
-      issued = it + 1;
-    }
-    if (*(volatile int*)&abort_s) {
-      // wind down: let the copies already in flight land before the CTA's shared memory is given up
-      for (int it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it) {
-        const unsigned long long t0 = globaltimer_ns();
-        while (!mbar_try_wait(smem_u32(&full_bar[it % STAGES]), (it / STAGES) & 1)) {
-          if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
-            atomicCAS(&g_error_word, 0, ERR_WAIT_DRAIN);
-            break;
-          }
+      gb::pdl_wait();
+      GB_STAMP(2);
+      for (int it = 0; it < early; ++it) {
+        tma_load_2d(tiles + it * G::STAGE_BYTES + G::NUM_M * G::A_BYTES, &map_n, smem_u32(&full_bar[it]),
+                    (kb_begin + it) * BK, n0);
+        issued = it + 1;
+      }
+      for (int it = early; it < num_kb; ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) & 1) ^ 1)) {
+          atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
+          abort_s = 1;
         }
+        if (*(volatile int*)&abort_s) break;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t base = tiles + s * G::STAGE_BYTES;
+        const int k0 = (kb_begin + it) * BK;
+        mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
+        tma_load_2d(base, &map_m, bar, k0, m0);
+        if (DUAL_M) tma_load_2d(base + G::A_BYTES, &map_m2, bar, k0, m0);
+        tma_load_2d(base + G::NUM_M * G::A_BYTES, &map_n, bar, k0, n0);
+        issued = it + 1;
       }
-    }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------------------------------------------------------- MMA issuer
-    constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
-    for (int it = 0; it < num_kb; ++it) {
-      const int s = it % STAGES;
-      const uint32_t phase = (it / STAGES) & 1;
-      if (!mbar_wait(smem_u32(&full_bar[s]), phase)) {
-        atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
-        abort_s = 1;
-        break;
-      }
-      tc_fence_after_sync();
-      const uint32_t base = tiles + s * G::STAGE_BYTES;
-#pragma unroll
-      for (int k = 0; k < BK / UMMA_K; ++k) {
-        const uint32_t koff = k * UMMA_K * 2;  // bytes along the swizzled row
-        const bool acc = it > 0 || k > 0;
-        const uint64_t da = smem_desc_sw128(base + koff);
-        const uint64_t db = smem_desc_sw128(base + G::NUM_M * G::A_BYTES + koff);
-        mma_bf16(tmem_base, da, db, idesc, acc);
-        if (DUAL_M) mma_bf16(tmem_base + BN, smem_desc_sw128(base + G::A_BYTES + koff), db, idesc, acc);
-        if (DUAL_N)
-          mma_bf16(tmem_base + BN, da, smem_desc_sw128(base + G::NUM_M * G::A_BYTES + G::B_BYTES + koff),
-                   idesc, acc);
-      }
-      mma_commit(smem_u32(&empty_bar[s]));  // the stage is free once these MMAs have read it
-    }
-    mma_commit(smem_u32(&accum_bar));       // fires when every MMA above has retired
-  }
-  __syncwarp();
-
-  // ---------------------------------------------------------- the accumulator is complete
-  bool have = mbar_wait(smem_u32(&accum_bar), 0);
-  if (!have && lane == 0) atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
-  have = have && !*(volatile int*)&abort_s;
-  tc_fence_after_sync();
-  const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
-  const int row_in_tile = warp * 32 + lane;
-
-  if (CLUSTER) {
-    // Every CTA of the cluster has finished its MMAs: the leader's pipeline memory is free
-    // to receive the partial sums. Both barriers are reached by every thread whatever happened
-    // before, so that no CTA waits for one that gave up.
-    cluster_arrive_wait();
-    if (rank != 0 && num_kb > 0) {
-      // partial[(rank - 1)][accumulator][column][row]: consecutive lanes write consecutive words
-      const uint32_t mine = tiles + (uint32_t)(rank - 1) * G::PARTIAL_BYTES + (uint32_t)row_in_tile * 4;
-      const uint32_t remote = map_to_rank(mine, 0);
-#pragma unroll 1
-      for (int a = 0; a < ACC; ++a) {
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-          uint32_t r[16];
-          tmem_ld_16(taddr + a * BN + c, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            st_cluster_f32(remote + (uint32_t)((a * BN + c + j) * BM * 4), have ? __uint_as_float(r[j]) : 0.f);
-        }
-      }
-    }
-    cluster_arrive_wait();
-  }
-
-  // -------------------------------------------------------------------- epilogue
-  if (have && rank == 0) {
-    const int row = m0 + row_in_tile;           // this thread's MMA row
-    const float* partial = reinterpret_cast<const float*>(smem_raw + (tiles - smem_u32(smem_raw)));
-#pragma unroll 1
-    for (int c = 0; c < BN; c += 16) {
-      uint32_t r0[16], r1[16];
-      tmem_ld_16(taddr + c, r0);
-      if (EPI == EPI_SWIGLU) tmem_ld_16(taddr + BN + c, r1);
-      tmem_ld_wait();
-      if (row < rows_m) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int col = n0 + c + j;
-          if (col >= rows_n) continue;
-          float v = __uint_as_float(r0[j]);
-          float v1 = EPI == EPI_SWIGLU ? __uint_as_float(r1[j]) : 0.f;
-          if (CLUSTER) {
-            for (int p = 1; p < ranks; ++p) {       // rank order: the same sum every time
-              if (p * kb_per_rank >= total_kb) break;  // that rank had no K blocks
-              const float* src = partial + (size_t)(p - 1) * (G::PARTIAL_BYTES / 4);
-              v += src[(c + j) * BM + row_in_tile];
-              if (EPI == EPI_SWIGLU) v1 += src[(BN + c + j) * BM + row_in_tile];
+      if (*(volatile int*)&abort_s) {
+        // wind down: let the copies already in flight land before the CTA's shared memory is given up
+        for (int it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it) {
+          const unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(&full_bar[it % STAGES]), (it / STAGES) & 1)) {
+            if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
+              atomicCAS(&g_error_word, 0, ERR_WAIT_DRAIN);
+              break;
             }
           }
-          if (EPI == EPI_SWIGLU) v = silu_gate(v, v1);
-          OT* p = TRANS ? out + (size_t)col * ldo + row : out + (size_t)row * ldo + col;
-          if (EPI == EPI_ACCUMULATE) v += gb::to_float<OT>(*p);
-          store_value<OT>(p, v);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // -------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+      for (int it = 0; it < num_kb; ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) {
+          atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
+          abort_s = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t base = tiles + s * G::STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint32_t koff = k * UMMA_K * 2;  // bytes along the swizzled row
+          const bool acc = it > 0;
+          const uint32_t d = tmem_base + k * ACC_COLS;
+          const uint64_t db = smem_desc_sw128(base + G::NUM_M * G::A_BYTES + koff);
+          mma_bf16(d, smem_desc_sw128(base + koff), db, idesc, acc);
+          if (DUAL_M) mma_bf16(d + BN, smem_desc_sw128(base + G::A_BYTES + koff), db, idesc, acc);
+        }
+        mma_commit(smem_u32(&empty_bar[s]));  // the stage is free once these MMAs have read it
+      }
+      mma_commit(smem_u32(&accum_bar));       // fires when every MMA above has retired
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps
+    const int quarter = warp & 3;                         // the TMEM lanes this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    const int row = m0 + row_in_tile;                     // output feature
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float old[EPI == EPI_ACCUMULATE ? BN : 1];
+    if (rank == 0) {
+      gb::pdl_wait();
+      if (EPI == EPI_ACCUMULATE) {
+        // what is to be added to is fetched while the matrix product runs
+#pragma unroll
+        for (int j = 0; j < BN; ++j)
+          old[j] = (row < rows_m && n0 + j < rows_n) ? gb::to_float<OT>(out[(size_t)(n0 + j) * ldo + row]) : 0.f;
+      }
+    }
+    bool have = mbar_wait(smem_u32(&accum_bar), 0);
+    if (!have && lane == 0) atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+    have = have && !*(volatile int*)&abort_s;
+    tc_fence_after_sync();
+    GB_STAMP_E(3);
+
+    // 16 columns of this thread's row, summed over the four accumulators
+    auto load16 = [&](int col, float (&v)[16]) {
+      uint32_t r[KSPLIT][16];
+#pragma unroll
+      for (int q = 0; q < KSPLIT; ++q) tmem_ld_16(taddr + q * ACC_COLS + col, r[q]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float t = __uint_as_float(r[0][j]);
+#pragma unroll
+        for (int q = 1; q < KSPLIT; ++q) t += __uint_as_float(r[q][j]);
+        v[j] = t;
+      }
+    };
+
+    if (rank != 0) {
+      if (num_kb > 0) {
+        // this thread's row of the accumulator into rank 0's shared memory
+        const uint32_t mine = partials + (uint32_t)(rank - 1) * G::PARTIAL_BYTES + (uint32_t)row_in_tile * 4;
+        const uint32_t remote = map_to_rank(mine, 0);
+        const uint32_t remote_bar = map_to_rank(smem_u32(&partial_bar), 0);
+#pragma unroll 1
+        for (int c = 0; c < ACC * BN; c += 16) {
+          float v[16];
+          load16(c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            st_async_f32(remote + (uint32_t)(c + j) * (BM * 4), remote_bar, have ? v[j] : 0.f);
+        }
+      }
+      GB_STAMP_E(5);
+    } else {
+      if (ranks > 1) {
+        const bool got = mbar_wait(smem_u32(&partial_bar), 0);
+        if (!got && lane == 0) atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+        have = have && got;
+      }
+      GB_STAMP_E(6);
+      if (have) {
+        const float* partial = reinterpret_cast<const float*>(smem_raw + (partials - smem_u32(smem_raw))) +
+                               row_in_tile;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float v[16], v1[16];
+          load16(c, v);
+          if (EPI == EPI_SWIGLU) load16(BN + c, v1);
+          // the other ranks' sums, in rank order (the same sum every time); sixteen independent
+          // loads per rank, so that they overlap
+          for (int p = 1; p < ranks; ++p) {
+            const float* src = partial + (size_t)(p - 1) * (G::PARTIAL_BYTES / 4) + c * BM;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += src[j * BM];
+            if (EPI == EPI_SWIGLU) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v1[j] += src[(BN + j) * BM];
+            }
+          }
+          if (row < rows_m) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int col = n0 + c + j;      // token
+              if (col >= rows_n) continue;
+              float x = v[j];
+              if (EPI == EPI_SWIGLU) x = silu_gate_fast(x, v1[j]);
+              if (EPI == EPI_ACCUMULATE) x += old[EPI == EPI_ACCUMULATE ? c + j : 0];
+              store_value<OT>(out + (size_t)col * ldo + row, x);
+            }
+          }
         }
       }
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, G::TMEM_COLS);
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  GB_STAMP(7);
 }
 
 // --------------------------------------------------------------------------
@@ -312,12 +412,6 @@ __device__ __forceinline__ void epilogue_store16<__nv_bfloat16>(__nv_bfloat16* p
 #pragma unroll
     for (int i = 0; i < 16; ++i) p[i] = __float2bfloat16_rn(v[i]);
   }
-}
-
-// The SiLU-gate of the fused epilogue. The exponential is the hardware's fast one: its error
-// (about 2 ulp of a float) is far below the rounding of the bfloat16 result.
-__device__ __forceinline__ float silu_gate_fast(float g, float u) {
-  return g * __frcp_rn(1.0f + __expf(-g)) * u;
 }
 
 template <int BN, bool DUAL, int EPI, typename OT>
@@ -367,6 +461,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
   volatile int* aborted = &abort_s;
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();     // the activations, and for an accumulating epilogue the output, come from earlier kernels
 
   if (warp == 0) {
     if (lane == 0) {
@@ -566,20 +662,19 @@ int tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows,
   return GB_OK;
 }
 
-// How many CTAs of a cluster share K: as many as fill the GPU in one wave, given how
-// many clusters of each size can run at once (asked of the runtime once per kernel).
-// `active[s]`: clusters of size s that can be resident at once (0: not asked yet), kept by the caller
-// per kernel.
-template <typename Kernel>
-int pick_cluster_size(Kernel kernel, int* active, int smem_bytes, int tiles, int total_kb, int max_cluster) {
+// How many CTAs of a cluster share K: what fills the GPU in the fewest rounds, given how many
+// clusters of each size can be resident at once (asked of the runtime once per kernel and size).
+// `active[s]`: clusters of size s that fit (0: not asked yet, -1: none), kept by the caller per kernel.
+template <typename Kernel, typename SmemFn>
+int pick_cluster_size(Kernel kernel, int* active, SmemFn smem_for, int tiles, int total_kb, int max_cluster) {
   int best = 1;
   double best_cost = 1e30;
   for (int s = 1; s <= max_cluster && s <= total_kb; ++s) {
     if (active[s] == 0) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(1, 148, s);
-      cfg.blockDim = dim3(THREADS);
-      cfg.dynamicSmemBytes = smem_bytes;
+      cfg.blockDim = dim3(C_THREADS);
+      cfg.dynamicSmemBytes = smem_for(s);
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
       attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = s;
@@ -595,48 +690,49 @@ int pick_cluster_size(Kernel kernel, int* active, int smem_bytes, int tiles, int
     if (active[s] < 1) continue;
     const int per = (total_kb + s - 1) / s;
     const int waves = (tiles + active[s] - 1) / active[s];
-    const double cost = waves * (per + 6.0 + 0.5 * s);   // K blocks per CTA, plus fixed and gathering costs
+    const double cost = waves * (per + 8.0 + 0.25 * s);   // K blocks per CTA, plus fixed and gathering costs
     if (cost < best_cost) { best_cost = cost; best = s; }
   }
   return best;
 }
 
-template <int BN, bool DUAL_M, bool DUAL_N, int EPI, bool TRANS, typename OT>
-int launch(const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn, const CUtensorMap& mn2, OT* out,
-           int ldo, int rows_m, int rows_n, int K, cudaStream_t stream) {
-  using G = Geometry<BN, DUAL_M, DUAL_N, TRANS>;
-  constexpr bool CLUSTER = TRANS;
-  auto kernel = gemm_tc_kernel<BN, DUAL_M, DUAL_N, EPI, TRANS, CLUSTER, OT>;
+template <int BN, bool DUAL_M, int EPI, typename OT>
+int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn, OT* out, int ldo, int rows_m,
+                   int rows_n, int K, cudaStream_t stream) {
+  using G = Geometry<BN, DUAL_M, false, true>;
+  auto kernel = gemm_tc_cluster_kernel<BN, DUAL_M, EPI, OT>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         G::smem_bytes(G::MAX_CLUSTER));
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
   const int tiles_n = (rows_n + BN - 1) / BN, tiles_m = (rows_m + BM - 1) / BM;
   const int total_kb = (K + BK - 1) / BK;
-  if (!CLUSTER) {
-    dim3 grid(tiles_n, tiles_m);
-    kernel<<<grid, THREADS, G::SMEM_BYTES, stream>>>(mm, mm2, mn, mn2, out, ldo, rows_m, rows_n, K, total_kb);
-    return gb::check_launch("gemm_tc");
-  }
   static int active[9] = {0};
-  int split = pick_cluster_size(kernel, active, G::SMEM_BYTES, tiles_n * tiles_m, total_kb, G::MAX_CLUSTER);
+  int split = pick_cluster_size(kernel, active, [](int s) { return G::smem_bytes(s); }, tiles_n * tiles_m, total_kb,
+                                G::MAX_CLUSTER);
   const int per = (total_kb + split - 1) / split;
   split = (total_kb + per - 1) / per;            // no rank without K blocks
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles_n, tiles_m, split);
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = G::SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = split;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mm, mm2, mn, mn2, out, ldo, rows_m, rows_n, K, per);
-  if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc (cluster of %d): %s", split, cudaGetErrorString(e));
-  return gb::check_launch("gemm_tc");
+  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(tiles_n, tiles_m, split), dim3(C_THREADS),
+                                             G::smem_bytes(split), stream, split, mm, mm2, mn, out, ldo, rows_m,
+                                             rows_n, K, per),
+                              "gemm_tc (cluster)");
+}
+
+// Few tokens: the weights are the MMA-row operand; BN tokens per tile.
+template <int BN>
+int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn,
+                     void* out, int ldo, int rows_m, int rows_n, int K, cudaStream_t stream) {
+  if (epi == EPI_STORE) {
+    if (out_dtype == GB_F32)
+      return launch_cluster<BN, false, EPI_STORE, float>(mm, mm2, mn, (float*)out, ldo, rows_m, rows_n, K, stream);
+    return launch_cluster<BN, false, EPI_STORE, __nv_bfloat16>(mm, mm2, mn, (__nv_bfloat16*)out, ldo, rows_m, rows_n, K, stream);
+  }
+  if (epi == EPI_ACCUMULATE)
+    return launch_cluster<BN, false, EPI_ACCUMULATE, float>(mm, mm2, mn, (float*)out, ldo, rows_m, rows_n, K, stream);
+  return launch_cluster<BN, true, EPI_SWIGLU, __nv_bfloat16>(mm, mm2, mn, (__nv_bfloat16*)out, ldo, rows_m, rows_n, K, stream);
 }
 
 int sm_count() {
@@ -663,8 +759,9 @@ int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, const CUtens
   const int tiles_m = (rows_m + BM - 1) / BM, tiles_n = (rows_n + BN - 1) / BN;
   const int total = tiles_m * tiles_n;
   const int grid = total < sm_count() ? total : sm_count();
-  kernel<<<grid, P_THREADS, G::SMEM_BYTES, stream>>>(mm, mn, mn2, out, ldo, rows_m, rows_n, K, tiles_m, tiles_n);
-  return gb::check_launch("gemm_tc (persistent)");
+  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(grid), dim3(P_THREADS), G::SMEM_BYTES, stream, 1, mm, mn, mn2,
+                                             out, ldo, rows_m, rows_n, K, tiles_m, tiles_n),
+                              "gemm_tc (persistent)");
 }
 
 // Tile width for many tokens: the one that needs fewer rounds over the SMs (a 256-wide tile costs
@@ -678,23 +775,15 @@ int pick_tile_width(int rows_m, int rows_n) {
   return cost(256) <= cost(128) ? 256 : 128;
 }
 
-template <int BN, bool TRANS>
-int dispatch(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn,
-             const CUtensorMap& mn2, void* out, int ldo, int rows_m, int rows_n, int K, cudaStream_t stream) {
-  constexpr bool DM = TRANS, DN = !TRANS;  // which side carries gate and up
-  if (epi == EPI_STORE) {
-    if (out_dtype == GB_F32)
-      return launch<BN, false, false, EPI_STORE, TRANS, float>(mm, mm2, mn, mn2, (float*)out, ldo, rows_m, rows_n, K, stream);
-    return launch<BN, false, false, EPI_STORE, TRANS, __nv_bfloat16>(mm, mm2, mn, mn2, (__nv_bfloat16*)out, ldo, rows_m, rows_n, K, stream);
-  }
-  if (epi == EPI_ACCUMULATE)
-    return launch<BN, false, false, EPI_ACCUMULATE, TRANS, float>(mm, mm2, mn, mn2, (float*)out, ldo, rows_m, rows_n, K, stream);
-  return launch<BN, DM, DN, EPI_SWIGLU, TRANS, __nv_bfloat16>(mm, mm2, mn, mn2, (__nv_bfloat16*)out, ldo, rows_m, rows_n, K, stream);
-}
-
 }  // namespace
 
 GB_DEFINE_LAST_ERROR()
+
+#ifdef GB_TIMELINE
+GB_EXPORT int gb_tc_timeline(unsigned long long* host_out, int ctas) {
+  return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(unsigned long long) * 8 * ctas) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 // Returns the device error word (0: none) and clears it. Synchronises the device.
 GB_EXPORT int gb_tc_error_check() {
@@ -736,10 +825,9 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
     if ((rc = tensor_map_2d(w, Nw, K, BM, &mm))) return rc;
     if ((rc = tensor_map_2d(w2, Nw, K, BM, &mm2))) return rc;
     if ((rc = tensor_map_2d(x, Mx, K, bn, &mn))) return rc;
-    mn2 = mn;
-    if (bn == 16) return dispatch<16, true>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Nw, Mx, K, stream);
-    if (bn == 32) return dispatch<32, true>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Nw, Mx, K, stream);
-    return dispatch<64, true>(epi, out_dtype, mm, mm2, mn, mn2, out, Nw, Nw, Mx, K, stream);
+    if (bn == 16) return dispatch_cluster<16>(epi, out_dtype, mm, mm2, mn, out, Nw, Nw, Mx, K, stream);
+    if (bn == 32) return dispatch_cluster<32>(epi, out_dtype, mm, mm2, mn, out, Nw, Nw, Mx, K, stream);
+    return dispatch_cluster<64>(epi, out_dtype, mm, mm2, mn, out, Nw, Nw, Mx, K, stream);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
   if (epi == EPI_SWIGLU) {

@@ -54,7 +54,8 @@ class Workspace:
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
 
-    def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """``zero``: the buffer is zeroed when it is created or grown (not on later calls)."""
         n = 1
         for s in shape:
             n *= int(s)
@@ -62,7 +63,9 @@ class Workspace:
         buf = self._bufs.get(name)
         if buf is None or buf.numel() < nbytes:
             # 256-byte multiple keeps every view aligned for vector and TMA access
-            buf = torch.empty(max((nbytes + 255) // 256 * 256, 256), dtype=torch.uint8, device=self.device)
+            size = max((nbytes + 255) // 256 * 256, 256)
+            make = torch.zeros if zero else torch.empty
+            buf = make(size, dtype=torch.uint8, device=self.device)
             self._bufs[name] = buf
         return buf[:nbytes].view(dtype).view(*shape)
 
