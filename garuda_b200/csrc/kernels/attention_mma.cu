@@ -46,6 +46,25 @@ constexpr int DEPTH_TILE = 2;
 constexpr int DEPTH_SPLIT = 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
+// Compiled in with -DGB_TIMELINE only: time stamps per CTA of the split kernel.
+#ifdef GB_TIMELINE
+__device__ unsigned long long g_timeline[8 * 4096];
+__device__ __forceinline__ unsigned long long timeline_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define GB_STAMP(i)                                                                                   \
+  do {                                                                                                \
+    if (SPLIT && threadIdx.x == 0) {                                                                  \
+      const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
+      if (cta < 4096) g_timeline[8 * cta + (i)] = timeline_now();                                     \
+    }                                                                                                 \
+  } while (0)
+#else
+#define GB_STAMP(i) do {} while (0)
+#endif
+
 struct Params {
   const __nv_bfloat16* q;        // [T, Hq, HD]
   const __nv_bfloat16* k_pool;   // [pages, Hkv, page_size, HD]
@@ -92,22 +111,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Keys [tile_start, tile_start + KT) of one kv head into shared memory, 16 bytes
-// per copy; keys outside [lo, hi] or without a page become zeros.
+// per copy; keys outside [lo, hi] or without a page become zeros. Two threads
+// share a key row, so each thread looks one page up per tile.
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const Params& p,
                                              const int32_t* table, int kvh, int tile_start, int lo, int hi) {
   constexpr int CHUNKS = HD / 8;  // 16-byte chunks per row
-  for (int c = threadIdx.x; c < KT * CHUNKS; c += THREADS) {
-    const int row = c / CHUNKS, ch = c % CHUNKS;
-    const int j = tile_start + row;
-    bool valid = j >= lo && j <= hi;
-    size_t off = 0;
-    if (valid) {
-      const int page = table[j / p.page_size];
-      valid = page >= 0;
-      if (valid) off = (((size_t)page * p.Hkv + kvh) * p.page_size + (j % p.page_size)) * HD + ch * 8;
-    }
-    cp_async_16(ks + row * LD + ch * 8, p.k_pool + off, valid);
-    cp_async_16(vs + row * LD + ch * 8, p.v_pool + off, valid);
+  static_assert(KT * 2 == THREADS && CHUNKS % 2 == 0, "two threads per key row");
+  const int row = threadIdx.x >> 1, first = (threadIdx.x & 1) * (CHUNKS / 2);
+  const int j = tile_start + row;
+  bool valid = j >= lo && j <= hi;
+  size_t off = 0;
+  if (valid) {
+    const int page = table[j / p.page_size];
+    valid = page >= 0;
+    if (valid) off = (((size_t)page * p.Hkv + kvh) * p.page_size + (j % p.page_size)) * HD;
+  }
+#pragma unroll
+  for (int c = 0; c < CHUNKS / 2; ++c) {
+    const int ch = first + c;
+    cp_async_16(ks + row * LD + ch * 8, p.k_pool + off + ch * 8, valid);
+    cp_async_16(vs + row * LD + ch * 8, p.v_pool + off + ch * 8, valid);
   }
 }
 
@@ -120,8 +143,10 @@ attention_mma_kernel(const Params p) {
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [ROWS][LD]
   __nv_bfloat16* kv = qs + ROWS * LD;                               // DEPTH stages x (K, V) x [KT][LD]
 
+  GB_STAMP(0);
   gb::pdl_launch_dependents();
-  gb::pdl_wait();     // queries and this step's keys and values come from the kernels in front
+  // The batch's lengths and block tables were copied in before the step's first kernel: they may be
+  // read at once. Queries and this step's own keys and values come from the kernels in front.
   const int r = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin;
   const int rows_total = q_len * p.g;
@@ -152,7 +177,23 @@ attention_mma_kernel(const Params p) {
     tile_end = min(tile_end, tile_begin + per);
   }
 
-  // ---- queries into shared memory (rows beyond nrows are zeros)
+  // Keys and values of earlier steps are final: a decode CTA asks for its tiles of them before
+  // waiting for the kernels in front, so that they arrive while those still run. One commit group
+  // per tile slot, empty if the slot has no tile or its tile holds positions of this step.
+  const int first_new = kv_len - q_len;
+  auto is_old = [&](int tile) { return SPLIT && (tile + 1) * KT <= first_new; };
+  for (int d = 0; d < DEPTH - 1; ++d) {
+    const int tile = tile_begin + d;
+    if (tile < tile_end && is_old(tile)) {
+      __nv_bfloat16* kd = kv + d * 2 * KT * LD;
+      load_kv_tile(kd, kd + KT * LD, p, table, kvh, tile * KT, lo, hi);
+    }
+    cp_async_commit();
+  }
+  gb::pdl_wait();
+  GB_STAMP(1);
+
+  // ---- queries into shared memory (rows beyond nrows are zeros), and the tiles not asked for yet
   {
     constexpr int CHUNKS = HD / 8;
     for (int c = threadIdx.x; c < ROWS * CHUNKS; c += THREADS) {
@@ -164,14 +205,14 @@ attention_mma_kernel(const Params p) {
       cp_async_16(qs + row * LD + ch * 8, src, valid);
     }
   }
-  // the first DEPTH - 1 tiles are requested at once (one commit group per tile, empty if there is none)
   for (int d = 0; d < DEPTH - 1; ++d) {
-    if (tile_begin + d < tile_end) {
+    const int tile = tile_begin + d;
+    if (tile < tile_end && !is_old(tile)) {
       __nv_bfloat16* kd = kv + d * 2 * KT * LD;
-      load_kv_tile(kd, kd + KT * LD, p, table, kvh, (tile_begin + d) * KT, lo, hi);
+      load_kv_tile(kd, kd + KT * LD, p, table, kvh, tile * KT, lo, hi);
     }
-    cp_async_commit();
   }
+  cp_async_commit();
 
   // this thread's two rows (lane / 4 and + 8) of the warp's 16
   const int wrow0 = SPLIT ? 0 : warp * 16;
@@ -211,8 +252,12 @@ attention_mma_kernel(const Params p) {
       load_kv_tile(kn, kn + KT * LD, p, table, kvh, (tile + DEPTH - 1) * KT, lo, hi);
     }
     cp_async_commit();
-    cp_async_wait<DEPTH - 1>();   // everything but the DEPTH - 1 newest groups: this tile has landed
+    // Everything but the DEPTH - 1 newest groups has landed: this tile has. Before the first tile
+    // the queries' group (the newest but one) must have landed too: wait for all of them.
+    if (tile == tile_begin) cp_async_wait<0>();
+    else cp_async_wait<DEPTH - 1>();
     __syncthreads();
+    if (tile == tile_begin) GB_STAMP(2);
 
     if (!q_loaded) {
 #pragma unroll
@@ -299,6 +344,7 @@ attention_mma_kernel(const Params p) {
     __syncthreads();  // the stage may be overwritten by the next iteration's loads
   }
   cp_async_wait<0>();
+  GB_STAMP(3);
 
   // the denominators: sum over the four threads that share a row
 #pragma unroll
@@ -367,6 +413,7 @@ attention_mma_kernel(const Params p) {
     }
   }
   if (p.num_splits == 1) return;
+  GB_STAMP(4);
 
   // ---- the CTA that finishes last for this (request, kv head) merges the splits
   __shared__ int ticket_s;
@@ -375,6 +422,7 @@ attention_mma_kernel(const Params p) {
   int* counter = p.counters + (size_t)r * p.Hkv + kvh;
   if (threadIdx.x == 0) ticket_s = atomicAdd(counter, 1);
   __syncthreads();
+  GB_STAMP(5);
   if (ticket_s != p.num_splits - 1) return;
   __threadfence();
   const int S = p.num_splits;                           // at most 64
@@ -410,6 +458,7 @@ attention_mma_kernel(const Params p) {
     p.out[orow * HD + c] = __float2bfloat16_rn(acc * inv[row]);
   }
   if (threadIdx.x == 0) *counter = 0;     // ready for the next launch
+  GB_STAMP(6);
 }
 
 constexpr int smem_bytes(bool split) {
@@ -423,6 +472,12 @@ static_assert((ROWS_SPLIT * 64 + ROWS_SPLIT) * 4 <= 2 * 2 * KT * LD * 2, "split 
 GB_DEFINE_LAST_ERROR()
 
 GB_EXPORT int gb_attention_mma_head_dim() { return HD; }
+
+#ifdef GB_TIMELINE
+GB_EXPORT int gb_attention_timeline(unsigned long long* host_out, int ctas) {
+  return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(unsigned long long) * 8 * ctas) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 // Floats of scratch that gb_attention_mma needs for `num_splits` splits (and R * Hkv ints of
 // ticket counters, zero before the first launch; every launch leaves them zero).
