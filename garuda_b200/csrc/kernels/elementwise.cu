@@ -205,13 +205,18 @@ __global__ void rope_inplace_kernel(float* __restrict__ x, int row_stride, int H
 }
 
 // ------------------------------------------------------------ SiLU-gate
+// gate_up rows hold either [gate(F) | up(F)] (group 0), or gate and up packed in groups of 64:
+// columns [128 q, 128 q + 64) gate features 64 q .., the next 64 their up values (group 64).
 template <typename IT, typename OT>
-__global__ void silu_mul_kernel(const IT* __restrict__ gate_up, OT* __restrict__ out, int M, int F) {
+__global__ void silu_mul_kernel(const IT* __restrict__ gate_up, OT* __restrict__ out, int M, int F, int group,
+                                int row_stride) {
   const size_t n = (size_t)M * F;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t m = i / F, f = i % F;
-    const float g = gb::to_float<IT>(gate_up[m * 2 * F + f]);
-    const float u = gb::to_float<IT>(gate_up[m * 2 * F + F + f]);
+    const size_t gi = group ? (f / group) * 2 * group + f % group : f;
+    const size_t ui = group ? gi + group : F + f;
+    const float g = gb::to_float<IT>(gate_up[m * row_stride + gi]);
+    const float u = gb::to_float<IT>(gate_up[m * row_stride + ui]);
     out[i] = gb::from_float<OT>((g / (1.0f + expf(-g))) * u);
   }
 }
@@ -285,13 +290,13 @@ GB_EXPORT int gb_rope_inplace(float* x, int row_stride, int T, int H, int hd, co
   return gb::check_launch("rope_inplace");
 }
 
-GB_EXPORT int gb_silu_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int M, int F,
-                          cudaStream_t stream) {
+GB_EXPORT int gb_silu_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int M, int F, int group,
+                          int row_stride, cudaStream_t stream) {
   if (M <= 0 || F <= 0) return GB_OK;
   return GB_DISPATCH_DTYPE(in_dtype, IT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
       silu_mul_kernel<IT, OT><<<grid_for((size_t)M * F, 256), 256, 0, stream>>>(
-          (const IT*)gate_up, (OT*)out, M, F);
+          (const IT*)gate_up, (OT*)out, M, F, group, row_stride);
       return gb::check_launch("silu_mul");
     });
   });

@@ -2,6 +2,10 @@
 //   out[Mx, Nw] (+)= x[Mx, K] * w[Nw, K]^T        (garuda/src/simd/mod.rs:96-129)
 // and the fused gate/up product with the SiLU-gate of the feed-forward
 //   out[Mx, F] = silu(x * gate^T) * (x * up^T)     (garuda/src/llama/mod.rs:1013-1017)
+// for which gate and up rows are packed into one matrix in groups of 64: rows
+// [128 g, 128 g + 64) are gate rows 64 g .., the next 64 the matching up rows
+// (zero rows pad the last group), so that every 128-row tile holds the gate and
+// the up values of the same 64 output features.
 //
 // One CTA computes a 128 x BN tile: a producer thread streams 128x64 and BNx64
 // operand tiles into shared memory with TMA (128-byte swizzle), one thread
@@ -134,12 +138,12 @@ constexpr int C_THREADS = 192;   // warp 0: producer, warp 1: MMA issuer, warps 
 // The CTAs of a cluster (gridDim.z of them, along z) split the K blocks, kb_per_rank each. Every
 // CTA but rank 0 sends its accumulator to rank 0's shared memory with st.async, counted on rank
 // 0's mbarrier; rank 0 adds them in rank order and writes the result.
-template <int BN, bool DUAL_M, int EPI, typename OT>
+template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(C_THREADS, 1)
-gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_m2,
-                       const __grid_constant__ CUtensorMap map_n, OT* __restrict__ out, int ldo, int rows_m,
-                       int rows_n, int K, int kb_per_rank) {
-  using G = Geometry<BN, DUAL_M, false, true>;
+gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
+                       OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int kb_per_rank) {
+  constexpr bool DUAL_M = false;
+  using G = Geometry<BN, false, false, true>;
   constexpr int STAGES = G::STAGES;
   constexpr int ACC = G::ACCUMULATORS;
   // With so few columns an MMA is over long before the next one that adds to the same accumulator
@@ -211,7 +215,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         const int k0 = (kb_begin + it) * BK;
         mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
         tma_load_2d(base, &map_m, bar, k0, m0);
-        if (DUAL_M) tma_load_2d(base + G::A_BYTES, &map_m2, bar, k0, m0);
       }
       gb::pdl_wait();
       GB_STAMP(2);
@@ -232,7 +235,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         const int k0 = (kb_begin + it) * BK;
         mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
         tma_load_2d(base, &map_m, bar, k0, m0);
-        if (DUAL_M) tma_load_2d(base + G::A_BYTES, &map_m2, bar, k0, m0);
         tma_load_2d(base + G::NUM_M * G::A_BYTES, &map_n, bar, k0, n0);
         issued = it + 1;
       }
@@ -269,7 +271,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
           const uint32_t d = tmem_base + k * ACC_COLS;
           const uint64_t db = smem_desc_sw128(base + G::NUM_M * G::A_BYTES + koff);
           mma_bf16(d, smem_desc_sw128(base + koff), db, idesc, acc);
-          if (DUAL_M) mma_bf16(d + BN, smem_desc_sw128(base + G::A_BYTES + koff), db, idesc, acc);
         }
         mma_commit(smem_u32(&empty_bar[s]));  // the stage is free once these MMAs have read it
       }
@@ -338,29 +339,43 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
       if (have) {
         const float* partial = reinterpret_cast<const float*>(smem_raw + (partials - smem_u32(smem_raw))) +
                                row_in_tile;
+        // SiLU-gate: rows 0-63 of the tile are gate rows, rows 64-127 the up rows of the same 64
+        // features. The up half hands its values over through shared memory (the pipeline's, which
+        // is idle by now).
+        float* xch = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)));   // [16][64]
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
-          float v[16], v1[16];
+          float v[16];
           load16(c, v);
-          if (EPI == EPI_SWIGLU) load16(BN + c, v1);
           // the other ranks' sums, in rank order (the same sum every time); sixteen independent
           // loads per rank, so that they overlap
           for (int p = 1; p < ranks; ++p) {
             const float* src = partial + (size_t)(p - 1) * (G::PARTIAL_BYTES / 4) + c * BM;
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] += src[j * BM];
-            if (EPI == EPI_SWIGLU) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v1[j] += src[(BN + j) * BM];
-            }
           }
-          if (row < rows_m) {
+          if (EPI == EPI_SWIGLU) {
+            if (row_in_tile >= 64) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) xch[j * 64 + row_in_tile - 64] = v[j];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+            const int feature = (m0 >> 1) + row_in_tile;         // 64 features per 128-row tile
+            if (row_in_tile < 64 && feature < rows_m) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int col = n0 + c + j;      // token
+                if (col < rows_n)
+                  store_value<OT>(out + (size_t)col * ldo + feature, silu_gate_fast(v[j], xch[j * 64 + row_in_tile]));
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");      // before the next chunk reuses the buffer
+          } else if (row < rows_m) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int col = n0 + c + j;      // token
               if (col >= rows_n) continue;
               float x = v[j];
-              if (EPI == EPI_SWIGLU) x = silu_gate_fast(x, v1[j]);
               if (EPI == EPI_ACCUMULATE) x += old[EPI == EPI_ACCUMULATE ? c + j : 0];
               store_value<OT>(out + (size_t)col * ldo + row, x);
             }
@@ -414,12 +429,15 @@ __device__ __forceinline__ void epilogue_store16<__nv_bfloat16>(__nv_bfloat16* p
   }
 }
 
-template <int BN, bool DUAL, int EPI, typename OT>
+// EPI_SWIGLU: the weight rows are packed gate/up groups; rows_n counts the output features and the
+// tiles run over the packed rows (twice as many).
+template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
-                          const __grid_constant__ CUtensorMap map_n2, OT* __restrict__ out, int ldo, int rows_m,
-                          int rows_n, int K, int tiles_m, int tiles_n) {
-  using G = Geometry<BN, false, DUAL, false>;
+                          OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m,
+                          int tiles_n) {
+  constexpr bool DUAL = false;
+  using G = Geometry<BN, false, false, false>;
   constexpr int STAGES = G::STAGES;
   constexpr int ACC_COLS = G::ACCUMULATORS * BN;        // columns of one accumulator stage
   constexpr int TMEM_COLS = 2 * ACC_COLS;               // two stages: 256 or 512
@@ -482,7 +500,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
           mbar_arrive_expect_tx(bar, G::STAGE_BYTES);
           tma_load_2d(base, &map_m, bar, kb * BK, m0);
           tma_load_2d(base + G::A_BYTES, &map_n, bar, kb * BK, n0);
-          if (DUAL) tma_load_2d(base + G::A_BYTES + G::B_BYTES, &map_n2, bar, kb * BK, n0);
           issued = it + 1;
         }
       }
@@ -527,8 +544,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
             const bool accumulate = kb > 0 || k > 0;
             const uint64_t da = smem_desc_sw128(base + koff);
             mma_bf16(acc, da, smem_desc_sw128(base + G::A_BYTES + koff), idesc, accumulate);
-            if (DUAL)
-              mma_bf16(acc + BN, da, smem_desc_sw128(base + G::A_BYTES + G::B_BYTES + koff), idesc, accumulate);
           }
           mma_commit(smem_u32(&empty_bar[s]));
         }
@@ -552,20 +567,41 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
       tc_fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + as * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      if (EPI == EPI_SWIGLU) {
+        // columns [128 q, 128 q + 64) of the tile are gate values, the next 64 the up values of
+        // the same features: feature = 64 * (packed row / 128) + offset
+#pragma unroll 1
+        for (int q = 0; q < BN / 128; ++q) {
+#pragma unroll 1
+          for (int c = 0; c < 64; c += 16) {
+            uint32_t r0[16], r1[16];
+            tmem_ld_16(taddr + q * 128 + c, r0);
+            tmem_ld_16(taddr + q * 128 + 64 + c, r1);
+            tmem_ld_wait();
+            const int col = (n0 >> 1) + q * 64 + c;      // output feature of the first of 16
+            if (row >= rows_m || col >= rows_n) continue;
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = silu_gate_fast(__uint_as_float(r0[j]), __uint_as_float(r1[j]));
+            OT* p = out + (size_t)row * ldo + col;
+            if (col + 16 <= rows_n) {
+              epilogue_store16<OT>(p, v, vec);
+            } else {
+              for (int j = 0; j < 16 && col + j < rows_n; ++j) store_value<OT>(p + j, v[j]);
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
-        uint32_t r0[16], r1[16];
+        uint32_t r0[16];
         tmem_ld_16(taddr + c, r0);
-        if (EPI == EPI_SWIGLU) tmem_ld_16(taddr + BN + c, r1);
         tmem_ld_wait();
         const int col = n0 + c;
         if (row >= rows_m || col >= rows_n) continue;
         float v[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          v[j] = __uint_as_float(r0[j]);
-          if (EPI == EPI_SWIGLU) v[j] = silu_gate_fast(v[j], __uint_as_float(r1[j]));
-        }
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]);
         OT* p = out + (size_t)row * ldo + col;
         if (col + 16 <= rows_n) {
           if (EPI == EPI_ACCUMULATE) {
@@ -588,6 +624,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
             store_value<OT>(p + j, x);
           }
         }
+      }
       }
       // every read of this accumulator stage has completed: hand it back to the MMA warp
       tc_fence_before_sync();
@@ -696,11 +733,13 @@ int pick_cluster_size(Kernel kernel, int* active, SmemFn smem_for, int tiles, in
   return best;
 }
 
-template <int BN, bool DUAL_M, int EPI, typename OT>
-int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn, OT* out, int ldo, int rows_m,
-                   int rows_n, int K, cudaStream_t stream) {
-  using G = Geometry<BN, DUAL_M, false, true>;
-  auto kernel = gemm_tc_cluster_kernel<BN, DUAL_M, EPI, OT>;
+// weight_rows: rows of the weight matrix as stored (for the SiLU-gate epilogue the packed rows,
+// twice the output features); out_features: columns of the output.
+template <int BN, int EPI, typename OT>
+int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int weight_rows, int out_features,
+                   int tokens, int K, cudaStream_t stream) {
+  using G = Geometry<BN, false, false, true>;
+  auto kernel = gemm_tc_cluster_kernel<BN, EPI, OT>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -708,7 +747,7 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensor
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
-  const int tiles_n = (rows_n + BN - 1) / BN, tiles_m = (rows_m + BM - 1) / BM;
+  const int tiles_n = (tokens + BN - 1) / BN, tiles_m = (weight_rows + BM - 1) / BM;
   const int total_kb = (K + BK - 1) / BK;
   static int active[9] = {0};
   int split = pick_cluster_size(kernel, active, [](int s) { return G::smem_bytes(s); }, tiles_n * tiles_m, total_kb,
@@ -716,23 +755,23 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensor
   const int per = (total_kb + split - 1) / split;
   split = (total_kb + per - 1) / per;            // no rank without K blocks
   return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(tiles_n, tiles_m, split), dim3(C_THREADS),
-                                             G::smem_bytes(split), stream, split, mm, mm2, mn, out, ldo, rows_m,
-                                             rows_n, K, per),
+                                             G::smem_bytes(split), stream, split, mm, mn, out, ldo, out_features,
+                                             tokens, K, per),
                               "gemm_tc (cluster)");
 }
 
 // Few tokens: the weights are the MMA-row operand; BN tokens per tile.
 template <int BN>
-int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mm2, const CUtensorMap& mn,
-                     void* out, int ldo, int rows_m, int rows_n, int K, cudaStream_t stream) {
+int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mn, void* out, int ldo,
+                     int weight_rows, int out_features, int tokens, int K, cudaStream_t stream) {
   if (epi == EPI_STORE) {
     if (out_dtype == GB_F32)
-      return launch_cluster<BN, false, EPI_STORE, float>(mm, mm2, mn, (float*)out, ldo, rows_m, rows_n, K, stream);
-    return launch_cluster<BN, false, EPI_STORE, __nv_bfloat16>(mm, mm2, mn, (__nv_bfloat16*)out, ldo, rows_m, rows_n, K, stream);
+      return launch_cluster<BN, EPI_STORE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream);
+    return launch_cluster<BN, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream);
   }
   if (epi == EPI_ACCUMULATE)
-    return launch_cluster<BN, false, EPI_ACCUMULATE, float>(mm, mm2, mn, (float*)out, ldo, rows_m, rows_n, K, stream);
-  return launch_cluster<BN, true, EPI_SWIGLU, __nv_bfloat16>(mm, mm2, mn, (__nv_bfloat16*)out, ldo, rows_m, rows_n, K, stream);
+    return launch_cluster<BN, EPI_ACCUMULATE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream);
+  return launch_cluster<BN, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream);
 }
 
 int sm_count() {
@@ -745,22 +784,22 @@ int sm_count() {
   return n;
 }
 
-template <int BN, bool DUAL, int EPI, typename OT>
-int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, const CUtensorMap& mn2, OT* out, int ldo,
-                      int rows_m, int rows_n, int K, cudaStream_t stream) {
-  using G = Geometry<BN, false, DUAL, false>;
-  auto kernel = gemm_tc_persistent_kernel<BN, DUAL, EPI, OT>;
+template <int BN, int EPI, typename OT>
+int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int tokens, int weight_rows,
+                      int out_features, int K, cudaStream_t stream) {
+  using G = Geometry<BN, false, false, false>;
+  auto kernel = gemm_tc_persistent_kernel<BN, EPI, OT>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
-  const int tiles_m = (rows_m + BM - 1) / BM, tiles_n = (rows_n + BN - 1) / BN;
+  const int tiles_m = (tokens + BM - 1) / BM, tiles_n = (weight_rows + BN - 1) / BN;
   const int total = tiles_m * tiles_n;
   const int grid = total < sm_count() ? total : sm_count();
-  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(grid), dim3(P_THREADS), G::SMEM_BYTES, stream, 1, mm, mn, mn2,
-                                             out, ldo, rows_m, rows_n, K, tiles_m, tiles_n),
+  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(grid), dim3(P_THREADS), G::SMEM_BYTES, stream, 1, mm, mn, out,
+                                             ldo, tokens, out_features, K, tiles_m, tiles_n),
                               "gemm_tc (persistent)");
 }
 
@@ -804,7 +843,8 @@ GB_EXPORT int gb_gemm_tc_supported(const void* x, const void* w, int Mx, int Nw,
 }
 
 // epi 0: out[Mx,Nw] = x w^T (out_dtype f32 or bf16); 1: out (f32) += x w^T;
-// 2: w holds gate rows then up rows ([2*Nw, K]); out[Mx,Nw] (bf16) = silu(x gate^T) * (x up^T).
+// 2: w holds gate and up rows packed in groups of 64 ([128 * ceil(Nw / 64), K], see the head of this
+// file); out[Mx,Nw] (bf16) = silu(x gate^T) * (x up^T).
 GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw, int K, int out_dtype, int epi,
                          cudaStream_t stream) {
   if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
@@ -813,39 +853,31 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: accumulation needs a 32-bit output");
   if (epi == EPI_SWIGLU && out_dtype != GB_BF16)
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: the SiLU-gate epilogue writes bfloat16");
-  const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
-  const void* w2 = epi == EPI_SWIGLU ? (const void*)(wp + (size_t)Nw * K) : w;
-  if (epi == EPI_SWIGLU && ((uintptr_t)w2 & 15))
-    return gb::fail(GB_UNSUPPORTED, "gemm_tc: the up rows do not start on a 16-byte boundary");
-  const bool swap = Mx <= 64;
-  const int bn = swap ? (Mx <= 16 ? 16 : Mx <= 32 ? 32 : 64) : 128;
-  CUtensorMap mm, mm2, mn, mn2;
+  const int weight_rows = epi == EPI_SWIGLU ? 128 * ((Nw + 63) / 64) : Nw;
+  CUtensorMap mm, mn;
   int rc;
-  if (swap) {
-    if ((rc = tensor_map_2d(w, Nw, K, BM, &mm))) return rc;
-    if ((rc = tensor_map_2d(w2, Nw, K, BM, &mm2))) return rc;
+  if (Mx <= 64) {
+    const int bn = Mx <= 16 ? 16 : Mx <= 32 ? 32 : 64;
+    if ((rc = tensor_map_2d(w, weight_rows, K, BM, &mm))) return rc;
     if ((rc = tensor_map_2d(x, Mx, K, bn, &mn))) return rc;
-    if (bn == 16) return dispatch_cluster<16>(epi, out_dtype, mm, mm2, mn, out, Nw, Nw, Mx, K, stream);
-    if (bn == 32) return dispatch_cluster<32>(epi, out_dtype, mm, mm2, mn, out, Nw, Nw, Mx, K, stream);
-    return dispatch_cluster<64>(epi, out_dtype, mm, mm2, mn, out, Nw, Nw, Mx, K, stream);
+    if (bn == 16) return dispatch_cluster<16>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream);
+    if (bn == 32) return dispatch_cluster<32>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream);
+    return dispatch_cluster<64>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
-  if (epi == EPI_SWIGLU) {
-    if ((rc = tensor_map_2d(w, Nw, K, 128, &mn))) return rc;
-    if ((rc = tensor_map_2d(w2, Nw, K, 128, &mn2))) return rc;
-    return launch_persistent<128, true, EPI_SWIGLU, __nv_bfloat16>(mm, mn, mn2, (__nv_bfloat16*)out, Nw, Mx, Nw, K, stream);
-  }
-  const int width = pick_tile_width(Mx, Nw);
-  if ((rc = tensor_map_2d(w, Nw, K, width, &mn))) return rc;
-  mn2 = mn;
-#define GB_PERSISTENT(BN_)                                                                                        \
-  do {                                                                                                            \
-    if (epi == EPI_ACCUMULATE)                                                                                    \
-      return launch_persistent<BN_, false, EPI_ACCUMULATE, float>(mm, mn, mn2, (float*)out, Nw, Mx, Nw, K, stream); \
-    if (out_dtype == GB_F32)                                                                                      \
-      return launch_persistent<BN_, false, EPI_STORE, float>(mm, mn, mn2, (float*)out, Nw, Mx, Nw, K, stream);   \
-    return launch_persistent<BN_, false, EPI_STORE, __nv_bfloat16>(mm, mn, mn2, (__nv_bfloat16*)out, Nw, Mx, Nw, \
-                                                                   K, stream);                                    \
+  const int width = pick_tile_width(Mx, weight_rows);
+  if ((rc = tensor_map_2d(w, weight_rows, K, width, &mn))) return rc;
+#define GB_PERSISTENT(BN_)                                                                                         \
+  do {                                                                                                             \
+    if (epi == EPI_SWIGLU)                                                                                         \
+      return launch_persistent<BN_, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows,   \
+                                                               Nw, K, stream);                                     \
+    if (epi == EPI_ACCUMULATE)                                                                                     \
+      return launch_persistent<BN_, EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream); \
+    if (out_dtype == GB_F32)                                                                                       \
+      return launch_persistent<BN_, EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);    \
+    return launch_persistent<BN_, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw,  \
+                                                            K, stream);                                            \
   } while (0)
   if (width == 256) GB_PERSISTENT(256);
   GB_PERSISTENT(128);

@@ -73,7 +73,7 @@ class CudaOps:
                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                   c_int, c_void_p],
             "gb_rope_inplace": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
-            "gb_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+            "gb_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
             "gb_residual_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
             "gb_gemm_simple": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
             "gb_attention_simple": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -153,26 +153,46 @@ class CudaOps:
             _tag(out, "linear output"), int(accumulate), self._stream()), "linear")
 
     def pack_gate_up(self, gate, up):
-        """The layout ``linear_swiglu`` wants: gate rows, then up rows."""
-        return torch.cat([gate, up], dim=0).contiguous()
+        """The layout ``linear_swiglu`` wants. With the tensor-core kernels: gate and
+        up rows packed in groups of 64 (rows ``[128 g, 128 g + 64)`` are gate rows
+        ``64 g ..``, the next 64 the matching up rows, zero rows padding the last
+        group), so that a 128-row tile holds both values of 64 features. Without
+        them: gate rows, then up rows."""
+        F, K = gate.shape
+        if self.tc is None or gate.dtype != torch.bfloat16:
+            return torch.cat([gate, up], dim=0).contiguous()
+        groups = (F + 63) // 64
+        halves = []
+        for m in (gate, up):
+            padded = torch.zeros(groups * 64, K, dtype=m.dtype, device=m.device)
+            padded[:F] = m
+            halves.append(padded.view(groups, 64, K))
+        packed = torch.stack(halves, dim=1).reshape(groups * 128, K).contiguous()
+        packed.gb_group = 64
+        return packed
 
     def linear_swiglu(self, ctx, h, w_gate_up, act):
         """``act[M,F] = silu(h @ gate^T) * (h @ up^T)``, the activation in 32-bit."""
         M, F = act.shape
-        if self.tc is not None and h.dtype == torch.bfloat16 and self.tc.linear_swiglu(h, w_gate_up, act):
+        group = getattr(w_gate_up, "gb_group", 0)
+        if (group == 64 and self.tc is not None and h.dtype == torch.bfloat16
+                and self.tc.linear_swiglu(h, w_gate_up, act)):
             return
-        tmp = ctx.ws.get("gate_up", (M, 2 * F), torch.float32)
+        tmp = ctx.ws.get("gate_up", (M, w_gate_up.shape[0]), torch.float32)
         self.linear(h, w_gate_up, tmp)
-        self.silu_mul(tmp, act)
+        self.silu_mul(tmp, act, group)
 
-    def silu_mul(self, gate_up, out):
+    def silu_mul(self, gate_up, out, group: int = 0):
+        """``out[M,F] = silu(gate) * up``; ``gate_up`` rows are ``[gate | up]``, or with
+        ``group`` 64 the packed layout of ``pack_gate_up``."""
         self._on_device(gate_up, out)
         M, F = out.shape
-        _need(gate_up.shape == (M, 2 * F) and gate_up.is_contiguous() and out.is_contiguous(),
-              "silu_mul: gate_up must be [M, 2F] for out [M, F]")
+        width = 2 * group * ((F + group - 1) // group) if group else 2 * F
+        _need(gate_up.shape == (M, width) and gate_up.is_contiguous() and out.is_contiguous(),
+              f"silu_mul: gate_up must be [M, {width}] for out [M, {F}]")
         self._check(self.core, self.core.gb_silu_mul(
             gate_up.data_ptr(), _tag(gate_up, "silu_mul in"), out.data_ptr(), _tag(out, "silu_mul out"),
-            M, F, self._stream()), "silu_mul")
+            M, F, group, width, self._stream()), "silu_mul")
 
     def residual_add(self, x, y):
         self._on_device(x, y)

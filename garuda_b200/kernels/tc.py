@@ -53,9 +53,12 @@ class TensorCoreKernels:
         return self._gemm(a, w, out, w.shape[0], 1 if accumulate else 0)
 
     def linear_swiglu(self, h, w_gate_up, act) -> bool:
-        if w_gate_up.dtype != torch.bfloat16 or act.dtype != torch.bfloat16:
+        """``w_gate_up``: the packed layout of ``CudaOps.pack_gate_up``."""
+        F = act.shape[1]
+        if (w_gate_up.dtype != torch.bfloat16 or act.dtype != torch.bfloat16
+                or w_gate_up.shape[0] != 128 * ((F + 63) // 64)):
             return False
-        return self._gemm(h, w_gate_up, act, act.shape[1], 2)
+        return self._gemm(h, w_gate_up, act, F, 2)
 
     # ------------------------------------------------------------------ attention
     def _attention_lib(self, head_dim: int):

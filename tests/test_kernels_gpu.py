@@ -106,9 +106,18 @@ def test_tensor_core_gate_up(ops, M, F, K):
     ref = torch.zeros(M, F)
     cpu.linear_swiglu(None, h, w, ref)
     out = torch.full((M, F), 9.0, dtype=torch.bfloat16, device="cuda")
-    assert ops.tc.linear_swiglu(dev(h), dev(w), out)
+    packed = ops.pack_gate_up(dev(w[:F]), dev(w[F:]))
+    assert packed.shape == (128 * ((F + 63) // 64), K)
+    assert ops.tc.linear_swiglu(dev(h), packed, out)
     close(out, ref, 8e-3, "swiglu")
     ops.tc.check_errors()
+    # the same packed weights through the plain product and the separate SiLU-gate kernel
+    tmp = torch.zeros(M, packed.shape[0], device="cuda")
+    out2 = torch.zeros(M, F, dtype=torch.bfloat16, device="cuda")
+    from garuda_b200.kernels import CudaOps
+    CudaOps("cuda:0", tensor_cores=False).linear(dev(h), packed, tmp)
+    ops.silu_mul(tmp, out2, 64)
+    close(out2, ref, 8e-3, "swiglu, unfused")
 
 
 def test_row_pitch_that_tma_cannot_take_uses_the_plain_kernel(ops):
