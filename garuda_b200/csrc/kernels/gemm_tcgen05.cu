@@ -699,14 +699,28 @@ int tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows,
   return GB_OK;
 }
 
-// How many CTAs of a cluster share K: what fills the GPU in the fewest rounds, given how many
-// clusters of each size can be resident at once (asked of the runtime once per kernel and size).
-// `active[s]`: clusters of size s that fit (0: not asked yet, -1: none), kept by the caller per kernel.
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v;
+  }();
+  return n;
+}
+
+// How many CTAs of a cluster share K. Measured on B200 (2048- to 5632-wide layers, 8 tokens): a CTA
+// costs about 3.5 us before and after its stream of K blocks and streams one 16 KB block in about
+// 0.26 us, so the fixed part weighs as much as 13 blocks; two CTAs on one SM halve each other's rate,
+// so the CTAs should not outnumber the SMs; clusters of more than six are placed badly.
+// `active[s]`: whether clusters of size s can be resident at all (0: not asked yet, -1: no), kept by the
+// caller per kernel.
 template <typename Kernel, typename SmemFn>
 int pick_cluster_size(Kernel kernel, int* active, SmemFn smem_for, int tiles, int total_kb, int max_cluster) {
   int best = 1;
   double best_cost = 1e30;
-  for (int s = 1; s <= max_cluster && s <= total_kb; ++s) {
+  const int sms = sm_count();
+  for (int s = 1; s <= max_cluster && s <= 6 && s <= total_kb; ++s) {
     if (active[s] == 0) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(1, 148, s);
@@ -726,8 +740,8 @@ int pick_cluster_size(Kernel kernel, int* active, SmemFn smem_for, int tiles, in
     }
     if (active[s] < 1) continue;
     const int per = (total_kb + s - 1) / s;
-    const int waves = (tiles + active[s] - 1) / active[s];
-    const double cost = waves * (per + 8.0 + 0.25 * s);   // K blocks per CTA, plus fixed and gathering costs
+    const int rounds = (tiles * s + sms - 1) / sms;
+    const double cost = rounds * (per + 13.5);
     if (cost < best_cost) { best_cost = cost; best = s; }
   }
   return best;
@@ -772,16 +786,6 @@ int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtens
   if (epi == EPI_ACCUMULATE)
     return launch_cluster<BN, EPI_ACCUMULATE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream);
   return launch_cluster<BN, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream);
-}
-
-int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v;
-  }();
-  return n;
 }
 
 template <int BN, int EPI, typename OT>
