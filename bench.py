@@ -48,7 +48,7 @@ def peaks():
 
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons while the timed region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
@@ -58,7 +58,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -67,7 +67,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark(self):
+        """Call at the start and at the end of the timed region."""
+        self.marks = getattr(self, "marks", []) + [time.time()]
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -77,23 +81,36 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             pass
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, v in zip(names, parts[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
+        marks = getattr(self, "marks", [])
+        lo, hi = (marks[0], marks[-1]) if len(marks) >= 2 else (0.0, float("inf"))
+
+        def collect(inside):
+            sm, mx, reasons = [], [], set()
+            for when, line in self.lines:
+                # a sample is printed up to one period after it was taken
+                if inside and not (lo <= when <= hi + 0.06):
+                    continue
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 8:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(names, parts[4:8]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            return sorted(sm), mx, reasons
+
+        sm, mx, reasons = collect(True)
+        window = "timed region"
+        if not sm:       # the region was shorter than the sampling period: the samples around it
+            sm, mx, reasons = collect(False)
+            window = "decode phase around the timed region"
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def model_bytes_and_flops(cfg, layers, batch, kv_len, itemsize=2):
@@ -160,6 +177,9 @@ def run_ours(args) -> dict:
         """Requests prefilled so that the last timed step reaches the full context."""
         start_len = CONTEXT - steps - warmup
         ids = list(range(batch))
+        sampler = ClockSampler() if sample_clocks else None
+        if sampler:
+            sampler.start()          # early: nvidia-smi takes a moment to print its first sample
         for r in ids:
             runner.run([StepEntry(r, rng.integers(0, V, start_len).tolist(), [])])
         feed = rng.integers(0, V, (steps + warmup, batch))
@@ -172,16 +192,18 @@ def run_ours(args) -> dict:
         for i in range(warmup):
             one(i)
         launches0 = ops.launches
-        sampler = ClockSampler() if sample_clocks else None
         s, e = ev(), ev()
         torch.cuda.synchronize()
         if sampler:
-            sampler.start()
+            sampler.mark()
         s.record()
         for i in range(warmup, warmup + steps):
             one(i)
         e.record()
         torch.cuda.synchronize()
+        if sampler:
+            sampler.mark()
+            time.sleep(0.12)         # let the sample taken at the end be printed
         clocks = sampler.stop() if sampler else None
         ms = s.elapsed_time(e) / steps
         launches = ops.launches - launches0 + runner.graphs.launches_replayed(batch) * steps
@@ -274,7 +296,7 @@ def run_one_phase(args, engine, cfg, rng) -> dict:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", choices=["prefill", "decode"], help="run one phase only (for profiling)")

@@ -12,19 +12,20 @@
 //
 // The rows of a query tile are (token, head-of-the-group) pairs that share one
 // kv head of one request, so a K/V tile is read once for the whole group.
-// Two variants of one kernel:
+// Two kernels:
 //  * TILE: 64 rows per CTA, 16 per warp; every warp walks all key tiles. For
 //    prompt portions.
-//  * SPLIT: at most 16 rows per CTA (a decode token's group); the four warps
-//    share the rows and split each key tile between them, and CTAs split a
-//    request's keys between them too. Partial results (unnormalised sum,
-//    maximum, denominator) go to scratch memory; the CTA that finishes last
-//    (a ticket counter per request and kv head) merges them.
-// A request belongs to SPLIT if q_len * g <= 16, else to TILE; each kernel skips
+//  * DECODE: at most 16 rows per CTA (a decode token's group). The CTAs of a
+//    thread-block cluster (up to 8) split the request's keys; within a CTA the
+//    four tiles of a round are in flight together and each warp takes one. The
+//    warps' results are merged in shared memory, the CTAs' results are sent to
+//    the cluster's first CTA through distributed shared memory (st.async counted
+//    on an mbarrier) and merged there: no scratch in global memory.
+// A request belongs to DECODE if q_len * g <= 16, else to TILE; each kernel skips
 // the other's requests.
 //
 // Compiled per head size: GB_HEAD_DIM (a multiple of 16, at most 128).
-#include "common.cuh"
+#include "tc_common.cuh"
 
 #ifndef GB_HEAD_DIM
 #define GB_HEAD_DIM 64
@@ -32,33 +33,31 @@
 
 namespace {
 
+using namespace tc;
+
 constexpr int HD = GB_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head_dim must be a multiple of 16 up to 128");
 constexpr int KT = 64;              // keys per tile
 constexpr int PAD = 8;              // bf16 of padding per shared-memory row (16 bytes)
 constexpr int LD = HD + PAD;        // shared-memory row length in bf16
 constexpr int THREADS = 128;
-constexpr int ROWS_TILE = 64;
-constexpr int ROWS_SPLIT = 16;
-// Key tiles in flight per CTA. A decode CTA has little arithmetic per byte, so what matters is how
-// many bytes it has asked for at once: four tiles. A prompt CTA reuses each tile for 64 rows: two.
-constexpr int DEPTH_TILE = 2;
-constexpr int DEPTH_SPLIT = 4;
+constexpr int ROWS_TILE = 64;       // query rows per CTA of the TILE kernel
+constexpr int ROWS_DECODE = 16;     // query rows per CTA of the DECODE kernel
+constexpr int SLOTS = 4;            // key tiles in flight per DECODE CTA: one per warp and round
+constexpr int MAX_CLUSTER = 8;      // CTAs that may share one request's keys
+constexpr int RS = HD + 2;          // floats of one row's partial result: sum, then maximum, denominator
 constexpr float LOG2E = 1.4426950408889634f;
 
-// Compiled in with -DGB_TIMELINE only: time stamps per CTA of the split kernel.
+__device__ int g_error_word;
+
+// Compiled in with -DGB_TIMELINE only: time stamps per CTA of the decode kernel.
 #ifdef GB_TIMELINE
 __device__ unsigned long long g_timeline[8 * 4096];
-__device__ __forceinline__ unsigned long long timeline_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
 #define GB_STAMP(i)                                                                                   \
   do {                                                                                                \
-    if (SPLIT && threadIdx.x == 0) {                                                                  \
+    if (threadIdx.x == 0) {                                                                           \
       const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
-      if (cta < 4096) g_timeline[8 * cta + (i)] = timeline_now();                                     \
+      if (cta < 4096) g_timeline[8 * cta + (i)] = globaltimer_ns();                                   \
     }                                                                                                 \
   } while (0)
 #else
@@ -70,12 +69,10 @@ struct Params {
   const __nv_bfloat16* k_pool;   // [pages, Hkv, page_size, HD]
   const __nv_bfloat16* v_pool;
   __nv_bfloat16* out;            // [T, Hq * HD]
-  float* partial;                // SPLIT with several splits: [T * Hq, splits, HD + 2]
-  int* counters;                 // SPLIT with several splits: [R * Hkv] tickets, zero between launches
   const int32_t* block_table;    // [R, table_width]
   const int32_t* cu_q;           // [R + 1]
   const int32_t* kv_lens;        // [R]
-  int table_width, Hq, Hkv, g, window, page_size, num_splits;
+  int table_width, Hq, Hkv, g, window, page_size;
   float scale_log2;              // scale * log2(e)
 };
 
@@ -134,338 +131,375 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
   }
 }
 
-template <bool SPLIT>
-__global__ void __launch_bounds__(THREADS)
-attention_mma_kernel(const Params p) {
-  constexpr int ROWS = SPLIT ? ROWS_SPLIT : ROWS_TILE;
-  constexpr int DEPTH = SPLIT ? DEPTH_SPLIT : DEPTH_TILE;
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [ROWS][LD]
-  __nv_bfloat16* kv = qs + ROWS * LD;                               // DEPTH stages x (K, V) x [KT][LD]
+// `rows` query rows (row = token_local * g + head_of_group) into shared memory; the rest zeros.
+__device__ __forceinline__ void load_queries(__nv_bfloat16* qs, const Params& p, int first_token, int kvh,
+                                             int nrows, int rows) {
+  constexpr int CHUNKS = HD / 8;
+  for (int c = threadIdx.x; c < rows * CHUNKS; c += THREADS) {
+    const int row = c / CHUNKS, ch = c % CHUNKS;
+    const bool valid = row < nrows;
+    const int tok = valid ? row / p.g : 0, gh = valid ? row % p.g : 0;
+    cp_async_16(qs + row * LD + ch * 8, p.q + ((size_t)(first_token + tok) * p.Hq + kvh * p.g + gh) * HD + ch * 8,
+                valid);
+  }
+}
 
-  GB_STAMP(0);
+// One warp's running state over the keys it has seen: 16 query rows, of which a thread holds the
+// two rows lane / 4 and lane / 4 + 8.
+struct WarpState {
+  float o[HD / 8][4];
+  float m[2], l[2];
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+  }
+};
+
+// One tile of 64 keys for one warp's 16 rows: S = Q K^T, scale and mask, running softmax in
+// 32-bit, O += P V. qf: the warp's query fragments; key0: position of the tile's first key;
+// row_pos / row_start: last and first key each of the thread's two rows may read.
+__device__ __forceinline__ void process_tile(WarpState& st, const uint32_t (&qf)[HD / 16][4],
+                                             const __nv_bfloat16* ks, const __nv_bfloat16* vs, int key0,
+                                             const int (&row_pos)[2], const int (&row_start)[2], float scale_log2) {
+  const int lane = threadIdx.x & 31;
+  float s[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+    for (int n2 = 0; n2 < 4; ++n2) {
+      uint32_t b[4];
+      const int key = n2 * 16 + (lane % 8) + (lane / 16) * 8;
+      ldmatrix_x4(b, ks + key * LD + kk * 16 + ((lane / 8) % 2) * 8);
+      mma_16816(s[2 * n2], qf[kk], b[0], b[1]);
+      mma_16816(s[2 * n2 + 1], qf[kk], b[2], b[3]);
+    }
+  }
+  float m_new[2] = {st.m[0], st.m[1]};
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = e >> 1;
+      const int j = key0 + n * 8 + (lane % 4) * 2 + (e & 1);
+      const bool ok = j >= row_start[i] && j <= row_pos[i];
+      s[n][e] = ok ? s[n][e] * scale_log2 : -INFINITY;
+      m_new[i] = fmaxf(m_new[i], s[n][e]);
+    }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+    m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+  }
+  float corr[2], m_use[2], l_add[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    m_use[i] = m_new[i] == -INFINITY ? 0.f : m_new[i];     // nothing valid yet: avoid inf - inf
+    corr[i] = st.m[i] == -INFINITY ? 0.f : exp2f(st.m[i] - m_use[i]);
+    st.m[i] = m_new[i];
+  }
+  uint32_t pf[4][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n) {
+    float pr[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      pr[e] = exp2f(s[n][e] - m_use[e >> 1]);   // exp2(-inf) = 0 for masked keys
+      l_add[e >> 1] += pr[e];
+    }
+    pf[n / 2][(n % 2) * 2 + 0] = pack_bf16(pr[0], pr[1]);
+    pf[n / 2][(n % 2) * 2 + 1] = pack_bf16(pr[2], pr[3]);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) st.l[i] = st.l[i] * corr[i] + l_add[i];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    st.o[n][0] *= corr[0]; st.o[n][1] *= corr[0];
+    st.o[n][2] *= corr[1]; st.o[n][3] *= corr[1];
+  }
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+    for (int n2 = 0; n2 < HD / 16; ++n2) {
+      uint32_t b[4];
+      const int key = kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8;
+      ldmatrix_x4_trans(b, vs + key * LD + n2 * 16 + (lane / 16) * 8);
+      mma_16816(st.o[2 * n2], pf[kk], b[0], b[1]);
+      mma_16816(st.o[2 * n2 + 1], pf[kk], b[2], b[3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ TILE (prompt portions)
+__global__ void __launch_bounds__(THREADS)
+attention_tile_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [ROWS_TILE][LD]
+  __nv_bfloat16* kv = qs + ROWS_TILE * LD;                          // 2 stages x (K, V) x [KT][LD]
   gb::pdl_launch_dependents();
-  // The batch's lengths and block tables were copied in before the step's first kernel: they may be
-  // read at once. Queries and this step's own keys and values come from the kernels in front.
+  gb::pdl_wait();     // queries and this step's keys and values come from the kernels in front
   const int r = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin;
-  const int rows_total = q_len * p.g;
-  const bool small = rows_total <= ROWS_SPLIT;
-  if (small != SPLIT || q_len <= 0) return;
+  if (q_len * p.g <= ROWS_DECODE) return;        // a DECODE request
+  const int tokens_per_tile = ROWS_TILE / p.g;
+  const int tok0 = blockIdx.x * tokens_per_tile;
+  if (tok0 >= q_len) return;
   const int kv_len = p.kv_lens[r];
   const int32_t* table = p.block_table + (size_t)r * p.table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // rows of this CTA: row = token_local * g + head_of_group
-  const int tokens_per_tile = SPLIT ? q_len : ROWS / p.g;
-  const int tok0 = SPLIT ? 0 : blockIdx.x * tokens_per_tile;
-  if (tok0 >= q_len) return;
   const int ntok = min(tokens_per_tile, q_len - tok0);
   const int nrows = ntok * p.g;
   const int pos0 = kv_len - q_len + tok0;            // position of the tile's first token
-  const int pos_last = pos0 + ntok - 1;
   const int lo = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;   // first key any row reads
-  const int hi = pos_last;                                         // last key any row reads
+  const int hi = pos0 + ntok - 1;                                  // last key any row reads
+  const int tile_begin = lo / KT, tile_end = hi / KT + 1;
 
-  // key tiles this CTA walks
-  const int first_tile = lo / KT;
-  int tile_begin = first_tile, tile_end = hi / KT + 1;
-  if (SPLIT && p.num_splits > 1) {
-    const int total = tile_end - first_tile;
-    const int per = (total + p.num_splits - 1) / p.num_splits;
-    tile_begin = first_tile + blockIdx.x * per;
-    tile_end = min(tile_end, tile_begin + per);
-  }
-
-  // Keys and values of earlier steps are final: a decode CTA asks for its tiles of them before
-  // waiting for the kernels in front, so that they arrive while those still run. One commit group
-  // per tile slot, empty if the slot has no tile or its tile holds positions of this step.
-  const int first_new = kv_len - q_len;
-  auto is_old = [&](int tile) { return SPLIT && (tile + 1) * KT <= first_new; };
-  for (int d = 0; d < DEPTH - 1; ++d) {
-    const int tile = tile_begin + d;
-    if (tile < tile_end && is_old(tile)) {
-      __nv_bfloat16* kd = kv + d * 2 * KT * LD;
-      load_kv_tile(kd, kd + KT * LD, p, table, kvh, tile * KT, lo, hi);
-    }
-    cp_async_commit();
-  }
-  gb::pdl_wait();
-  GB_STAMP(1);
-
-  // ---- queries into shared memory (rows beyond nrows are zeros), and the tiles not asked for yet
-  {
-    constexpr int CHUNKS = HD / 8;
-    for (int c = threadIdx.x; c < ROWS * CHUNKS; c += THREADS) {
-      const int row = c / CHUNKS, ch = c % CHUNKS;
-      const bool valid = row < nrows;
-      const int tok = row / p.g, gh = row % p.g;
-      const __nv_bfloat16* src =
-          p.q + ((size_t)(q_begin + tok0 + (valid ? tok : 0)) * p.Hq + kvh * p.g + (valid ? gh : 0)) * HD + ch * 8;
-      cp_async_16(qs + row * LD + ch * 8, src, valid);
-    }
-  }
-  for (int d = 0; d < DEPTH - 1; ++d) {
-    const int tile = tile_begin + d;
-    if (tile < tile_end && !is_old(tile)) {
-      __nv_bfloat16* kd = kv + d * 2 * KT * LD;
-      load_kv_tile(kd, kd + KT * LD, p, table, kvh, tile * KT, lo, hi);
-    }
-  }
+  load_queries(qs, p, q_begin + tok0, kvh, nrows, ROWS_TILE);
+  load_kv_tile(kv, kv + KT * LD, p, table, kvh, tile_begin * KT, lo, hi);
   cp_async_commit();
 
-  // this thread's two rows (lane / 4 and + 8) of the warp's 16
-  const int wrow0 = SPLIT ? 0 : warp * 16;
   int row_pos[2], row_start[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int row = wrow0 + lane / 4 + 8 * i;
-    if (row < nrows) {
-      row_pos[i] = pos0 + row / p.g;
-      row_start[i] = p.window > 0 ? max(0, row_pos[i] + 1 - p.window) : 0;
-    } else {
-      row_pos[i] = -1;  // no key is valid for a padding row
-      row_start[i] = 0;
-    }
+    const int row = warp * 16 + lane / 4 + 8 * i;
+    row_pos[i] = row < nrows ? pos0 + row / p.g : -1;      // no key is valid for a padding row
+    row_start[i] = (row < nrows && p.window > 0) ? max(0, row_pos[i] + 1 - p.window) : 0;
   }
-
-  float o[HD / 8][4];
-#pragma unroll
-  for (int n = 0; n < HD / 8; ++n)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  WarpState st;
+  st.reset();
   uint32_t qf[HD / 16][4];
-  bool q_loaded = false;
-
-  // keys of a tile that this warp handles: all 64 (TILE) or 16 of them (SPLIT)
-  constexpr int NB = SPLIT ? 2 : 8;          // 8-key blocks per warp per tile
-  const int key_off = SPLIT ? warp * 16 : 0;
-
   for (int tile = tile_begin; tile < tile_end; ++tile) {
-    const int stage = (tile - tile_begin) % DEPTH;
+    const int stage = (tile - tile_begin) & 1;
     __nv_bfloat16* ks = kv + stage * 2 * KT * LD;
     __nv_bfloat16* vs = ks + KT * LD;
-    if (tile + DEPTH - 1 < tile_end) {
-      // into the stage that the previous iteration finished with
-      __nv_bfloat16* kn = kv + ((tile - tile_begin + DEPTH - 1) % DEPTH) * 2 * KT * LD;
-      load_kv_tile(kn, kn + KT * LD, p, table, kvh, (tile + DEPTH - 1) * KT, lo, hi);
+    if (tile + 1 < tile_end) {
+      __nv_bfloat16* kn = kv + (stage ^ 1) * 2 * KT * LD;
+      load_kv_tile(kn, kn + KT * LD, p, table, kvh, (tile + 1) * KT, lo, hi);
     }
     cp_async_commit();
-    // Everything but the DEPTH - 1 newest groups has landed: this tile has. Before the first tile
-    // the queries' group (the newest but one) must have landed too: wait for all of them.
-    if (tile == tile_begin) cp_async_wait<0>();
-    else cp_async_wait<DEPTH - 1>();
+    cp_async_wait<1>();
     __syncthreads();
-    if (tile == tile_begin) GB_STAMP(2);
-
-    if (!q_loaded) {
+    if (tile == tile_begin) {
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk)
-        ldmatrix_x4(qf[kk], qs + (wrow0 + (lane % 16)) * LD + kk * 16 + (lane / 16) * 8);
-      q_loaded = true;
+        ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane % 16)) * LD + kk * 16 + (lane / 16) * 8);
     }
-
-    // ---- S = Q K^T for this warp's keys
-    float s[NB][4];
-#pragma unroll
-    for (int n = 0; n < NB; ++n)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-#pragma unroll
-      for (int n2 = 0; n2 < NB / 2; ++n2) {
-        uint32_t b[4];
-        const int key = key_off + n2 * 16 + (lane % 8) + (lane / 16) * 8;
-        ldmatrix_x4(b, ks + key * LD + kk * 16 + ((lane / 8) % 2) * 8);
-        mma_16816(s[2 * n2], qf[kk], b[0], b[1]);
-        mma_16816(s[2 * n2 + 1], qf[kk], b[2], b[3]);
-      }
-    }
-
-    // ---- scale, mask, running softmax (32-bit)
-    const int tile_key0 = tile * KT + key_off;
-    float m_new[2] = {m_run[0], m_run[1]};
-#pragma unroll
-    for (int n = 0; n < NB; ++n)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const int j = tile_key0 + n * 8 + (lane % 4) * 2 + (e & 1);
-        const bool ok = j >= row_start[i] && j <= row_pos[i];
-        s[n][e] = ok ? s[n][e] * p.scale_log2 : -INFINITY;
-        m_new[i] = fmaxf(m_new[i], s[n][e]);
-      }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
-      m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
-    }
-    float corr[2], m_use[2], l_add[2] = {0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      m_use[i] = m_new[i] == -INFINITY ? 0.f : m_new[i];     // nothing valid yet: avoid inf - inf
-      corr[i] = m_run[i] == -INFINITY ? 0.f : exp2f(m_run[i] - m_use[i]);
-      m_run[i] = m_new[i];
-    }
-    uint32_t pf[NB / 2][4];
-#pragma unroll
-    for (int n = 0; n < NB; ++n) {
-      float pr[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        pr[e] = exp2f(s[n][e] - m_use[e >> 1]);   // exp2(-inf) = 0 for masked keys
-        l_add[e >> 1] += pr[e];
-      }
-      pf[n / 2][(n % 2) * 2 + 0] = pack_bf16(pr[0], pr[1]);
-      pf[n / 2][(n % 2) * 2 + 1] = pack_bf16(pr[2], pr[3]);
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
-#pragma unroll
-    for (int n = 0; n < HD / 8; ++n) {
-      o[n][0] *= corr[0]; o[n][1] *= corr[0];
-      o[n][2] *= corr[1]; o[n][3] *= corr[1];
-    }
-
-    // ---- O += P V
-#pragma unroll
-    for (int kk = 0; kk < NB / 2; ++kk) {
-#pragma unroll
-      for (int n2 = 0; n2 < HD / 16; ++n2) {
-        uint32_t b[4];
-        const int key = key_off + kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8;
-        ldmatrix_x4_trans(b, vs + key * LD + n2 * 16 + (lane / 16) * 8);
-        mma_16816(o[2 * n2], pf[kk], b[0], b[1]);
-        mma_16816(o[2 * n2 + 1], pf[kk], b[2], b[3]);
-      }
-    }
+    process_tile(st, qf, ks, vs, tile * KT, row_pos, row_start, p.scale_log2);
     __syncthreads();  // the stage may be overwritten by the next iteration's loads
   }
   cp_async_wait<0>();
-  GB_STAMP(3);
-
-  // the denominators: sum over the four threads that share a row
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
-    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
-  }
-
-  if (!SPLIT) {
+    st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
+    st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 2);
+    const int row = warp * 16 + lane / 4 + 8 * i;
+    if (row >= nrows) continue;
+    const float inv = st.l[i] > 0.f ? 1.0f / st.l[i] : 0.f;
+    __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row / p.g) * p.Hq + kvh * p.g + row % p.g) * HD;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int row = wrow0 + lane / 4 + 8 * i;
-      if (row >= nrows) continue;
-      const int tok = row / p.g, gh = row % p.g;
-      const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
-      __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + tok) * p.Hq + kvh * p.g + gh) * HD;
-#pragma unroll
-      for (int n = 0; n < HD / 8; ++n) {
-        const uint32_t v = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
-        *reinterpret_cast<uint32_t*>(dst + n * 8 + (lane % 4) * 2) = v;
-      }
-    }
-    return;
+    for (int n = 0; n < HD / 8; ++n)
+      *reinterpret_cast<uint32_t*>(dst + n * 8 + (lane % 4) * 2) = pack_bf16(st.o[n][2 * i] * inv, st.o[n][2 * i + 1] * inv);
   }
+}
 
-  // ---- SPLIT: merge the four warps (each saw a quarter of every tile's keys)
+// ------------------------------------------------------------------ DECODE
+// grid (ranks, Hkv, R), the `ranks` CTAs along x forming one cluster.
+__global__ void __launch_bounds__(THREADS)
+attention_decode_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [ROWS_DECODE][LD]
+  __nv_bfloat16* kv = qs + ROWS_DECODE * LD;                        // SLOTS x (K, V) x [KT][LD]
+  float* red = reinterpret_cast<float*>(kv);                        // after the last round: [4 warps][16][RS]
+  float* parts = reinterpret_cast<float*>(kv + SLOTS * 2 * KT * LD);  // rank 0: [ranks - 1][16][RS] received
+  __shared__ __align__(8) uint64_t part_bar;
+
+  GB_STAMP(0);
+  const int r = blockIdx.z, kvh = blockIdx.y;
+  const int rank = blockIdx.x, ranks = gridDim.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The batch's lengths and block tables were copied in before the step's first kernel: they may be
+  // read at once. Queries and this step's own keys and values come from the kernels in front.
+  const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin;
+  const int nrows = q_len * p.g;
+  if (q_len <= 0 || nrows > ROWS_DECODE) return;   // a TILE request (the whole cluster leaves together)
+  const int kv_len = p.kv_lens[r];
+  const int32_t* table = p.block_table + (size_t)r * p.table_width;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&part_bar), 1);
+    fence_barrier_init();
+    if (rank == 0 && ranks > 1)
+      mbar_arrive_expect_tx(smem_u32(&part_bar), (uint32_t)(ranks - 1) * ROWS_DECODE * RS * 4);
+  }
   __syncthreads();
-  float* red = reinterpret_cast<float*>(kv);            // [4 warps][16 rows][HD + 2]
-  constexpr int RS = HD + 2;
+  if (ranks > 1) cluster_arrive_wait();      // rank 0's barrier is armed before anyone sends to it
+  GB_STAMP(1);
+  gb::pdl_launch_dependents();
+
+  const int pos0 = kv_len - q_len;                                  // position of the first token
+  const int lo = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;    // first key any row reads
+  const int hi = kv_len - 1;
+  const int first_tile = lo / KT, total = hi / KT + 1 - first_tile;
+  const int per = (total + ranks - 1) / ranks;
+  const int tile_begin = first_tile + rank * per;
+  const int tile_end = min(hi / KT + 1, tile_begin + per);
+
+  int row_pos[2], row_start[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = lane / 4 + 8 * i;
-    float* dst = red + (warp * 16 + row) * RS;
+    row_pos[i] = row < nrows ? pos0 + row / p.g : -1;
+    row_start[i] = (row < nrows && p.window > 0) ? max(0, row_pos[i] + 1 - p.window) : 0;
+  }
+  WarpState st;
+  st.reset();
+  uint32_t qf[HD / 16][4];
+  bool waited = false;
+  for (int base = tile_begin; base < tile_end; base += SLOTS) {
+    // Keys and values of earlier steps are final: in the first round their tiles are asked for
+    // before waiting for the kernels in front, so that they arrive while those still run.
+    if (!waited) {
+      for (int d = 0; d < SLOTS; ++d) {
+        const int tile = base + d;
+        if (tile < tile_end && (tile + 1) * KT <= pos0) {
+          __nv_bfloat16* kd = kv + d * 2 * KT * LD;
+          load_kv_tile(kd, kd + KT * LD, p, table, kvh, tile * KT, lo, hi);
+        }
+      }
+      gb::pdl_wait();
+      GB_STAMP(2);
+      load_queries(qs, p, q_begin, kvh, nrows, ROWS_DECODE);
+    }
+    for (int d = 0; d < SLOTS; ++d) {
+      const int tile = base + d;
+      if (tile < tile_end && (waited || (tile + 1) * KT > pos0)) {
+        __nv_bfloat16* kd = kv + d * 2 * KT * LD;
+        load_kv_tile(kd, kd + KT * LD, p, table, kvh, tile * KT, lo, hi);
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    GB_STAMP(3);
+    if (!waited) {
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk)
+        ldmatrix_x4(qf[kk], qs + (lane % 16) * LD + kk * 16 + (lane / 16) * 8);
+      waited = true;
+    }
+    const int tile = base + warp;               // each warp takes one of the round's tiles
+    if (tile < tile_end) {
+      const __nv_bfloat16* ks = kv + warp * 2 * KT * LD;
+      process_tile(st, qf, ks, ks + KT * LD, tile * KT, row_pos, row_start, p.scale_log2);
+    }
+    __syncthreads();   // the slots are overwritten by the next round, or by the merge
+  }
+  if (!waited) gb::pdl_wait();   // a CTA without tiles still must not run ahead of what it may overwrite
+
+  GB_STAMP(4);
+  // ---- the four warps' results into shared memory: [warp][row][RS]
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
+    st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 2);
+    float* dst = red + (warp * 16 + lane / 4 + 8 * i) * RS;
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
-      dst[n * 8 + (lane % 4) * 2] = o[n][2 * i];
-      dst[n * 8 + (lane % 4) * 2 + 1] = o[n][2 * i + 1];
+      dst[n * 8 + (lane % 4) * 2] = st.o[n][2 * i];
+      dst[n * 8 + (lane % 4) * 2 + 1] = st.o[n][2 * i + 1];
     }
     if (lane % 4 == 0) {
-      dst[HD] = m_run[i];
-      dst[HD + 1] = l_run[i];
+      dst[HD] = st.m[i];
+      dst[HD + 1] = st.l[i];
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < nrows * HD; idx += THREADS) {
-    const int row = idx / HD, c = idx % HD;
+  // ---- merge the warps; a CTA that is alone writes the result, one of several passes it on.
+  // The weights exp2(m_w - m) are computed once per row and warp, not once per element.
+  float* wfac = red + (4 * 16 + 16) * RS;   // [16 rows][4 warps] weights, then [16] merged maxima
+  float* mine = red + 4 * 16 * RS;          // this CTA's merged rows: [16][RS]
+  if (threadIdx.x < ROWS_DECODE) {
+    const int row = threadIdx.x;
     float m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) m = fmaxf(m, red[(w * 16 + row) * RS + HD]);
-    float acc = 0.f, l = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = red[(w * 16 + row) * RS + HD];
-      const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
-      acc += f * red[(w * 16 + row) * RS + c];
-      l += f * red[(w * 16 + row) * RS + HD + 1];
+      wfac[row * 4 + w] = mw == -INFINITY ? 0.f : exp2f(mw - m);
     }
-    const int tok = row / p.g, gh = row % p.g;
-    const size_t orow = (size_t)(q_begin + tok) * p.Hq + kvh * p.g + gh;
-    if (p.num_splits > 1) {
-      float* dst = p.partial + (orow * p.num_splits + blockIdx.x) * RS;
-      dst[c] = acc;
-      if (c == 0) { dst[HD] = m; dst[HD + 1] = l; }
-    } else {
-      p.out[orow * HD + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-    }
+    wfac[64 + row] = m;
   }
-  if (p.num_splits == 1) return;
-  GB_STAMP(4);
-
-  // ---- the CTA that finishes last for this (request, kv head) merges the splits
-  __shared__ int ticket_s;
-  __threadfence();
   __syncthreads();
-  int* counter = p.counters + (size_t)r * p.Hkv + kvh;
-  if (threadIdx.x == 0) ticket_s = atomicAdd(counter, 1);
-  __syncthreads();
+  const bool send = ranks > 1 && rank != 0;
+  const uint32_t remote = send ? map_to_rank(smem_u32(parts) + (uint32_t)(rank - 1) * ROWS_DECODE * RS * 4, 0) : 0;
+  const uint32_t remote_bar = send ? map_to_rank(smem_u32(&part_bar), 0) : 0;
+  for (int idx = threadIdx.x; idx < ROWS_DECODE * RS; idx += THREADS) {
+    const int row = idx / RS, c = idx % RS;
+    float v;
+    if (c == HD) {
+      v = wfac[64 + row];
+    } else {       // the sum (c < HD) or the denominator (c == HD + 1), both weighted alike
+      v = wfac[row * 4] * red[row * RS + c] + wfac[row * 4 + 1] * red[(16 + row) * RS + c] +
+          wfac[row * 4 + 2] * red[(32 + row) * RS + c] + wfac[row * 4 + 3] * red[(48 + row) * RS + c];
+    }
+    if (send) st_async_f32(remote + (uint32_t)idx * 4, remote_bar, v);
+    else mine[idx] = v;
+  }
   GB_STAMP(5);
-  if (ticket_s != p.num_splits - 1) return;
-  __threadfence();
-  const int S = p.num_splits;                           // at most 64
-  float* fac = red;                                     // [nrows][S]: weight of each split
-  float* inv = red + ROWS_SPLIT * 64;                   // [nrows]: 1 / denominator
-  for (int idx = threadIdx.x; idx < nrows * S; idx += THREADS) {
-    const int row = idx / S, sp = idx % S;
-    const size_t orow = (size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g;
-    fac[row * 64 + sp] = __ldcg(p.partial + (orow * S + sp) * RS + HD);      // its maximum, for now
+  if (rank != 0) return;
+  if (ranks > 1 && !mbar_wait(smem_u32(&part_bar), 0)) {
+    if (threadIdx.x == 0) atomicCAS(&g_error_word, 0, 1);
+    return;
   }
   __syncthreads();
+  GB_STAMP(6);
+  // ---- rank 0: its own rows and the others', in rank order; again the weights once per row
+  float* rfac = wfac + 96;                  // [16 rows][8 ranks] weights, then [16] 1 / denominator
   if (threadIdx.x < nrows) {
     const int row = threadIdx.x;
-    const size_t orow = (size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g;
-    float m = -INFINITY;
-    for (int sp = 0; sp < S; ++sp) m = fmaxf(m, fac[row * 64 + sp]);
-    float l = 0.f;
-    for (int sp = 0; sp < S; ++sp) {
-      const float ms = fac[row * 64 + sp];
-      const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
-      fac[row * 64 + sp] = f;
-      l += f * __ldcg(p.partial + (orow * S + sp) * RS + HD + 1);
+    float ms[MAX_CLUSTER];
+    float m = ms[0] = mine[row * RS + HD];
+#pragma unroll
+    for (int q = 1; q < MAX_CLUSTER; ++q) {
+      ms[q] = q < ranks ? parts[((q - 1) * ROWS_DECODE + row) * RS + HD] : -INFINITY;
+      m = fmaxf(m, ms[q]);
     }
-    inv[row] = l > 0.f ? 1.0f / l : 0.f;
+    float l = 0.f;
+#pragma unroll
+    for (int q = 0; q < MAX_CLUSTER; ++q) {
+      const float f = ms[q] == -INFINITY ? 0.f : exp2f(ms[q] - m);
+      rfac[row * MAX_CLUSTER + q] = f;
+      if (q < ranks) l += f * (q == 0 ? mine[row * RS + HD + 1] : parts[((q - 1) * ROWS_DECODE + row) * RS + HD + 1]);
+    }
+    rfac[ROWS_DECODE * MAX_CLUSTER + row] = l > 0.f ? 1.0f / l : 0.f;
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < nrows * HD; idx += THREADS) {
     const int row = idx / HD, c = idx % HD;
-    const size_t orow = (size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g;
-    const float* src = p.partial + orow * S * RS + c;
-    float acc = 0.f;
-    for (int sp = 0; sp < S; ++sp) acc += fac[row * 64 + sp] * __ldcg(src + (size_t)sp * RS);
-    p.out[orow * HD + c] = __float2bfloat16_rn(acc * inv[row]);
+    float acc = rfac[row * MAX_CLUSTER] * mine[row * RS + c];
+#pragma unroll
+    for (int q = 1; q < MAX_CLUSTER; ++q)
+      if (q < ranks) acc += rfac[row * MAX_CLUSTER + q] * parts[((q - 1) * ROWS_DECODE + row) * RS + c];
+    p.out[((size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g) * HD + c] =
+        __float2bfloat16_rn(acc * rfac[ROWS_DECODE * MAX_CLUSTER + row]);
   }
-  if (threadIdx.x == 0) *counter = 0;     // ready for the next launch
-  GB_STAMP(6);
+  GB_STAMP(7);
 }
 
-constexpr int smem_bytes(bool split) {
-  return ((split ? ROWS_SPLIT : ROWS_TILE) * LD + (split ? DEPTH_SPLIT : DEPTH_TILE) * 2 * KT * LD) * 2;
+constexpr int SMEM_TILE = (ROWS_TILE * LD + 2 * 2 * KT * LD) * 2;
+constexpr int smem_decode(int ranks) {
+  return (ROWS_DECODE * LD + SLOTS * 2 * KT * LD) * 2 + (ranks > 1 ? (ranks - 1) * ROWS_DECODE * RS * 4 : 0);
 }
-static_assert(4 * 16 * (HD + 2) * 4 <= 2 * 2 * KT * LD * 2, "merge buffer must fit in the K/V stages");
-static_assert((ROWS_SPLIT * 64 + ROWS_SPLIT) * 4 <= 2 * 2 * KT * LD * 2, "split weights must fit in the K/V stages");
+static_assert(((4 * 16 + 16) * RS + 96 + 16 * MAX_CLUSTER + 16) * 4 <= SLOTS * 2 * KT * LD * 2,
+              "the merge buffers must fit in the key slots");
 
 }  // namespace
 
@@ -479,57 +513,56 @@ GB_EXPORT int gb_attention_timeline(unsigned long long* host_out, int ctas) {
 }
 #endif
 
-// Floats of scratch that gb_attention_mma needs for `num_splits` splits (and R * Hkv ints of
-// ticket counters, zero before the first launch; every launch leaves them zero).
-GB_EXPORT long long gb_attention_mma_scratch_floats(int T, int Hq, int num_splits) {
-  return num_splits > 1 ? (long long)T * Hq * num_splits * (HD + 2) : 0;
+// Non-zero if a decode CTA gave up waiting for its cluster since the last call; clears it.
+GB_EXPORT int gb_attention_error_check() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_error_word, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_error_word, &zero, sizeof(int));
+  }
+  return v;
 }
 
 // q [T, Hq, HD], pools [pages, Hkv, page_size, HD], out [T, Hq*HD], all bfloat16.
-// num_splits: CTAs that share the keys of a decode request (1: no scratch needed).
-// max_q_len and min_q_len (over the batch's requests) decide which variants are launched.
-GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
-                               int* counters, const int32_t* block_table, int table_width, const int32_t* cu_q,
-                               const int32_t* kv_lens, const int32_t* token_req, int T, int R, int Hq, int Hkv,
-                               float scale, int window, int page_size, int max_q_len, int min_q_len,
-                               int num_splits, cudaStream_t stream) {
+// num_splits: CTAs (one cluster, at most 8) that share the keys of a decode request.
+// max_q_len and min_q_len (over the batch's requests) decide which kernels are launched.
+GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
+                               const int32_t* block_table, int table_width, const int32_t* cu_q,
+                               const int32_t* kv_lens, int T, int R, int Hq, int Hkv, float scale, int window,
+                               int page_size, int max_q_len, int min_q_len, int num_splits, cudaStream_t stream) {
   if (T <= 0 || R <= 0) return GB_OK;
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "attention: %d query heads for %d kv heads", Hq, Hkv);
   const int g = Hq / Hkv;
   if (g > ROWS_TILE) return gb::fail(GB_UNSUPPORTED, "attention_mma: a group of %d query heads per kv head", g);
-  if (num_splits < 1) num_splits = 1;
-  if (num_splits > 64) num_splits = 64;
-  if (num_splits > 1 && (!scratch || !counters))
-    return gb::fail(GB_BAD_ARGUMENT, "attention_mma: splits need scratch memory and ticket counters");
+  num_splits = num_splits < 1 ? 1 : (num_splits > MAX_CLUSTER ? MAX_CLUSTER : num_splits);
   Params p;
   p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
-  p.out = (__nv_bfloat16*)out; p.partial = scratch; p.counters = counters; p.block_table = block_table; p.cu_q = cu_q;
-  p.kv_lens = kv_lens; p.table_width = table_width; p.Hq = Hq; p.Hkv = Hkv; p.g = g; p.window = window;
-  p.page_size = page_size; p.num_splits = num_splits; p.scale_log2 = scale * LOG2E;
+  p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens;
+  p.table_width = table_width; p.Hq = Hq; p.Hkv = Hkv; p.g = g; p.window = window; p.page_size = page_size;
+  p.scale_log2 = scale * LOG2E;
 
   static bool configured = false;
   if (!configured) {
-    cudaError_t e1 = cudaFuncSetAttribute(attention_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          smem_bytes(false));
-    cudaError_t e2 = cudaFuncSetAttribute(attention_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          smem_bytes(true));
+    cudaError_t e1 = cudaFuncSetAttribute(attention_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TILE);
+    cudaError_t e2 = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          smem_decode(MAX_CLUSTER));
     if (e1 != cudaSuccess || e2 != cudaSuccess)
       return gb::fail(GB_CUDA_ERROR, "attention_mma: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     configured = true;
   }
-  // SPLIT requests (a decode token's group, or a very short portion), if the batch can hold any
-  if (min_q_len * g <= ROWS_SPLIT) {
-    int rc = gb::check_pdl_launch(gb::launch_pdl(attention_mma_kernel<true>, dim3(num_splits, Hkv, R), dim3(THREADS),
-                                                 smem_bytes(true), stream, 1, p),
-                                  "attention_mma (split)");
+  // DECODE requests (a decode token's group, or a very short portion), if the batch can hold any
+  if (min_q_len * g <= ROWS_DECODE) {
+    int rc = gb::check_pdl_launch(gb::launch_pdl(attention_decode_kernel, dim3(num_splits, Hkv, R), dim3(THREADS),
+                                                 smem_decode(num_splits), stream, dim3(num_splits, 1, 1), p),
+                                  "attention_mma (decode)");
     if (rc) return rc;
   }
   // TILE requests
-  if (max_q_len * g > ROWS_SPLIT) {
+  if (max_q_len * g > ROWS_DECODE) {
     const int tokens_per_tile = ROWS_TILE / g;
     dim3 grid((max_q_len + tokens_per_tile - 1) / tokens_per_tile, Hkv, R);
-    return gb::check_pdl_launch(gb::launch_pdl(attention_mma_kernel<false>, grid, dim3(THREADS), smem_bytes(false),
-                                               stream, 1, p),
+    return gb::check_pdl_launch(gb::launch_pdl(attention_tile_kernel, grid, dim3(THREADS), SMEM_TILE, stream, dim3(1, 1, 1), p),
                                 "attention_mma (tile)");
   }
   return GB_OK;

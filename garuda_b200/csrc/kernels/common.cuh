@@ -85,10 +85,11 @@ inline bool pdl_enabled() {
   return on;
 }
 
-// Launch with the programmatic-serialization attribute (and a cluster shape along z, if cluster_z > 1).
+// Launch with the programmatic-serialization attribute, and as clusters of the given shape if it
+// holds more than one CTA.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              int cluster_z, Args... args) {
+                              dim3 cluster, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -101,11 +102,11 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attrs[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
   }
-  if (cluster_z > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attrs[n].id = cudaLaunchAttributeClusterDimension;
-    attrs[n].val.clusterDim.x = 1;
-    attrs[n].val.clusterDim.y = 1;
-    attrs[n].val.clusterDim.z = cluster_z;
+    attrs[n].val.clusterDim.x = cluster.x;
+    attrs[n].val.clusterDim.y = cluster.y;
+    attrs[n].val.clusterDim.z = cluster.z;
     ++n;
   }
   cfg.attrs = attrs;

@@ -238,7 +238,7 @@ GB_EXPORT int gb_embedding(const void* table, int table_dtype, const int32_t* id
                            int d, int vocab, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   return GB_DISPATCH_DTYPE(table_dtype, TT, [&]() -> int {
-    return gb::check_pdl_launch(gb::launch_pdl(embedding_kernel<TT>, dim3(T), dim3(256), 0, stream, 1,
+    return gb::check_pdl_launch(gb::launch_pdl(embedding_kernel<TT>, dim3(T), dim3(256), 0, stream, dim3(1, 1, 1),
                                                (const TT*)table, ids, out, d, vocab), "embedding");
   });
 }
@@ -250,9 +250,9 @@ GB_EXPORT int gb_rmsnorm(const float* x, const void* w, int w_dtype, float eps, 
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
       if (d % 4 == 0 && d <= 4096 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0)
-        return gb::check_pdl_launch(gb::launch_pdl(rmsnorm_vec_kernel<WT, OT>, dim3(n_rows), dim3(256), 0, stream, 1,
+        return gb::check_pdl_launch(gb::launch_pdl(rmsnorm_vec_kernel<WT, OT>, dim3(n_rows), dim3(256), 0, stream, dim3(1, 1, 1),
                                                    x, (const WT*)w, eps, (OT*)out, rows, d), "rmsnorm");
-      return gb::check_pdl_launch(gb::launch_pdl(rmsnorm_kernel<WT, OT>, dim3(n_rows), dim3(block), 0, stream, 1,
+      return gb::check_pdl_launch(gb::launch_pdl(rmsnorm_kernel<WT, OT>, dim3(n_rows), dim3(block), 0, stream, dim3(1, 1, 1),
                                                  x, (const WT*)w, eps, (OT*)out, rows, d), "rmsnorm");
     });
   });
@@ -273,7 +273,7 @@ GB_EXPORT int gb_rope_kv_append(const void* qkv, int in_dtype, int row_stride, v
   return GB_DISPATCH_DTYPE(in_dtype, IT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
       return gb::check_pdl_launch(
-          gb::launch_pdl(rope_kv_append_kernel<IT, OT>, dim3(T), dim3(block), 0, stream, 1, (const IT*)qkv,
+          gb::launch_pdl(rope_kv_append_kernel<IT, OT>, dim3(T), dim3(block), 0, stream, dim3(1, 1, 1), (const IT*)qkv,
                          row_stride, (OT*)q_out, (OT*)k_pool, (OT*)v_pool, positions, token_req, block_table,
                          table_width, Hq, Hkv, hd, inv_freq, interleaved, page_size),
           "rope_kv_append");

@@ -112,25 +112,6 @@ __device__ __forceinline__ float silu_gate_fast(float g, float u) {
   return g * __frcp_rn(1.0f + __expf(-g)) * u;
 }
 
-// ---- thread-block cluster helpers (split-K over distributed shared memory)
-__device__ __forceinline__ void cluster_arrive_wait() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// The address, in the cluster's shared window, of `local` in the CTA of rank `rank`.
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-  return r;
-}
-
-// Four bytes into the shared memory of another CTA of the cluster; they are counted on that CTA's
-// mbarrier when they have landed.
-__device__ __forceinline__ void st_async_f32(uint32_t remote_addr, uint32_t remote_bar, float v) {
-  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %2, [%1];"
-               ::"r"(remote_addr), "r"(remote_bar), "r"(__float_as_uint(v))
-               : "memory");
-}
-
 constexpr int C_THREADS = 192;   // warp 0: producer, warp 1: MMA issuer, warps 2-5: epilogue
 
 // Few tokens. rows_m / rows_n: valid rows of the MMA-row operand (the weights: output features)
@@ -769,7 +750,7 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ld
   const int per = (total_kb + split - 1) / split;
   split = (total_kb + per - 1) / per;            // no rank without K blocks
   return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(tiles_n, tiles_m, split), dim3(C_THREADS),
-                                             G::smem_bytes(split), stream, split, mm, mn, out, ldo, out_features,
+                                             G::smem_bytes(split), stream, dim3(1, 1, split), mm, mn, out, ldo, out_features,
                                              tokens, K, per),
                               "gemm_tc (cluster)");
 }
@@ -802,7 +783,7 @@ int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int
   const int tiles_m = (tokens + BM - 1) / BM, tiles_n = (weight_rows + BN - 1) / BN;
   const int total = tiles_m * tiles_n;
   const int grid = total < sm_count() ? total : sm_count();
-  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(grid), dim3(P_THREADS), G::SMEM_BYTES, stream, 1, mm, mn, out,
+  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(grid), dim3(P_THREADS), G::SMEM_BYTES, stream, dim3(1, 1, 1), mm, mn, out,
                                              ldo, tokens, out_features, K, tiles_m, tiles_n),
                               "gemm_tc (persistent)");
 }

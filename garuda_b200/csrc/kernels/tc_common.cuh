@@ -96,6 +96,26 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
+// ------------------------------------------------------------------ clusters
+__device__ __forceinline__ void cluster_arrive_wait() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address, in the cluster's shared window, of `local` in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+
+// Four bytes into the shared memory of another CTA of the cluster; they are counted on that CTA's
+// mbarrier when they have landed.
+__device__ __forceinline__ void st_async_f32(uint32_t remote_addr, uint32_t remote_bar, float v) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %2, [%1];"
+               ::"r"(remote_addr), "r"(remote_bar), "r"(__float_as_uint(v))
+               : "memory");
+}
+
+
 // ------------------------------------------------------------------ TMEM
 // Allocation is done by one whole warp; the base address lands in shared memory.
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {

@@ -14,7 +14,8 @@ import torch
 from ..csrc.build import load_kernel_lib, attention_lib_name
 
 _WAIT_NAMES = {1: "an operand tile never arrived (TMA)", 2: "a pipeline stage was never released",
-               3: "the accumulator never completed", 4: "copies in flight did not land while winding down"}
+               3: "the accumulator never completed", 4: "copies in flight did not land while winding down",
+               5: "a decode attention cluster never delivered its partial results"}
 
 
 class TensorCoreKernels:
@@ -33,6 +34,9 @@ class TensorCoreKernels:
     def check_errors(self) -> None:
         """Synchronises, and raises if a kernel gave up on a wait since the last check."""
         code = self.lib.gb_tc_error_check()
+        for lib in self._attn.values():
+            if lib.gb_attention_error_check():
+                code = code or 5
         if code:
             from .ops import KernelError
             raise KernelError("a tensor-core kernel gave up waiting: " + _WAIT_NAMES.get(code, f"code {code}"))
@@ -66,23 +70,21 @@ class TensorCoreKernels:
         if lib is None:
             lib = load_kernel_lib(attention_lib_name(head_dim))
             lib.gb_last_error.restype = ctypes.c_char_p
-            lib.gb_attention_mma.argtypes = ([c_void_p] * 7 + [c_int] + [c_void_p] * 3 + [c_int] * 4 + [c_float]
+            lib.gb_attention_mma.argtypes = ([c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 4 + [c_float]
                                              + [c_int] * 5 + [c_void_p])
             lib.gb_attention_mma.restype = c_int
-            lib.gb_attention_mma_scratch_floats.argtypes = [c_int, c_int, c_int]
-            lib.gb_attention_mma_scratch_floats.restype = ctypes.c_longlong
+            lib.gb_attention_error_check.restype = c_int
             self._attn[head_dim] = lib
         return lib
 
     @staticmethod
     def attention_splits(num_requests: int, kv_heads: int, max_kv_len: int) -> int:
-        """CTAs that share one decode request's keys: enough to fill the GPU twice
-        over; four tiles of 64 keys each where the context allows (a CTA asks for
-        four tiles at once), never less than one."""
+        """CTAs (one cluster, at most 8) that share one decode request's keys: enough
+        to fill the GPU, but no CTA with less than one round of four 64-key tiles
+        where that can be avoided."""
         tiles = max((max_kv_len + 63) // 64, 1)
         want = -(-2 * 148 // max(num_requests * kv_heads, 1))
-        want = max(want, -(-tiles // 4)) if num_requests * kv_heads * (-(-tiles // 4)) <= 8 * 148 else want
-        return max(1, min(want, tiles, 64))
+        return max(1, min(want, -(-tiles // 4), 8))
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale,
                         window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1) -> bool:
@@ -92,28 +94,11 @@ class TensorCoreKernels:
             return False
         lib = self._attention_lib(hd)
         g = Hq // Hkv
-        has_split = min_q_len * g <= 16
-        splits = self.attention_splits(num_requests, Hkv, max_kv_len) if has_split else 1
-        scratch = counters = None
-        if splits > 1:
-            n = lib.gb_attention_mma_scratch_floats(T, Hq, splits)
-            space = ws or self.ops.private_ws
-            scratch = space.get("attention_partial", (n,), torch.float32)
-            counters = space.get("attention_tickets", (num_requests * Hkv,), torch.int32, zero=True)
-        code = self._call_attention(lib, q, k_pool, v_pool, out, scratch, counters, block_table, cu_q, kv_lens,
-                                    token_req, T, num_requests, Hq, Hkv, scale, window, page_size,
-                                    max_q_len, min_q_len, splits)
-        kernels = (1 if has_split else 0) + (1 if max_q_len * g > 16 else 0)
-        self.ops._check(lib, code, "attention_mma", kernels)
+        has_decode = min_q_len * g <= 16
+        splits = self.attention_splits(num_requests, Hkv, max_kv_len) if has_decode else 1
+        code = lib.gb_attention_mma(
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), block_table.data_ptr(),
+            block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), T, num_requests, Hq, Hkv, float(scale),
+            int(window), int(page_size), int(max_q_len), int(min_q_len), int(splits), self.ops._stream())
+        self.ops._check(lib, code, "attention_mma", (1 if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
         return True
-
-    def _call_attention(self, lib, q, k_pool, v_pool, out, scratch, counters, block_table, cu_q, kv_lens, token_req,
-                        T, R, Hq, Hkv, scale, window, page_size, max_q_len, min_q_len, splits) -> int:
-        return lib.gb_attention_mma(
-            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
-            None if scratch is None else scratch.data_ptr(),
-            None if counters is None else counters.data_ptr(), block_table.data_ptr(),
-            block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), token_req.data_ptr(),
-            T, R, Hq, Hkv, float(scale), int(window), int(page_size), int(max_q_len), int(min_q_len),
-            int(splits),
-            self.ops._stream())
