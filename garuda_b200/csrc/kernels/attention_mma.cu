@@ -102,6 +102,13 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (about 2^-22 relative error; the result feeds a bfloat16 operand
+// and 32-bit sums). -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -161,10 +168,13 @@ struct WarpState {
 
 // One tile of 64 keys for one warp's 16 rows: S = Q K^T, scale and mask, running softmax in
 // 32-bit, O += P V. qf: the warp's query fragments; key0: position of the tile's first key;
-// row_pos / row_start: last and first key each of the thread's two rows may read.
+// row_pos / row_start: last and first key each of the thread's two rows may read; full: every key
+// of the tile is inside every row's range (no mask needed). The running maximum st.m is kept
+// unscaled (a raw dot product); the merges scale it.
 __device__ __forceinline__ void process_tile(WarpState& st, const uint32_t (&qf)[HD / 16][4],
                                              const __nv_bfloat16* ks, const __nv_bfloat16* vs, int key0,
-                                             const int (&row_pos)[2], const int (&row_start)[2], float scale_log2) {
+                                             const int (&row_pos)[2], const int (&row_start)[2], float scale_log2,
+                                             bool full) {
   const int lane = threadIdx.x & 31;
   float s[8][4];
 #pragma unroll
@@ -182,27 +192,35 @@ __device__ __forceinline__ void process_tile(WarpState& st, const uint32_t (&qf)
       mma_16816(s[2 * n2 + 1], qf[kk], b[2], b[3]);
     }
   }
+  // Mask (only where the tile is not wholly inside every row's range), then the running maximum of
+  // the raw dot products: the scale is positive, so it can wait until the exponent, where
+  // exp2(s * scale_log2 - m * scale_log2) is one multiply-add and one special-function op.
   float m_new[2] = {st.m[0], st.m[1]};
+  if (!full) {
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int j = key0 + n * 8 + (lane % 4) * 2 + (e & 1);
+        if (!(j >= row_start[i] && j <= row_pos[i])) s[n][e] = -INFINITY;
+      }
+  }
 #pragma unroll
   for (int n = 0; n < 8; ++n)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = e >> 1;
-      const int j = key0 + n * 8 + (lane % 4) * 2 + (e & 1);
-      const bool ok = j >= row_start[i] && j <= row_pos[i];
-      s[n][e] = ok ? s[n][e] * scale_log2 : -INFINITY;
-      m_new[i] = fmaxf(m_new[i], s[n][e]);
-    }
+    for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], s[n][e]);
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
     m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
   }
-  float corr[2], m_use[2], l_add[2] = {0.f, 0.f};
+  float corr[2], neg_m[2], l_add[2] = {0.f, 0.f};
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    m_use[i] = m_new[i] == -INFINITY ? 0.f : m_new[i];     // nothing valid yet: avoid inf - inf
-    corr[i] = st.m[i] == -INFINITY ? 0.f : exp2f(st.m[i] - m_use[i]);
+    const float m_use = m_new[i] == -INFINITY ? 0.f : m_new[i];     // nothing valid yet: avoid inf - inf
+    corr[i] = st.m[i] == -INFINITY ? 0.f : fast_exp2((st.m[i] - m_use) * scale_log2);
+    neg_m[i] = -m_use * scale_log2;
     st.m[i] = m_new[i];
   }
   uint32_t pf[4][4];
@@ -211,7 +229,7 @@ __device__ __forceinline__ void process_tile(WarpState& st, const uint32_t (&qf)
     float pr[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      pr[e] = exp2f(s[n][e] - m_use[e >> 1]);   // exp2(-inf) = 0 for masked keys
+      pr[e] = fast_exp2(fmaf(s[n][e], scale_log2, neg_m[e >> 1]));   // exp2(-inf) = 0 for masked keys
       l_add[e >> 1] += pr[e];
     }
     pf[n / 2][(n % 2) * 2 + 0] = pack_bf16(pr[0], pr[1]);
@@ -291,7 +309,10 @@ attention_tile_kernel(const Params p) {
       for (int kk = 0; kk < HD / 16; ++kk)
         ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane % 16)) * LD + kk * 16 + (lane / 16) * 8);
     }
-    process_tile(st, qf, ks, vs, tile * KT, row_pos, row_start, p.scale_log2);
+    // a tile needs no mask if it lies wholly before the first row's position and inside the last
+    // row's window
+    const bool full = (tile + 1) * KT - 1 <= pos0 && (p.window <= 0 || tile * KT >= hi + 1 - p.window);
+    process_tile(st, qf, ks, vs, tile * KT, row_pos, row_start, p.scale_log2, full);
     __syncthreads();  // the stage may be overwritten by the next iteration's loads
   }
   cp_async_wait<0>();
@@ -397,7 +418,7 @@ attention_decode_kernel(const Params p) {
     const int tile = base + warp;               // each warp takes one of the round's tiles
     if (tile < tile_end) {
       const __nv_bfloat16* ks = kv + warp * 2 * KT * LD;
-      process_tile(st, qf, ks, ks + KT * LD, tile * KT, row_pos, row_start, p.scale_log2);
+      process_tile(st, qf, ks, ks + KT * LD, tile * KT, row_pos, row_start, p.scale_log2, false);
     }
     __syncthreads();   // the slots are overwritten by the next round, or by the merge
   }
@@ -416,7 +437,7 @@ attention_decode_kernel(const Params p) {
       dst[n * 8 + (lane % 4) * 2 + 1] = st.o[n][2 * i + 1];
     }
     if (lane % 4 == 0) {
-      dst[HD] = st.m[i];
+      dst[HD] = st.m[i] * p.scale_log2;     // in units of the exponent, as the merges want it
       dst[HD + 1] = st.l[i];
     }
   }
@@ -535,6 +556,8 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "attention: %d query heads for %d kv heads", Hq, Hkv);
   const int g = Hq / Hkv;
   if (g > ROWS_TILE) return gb::fail(GB_UNSUPPORTED, "attention_mma: a group of %d query heads per kv head", g);
+  // the running maximum is taken before the scale is applied, which needs the scale to be positive
+  if (!(scale > 0.f)) return gb::fail(GB_UNSUPPORTED, "attention_mma: scale %g is not positive", (double)scale);
   num_splits = num_splits < 1 ? 1 : (num_splits > MAX_CLUSTER ? MAX_CLUSTER : num_splits);
   Params p;
   p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;

@@ -90,7 +90,7 @@ class TensorCoreKernels:
                         window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1) -> bool:
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
-        if hd % 16 or hd > 128 or Hq // Hkv > 64:
+        if hd % 16 or hd > 128 or Hq // Hkv > 64 or not scale > 0:
             return False
         lib = self._attention_lib(hd)
         g = Hq // Hkv
