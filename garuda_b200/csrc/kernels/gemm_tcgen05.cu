@@ -47,7 +47,35 @@ constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // many tokens: one CTA per SM, 
 constexpr int SMEM_BUDGET_SMALL = 110 * 1024;   // few tokens: pipeline of a CTA that may share its SM
 constexpr int SMEM_BUDGET_DUAL = 140 * 1024;    // few tokens, gate and up together
 
-enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2 };
+enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
+
+// What the query/key/value epilogue needs: the output features are (heads + 2 kv_heads) heads of
+// head_dim; query and key heads are rotated at the token's position (garuda/src/simd/mod.rs:196-206,
+// angle = (float)pos * inv_freq[i] in 32-bit), queries go to q_out, rotated keys and raw values into
+// their pages (garuda/src/llama/mod.rs:784-791). head_dim divides 128, so no head straddles a tile.
+struct RopeArgs {
+  __nv_bfloat16* q_out;          // [T, heads, head_dim]
+  __nv_bfloat16* k_pool;         // [pages, kv_heads, page_size, head_dim]
+  __nv_bfloat16* v_pool;
+  const int32_t* positions;      // [T]
+  const int32_t* token_req;      // [T]
+  const int32_t* block_table;    // [R, table_width]
+  const float* inv_freq;         // [head_dim / 2], or null: no rotation
+  int table_width, heads, kv_heads, head_dim, interleaved, page_size;
+};
+
+// Where feature `head`, channel d of the token at `pos` (request row `req`) is stored; null if the
+// position has no page.
+__device__ __forceinline__ __nv_bfloat16* rope_destination(const RopeArgs& ra, int token, int req, int pos,
+                                                           int head, int d) {
+  if (head < ra.heads) return ra.q_out + ((size_t)token * ra.heads + head) * ra.head_dim + d;
+  const int page = ra.block_table[(size_t)req * ra.table_width + pos / ra.page_size];
+  if (page < 0) return nullptr;
+  const bool is_k = head < ra.heads + ra.kv_heads;
+  const int kvh = head - ra.heads - (is_k ? 0 : ra.kv_heads);
+  return (is_k ? ra.k_pool : ra.v_pool) +
+         (((size_t)page * ra.kv_heads + kvh) * ra.page_size + pos % ra.page_size) * ra.head_dim + d;
+}
 
 __device__ int g_error_word;
 
@@ -122,7 +150,8 @@ constexpr int C_THREADS = 192;   // warp 0: producer, warp 1: MMA issuer, warps 
 template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(C_THREADS, 1)
 gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
-                       OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int kb_per_rank) {
+                       OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int kb_per_rank,
+                       const RopeArgs ra) {
   constexpr bool DUAL_M = false;
   using G = Geometry<BN, false, false, true>;
   constexpr int STAGES = G::STAGES;
@@ -323,7 +352,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         // SiLU-gate: rows 0-63 of the tile are gate rows, rows 64-127 the up rows of the same 64
         // features. The up half hands its values over through shared memory (the pipeline's, which
         // is idle by now).
-        float* xch = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)));   // [16][64]
+        float* xch = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)));   // [16][64 or 128]
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
           float v[16];
@@ -351,6 +380,36 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");      // before the next chunk reuses the buffer
+          } else if (EPI == EPI_ROPE) {
+            // A rotation pairs two rows of the tile (channels i and i + head_dim / 2 of a head, or
+            // 2i and 2i + 1): every thread shows its values, then computes its own rotated channel.
+#pragma unroll
+            for (int j = 0; j < 16; ++j) xch[j * BM + row_in_tile] = v[j];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (row < rows_m) {
+              const int hd = ra.head_dim, half = hd >> 1;
+              const int head = row / hd, d = row % hd;
+              const bool rotate = ra.inv_freq != nullptr && head < ra.heads + ra.kv_heads;
+              const bool low = ra.interleaved ? (d & 1) == 0 : d < half;
+              const int partner = ra.interleaved ? (row_in_tile ^ 1) : (low ? row_in_tile + half : row_in_tile - half);
+              const float freq = rotate ? ra.inv_freq[ra.interleaved ? d >> 1 : d % half] : 0.f;
+#pragma unroll 4
+              for (int j = 0; j < 16; ++j) {
+                const int col = n0 + c + j;      // token
+                if (col >= rows_n) break;
+                const int pos = ra.positions[col];
+                float x = v[j];
+                if (rotate) {
+                  float sn, cs;
+                  sincosf((float)pos * freq, &sn, &cs);
+                  const float other = xch[j * BM + partner];
+                  x = low ? x * cs - other * sn : other * sn + x * cs;
+                }
+                __nv_bfloat16* dst = rope_destination(ra, col, ra.token_req[col], pos, head, d);
+                if (dst) *dst = __float2bfloat16_rn(x);
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
           } else if (row < rows_m) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -416,7 +475,7 @@ template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
                           OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m,
-                          int tiles_n) {
+                          int tiles_n, const RopeArgs ra) {
   constexpr bool DUAL = false;
   using G = Geometry<BN, false, false, false>;
   constexpr int STAGES = G::STAGES;
@@ -548,7 +607,61 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
       tc_fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + as * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      if (EPI == EPI_SWIGLU) {
+      if (EPI == EPI_ROPE) {
+        // This thread holds one token's row: whole heads, so both channels of every rotation pair.
+        const int hd = ra.head_dim, half = hd >> 1;
+        const bool token_ok = row < rows_m;
+        const int pos = token_ok ? ra.positions[row] : 0;
+        const int req = token_ok ? ra.token_req[row] : 0;
+#pragma unroll 1
+        for (int hc = 0; hc < BN && n0 + hc < rows_n; hc += hd) {
+          const int head = (n0 + hc) / hd;
+          const bool rotate = ra.inv_freq != nullptr && head < ra.heads + ra.kv_heads;
+          __nv_bfloat16* dst = token_ok ? rope_destination(ra, row, req, pos, head, 0) : nullptr;
+          const bool split_halves = rotate && !ra.interleaved && half >= 16;
+#pragma unroll 1
+          for (int dd = 0; dd < (split_halves ? half : hd); dd += 16) {
+            uint32_t ra_[16], rb_[16];
+            tmem_ld_16(taddr + hc + dd, ra_);
+            if (split_halves) tmem_ld_16(taddr + hc + half + dd, rb_);
+            tmem_ld_wait();
+            if (!dst) continue;
+            float a[16], b[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              a[j] = __uint_as_float(ra_[j]);
+              b[j] = split_halves ? __uint_as_float(rb_[j]) : 0.f;
+            }
+            if (split_halves) {
+              // channels dd .. dd + 15 pair with half + dd ..
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float sn, cs;
+                sincosf((float)pos * ra.inv_freq[dd + j], &sn, &cs);
+                const float x = a[j], y = b[j];
+                a[j] = x * cs - y * sn;
+                b[j] = x * sn + y * cs;
+              }
+              epilogue_store16<__nv_bfloat16>(dst + dd, a, true);
+              epilogue_store16<__nv_bfloat16>(dst + half + dd, b, true);
+            } else {
+              if (rotate) {
+                // pairs inside the chunk: (2k, 2k + 1), or for a head of 16 channels (k, k + 8)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  const int ia = ra.interleaved ? 2 * k : k, ib = ra.interleaved ? 2 * k + 1 : k + 8;
+                  float sn, cs;
+                  sincosf((float)pos * ra.inv_freq[ra.interleaved ? (dd >> 1) + k : k], &sn, &cs);
+                  const float x = a[ia], y = a[ib];
+                  a[ia] = x * cs - y * sn;
+                  a[ib] = x * sn + y * cs;
+                }
+              }
+              epilogue_store16<__nv_bfloat16>(dst + dd, a, true);
+            }
+          }
+        }
+      } else if (EPI == EPI_SWIGLU) {
         // columns [128 q, 128 q + 64) of the tile are gate values, the next 64 the up values of
         // the same features: feature = 64 * (packed row / 128) + offset
 #pragma unroll 1
@@ -732,7 +845,7 @@ int pick_cluster_size(Kernel kernel, int* active, SmemFn smem_for, int tiles, in
 // twice the output features); out_features: columns of the output.
 template <int BN, int EPI, typename OT>
 int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int weight_rows, int out_features,
-                   int tokens, int K, cudaStream_t stream) {
+                   int tokens, int K, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
   using G = Geometry<BN, false, false, true>;
   auto kernel = gemm_tc_cluster_kernel<BN, EPI, OT>;
   static bool configured = false;
@@ -751,7 +864,7 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ld
   split = (total_kb + per - 1) / per;            // no rank without K blocks
   return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(tiles_n, tiles_m, split), dim3(C_THREADS),
                                              G::smem_bytes(split), stream, dim3(1, 1, split), mm, mn, out, ldo, out_features,
-                                             tokens, K, per),
+                                             tokens, K, per, ra),
                               "gemm_tc (cluster)");
 }
 
@@ -771,7 +884,7 @@ int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtens
 
 template <int BN, int EPI, typename OT>
 int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int tokens, int weight_rows,
-                      int out_features, int K, cudaStream_t stream) {
+                      int out_features, int K, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
   using G = Geometry<BN, false, false, false>;
   auto kernel = gemm_tc_persistent_kernel<BN, EPI, OT>;
   static bool configured = false;
@@ -784,7 +897,7 @@ int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int
   const int total = tiles_m * tiles_n;
   const int grid = total < sm_count() ? total : sm_count();
   return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(grid), dim3(P_THREADS), G::SMEM_BYTES, stream, dim3(1, 1, 1), mm, mn, out,
-                                             ldo, tokens, out_features, K, tiles_m, tiles_n),
+                                             ldo, tokens, out_features, K, tiles_m, tiles_n, ra),
                               "gemm_tc (persistent)");
 }
 
@@ -867,4 +980,42 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   if (width == 256) GB_PERSISTENT(256);
   GB_PERSISTENT(128);
 #undef GB_PERSISTENT
+}
+
+// The query/key/value product with the rotation and the cache write in its epilogue:
+// x [Mx, K] times w [(heads + 2 kv_heads) * head_dim, K]^T; rotated queries to q_out [Mx, heads,
+// head_dim], rotated keys and raw values into their pages (all bfloat16). inv_freq null: no rotation.
+// head_dim must divide 128 (so that no head straddles a tile); returns GB_UNSUPPORTED otherwise.
+GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* q_out, void* k_pool, void* v_pool,
+                             const int32_t* positions, const int32_t* token_req, const int32_t* block_table,
+                             int table_width, int heads, int kv_heads, int head_dim, const float* inv_freq,
+                             int interleaved, int page_size, cudaStream_t stream) {
+  const int Nw = (heads + 2 * kv_heads) * head_dim;
+  if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc: needs K a multiple of 8 and 16-byte aligned operands (K = %d)", K);
+  if (head_dim < 16 || 128 % head_dim || head_dim % 16)
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc_qkv: head_dim %d does not divide 128", head_dim);
+  if (kv_heads > 0 && (!k_pool || !v_pool || !block_table || page_size < 1))
+    return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_qkv: kv heads given without a cache to store them in");
+  RopeArgs ra;
+  ra.q_out = (__nv_bfloat16*)q_out; ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool;
+  ra.positions = positions; ra.token_req = token_req; ra.block_table = block_table; ra.inv_freq = inv_freq;
+  ra.table_width = table_width; ra.heads = heads; ra.kv_heads = kv_heads; ra.head_dim = head_dim;
+  ra.interleaved = interleaved; ra.page_size = page_size;
+  CUtensorMap mm, mn;
+  int rc;
+  __nv_bfloat16* none = nullptr;
+  if (Mx <= 64) {
+    const int bn = Mx <= 16 ? 16 : Mx <= 32 ? 32 : 64;
+    if ((rc = tensor_map_2d(w, Nw, K, BM, &mm))) return rc;
+    if ((rc = tensor_map_2d(x, Mx, K, bn, &mn))) return rc;
+    if (bn == 16) return launch_cluster<16, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Nw, Nw, Mx, K, stream, ra);
+    if (bn == 32) return launch_cluster<32, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Nw, Nw, Mx, K, stream, ra);
+    return launch_cluster<64, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Nw, Nw, Mx, K, stream, ra);
+  }
+  if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
+  const int width = pick_tile_width(Mx, Nw);
+  if ((rc = tensor_map_2d(w, Nw, K, width, &mn))) return rc;
+  if (width == 256) return launch_persistent<256, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Mx, Nw, Nw, K, stream, ra);
+  return launch_persistent<128, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Mx, Nw, Nw, K, stream, ra);
 }

@@ -201,6 +201,30 @@ class CudaOps:
         self._check(self.core, self.core.gb_residual_add(
             x.data_ptr(), y.data_ptr(), _tag(y, "residual_add y"), x.numel(), self._stream()), "residual_add")
 
+    def qkv_rope_append(self, ctx, h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
+                        heads, kv_heads, head_dim, rotary, page_size):
+        """``h @ w_qkv^T``, split into heads; queries and keys rotated (``rotary`` None:
+        not), queries to ``q_out [T, heads, head_dim]``, keys and values into their
+        pages. One kernel where the tensor-core product takes the shape, else the
+        product in 32-bit followed by ``rope_kv_append``."""
+        self._on_device(h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table)
+        T = h.shape[0]
+        _need(w_qkv.shape == ((heads + 2 * kv_heads) * head_dim, h.shape[1]), "qkv_rope_append: weight shape")
+        _need(q_out.is_contiguous() and q_out.shape == (T, heads, head_dim), "qkv_rope_append: q_out shape")
+        if kv_heads:
+            _need(k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.dtype == q_out.dtype
+                  and tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim), "qkv_rope_append: pool shape")
+            _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "qkv_rope_append: block table")
+        _need(positions.dtype == torch.int32 and token_req.dtype == torch.int32, "qkv_rope_append: int32 indices")
+        if self.tc is not None and self.tc.qkv_rope_append(h, w_qkv, q_out, k_pool, v_pool, positions, token_req,
+                                                           block_table, heads, kv_heads, head_dim, rotary,
+                                                           page_size):
+            return
+        qkv = ctx.ws.get("qkv", (T, w_qkv.shape[0]), torch.float32)
+        self.linear(h, w_qkv, qkv)
+        self.rope_kv_append(qkv, q_out, k_pool, v_pool, positions, token_req, block_table, heads, kv_heads,
+                            head_dim, rotary, page_size)
+
     def rope_kv_append(self, qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
                        heads, kv_heads, head_dim, rotary, page_size):
         """Split ``qkv [T, (heads + 2 kv_heads) head_dim]``, rotate queries and keys

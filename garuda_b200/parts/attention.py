@@ -69,21 +69,27 @@ class PagedAttention(Mixer):
         T = h.shape[0]
         writes = cache.writes and not self.reads_shared_cache
         cols = self.q_dim + (2 * self.kv_dim if writes else 0)
-        qkv = ws.get("qkv", (T, cols), torch.float32)
         # a call that reads another call's cache projects queries only (the first rows)
-        ops.linear(h, self.w_qkv if self.w_qkv.shape[0] == cols else self.w_qkv[:cols], qkv)
+        w_qkv = self.w_qkv if self.w_qkv.shape[0] == cols else self.w_qkv[:cols]
         q = ws.get("q_heads", (T, self.heads, self.head_dim), self.dtype)
         rotary = self.position.rotary
-        if rotary is None and self.position.changes_vectors:
+        kv_heads = self.kv_heads if writes else 0
+        if rotary is not None or not self.position.changes_vectors:
+            # the product, the rotation and the write into the pages, fused where the kernels allow
+            ops.qkv_rope_append(ctx, h, w_qkv, q, cache.k if writes else None, cache.v if writes else None,
+                                b.positions, b.token_req, cache.block_table, self.heads, kv_heads,
+                                self.head_dim, rotary, cache.page_size)
+        else:
             # an encoding the fused kernel does not know: let the part change q and k in place
+            qkv = ws.get("qkv", (T, cols), torch.float32)
+            ops.linear(h, w_qkv, qkv)
             qv = qkv[:, :self.q_dim].unflatten(1, (self.heads, self.head_dim))
             kv = (qkv[:, self.q_dim:self.q_dim + self.kv_dim].unflatten(1, (self.kv_heads, self.head_dim))
                   if writes else None)
             self.position.apply(ctx, qv, kv, b.positions)
-        ops.rope_kv_append(qkv, q, cache.k if writes else None, cache.v if writes else None,
-                           b.positions, b.token_req, cache.block_table,
-                           self.heads, self.kv_heads if writes else 0, self.head_dim,
-                           rotary, cache.page_size)
+            ops.rope_kv_append(qkv, q, cache.k if writes else None, cache.v if writes else None,
+                               b.positions, b.token_req, cache.block_table, self.heads, kv_heads,
+                               self.head_dim, None, cache.page_size)
         out = ws.get("attn_ctx", (T, self.q_dim), self.dtype)
         ops.paged_attention(q, cache.k, cache.v, cache.block_table, b.cu_q, b.kv_lens, b.token_req, out,
                             self.scale, self.window or 0, cache.page_size,

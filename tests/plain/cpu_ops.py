@@ -83,6 +83,13 @@ class CpuOps:
     def rope_inplace(self, x, positions, theta, interleaved):
         x.copy_(self._rotate(x.clone(), positions, theta, interleaved))
 
+    # garuda/src/llama/mod.rs:743-757 (the projections), then rotate and store
+    def qkv_rope_append(self, ctx, h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
+                        heads, kv_heads, head_dim, rotary, page_size):
+        qkv = h.float() @ w_qkv.float().t()
+        self.rope_kv_append(qkv, q_out, k_pool, v_pool, positions, token_req, block_table, heads, kv_heads,
+                            head_dim, rotary, page_size)
+
     # garuda/src/llama/mod.rs:784-791 (rotate, then store the rotated key and the raw value)
     def rope_kv_append(self, qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
                        heads, kv_heads, head_dim, rotary, page_size):

@@ -156,6 +156,47 @@ def test_rotate_and_store(ops, interleaved, dtype):
     close(xd, ref, 2e-6, "in place")
 
 
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("Hq,Hkv,hd,d", [(4, 2, 16, 64), (3, 1, 32, 96), (32, 4, 64, 256), (2, 2, 128, 72), (6, 3, 48, 72)])
+@pytest.mark.parametrize("T", [1, 11, 70, 200])
+def test_fused_projection_rotation_and_cache_write(ops, interleaved, Hq, Hkv, hd, d, T):
+    """The query/key/value product with rotation and page write in its epilogue
+    against the plain product followed by the plain rotate-and-store."""
+    from garuda_b200.parts.rotary import RotaryParams
+    from garuda_b200.engine.batch import Workspace
+
+    class Ctx:
+        ws = Workspace("cuda:0")
+
+    g = torch.Generator().manual_seed(T + hd)
+    rot = RotaryParams(10000.0, hd, interleaved)
+    page = 8
+    h = (torch.randn(T, d, generator=g) * 0.5).bfloat16()
+    w = (torch.randn((Hq + 2 * Hkv) * hd, d, generator=g) * 0.2).bfloat16()
+    # three requests share the tokens; positions start at different offsets
+    starts = [0, 37, 100]
+    req = torch.tensor([i % 3 for i in range(T)], dtype=torch.int32).sort().values
+    positions = torch.zeros(T, dtype=torch.int32)
+    seen = [0, 0, 0]
+    for t in range(T):
+        r = int(req[t])
+        positions[t] = starts[r] + seen[r]
+        seen[r] += 1
+    width = (max(int(positions.max()) + 1, 1) + page - 1) // page + 1
+    perm = torch.randperm(3 * width, generator=g).int().view(3, width)
+    npages = 3 * width
+    for rotary in (rot, None):
+        k_ref, v_ref = torch.zeros(npages, Hkv, page, hd), torch.zeros(npages, Hkv, page, hd)
+        q_ref = torch.zeros(T, Hq, hd)
+        cpu.qkv_rope_append(None, h, w, q_ref, k_ref, v_ref, positions, req, perm, Hq, Hkv, hd, rotary, page)
+        k = torch.zeros(npages, Hkv, page, hd, dtype=torch.bfloat16, device="cuda")
+        v = torch.zeros_like(k)
+        q = torch.zeros(T, Hq, hd, dtype=torch.bfloat16, device="cuda")
+        ops.qkv_rope_append(Ctx, dev(h), dev(w), q, k, v, dev(positions), dev(req), dev(perm), Hq, Hkv, hd, rotary, page)
+        close(q, q_ref, 1e-2, "q"), close(k, k_ref, 1e-2, "k"), close(v, v_ref, 1e-2, "v")
+    ops.tc.check_errors()
+
+
 def _attention_case(Hq, Hkv, hd, page, reqs, window, dtype, seed=0):
     g = torch.Generator().manual_seed(seed)
     R, T = len(reqs), sum(q for _, q in reqs)
