@@ -44,7 +44,10 @@ constexpr int BK = 64;    // bf16 per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int SMEM_LIMIT = 227 * 1024;          // most dynamic shared memory a CTA can have
 constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // many tokens: one CTA per SM, all of it pipeline
-constexpr int SMEM_BUDGET_SMALL = 110 * 1024;   // few tokens: pipeline of a CTA that may share its SM
+#ifndef GB_SMEM_BUDGET_SMALL_KB
+#define GB_SMEM_BUDGET_SMALL_KB 110
+#endif
+constexpr int SMEM_BUDGET_SMALL = GB_SMEM_BUDGET_SMALL_KB * 1024;   // few tokens: pipeline depth that the stream of weights needs
 constexpr int SMEM_BUDGET_DUAL = 140 * 1024;    // few tokens, gate and up together
 
 enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
@@ -118,7 +121,9 @@ struct Geometry {
   static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
   // bytes one CTA of a cluster sends to the leader: its whole accumulator
   static constexpr int PARTIAL_BYTES = ACCUMULATORS * BN * BM * 4;
-  static constexpr int MAX_CLUSTER_RAW = 1 + (SMEM_LIMIT - 1024 - PIPE_BYTES) / PARTIAL_BYTES;
+  // statically declared shared memory (barriers, the rotation's tables) comes out of the same limit
+  static constexpr int STATIC_RESERVE = 18 * 1024;
+  static constexpr int MAX_CLUSTER_RAW = 1 + (SMEM_LIMIT - STATIC_RESERVE - 1024 - PIPE_BYTES) / PARTIAL_BYTES;
   static constexpr int MAX_CLUSTER = !TRANS ? 1 : (MAX_CLUSTER_RAW < 8 ? MAX_CLUSTER_RAW : 8);
   // + slack to align the tiles to 1024 B
   static constexpr int smem_bytes(int cluster) { return PIPE_BYTES + 1024 + (cluster - 1) * PARTIAL_BYTES; }
@@ -292,6 +297,39 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     const int row_in_tile = quarter * 32 + lane;
     const int row = m0 + row_in_tile;                     // output feature
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    // Rotation with few tokens: the epilogue threads of the leading CTA fill, before anything else,
+    // a table of cosines and sines [token][frequency] and each token's row in the pools, sharing
+    // the work (a thread alone would compute every angle of its feature: thousands of dependent
+    // instructions). Positions, request rows and block tables are written by copies that end
+    // before the first kernel of a chain starts, so they are read without waiting for the kernel
+    // in front. The table is complete for every thread after the first barrier of the loop below.
+    constexpr bool ROPE_EARLY = EPI == EPI_ROPE && BN <= 32;
+    constexpr int NE = ROPE_EARLY ? BN : 1;
+    __shared__ float rope_cs[NE][64], rope_sn[NE][64];     // head_dim <= 128
+    __shared__ long long rope_slot[NE];                     // element offset of the token's row, head 0; -1: no page
+    if (ROPE_EARLY && rank == 0) {
+      const int t = (int)threadIdx.x - 64;
+      const int half = ra.head_dim >> 1, lg = 31 - __clz(half);      // head_dim divides 128: a power of two
+      for (int e = t; e < BN * half; e += 128) {
+        const int j = e >> lg, fi = e & (half - 1);
+        float sn = 0.f, cs = 1.f;
+        if (ra.inv_freq != nullptr && n0 + j < rows_n)
+          sincosf((float)ra.positions[n0 + j] * ra.inv_freq[fi], &sn, &cs);
+        rope_cs[j][fi] = cs;
+        rope_sn[j][fi] = sn;
+      }
+      if (t < BN) {
+        long long slot = -1;
+        const int col = n0 + t;
+        if (col < rows_n && ra.kv_heads > 0) {
+          const int pos = ra.positions[col];
+          const int page = ra.block_table[(size_t)ra.token_req[col] * ra.table_width + pos / ra.page_size];
+          if (page >= 0) slot = (((long long)page * ra.kv_heads) * ra.page_size + pos % ra.page_size) * ra.head_dim;
+        }
+        rope_slot[t] = slot;
+      }
+    }
+    if (rank == 0) GB_STAMP_E(5);
     float old[EPI == EPI_ACCUMULATE ? BN : 1];
     if (rank == 0) {
       gb::pdl_wait();
@@ -302,6 +340,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
           old[j] = (row < rows_m && n0 + j < rows_n) ? gb::to_float<OT>(out[(size_t)(n0 + j) * ldo + row]) : 0.f;
       }
     }
+    GB_STAMP_E(4);
     bool have = mbar_wait(smem_u32(&accum_bar), 0);
     if (!have && lane == 0) atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
     have = have && !*(volatile int*)&abort_s;
@@ -392,7 +431,26 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               const bool rotate = ra.inv_freq != nullptr && head < ra.heads + ra.kv_heads;
               const bool low = ra.interleaved ? (d & 1) == 0 : d < half;
               const int partner = ra.interleaved ? (row_in_tile ^ 1) : (low ? row_in_tile + half : row_in_tile - half);
-              const float freq = rotate ? ra.inv_freq[ra.interleaved ? d >> 1 : d % half] : 0.f;
+              const float freq = rotate && !ROPE_EARLY ? ra.inv_freq[ra.interleaved ? d >> 1 : d % half] : 0.f;
+              if (ROPE_EARLY) {
+                const int fi = ra.interleaved ? d >> 1 : d & (half - 1);
+                const bool is_q = head < ra.heads, is_k = head < ra.heads + ra.kv_heads;
+                __nv_bfloat16* base = is_q ? ra.q_out + row
+                                           : (is_k ? ra.k_pool : ra.v_pool) +
+                                                 (size_t)(head - ra.heads - (is_k ? 0 : ra.kv_heads)) * ra.page_size * hd + d;
+                const size_t q_stride = (size_t)ra.heads * hd;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int e = ROPE_EARLY ? c + j : 0;
+                  const int col = n0 + c + j;
+                  const float other = xch[j * BM + partner];
+                  const float cs = rope_cs[e][fi], sn = rope_sn[e][fi];
+                  const float x = !rotate ? v[j] : low ? v[j] * cs - other * sn : other * sn + v[j] * cs;
+                  const long long slot = rope_slot[e];
+                  if (col < rows_n && (is_q || slot >= 0))
+                    base[is_q ? (size_t)col * q_stride : (size_t)slot] = __float2bfloat16_rn(x);
+                }
+              } else
 #pragma unroll 4
               for (int j = 0; j < 16; ++j) {
                 const int col = n0 + c + j;      // token
