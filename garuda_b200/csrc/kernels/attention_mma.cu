@@ -114,28 +114,52 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Keys [tile_start, tile_start + KT) of one kv head into shared memory, 16 bytes
-// per copy; keys outside [lo, hi] or without a page become zeros. Two threads
-// share a key row, so each thread looks one page up per tile.
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const Params& p,
-                                             const int32_t* table, int kvh, int tile_start, int lo, int hi) {
+// One warp copies NR key rows (keys first_key ..., shared-memory rows first_row ...) of one kv head,
+// keys and values, 16 bytes per copy. Consecutive lanes copy consecutive chunks, so that one
+// instruction of the warp reads whole 128-byte lines; a row's place in the pool is looked up by
+// one lane and handed round with a shuffle. Keys outside [lo, hi] or without a page become zeros.
+template <int NR>
+__device__ __forceinline__ void warp_load_rows(__nv_bfloat16* ks, __nv_bfloat16* vs, const Params& p,
+                                               const int32_t* table, int kvh, int first_key, int first_row,
+                                               int lo, int hi) {
   constexpr int CHUNKS = HD / 8;  // 16-byte chunks per row
-  static_assert(KT * 2 == THREADS && CHUNKS % 2 == 0, "two threads per key row");
-  const int row = threadIdx.x >> 1, first = (threadIdx.x & 1) * (CHUNKS / 2);
-  const int j = tile_start + row;
-  bool valid = j >= lo && j <= hi;
-  size_t off = 0;
-  if (valid) {
-    const int page = table[j / p.page_size];
-    valid = page >= 0;
-    if (valid) off = (((size_t)page * p.Hkv + kvh) * p.page_size + (j % p.page_size)) * HD;
+  constexpr int ITERS = NR * CHUNKS / 32, LOOKUPS = (NR + 31) / 32;
+  static_assert(NR * CHUNKS % 32 == 0, "whole warp instructions");
+  constexpr uint32_t NONE = 0xFFFFFFFFu;
+  const int lane = threadIdx.x & 31;
+  uint32_t where[LOOKUPS];        // the row's offset in the pool in units of 16 bytes
+#pragma unroll
+  for (int h = 0; h < LOOKUPS; ++h) {
+    const int j = first_key + lane + 32 * h;
+    where[h] = NONE;
+    if (lane + 32 * h < NR && j >= lo && j <= hi) {
+      const int page = table[j / p.page_size];
+      if (page >= 0) where[h] = (uint32_t)((((size_t)page * p.Hkv + kvh) * p.page_size + (j % p.page_size)) * CHUNKS);
+    }
   }
 #pragma unroll
-  for (int c = 0; c < CHUNKS / 2; ++c) {
-    const int ch = first + c;
-    cp_async_16(ks + row * LD + ch * 8, p.k_pool + off + ch * 8, valid);
-    cp_async_16(vs + row * LD + ch * 8, p.v_pool + off + ch * 8, valid);
+  for (int it = 0; it < ITERS; ++it) {
+    const int c = it * 32 + lane, row = c / CHUNKS, ch = c % CHUNKS;
+    uint32_t w = __shfl_sync(0xffffffffu, where[0], row & 31);
+#pragma unroll
+    for (int h = 1; h < LOOKUPS; ++h) {
+      const uint32_t other = __shfl_sync(0xffffffffu, where[h], row & 31);
+      if (row >> 5 == h) w = other;
+    }
+    const bool valid = w != NONE;
+    const size_t off = valid ? ((size_t)w + ch) * 8 : 0;
+    cp_async_16(ks + (first_row + row) * LD + ch * 8, p.k_pool + off, valid);
+    cp_async_16(vs + (first_row + row) * LD + ch * 8, p.v_pool + off, valid);
   }
+}
+
+// Keys [tile_start, tile_start + KT) of one kv head into shared memory by the whole CTA: each of
+// the four warps copies a quarter of the rows.
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const Params& p,
+                                             const int32_t* table, int kvh, int tile_start, int lo, int hi) {
+  static_assert(KT == 64 && THREADS == 128, "four warps, sixteen rows each");
+  const int warp = threadIdx.x >> 5;
+  warp_load_rows<16>(ks, vs, p, table, kvh, tile_start + 16 * warp, 16 * warp, lo, hi);
 }
 
 // `rows` query rows (row = token_local * g + head_of_group) into shared memory; the rest zeros.
@@ -331,14 +355,16 @@ attention_tile_kernel(const Params p) {
 }
 
 // ------------------------------------------------------------------ DECODE
-// grid (ranks, Hkv, R), the `ranks` CTAs along x forming one cluster.
+// grid (ranks, Hkv, R), the `ranks` CTAs along x forming one cluster. Every warp walks its own
+// tiles (the CTA's tiles w, w + 4, ...) through a ring of `stages` slots of its own, so that no
+// warp waits for another before the merge and the next tile is on its way while one is computed.
 __global__ void __launch_bounds__(THREADS)
-attention_decode_kernel(const Params p) {
+attention_decode_kernel(const Params p, const int stages) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [ROWS_DECODE][LD]
-  __nv_bfloat16* kv = qs + ROWS_DECODE * LD;                        // SLOTS x (K, V) x [KT][LD]
-  float* red = reinterpret_cast<float*>(kv);                        // after the last round: [4 warps][16][RS]
-  float* parts = reinterpret_cast<float*>(kv + SLOTS * 2 * KT * LD);  // rank 0: [ranks - 1][16][RS] received
+  __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [4 warps][stages] x (K, V) x [KT][LD]
+  float* red = reinterpret_cast<float*>(kv);                        // after the last tile: [4 warps][16][RS]
+  float* mine = red + 4 * ROWS_DECODE * RS;                         // this CTA's merged rows: [16][RS]
+  float* parts = reinterpret_cast<float*>(kv + (size_t)stages * 4 * 2 * KT * LD);  // rank 0: [ranks - 1][16][RS]
   __shared__ __align__(8) uint64_t part_bar;
 
   GB_STAMP(0);
@@ -357,7 +383,7 @@ attention_decode_kernel(const Params p) {
     mbar_init(smem_u32(&part_bar), 1);
     fence_barrier_init();
     if (rank == 0 && ranks > 1)
-      mbar_arrive_expect_tx(smem_u32(&part_bar), (uint32_t)(ranks - 1) * ROWS_DECODE * RS * 4);
+      mbar_arrive_expect_tx(smem_u32(&part_bar), (uint32_t)(ranks - 1) * nrows * RS * 4);
   }
   __syncthreads();
   if (ranks > 1) cluster_arrive_wait();      // rank 0's barrier is armed before anyone sends to it
@@ -371,6 +397,7 @@ attention_decode_kernel(const Params p) {
   const int per = (total + ranks - 1) / ranks;
   const int tile_begin = first_tile + rank * per;
   const int tile_end = min(hi / KT + 1, tile_begin + per);
+  const int mine_n = tile_begin + warp < tile_end ? (tile_end - tile_begin - warp + 3) / 4 : 0;   // this warp's tiles
 
   int row_pos[2], row_start[2];
 #pragma unroll
@@ -379,100 +406,92 @@ attention_decode_kernel(const Params p) {
     row_pos[i] = row < nrows ? pos0 + row / p.g : -1;
     row_start[i] = (row < nrows && p.window > 0) ? max(0, row_pos[i] + 1 - p.window) : 0;
   }
-  WarpState st;
-  st.reset();
-  uint32_t qf[HD / 16][4];
-  bool waited = false;
-  for (int base = tile_begin; base < tile_end; base += SLOTS) {
-    // Keys and values of earlier steps are final: in the first round their tiles are asked for
-    // before waiting for the kernels in front, so that they arrive while those still run.
-    if (!waited) {
-      for (int d = 0; d < SLOTS; ++d) {
-        const int tile = base + d;
-        if (tile < tile_end && (tile + 1) * KT <= pos0) {
-          __nv_bfloat16* kd = kv + d * 2 * KT * LD;
-          load_kv_tile(kd, kd + KT * LD, p, table, kvh, tile * KT, lo, hi);
-        }
-      }
-      gb::pdl_wait();
-      GB_STAMP(2);
-      load_queries(qs, p, q_begin, kvh, nrows, ROWS_DECODE);
-    }
-    for (int d = 0; d < SLOTS; ++d) {
-      const int tile = base + d;
-      if (tile < tile_end && (waited || (tile + 1) * KT > pos0)) {
-        __nv_bfloat16* kd = kv + d * 2 * KT * LD;
-        load_kv_tile(kd, kd + KT * LD, p, table, kvh, tile * KT, lo, hi);
-      }
+  __nv_bfloat16* ring = kv + (size_t)warp * stages * 2 * KT * LD;
+  auto issue = [&](int i) {    // the warp's i-th tile into its slot; one group per call, even when empty
+    if (i < mine_n) {
+      __nv_bfloat16* kd = ring + (size_t)(i % stages) * 2 * KT * LD;
+      warp_load_rows<KT>(kd, kd + KT * LD, p, table, kvh, (tile_begin + warp + 4 * i) * KT, 0, lo, hi);
     }
     cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-    GB_STAMP(3);
-    if (!waited) {
-#pragma unroll
-      for (int kk = 0; kk < HD / 16; ++kk)
-        ldmatrix_x4(qf[kk], qs + (lane % 16) * LD + kk * 16 + (lane / 16) * 8);
-      waited = true;
-    }
-    const int tile = base + warp;               // each warp takes one of the round's tiles
-    if (tile < tile_end) {
-      const __nv_bfloat16* ks = kv + warp * 2 * KT * LD;
-      process_tile(st, qf, ks, ks + KT * LD, tile * KT, row_pos, row_start, p.scale_log2, false);
-    }
-    __syncthreads();   // the slots are overwritten by the next round, or by the merge
-  }
-  if (!waited) gb::pdl_wait();   // a CTA without tiles still must not run ahead of what it may overwrite
+  };
+  // Keys and values of earlier steps are final: tiles that lie wholly before the first token are
+  // asked for before waiting for the kernels in front, so that they arrive while those still run.
+  // Only a warp's last tile can hold new keys, so the order of the groups stays the tiles' order.
+  int issued = 0;
+  while (issued < stages && issued < mine_n && (tile_begin + warp + 4 * issued + 1) * KT <= pos0) issue(issued++);
+  gb::pdl_wait();
+  GB_STAMP(2);
+  while (issued < stages) issue(issued++);
 
+  // the query fragments of the m16n8k16 A operand, straight from global memory
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int row = lane / 4 + 8 * (e & 1);
+    const __nv_bfloat16* src =
+        p.q + ((size_t)(q_begin + (row < nrows ? row / p.g : 0)) * p.Hq + kvh * p.g + (row < nrows ? row % p.g : 0)) * HD +
+        (lane % 4) * 2 + 8 * (e >> 1);
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk)
+      qf[kk][e] = row < nrows ? *reinterpret_cast<const uint32_t*>(src + kk * 16) : 0u;
+  }
+
+  WarpState st;
+  st.reset();
+  for (int i = 0; i < mine_n; ++i) {
+    if (stages == 1) cp_async_wait<0>(); else cp_async_wait<1>();
+    __syncwarp();
+    const __nv_bfloat16* ks = ring + (size_t)(i % stages) * 2 * KT * LD;
+    process_tile(st, qf, ks, ks + KT * LD, (tile_begin + warp + 4 * i) * KT, row_pos, row_start, p.scale_log2, false);
+    __syncwarp();             // every lane is done with the slot before it is filled again
+    issue(i + stages);
+  }
+  cp_async_wait<0>();
   GB_STAMP(4);
+  __syncthreads();            // the slots become the merge buffers
   // ---- the four warps' results into shared memory: [warp][row][RS]
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
     st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 2);
-    float* dst = red + (warp * 16 + lane / 4 + 8 * i) * RS;
+    const int row = lane / 4 + 8 * i;
+    if (row >= nrows) continue;
+    float* dst = red + (warp * ROWS_DECODE + row) * RS;
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) {
-      dst[n * 8 + (lane % 4) * 2] = st.o[n][2 * i];
-      dst[n * 8 + (lane % 4) * 2 + 1] = st.o[n][2 * i + 1];
-    }
+    for (int n = 0; n < HD / 8; ++n)
+      *reinterpret_cast<float2*>(dst + n * 8 + (lane % 4) * 2) = make_float2(st.o[n][2 * i], st.o[n][2 * i + 1]);
     if (lane % 4 == 0) {
       dst[HD] = st.m[i] * p.scale_log2;     // in units of the exponent, as the merges want it
       dst[HD + 1] = st.l[i];
     }
   }
   __syncthreads();
-  // ---- merge the warps; a CTA that is alone writes the result, one of several passes it on.
-  // The weights exp2(m_w - m) are computed once per row and warp, not once per element.
-  float* wfac = red + (4 * 16 + 16) * RS;   // [16 rows][4 warps] weights, then [16] merged maxima
-  float* mine = red + 4 * 16 * RS;          // this CTA's merged rows: [16][RS]
-  if (threadIdx.x < ROWS_DECODE) {
-    const int row = threadIdx.x;
-    float m = -INFINITY;
+  // ---- merge the warps: sixteen threads share a row, each computes the row's four weights
+  // exp2(m_w - m) itself. A CTA that is alone or leads keeps the result, the others pass it on.
+  const bool send = ranks > 1 && rank != 0;
+  const uint32_t remote = send ? map_to_rank(smem_u32(parts) + (uint32_t)(rank - 1) * nrows * RS * 4, 0) : 0;
+  const uint32_t remote_bar = send ? map_to_rank(smem_u32(&part_bar), 0) : 0;
+  const int sub = threadIdx.x & 15;
+  for (int row = threadIdx.x >> 4; row < nrows; row += THREADS / 16) {
+    float f[4], m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, red[(w * 16 + row) * RS + HD]);
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, red[(w * ROWS_DECODE + row) * RS + HD]);
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float mw = red[(w * 16 + row) * RS + HD];
-      wfac[row * 4 + w] = mw == -INFINITY ? 0.f : exp2f(mw - m);
+      const float mw = red[(w * ROWS_DECODE + row) * RS + HD];
+      f[w] = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
     }
-    wfac[64 + row] = m;
-  }
-  __syncthreads();
-  const bool send = ranks > 1 && rank != 0;
-  const uint32_t remote = send ? map_to_rank(smem_u32(parts) + (uint32_t)(rank - 1) * ROWS_DECODE * RS * 4, 0) : 0;
-  const uint32_t remote_bar = send ? map_to_rank(smem_u32(&part_bar), 0) : 0;
-  for (int idx = threadIdx.x; idx < ROWS_DECODE * RS; idx += THREADS) {
-    const int row = idx / RS, c = idx % RS;
-    float v;
-    if (c == HD) {
-      v = wfac[64 + row];
-    } else {       // the sum (c < HD) or the denominator (c == HD + 1), both weighted alike
-      v = wfac[row * 4] * red[row * RS + c] + wfac[row * 4 + 1] * red[(16 + row) * RS + c] +
-          wfac[row * 4 + 2] * red[(32 + row) * RS + c] + wfac[row * 4 + 3] * red[(48 + row) * RS + c];
+    // columns sub, sub + 16, ...; column HD is the maximum, HD + 1 the denominator (weighted like the sums)
+    for (int c = sub; c < RS; c += 16) {
+      float v = m;
+      if (c != HD) {
+        v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) v += f[w] * red[(w * ROWS_DECODE + row) * RS + c];
+      }
+      if (send) st_async_f32(remote + (uint32_t)(row * RS + c) * 4, remote_bar, v);
+      else mine[row * RS + c] = v;
     }
-    if (send) st_async_f32(remote + (uint32_t)idx * 4, remote_bar, v);
-    else mine[idx] = v;
   }
   GB_STAMP(5);
   if (rank != 0) return;
@@ -482,45 +501,39 @@ attention_decode_kernel(const Params p) {
   }
   __syncthreads();
   GB_STAMP(6);
-  // ---- rank 0: its own rows and the others', in rank order; again the weights once per row
-  float* rfac = wfac + 96;                  // [16 rows][8 ranks] weights, then [16] 1 / denominator
-  if (threadIdx.x < nrows) {
-    const int row = threadIdx.x;
-    float ms[MAX_CLUSTER];
-    float m = ms[0] = mine[row * RS + HD];
-#pragma unroll
-    for (int q = 1; q < MAX_CLUSTER; ++q) {
-      ms[q] = q < ranks ? parts[((q - 1) * ROWS_DECODE + row) * RS + HD] : -INFINITY;
-      m = fmaxf(m, ms[q]);
-    }
+  // ---- rank 0: its own rows and the others' [rank - 1][nrows][RS], in rank order
+  for (int row = threadIdx.x >> 4; row < nrows; row += THREADS / 16) {
+    float f[MAX_CLUSTER], m = mine[row * RS + HD];
+    for (int q = 1; q < ranks; ++q) m = fmaxf(m, parts[((q - 1) * nrows + row) * RS + HD]);
     float l = 0.f;
 #pragma unroll
     for (int q = 0; q < MAX_CLUSTER; ++q) {
-      const float f = ms[q] == -INFINITY ? 0.f : exp2f(ms[q] - m);
-      rfac[row * MAX_CLUSTER + q] = f;
-      if (q < ranks) l += f * (q == 0 ? mine[row * RS + HD + 1] : parts[((q - 1) * ROWS_DECODE + row) * RS + HD + 1]);
+      f[q] = 0.f;
+      if (q < ranks) {
+        const float* src = q == 0 ? mine + row * RS : parts + ((q - 1) * nrows + row) * RS;
+        f[q] = src[HD] == -INFINITY ? 0.f : fast_exp2(src[HD] - m);
+        l += f[q] * src[HD + 1];
+      }
     }
-    rfac[ROWS_DECODE * MAX_CLUSTER + row] = l > 0.f ? 1.0f / l : 0.f;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < nrows * HD; idx += THREADS) {
-    const int row = idx / HD, c = idx % HD;
-    float acc = rfac[row * MAX_CLUSTER] * mine[row * RS + c];
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    __nv_bfloat16* dst = p.out + ((size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g) * HD;
+    for (int c = sub; c < HD; c += 16) {
+      float acc = f[0] * mine[row * RS + c];
 #pragma unroll
-    for (int q = 1; q < MAX_CLUSTER; ++q)
-      if (q < ranks) acc += rfac[row * MAX_CLUSTER + q] * parts[((q - 1) * ROWS_DECODE + row) * RS + c];
-    p.out[((size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g) * HD + c] =
-        __float2bfloat16_rn(acc * rfac[ROWS_DECODE * MAX_CLUSTER + row]);
+      for (int q = 1; q < MAX_CLUSTER; ++q)
+        if (q < ranks) acc += f[q] * parts[((q - 1) * nrows + row) * RS + c];
+      dst[c] = __float2bfloat16_rn(acc * inv);
+    }
   }
   GB_STAMP(7);
 }
 
 constexpr int SMEM_TILE = (ROWS_TILE * LD + 2 * 2 * KT * LD) * 2;
-constexpr int smem_decode(int ranks) {
-  return (ROWS_DECODE * LD + SLOTS * 2 * KT * LD) * 2 + (ranks > 1 ? (ranks - 1) * ROWS_DECODE * RS * 4 : 0);
+constexpr int smem_decode(int ranks, int stages) {
+  return stages * 4 * 2 * KT * LD * 2 + (ranks > 1 ? (ranks - 1) * ROWS_DECODE * RS * 4 : 0);
 }
-static_assert(((4 * 16 + 16) * RS + 96 + 16 * MAX_CLUSTER + 16) * 4 <= SLOTS * 2 * KT * LD * 2,
-              "the merge buffers must fit in the key slots");
+constexpr int MAX_STAGES = smem_decode(MAX_CLUSTER, 2) <= 200 * 1024 ? 2 : 1;
+static_assert((4 * ROWS_DECODE + ROWS_DECODE) * RS * 4 <= 4 * 2 * KT * LD * 2, "the merge buffers must fit in the key slots");
 
 }  // namespace
 
@@ -546,12 +559,15 @@ GB_EXPORT int gb_attention_error_check() {
 }
 
 // q [T, Hq, HD], pools [pages, Hkv, page_size, HD], out [T, Hq*HD], all bfloat16.
-// num_splits: CTAs (one cluster, at most 8) that share the keys of a decode request.
+// num_splits: CTAs (one cluster, at most 8) that share the keys of a decode request. stages: slots
+// per warp of the decode kernel (2: the next tile is fetched while one is computed; clamped to what
+// shared memory holds for this head size).
 // max_q_len and min_q_len (over the batch's requests) decide which kernels are launched.
 GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                const int32_t* block_table, int table_width, const int32_t* cu_q,
                                const int32_t* kv_lens, int T, int R, int Hq, int Hkv, float scale, int window,
-                               int page_size, int max_q_len, int min_q_len, int num_splits, cudaStream_t stream) {
+                               int page_size, int max_q_len, int min_q_len, int num_splits, int stages,
+                               cudaStream_t stream) {
   if (T <= 0 || R <= 0) return GB_OK;
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "attention: %d query heads for %d kv heads", Hq, Hkv);
   const int g = Hq / Hkv;
@@ -569,15 +585,17 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
   if (!configured) {
     cudaError_t e1 = cudaFuncSetAttribute(attention_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TILE);
     cudaError_t e2 = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          smem_decode(MAX_CLUSTER));
+                                          smem_decode(MAX_CLUSTER, MAX_STAGES));
     if (e1 != cudaSuccess || e2 != cudaSuccess)
       return gb::fail(GB_CUDA_ERROR, "attention_mma: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     configured = true;
   }
   // DECODE requests (a decode token's group, or a very short portion), if the batch can hold any
   if (min_q_len * g <= ROWS_DECODE) {
+    stages = stages < 1 ? 1 : (stages > MAX_STAGES ? MAX_STAGES : stages);
     int rc = gb::check_pdl_launch(gb::launch_pdl(attention_decode_kernel, dim3(num_splits, Hkv, R), dim3(THREADS),
-                                                 smem_decode(num_splits), stream, dim3(num_splits, 1, 1), p),
+                                                 smem_decode(num_splits, stages), stream, dim3(num_splits, 1, 1), p,
+                                                 stages),
                                   "attention_mma (decode)");
     if (rc) return rc;
   }

@@ -105,7 +105,11 @@ __device__ unsigned long long g_timeline[8 * 4096];
 #define GB_STAMP_E(i) do {} while (0)
 #endif
 
-template <int BN, bool DUAL_M, bool DUAL_N, bool TRANS = false>
+// Bytes of the rotation's tables in the few-token kernel: cosines and sines [BN tokens][64
+// frequencies] and each token's row in the pools.
+__host__ __device__ constexpr int rope_table_bytes(int epi, int bn) { return epi == EPI_ROPE ? bn * 64 * 8 + bn * 8 : 0; }
+
+template <int BN, bool DUAL_M, bool DUAL_N, bool TRANS = false, int EXTRA = 0>
 struct Geometry {
   static constexpr int NUM_M = DUAL_M ? 2 : 1, NUM_N = DUAL_N ? 2 : 1;
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -121,12 +125,14 @@ struct Geometry {
   static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
   // bytes one CTA of a cluster sends to the leader: its whole accumulator
   static constexpr int PARTIAL_BYTES = ACCUMULATORS * BN * BM * 4;
-  // statically declared shared memory (barriers, the rotation's tables) comes out of the same limit
-  static constexpr int STATIC_RESERVE = 18 * 1024;
-  static constexpr int MAX_CLUSTER_RAW = 1 + (SMEM_LIMIT - STATIC_RESERVE - 1024 - PIPE_BYTES) / PARTIAL_BYTES;
-  static constexpr int MAX_CLUSTER = !TRANS ? 1 : (MAX_CLUSTER_RAW < 8 ? MAX_CLUSTER_RAW : 8);
+  // statically declared shared memory (barriers) comes out of the same limit; EXTRA bytes lie
+  // between the pipeline and the partial sums
+  static constexpr int STATIC_RESERVE = 2 * 1024;
+  static constexpr int MAX_CLUSTER_RAW = 1 + (SMEM_LIMIT - STATIC_RESERVE - 1024 - PIPE_BYTES - EXTRA) / PARTIAL_BYTES;
+  static constexpr int MAX_CLUSTER = !TRANS ? 1 : (MAX_CLUSTER_RAW < 1 ? 1 : MAX_CLUSTER_RAW < 8 ? MAX_CLUSTER_RAW : 8);
   // + slack to align the tiles to 1024 B
-  static constexpr int smem_bytes(int cluster) { return PIPE_BYTES + 1024 + (cluster - 1) * PARTIAL_BYTES; }
+  static constexpr int smem_bytes(int cluster) { return PIPE_BYTES + 1024 + EXTRA + (cluster - 1) * PARTIAL_BYTES; }
+  static_assert(PIPE_BYTES + 1024 + EXTRA + STATIC_RESERVE <= SMEM_LIMIT, "tile and tables too large for shared memory");
   static constexpr int SMEM_BYTES = smem_bytes(1);
   static_assert(STAGES >= 2, "tile too large for shared memory");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
@@ -158,7 +164,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
                        OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int kb_per_rank,
                        const RopeArgs ra) {
   constexpr bool DUAL_M = false;
-  using G = Geometry<BN, false, false, true>;
+  using G = Geometry<BN, false, false, true, rope_table_bytes(EPI, BN)>;
   constexpr int STAGES = G::STAGES;
   constexpr int ACC = G::ACCUMULATORS;
   // With so few columns an MMA is over long before the next one that adds to the same accumulator
@@ -187,7 +193,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // [rank - 1][ACC * BN columns][128 rows] floats: the threads of a warp (consecutive rows) write and
   // read consecutive words, so neither the remote stores nor the leader's loads collide on a bank
-  const uint32_t partials = tiles + G::PIPE_BYTES;
+  const uint32_t partials = tiles + G::PIPE_BYTES + rope_table_bytes(EPI, BN);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -297,16 +303,16 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     const int row_in_tile = quarter * 32 + lane;
     const int row = m0 + row_in_tile;                     // output feature
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    // Rotation with few tokens: the epilogue threads of the leading CTA fill, before anything else,
+    // Rotation: the epilogue threads of the leading CTA fill, before anything else,
     // a table of cosines and sines [token][frequency] and each token's row in the pools, sharing
     // the work (a thread alone would compute every angle of its feature: thousands of dependent
     // instructions). Positions, request rows and block tables are written by copies that end
     // before the first kernel of a chain starts, so they are read without waiting for the kernel
     // in front. The table is complete for every thread after the first barrier of the loop below.
-    constexpr bool ROPE_EARLY = EPI == EPI_ROPE && BN <= 32;
-    constexpr int NE = ROPE_EARLY ? BN : 1;
-    __shared__ float rope_cs[NE][64], rope_sn[NE][64];     // head_dim <= 128
-    __shared__ long long rope_slot[NE];                     // element offset of the token's row, head 0; -1: no page
+    constexpr bool ROPE_EARLY = EPI == EPI_ROPE;
+    float (*rope_cs)[64] = reinterpret_cast<float (*)[64]>(smem_raw + (tiles - smem_u32(smem_raw)) + G::PIPE_BYTES);
+    float (*rope_sn)[64] = rope_cs + BN;
+    long long* rope_slot = reinterpret_cast<long long*>(rope_sn + BN);   // element offset of the token's row, head 0; -1: no page
     if (ROPE_EARLY && rank == 0) {
       const int t = (int)threadIdx.x - 64;
       const int half = ra.head_dim >> 1, lg = 31 - __clz(half);      // head_dim divides 128: a power of two
@@ -329,7 +335,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         rope_slot[t] = slot;
       }
     }
-    if (rank == 0) GB_STAMP_E(5);
     float old[EPI == EPI_ACCUMULATE ? BN : 1];
     if (rank == 0) {
       gb::pdl_wait();
@@ -431,7 +436,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               const bool rotate = ra.inv_freq != nullptr && head < ra.heads + ra.kv_heads;
               const bool low = ra.interleaved ? (d & 1) == 0 : d < half;
               const int partner = ra.interleaved ? (row_in_tile ^ 1) : (low ? row_in_tile + half : row_in_tile - half);
-              const float freq = rotate && !ROPE_EARLY ? ra.inv_freq[ra.interleaved ? d >> 1 : d % half] : 0.f;
               if (ROPE_EARLY) {
                 const int fi = ra.interleaved ? d >> 1 : d & (half - 1);
                 const bool is_q = head < ra.heads, is_k = head < ra.heads + ra.kv_heads;
@@ -450,21 +454,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
                   if (col < rows_n && (is_q || slot >= 0))
                     base[is_q ? (size_t)col * q_stride : (size_t)slot] = __float2bfloat16_rn(x);
                 }
-              } else
-#pragma unroll 4
-              for (int j = 0; j < 16; ++j) {
-                const int col = n0 + c + j;      // token
-                if (col >= rows_n) break;
-                const int pos = ra.positions[col];
-                float x = v[j];
-                if (rotate) {
-                  float sn, cs;
-                  sincosf((float)pos * freq, &sn, &cs);
-                  const float other = xch[j * BM + partner];
-                  x = low ? x * cs - other * sn : other * sn + x * cs;
-                }
-                __nv_bfloat16* dst = rope_destination(ra, col, ra.token_req[col], pos, head, d);
-                if (dst) *dst = __float2bfloat16_rn(x);
               }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -904,7 +893,7 @@ int pick_cluster_size(Kernel kernel, int* active, SmemFn smem_for, int tiles, in
 template <int BN, int EPI, typename OT>
 int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int weight_rows, int out_features,
                    int tokens, int K, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
-  using G = Geometry<BN, false, false, true>;
+  using G = Geometry<BN, false, false, true, rope_table_bytes(EPI, BN)>;
   auto kernel = gemm_tc_cluster_kernel<BN, EPI, OT>;
   static bool configured = false;
   if (!configured) {

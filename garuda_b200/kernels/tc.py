@@ -94,20 +94,28 @@ class TensorCoreKernels:
             lib = load_kernel_lib(attention_lib_name(head_dim))
             lib.gb_last_error.restype = ctypes.c_char_p
             lib.gb_attention_mma.argtypes = ([c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 4 + [c_float]
-                                             + [c_int] * 5 + [c_void_p])
+                                             + [c_int] * 6 + [c_void_p])
             lib.gb_attention_mma.restype = c_int
             lib.gb_attention_error_check.restype = c_int
             self._attn[head_dim] = lib
         return lib
 
     @staticmethod
-    def attention_splits(num_requests: int, kv_heads: int, max_kv_len: int) -> int:
-        """CTAs (one cluster, at most 8) that share one decode request's keys: enough
-        to fill the GPU, but no CTA with less than one round of four 64-key tiles
-        where that can be avoided."""
+    def attention_plan(num_requests: int, kv_heads: int, max_kv_len: int):
+        """(CTAs that share one decode request's keys, slots per warp), from timings
+        at 1 to 64 requests: about two CTAs per SM; no warp without a tile where
+        that can be avoided; clusters above four only while the whole grid stays
+        under 64 CTAs (larger clusters are placed late and merge longer); a second
+        slot per warp, so that the next tile is fetched while one is computed, only
+        while every CTA has an SM to itself (two slots take most of its shared
+        memory)."""
         tiles = max((max_kv_len + 63) // 64, 1)
-        want = -(-2 * 148 // max(num_requests * kv_heads, 1))
-        return max(1, min(want, -(-tiles // 4), 8))
+        pairs = max(num_requests * kv_heads, 1)
+        splits = max(1, min(2 * 148 // pairs, -(-tiles // 4), 8))
+        if splits > 4 and pairs * 4 >= 64:
+            splits = 4
+        stages = 2 if tiles > 4 * splits and pairs * splits <= 148 else 1
+        return splits, stages
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale,
                         window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1) -> bool:
@@ -118,10 +126,11 @@ class TensorCoreKernels:
         lib = self._attention_lib(hd)
         g = Hq // Hkv
         has_decode = min_q_len * g <= 16
-        splits = self.attention_splits(num_requests, Hkv, max_kv_len) if has_decode else 1
+        splits, stages = self.attention_plan(num_requests, Hkv, max_kv_len) if has_decode else (1, 1)
         code = lib.gb_attention_mma(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), T, num_requests, Hq, Hkv, float(scale),
-            int(window), int(page_size), int(max_q_len), int(min_q_len), int(splits), self.ops._stream())
+            int(window), int(page_size), int(max_q_len), int(min_q_len), int(splits), int(stages),
+            self.ops._stream())
         self.ops._check(lib, code, "attention_mma", (1 if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
         return True
