@@ -280,7 +280,7 @@ __device__ __forceinline__ void process_tile(WarpState& st, const uint32_t (&qf)
 }
 
 // ------------------------------------------------------------------ TILE (prompt portions)
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 1)
 attention_tile_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [ROWS_TILE][LD]
