@@ -1,0 +1,31 @@
+// What the attention kernels of one library share: the argument block and the hand-over from the
+// general entry point to the tcgen05 kernel for prompt portions.
+#pragma once
+
+#include "common.cuh"
+
+namespace attn {
+
+constexpr int ROWS_DECODE = 16;     // a request with at most this many (token, head-of-group) rows is a decode request
+
+struct Params {
+  const __nv_bfloat16* q;        // [T, Hq, HD]
+  const __nv_bfloat16* k_pool;   // [pages, Hkv, page_size, HD]
+  const __nv_bfloat16* v_pool;
+  __nv_bfloat16* out;            // [T, Hq * HD]
+  const int32_t* block_table;    // [R, table_width]
+  const int32_t* cu_q;           // [R + 1]
+  const int32_t* kv_lens;        // [R]
+  int table_width, Hq, Hkv, g, window, page_size;
+  float scale_log2;              // scale * log2(e)
+};
+
+// True if the tcgen05 kernel takes this shape (head size 64, a power-of-two group, pages of a
+// multiple of 8 keys that divide 128).
+bool tile_tc_takes(const Params& p, int T, long long pages);
+// Launches it for every request with more than ROWS_DECODE rows. Returns a GbStatus.
+int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len, cudaStream_t stream);
+// Non-zero if one of its CTAs gave up on a wait since the last call; clears it.
+int tile_tc_error_check();
+
+}  // namespace attn

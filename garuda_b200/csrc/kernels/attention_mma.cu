@@ -25,6 +25,7 @@
 // the other's requests.
 //
 // Compiled per head size: GB_HEAD_DIM (a multiple of 16, at most 128).
+#include "attention_common.cuh"
 #include "tc_common.cuh"
 
 #ifndef GB_HEAD_DIM
@@ -42,7 +43,7 @@ constexpr int PAD = 8;              // bf16 of padding per shared-memory row (16
 constexpr int LD = HD + PAD;        // shared-memory row length in bf16
 constexpr int THREADS = 128;
 constexpr int ROWS_TILE = 64;       // query rows per CTA of the TILE kernel
-constexpr int ROWS_DECODE = 16;     // query rows per CTA of the DECODE kernel
+constexpr int ROWS_DECODE = attn::ROWS_DECODE;     // query rows per CTA of the DECODE kernel
 constexpr int SLOTS = 4;            // key tiles in flight per DECODE CTA: one per warp and round
 constexpr int MAX_CLUSTER = 8;      // CTAs that may share one request's keys
 constexpr int RS = HD + 2;          // floats of one row's partial result: sum, then maximum, denominator
@@ -64,17 +65,7 @@ __device__ unsigned long long g_timeline[8 * 4096];
 #define GB_STAMP(i) do {} while (0)
 #endif
 
-struct Params {
-  const __nv_bfloat16* q;        // [T, Hq, HD]
-  const __nv_bfloat16* k_pool;   // [pages, Hkv, page_size, HD]
-  const __nv_bfloat16* v_pool;
-  __nv_bfloat16* out;            // [T, Hq * HD]
-  const int32_t* block_table;    // [R, table_width]
-  const int32_t* cu_q;           // [R + 1]
-  const int32_t* kv_lens;        // [R]
-  int table_width, Hq, Hkv, g, window, page_size;
-  float scale_log2;              // scale * log2(e)
-};
+using attn::Params;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -541,6 +532,10 @@ GB_DEFINE_LAST_ERROR()
 
 GB_EXPORT int gb_attention_mma_head_dim() { return HD; }
 
+// How often prompt portions went to the tcgen05 kernel (for tests and launch counts).
+static long long g_tc_tile_launches = 0;
+GB_EXPORT long long gb_attention_tc_tile_launches() { return g_tc_tile_launches; }
+
 #ifdef GB_TIMELINE
 GB_EXPORT int gb_attention_timeline(unsigned long long* host_out, int ctas) {
   return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(unsigned long long) * 8 * ctas) == cudaSuccess ? 0 : 1;
@@ -550,6 +545,8 @@ GB_EXPORT int gb_attention_timeline(unsigned long long* host_out, int ctas) {
 // Non-zero if a decode CTA gave up waiting for its cluster since the last call; clears it.
 GB_EXPORT int gb_attention_error_check() {
   int v = 0;
+  const int tc = attn::tile_tc_error_check();
+  if (tc != 0) return tc;
   if (cudaMemcpyFromSymbol(&v, g_error_word, sizeof(int)) != cudaSuccess) return -1;
   if (v != 0) {
     int zero = 0;
@@ -562,12 +559,13 @@ GB_EXPORT int gb_attention_error_check() {
 // num_splits: CTAs (one cluster, at most 8) that share the keys of a decode request. stages: slots
 // per warp of the decode kernel (2: the next tile is fetched while one is computed; clamped to what
 // shared memory holds for this head size).
-// max_q_len and min_q_len (over the batch's requests) decide which kernels are launched.
+// max_q_len and min_q_len (over the batch's requests) decide which kernels are launched; num_pages:
+// pages in each pool.
 GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                const int32_t* block_table, int table_width, const int32_t* cu_q,
                                const int32_t* kv_lens, int T, int R, int Hq, int Hkv, float scale, int window,
                                int page_size, int max_q_len, int min_q_len, int num_splits, int stages,
-                               cudaStream_t stream) {
+                               long long num_pages, cudaStream_t stream) {
   if (T <= 0 || R <= 0) return GB_OK;
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "attention: %d query heads for %d kv heads", Hq, Hkv);
   const int g = Hq / Hkv;
@@ -599,8 +597,16 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
                                   "attention_mma (decode)");
     if (rc) return rc;
   }
-  // TILE requests
+  // TILE requests: on the tcgen05 kernel where it takes the shape
   if (max_q_len * g > ROWS_DECODE) {
+    static const bool tc_on = [] {
+      const char* v = getenv("GARUDA_B200_ATTN_TC");
+      return !(v && v[0] == '0');
+    }();
+    if (tc_on && attn::tile_tc_takes(p, T, num_pages)) {
+      ++g_tc_tile_launches;
+      return attn::launch_tile_tc(p, T, num_pages, R, max_q_len, stream);
+    }
     const int tokens_per_tile = ROWS_TILE / g;
     dim3 grid((max_q_len + tokens_per_tile - 1) / tokens_per_tile, Hkv, R);
     return gb::check_pdl_launch(gb::launch_pdl(attention_tile_kernel, grid, dim3(THREADS), SMEM_TILE, stream, dim3(1, 1, 1), p),

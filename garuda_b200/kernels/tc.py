@@ -94,7 +94,7 @@ class TensorCoreKernels:
             lib = load_kernel_lib(attention_lib_name(head_dim))
             lib.gb_last_error.restype = ctypes.c_char_p
             lib.gb_attention_mma.argtypes = ([c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 4 + [c_float]
-                                             + [c_int] * 6 + [c_void_p])
+                                             + [c_int] * 6 + [ctypes.c_longlong, c_void_p])
             lib.gb_attention_mma.restype = c_int
             lib.gb_attention_error_check.restype = c_int
             self._attn[head_dim] = lib
@@ -131,6 +131,6 @@ class TensorCoreKernels:
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), T, num_requests, Hq, Hkv, float(scale),
             int(window), int(page_size), int(max_q_len), int(min_q_len), int(splits), int(stages),
-            self.ops._stream())
+            int(k_pool.shape[0]), self.ops._stream())
         self.ops._check(lib, code, "attention_mma", (1 if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
         return True

@@ -1,6 +1,8 @@
 """Each CUDA kernel alone against its plain reference (tests/plain/cpu_ops.py),
 at sizes other than the tiny models': widths and vocabularies that are no power
 of two, head sizes in steps of 16, odd numbers of heads and groups."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -250,6 +252,57 @@ def test_attention_tensor_core_kernel(ops, Hq, Hkv, hd, page, reqs, window):
     assert ops.tc.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5,
                                   window, page, len(reqs), max(x for _, x in reqs), max(x for x, _ in reqs))
     close(out, ref, 1e-2, "tensor-core attention")
+
+
+TCGEN05_ATTENTION_CASES = [
+    (32, 4, 64, 32, [(700, 700)], 0),                          # a whole prompt, groups of 8
+    (8, 8, 64, 16, [(300, 300), (520, 130), (64, 1)], 0),      # no grouping; a portion, a decode token beside it
+    (16, 2, 64, 64, [(1000, 257)], 0),                         # the end of a long context, pages of 64
+    (32, 4, 64, 32, [(900, 400)], 200),                        # a window shorter than the context
+    (4, 1, 64, 8, [(500, 500), (129, 129)], 50),               # groups of 4, pages of 8, a short window
+    (2, 1, 64, 128, [(3, 3), (131, 131), (256, 128)], 0),      # pages as long as a key tile
+]
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page,reqs,window", TCGEN05_ATTENTION_CASES)
+def test_attention_tcgen05_prompt_portions(ops, Hq, Hkv, hd, page, reqs, window):
+    """Prompt portions on the tcgen05 kernel. Every cache slot that no query may read holds NaN:
+    a key or value fetched from beyond a request's length, or from another request's page, shows."""
+    q, k, v, bt, cu, kvl, treq, ref = _attention_case(Hq, Hkv, hd, page, reqs, window, torch.bfloat16)
+    used = torch.zeros(k.shape[0], page, dtype=torch.bool)
+    for i, (kv, _) in enumerate(reqs):
+        for j in range(kv):
+            used[int(bt[i, j // page]), j % page] = True
+    k = k.clone(); v = v.clone()
+    k.transpose(1, 2)[~used] = float("nan")
+    v.transpose(1, 2)[~used] = float("nan")
+    lib = ops.tc._attention_lib(hd)
+    lib.gb_attention_tc_tile_launches.restype = ctypes.c_longlong
+    before = lib.gb_attention_tc_tile_launches()
+    out = torch.zeros(ref.shape, dtype=torch.bfloat16, device="cuda")
+    assert ops.tc.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5,
+                                  window, page, len(reqs), max(x for _, x in reqs), max(x for x, _ in reqs),
+                                  min_q_len=min(x for _, x in reqs))
+    ops.tc.check_errors()
+    assert lib.gb_attention_tc_tile_launches() == before + 1, "the tcgen05 kernel did not take the shape"
+    close(out, ref, 1e-2, "tcgen05 attention")
+
+
+def test_attention_tcgen05_far_key(ops):
+    """One early key stands out for one late query row of a long portion."""
+    Hq, Hkv, hd, page = 8, 2, 64, 32
+    q, k, v, bt, cu, kvl, treq, _ = _attention_case(Hq, Hkv, hd, page, [(1100, 600)], 0, torch.bfloat16)
+    far, tok, head = 5, 577, 6                               # head 6 reads kv head 1
+    pg = int(bt[0, far // page])
+    k[pg, 1, far % page] = (q[tok, head].float() * 4).bfloat16()
+    v[pg, 1, far % page] = 50.0
+    ref = torch.zeros(600, Hq * hd)
+    cpu.paged_attention(q.float(), k.float(), v.float(), bt, cu, kvl, treq, ref, hd ** -0.5, 0, page, 1, 0, 0)
+    assert ref[tok, head * hd:(head + 1) * hd].mean() > 40
+    out = torch.zeros(ref.shape, dtype=torch.bfloat16, device="cuda")
+    ops.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5, 0, page, 1,
+                        600, 1100, min_q_len=600)
+    close(out, ref, 1e-2, "far key, tcgen05")
 
 
 def test_attention_finds_one_far_key_among_hundreds(ops):
