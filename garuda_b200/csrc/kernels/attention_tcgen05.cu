@@ -7,21 +7,30 @@
 // softmax with the maximum subtracted, sum of p_j V_j; query head h reads kv head h / g;
 // start = max(0, pos + 1 - window) with a window (garuda/src/cache/mod.rs:333-338).
 //
-// One CTA takes 128 query rows, (token, head-of-group) pairs that share one kv head of
-// one request, and walks the keys in tiles of 128:
-//   warp 0   one lane: TMA. The query tile once (a 3-D box [tokens][group][64]); per key
-//            tile one 4-D box per page for keys and for values, three stages.
-//   warp 1   one lane: S = Q K^T into one of two S buffers in tensor memory (128 columns
-//            each); after the softmax of a tile, O_tile = P V into one of two O buffers
-//            (64 columns each). V is read as it lies in the cache, keys along the rows
-//            (an MN-major operand).
-//   warps 2-5  a thread owns a query row: reads its 128 scores from tensor memory, masks
-//            (only on tiles that touch a row's limits), running maximum, exp2 with the
-//            scale folded in, writes P in bfloat16 into shared memory in the layout the
-//            second product reads (128-byte swizzle), and adds the previous tile's
-//            O_tile, rescaled, to its 64 sums in registers.
-// The S product of tile j + 1 runs while tile j is in the softmax; O_tile j is folded in
-// after the softmax of tile j + 1, so the tensor cores never wait for the fold.
+// A piece of work is 128 query rows, (token, head-of-group) pairs that share one kv head of one
+// request; its keys are walked in tiles of 128. The kernel is persistent: one CTA per SM takes
+// pieces until none are left (rounds of gridDim.x pieces, walked forth and back so that long and
+// short ones mix), keeping its tensor memory and barriers; the queries and first keys of the next
+// piece arrive, and its first S products run, while the last tiles of the one before are in the
+// softmax.
+//   warp 0   one lane: TMA. The query tile (a 3-D box [tokens][group][64], two buffers); per key
+//            tile one 4-D box per page for keys and for values, four stages.
+//   warp 1   one lane: S = Q K^T for the tile two ahead into one of two S buffers in tensor memory
+//            (128 columns), then O_tile = P V of the tile whose softmax just ended into one of two O
+//            buffers per group (64 columns each). V is read as it lies in the cache, keys along
+//            the rows (an MN-major operand). This warp is the one the tensor cores wait for, so it
+//            steps counters instead of dividing, advances descriptors made once, and learns the
+//            pieces' lengths 32 at a time from its lanes.
+//   warps 2-9  two groups of 128 threads; a thread owns a query row and its group's 64 keys of
+//            every tile, an attention stream of its own: reads its 64 scores from tensor memory,
+//            masks (only on tiles that touch a row's limits), running maximum, exp2 with the
+//            scale folded in, writes P in bfloat16 into shared memory in the layout the second
+//            product reads (128-byte swizzle), and adds the previous tile's O_tile, rescaled, to
+//            its 64 sums in registers. At the end of a piece the two groups' streams are merged.
+//            They also clear the value rows no query may read (a stray NaN times a zero
+//            probability would spoil a sum).
+// Measured on this hardware: a product with fewer than 128 columns costs as much as one with 128
+// (about 70 cycles for M = 128, K = 16), which is why S is one 128-column product for both groups.
 // Every wait is bounded; a wait that runs out sets the error word and the CTA winds down.
 //
 // Built for head size 64 only (one 128-byte swizzled row per key); other head sizes use the
@@ -46,18 +55,35 @@ using attn::Params;
 constexpr int HD = 64;
 constexpr int QROWS = 128;          // query rows per CTA
 constexpr int KT = 128;             // keys per tile
-constexpr int STAGES = 3;
+constexpr int GROUPS = 2;           // softmax groups: each walks its own half of every key tile
+constexpr int GK = KT / GROUPS;     // keys per group and tile
+constexpr int STAGES = 4;
 constexpr int ROW_BYTES = HD * 2;   // 128: one swizzled row
 constexpr int Q_BYTES = QROWS * ROW_BYTES;
 constexpr int K_BYTES = KT * ROW_BYTES, V_BYTES = K_BYTES;
 constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
-constexpr int P_BYTES = QROWS * KT * 2;             // two blocks of 64 keys, [128 rows][128 bytes] each
-constexpr int SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES;
-constexpr int TMEM_COLS = 512;                      // S: 2 x 128 columns, O: 2 x 64 columns
-constexpr int O_COL0 = 256;
-constexpr int THREADS = 192;
+constexpr int P_BYTES = QROWS * GK * 2;             // one group's probabilities of a tile: [128 rows][128 bytes]
+constexpr int SMEM_BYTES = 1024 + 2 * Q_BYTES + STAGES * STAGE_BYTES + GROUPS * 2 * P_BYTES;
+constexpr int TMEM_COLS = 512;                      // S: 2 buffers x 2 groups x 64 columns; O: 2 groups x 2 buffers x 64
+constexpr int O_COL0 = GROUPS * 2 * GK;
+constexpr int THREADS = 64 + GROUPS * 128;
+static_assert(GK == 64 && O_COL0 + GROUPS * 2 * HD <= TMEM_COLS, "tensor memory layout");
 
 __device__ int g_tc_error_word;
+
+// Compiled in with -DGB_ATTN_PROFILE only: where a softmax thread and the MMA issuer spend their
+// cycles, summed over the CTAs (eight counters, then the number of tiles).
+#ifdef GB_ATTN_PROFILE
+__device__ unsigned long long g_prof[24];
+#define GB_PROF_DECL long long pt0 = clock64(), pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define GB_PROF(i) do { const long long t = clock64(); pacc[i] += t - pt0; pt0 = t; } while (0)
+#define GB_PROF_FLUSH(base, tiles_done) do { for (int i = 0; i < 8; ++i) if (pacc[i]) atomicAdd(&g_prof[(base) + i], (unsigned long long)pacc[i]); \
+    atomicAdd(&g_prof[23], (unsigned long long)(tiles_done)); } while (0)
+#else
+#define GB_PROF_DECL do {} while (0)
+#define GB_PROF(i) do {} while (0)
+#define GB_PROF_FLUSH(base, tiles_done) do {} while (0)
+#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -68,50 +94,167 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// The largest of three in one instruction.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// One piece of work: 128 query rows of one request and kv head.
+struct Item {
+  bool valid;
+  int kvh, q_begin, tok0, nrows, pos0, lo, hi, tile_begin, n_tiles;
+  const int32_t* table;
+};
+
+// Items are numbered request by request, the tiles of a request from its end (the longest first), the
+// kv heads innermost. A CTA takes every gridDim.x-th item, so each gets long and short ones.
+__device__ __forceinline__ Item decode_item(const Params& p, int q_tiles, int item) {
+  Item w;
+  const int per_req = q_tiles * p.Hkv;
+  const int r = item / per_req, rem = item % per_req;
+  const int qt = q_tiles - 1 - rem / p.Hkv;
+  w.kvh = rem % p.Hkv;
+  // The batch's lengths and block tables were copied in before the step's first kernel.
+  w.q_begin = p.cu_q[r];
+  const int q_len = p.cu_q[r + 1] - w.q_begin;
+  const int tokens_per_tile = QROWS / p.g;
+  w.tok0 = qt * tokens_per_tile;
+  w.valid = q_len * p.g > attn::ROWS_DECODE && w.tok0 < q_len;      // else a decode request, or past its end
+  const int kv_len = p.kv_lens[r];
+  const int ntok = min(tokens_per_tile, q_len - w.tok0);
+  w.nrows = ntok * p.g;
+  w.pos0 = kv_len - q_len + w.tok0;                                 // position of the tile's first token
+  w.lo = p.window > 0 ? max(0, w.pos0 + 1 - p.window) : 0;          // first key any row reads
+  w.hi = w.pos0 + ntok - 1;                                         // last key any row reads
+  w.tile_begin = w.lo / KT;
+  w.n_tiles = w.valid ? w.hi / KT + 1 - w.tile_begin : 0;
+  w.table = p.block_table + (size_t)r * p.table_width;
+  return w;
+}
+
+// Walks this CTA's items tile by tile.
+// The k-th item of this CTA: rounds of gridDim.x items, walked forth and back in turn, so that the
+// CTA that got the longest item of one round gets the shortest of the next.
+__device__ __forceinline__ int cta_item(int k) {
+  const int g = (int)gridDim.x, b = (int)blockIdx.x;
+  return k * g + ((k & 1) ? g - 1 - b : b);
+}
+
+struct Cursor {
+  int item, total, step, q_tiles, round;
+  int it;          // valid items before this one
+  int j;           // tile within the item
+  Item w;
+  bool done;
+  __device__ __forceinline__ void seek(const Params& p) {
+    done = true;
+    while ((long long)round * step < total) {       // a round may end before this CTA's place in it
+      if (item < total) {
+        w = decode_item(p, q_tiles, item);
+        if (w.valid) { done = false; break; }
+      }
+      item = cta_item(++round);
+    }
+  }
+  __device__ __forceinline__ void start(const Params& p, int q_tiles_, int total_) {
+    round = 0, step = gridDim.x, total = total_, q_tiles = q_tiles_, it = 0, j = 0;
+    item = cta_item(0);
+    seek(p);
+  }
+  __device__ __forceinline__ void next_item(const Params& p) {
+    item = cta_item(++round), ++it, j = 0;
+    seek(p);
+  }
+  __device__ __forceinline__ void next_tile(const Params& p) {
+    if (++j >= w.n_tiles) next_item(p);
+  }
+};
+
+// The same walk for the warp that issues the matrix products: it needs nothing of an item but its
+// number of tiles, and everything it executes delays the tensor cores. Its lanes decode 32 items at
+// a time, one each; the walk then only shuffles the counts out.
+struct TileWalk {
+  int base;        // this CTA's items before the batch
+  int my_n;        // tiles of this lane's item of the batch (0: none, or not a valid item)
+  int lane_i;      // the current item's lane
+  int n, j;        // the current item's tiles, the current tile
+  int it;          // valid items before the current one
+  bool done;
+  __device__ __forceinline__ void load(const Params& p, int q_tiles, int total) {
+    const int k = base + (int)(threadIdx.x & 31);
+    const long long item = (long long)k * gridDim.x < total ? cta_item(k) : total;
+    my_n = item < total ? decode_item(p, q_tiles, (int)item).n_tiles : 0;
+  }
+  __device__ __forceinline__ void seek(const Params& p, int q_tiles, int total) {
+    for (;;) {
+      // the next lane of the batch with tiles, if any
+      const unsigned have = __ballot_sync(0xffffffffu, my_n > 0) & (0xffffffffu << lane_i);
+      if (lane_i < 32 && have != 0) {
+        lane_i = __ffs(have) - 1;
+        n = __shfl_sync(0xffffffffu, my_n, lane_i);
+        return;
+      }
+      base += 32;
+      lane_i = 0;
+      if ((long long)base * gridDim.x >= total) {
+        done = true;
+        return;
+      }
+      load(p, q_tiles, total);
+    }
+  }
+  __device__ __forceinline__ void start(const Params& p, int q_tiles, int total) {
+    base = 0, lane_i = 0, j = 0, it = 0, n = 0, done = false;
+    load(p, q_tiles, total);
+    seek(p, q_tiles, total);
+  }
+  __device__ __forceinline__ void next_tile(const Params& p, int q_tiles, int total) {
+    if (++j >= n) {
+      j = 0, ++it, ++lane_i;
+      if (lane_i >= 32) lane_i = 32;
+      seek(p, q_tiles, total);
+    }
+  }
+};
+
+// A persistent kernel: one CTA per SM takes items until none are left, keeping its tensor memory and
+// barriers, so that the queries and first keys of the next item arrive, and its first S products
+// run, while the last tiles of the one before are still in the softmax.
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                         const __grid_constant__ CUtensorMap v_map, const Params p) {
+                         const __grid_constant__ CUtensorMap v_map, const Params p, const int q_tiles,
+                         const int total_items) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_ready[2], p_ready[2], o_ready[2];
+  __shared__ __align__(8) uint64_t q_full[2], q_empty[2], kv_full[STAGES], kv_empty[STAGES];
+  __shared__ __align__(8) uint64_t s_ready[2], p_ready[GROUPS][2], o_ready[2];   // s and o: one for both groups (a commit costs the issuer about as much as a product)
+  __shared__ float other_ml[QROWS][2];      // the second group's maximum and denominator, for the merge
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = blockIdx.z, kvh = blockIdx.y;
-  // The batch's lengths and block tables were copied in before the step's first kernel.
-  const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin;
-  if (q_len * p.g <= attn::ROWS_DECODE) return;      // a decode request: the other kernel's
-  const int tokens_per_tile = QROWS / p.g;
-  const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * tokens_per_tile;   // the longest tiles start first
-  if (tok0 >= q_len) return;
-  const int kv_len = p.kv_lens[r];
-  const int32_t* table = p.block_table + (size_t)r * p.table_width;
-  const int ntok = min(tokens_per_tile, q_len - tok0);
-  const int nrows = ntok * p.g;
-  const int pos0 = kv_len - q_len + tok0;                          // position of the tile's first token
-  const int lo = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;   // first key any row reads
-  const int hi = pos0 + ntok - 1;                                  // last key any row reads
-  const int tile_begin = lo / KT, n_tiles = hi / KT + 1 - tile_begin;
-
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_s = tiles;
-  const uint32_t kv_s = tiles + Q_BYTES;                           // stage s: K at kv_s + s * STAGE_BYTES, V after it
-  const uint32_t p_s = kv_s + STAGES * STAGE_BYTES;                // buffer b at p_s + b * P_BYTES
+  const uint32_t q_s = tiles;                                      // two query buffers
+  const uint32_t kv_s = tiles + 2 * Q_BYTES;                       // stage s: K at kv_s + s * STAGE_BYTES, V after it
+  const uint32_t p_s = kv_s + STAGES * STAGE_BYTES;                // group g, buffer b at p_s + (2 g + b) * P_BYTES
 
   if (threadIdx.x == 0) {
-    mbar_init(smem_u32(&q_full), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&q_full[b]), 1);
+      mbar_init(smem_u32(&q_empty[b]), 1);
+    }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&kv_full[s]), 1);
       mbar_init(smem_u32(&kv_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&s_ready[b]), 1);
-      mbar_init(smem_u32(&p_ready[b]), 128);
       mbar_init(smem_u32(&o_ready[b]), 1);
+      for (int g = 0; g < GROUPS; ++g) mbar_init(smem_u32(&p_ready[g][b]), 128);
     }
     abort_s = 0;
     fence_barrier_init();
@@ -134,45 +277,59 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------------------------ TMA
-      mbar_arrive_expect_tx(smem_u32(&q_full), Q_BYTES);
-      tma_load_3d(q_s, &q_map, smem_u32(&q_full), 0, kvh * p.g, q_begin + tok0);
-      const int pages_per_tile = KT / p.page_size;
+      const int page_shift = __ffs(p.page_size) - 1;         // pages are a power of two of keys
+      const int pages_per_tile = KT >> page_shift;
       const uint32_t page_bytes = (uint32_t)p.page_size * ROW_BYTES;
-      int issued = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % STAGES;
-        if (j >= STAGES && !mbar_wait(smem_u32(&kv_empty[s]), ((j / STAGES) & 1) ^ 1)) {
+      int gt = 0;               // tiles so far, over all items
+      int stage = 0, par = 1;   // the stage to fill and the phase of its "empty" barrier to wait for
+      Cursor c;
+      for (c.start(p, q_tiles, total_items); !c.done; c.next_item(p)) {
+        const Item& w = c.w;
+        const int qb = c.it & 1;
+        if (c.it >= 2 && !mbar_wait(smem_u32(&q_empty[qb]), ((c.it >> 1) & 1) ^ 1)) {
           atomicCAS(&g_tc_error_word, 0, ERR_WAIT_EMPTY);
           abort_s = 1;
         }
         if (*(volatile int*)&abort_s) break;
-        const int key0 = (tile_begin + j) * KT;
-        const uint32_t bar = smem_u32(&kv_full[s]);
-        const uint32_t kdst = kv_s + s * STAGE_BYTES, vdst = kdst + K_BYTES;
-        // pages that hold a key some row reads, and exist
-        int pages[16], count = 0;
-        for (int g = 0; g < pages_per_tile; ++g) {
-          const int first = key0 + g * p.page_size;
-          pages[g] = (first <= hi && first + p.page_size > lo) ? table[first / p.page_size] : -1;
-          count += pages[g] >= 0;
-        }
-        if (count == 0) {
-          mbar_arrive(bar);
-        } else {
-          mbar_arrive_expect_tx(bar, 2u * count * page_bytes);
+        mbar_arrive_expect_tx(smem_u32(&q_full[qb]), Q_BYTES);
+        tma_load_3d(q_s + qb * Q_BYTES, &q_map, smem_u32(&q_full[qb]), 0, w.kvh * p.g, w.q_begin + w.tok0);
+        for (int j = 0; j < w.n_tiles; ++j, ++gt) {
+          const int s = stage;
+          const int key0 = (w.tile_begin + j) * KT;
+          // pages that hold a key some row reads, and exist; looked up before waiting for the
+          // stage, so that the table's latency passes during the wait
+          int pages[16], count = 0;
           for (int g = 0; g < pages_per_tile; ++g) {
-            if (pages[g] < 0) continue;
-            tma_load_4d(kdst + g * page_bytes, &k_map, bar, 0, 0, kvh, pages[g]);
-            tma_load_4d(vdst + g * page_bytes, &v_map, bar, 0, 0, kvh, pages[g]);
+            const int first = key0 + g * p.page_size;
+            pages[g] = (first <= w.hi && first + p.page_size > w.lo) ? w.table[first >> page_shift] : -1;
+            count += pages[g] >= 0;
           }
+          if (gt >= STAGES && !mbar_wait(smem_u32(&kv_empty[s]), par)) {
+            atomicCAS(&g_tc_error_word, 0, ERR_WAIT_EMPTY);
+            abort_s = 1;
+          }
+          if (*(volatile int*)&abort_s) break;
+          const uint32_t bar = smem_u32(&kv_full[s]);
+          const uint32_t kdst = kv_s + s * STAGE_BYTES, vdst = kdst + K_BYTES;
+          if (count == 0) {
+            mbar_arrive(bar);
+          } else {
+            mbar_arrive_expect_tx(bar, 2u * count * page_bytes);
+            for (int g = 0; g < pages_per_tile; ++g) {
+              if (pages[g] < 0) continue;
+              tma_load_4d(kdst + g * page_bytes, &k_map, bar, 0, 0, w.kvh, pages[g]);
+              tma_load_4d(vdst + g * page_bytes, &v_map, bar, 0, 0, w.kvh, pages[g]);
+            }
+          }
+          if (++stage == STAGES) stage = 0, par ^= 1;
         }
-        issued = j + 1;
+        if (*(volatile int*)&abort_s) break;
       }
       if (*(volatile int*)&abort_s) {
         // wind down: let the copies in flight land before the CTA's shared memory is given up
-        for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
+        for (int t = gt > STAGES ? gt - STAGES : 0; t < gt; ++t) {
           const unsigned long long t0 = globaltimer_ns();
-          while (!mbar_try_wait(smem_u32(&kv_full[j % STAGES]), (j / STAGES) & 1)) {
+          while (!mbar_try_wait(smem_u32(&kv_full[t % STAGES]), (t / STAGES) & 1)) {
             if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
               atomicCAS(&g_tc_error_word, 0, ERR_WAIT_DRAIN);
               break;
@@ -183,170 +340,251 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------------- MMA issuer
+    // The S products run two tiles ahead of the P V products, across the items' borders. Whatever
+    // this warp executes between two products delays the tensor cores, so it is kept short: stage
+    // and buffer counters are stepped, not divided; descriptors are made once and advanced. On
+    // this hardware a product with fewer than 128 columns takes as long as one with 128 (about
+    // 70 cycles for M = 128, K = 16), so S is computed for both groups at once (their S buffers
+    // lie side by side). After a tile's softmax the S product two tiles ahead goes first: the
+    // softmax warps wait for it next, for P V only a tile later.
     constexpr uint32_t idesc_s = instr_desc_bf16(QROWS, KT);
     constexpr uint32_t idesc_o = instr_desc_bf16(QROWS, HD) | INSTR_B_MN_MAJOR;
-    bool ok = mbar_wait(smem_u32(&q_full), 0);
-    if (!ok && lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_FULL);
-    auto issue_s = [&](int j) {      // S(j) = Q K(j)^T into S buffer j & 1
-      const int s = j % STAGES;
-      if (!mbar_wait(smem_u32(&kv_full[s]), (j / STAGES) & 1)) {
+    const uint64_t dq0 = smem_desc_sw128(q_s), dk0 = smem_desc_sw128(kv_s), dv0 = smem_desc_sw128_mn(kv_s + K_BYTES),
+                   dp0 = smem_desc_sw128(p_s);
+    bool ok = true;
+    TileWalk ws, wp;               // the S products' tile, the P V products' tile
+    ws.start(p, q_tiles, total_items);
+    wp = ws;
+    int s_stage = 0, s_par = 0, p_stage = 0;       // stage (and its phase) of the S tile, stage of the P V tile
+    int s_buf = 0;                                 // S buffer of the S tile
+    int p_buf = 0, p_par = 0;                      // buffers of the P V tile and their phase
+    GB_PROF_DECL;
+    auto issue_s = [&]() {      // S = Q K^T of the S tile into S buffer s_buf (both groups' columns)
+      const int qb = ws.it & 1;
+      GB_PROF(0);
+      if (ws.j == 0 && !mbar_wait(smem_u32(&q_full[qb]), (ws.it >> 1) & 1)) ok = false;
+      GB_PROF(1);
+      if (ok && !mbar_wait(smem_u32(&kv_full[s_stage]), s_par)) ok = false;
+      GB_PROF(2);
+      if (!ok) {
         if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_FULL);
-        ok = false;
         return;
       }
       tc_fence_after_sync();
       if (lane == 0) {
-        const uint32_t kb = kv_s + s * STAGE_BYTES;
+        const uint64_t dq = dq0 + (uint64_t)(qb * (Q_BYTES >> 4)), dk = dk0 + (uint64_t)(s_stage * (STAGE_BYTES >> 4));
+        const uint32_t d = tmem_base + s_buf * KT;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          mma_bf16(tmem_base + (j & 1) * KT, smem_desc_sw128(q_s + k * 32), smem_desc_sw128(kb + k * 32), idesc_s, k > 0);
-        mma_commit(smem_u32(&s_ready[j & 1]));
+        for (int k = 0; k < HD / 16; ++k) mma_bf16(d, dq + 2 * k, dk + 2 * k, idesc_s, k > 0);
+        mma_commit(smem_u32(&s_ready[s_buf]));
+        if (ws.j == ws.n - 1) mma_commit(smem_u32(&q_empty[qb]));   // the item's queries have been read
       }
       __syncwarp();
+      GB_PROF(3);
+      if (++s_stage == STAGES) s_stage = 0, s_par ^= 1;
+      s_buf ^= 1;
+      ws.next_tile(p, q_tiles, total_items);
+      GB_PROF(4);
     };
-    if (ok) issue_s(0);
-    if (ok && n_tiles > 1) issue_s(1);
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    if (!ws.done) issue_s();
+    if (ok && !ws.done) issue_s();
+    while (ok && !wp.done) {
       if (*(volatile int*)&abort_s) break;
-      if (!mbar_wait(smem_u32(&p_ready[j & 1]), (j >> 1) & 1)) {
-        if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      const int s = j % STAGES;
-      const uint32_t vb = kv_s + s * STAGE_BYTES + K_BYTES;
-      const int key0 = (tile_begin + j) * KT;
-      if (key0 < lo || key0 + KT - 1 > hi) {
-        // Value rows that no row may read hold whatever was there (a page that was not fetched,
-        // the unwritten end of the last page): their probabilities are zero, but zero times a
-        // stray NaN is not. Clear them.
-        for (int row = lane; row < KT; row += 32) {
-          const int key = key0 + row;
-          if (key < lo || key > hi) {
+      GB_PROF(0);
 #pragma unroll
-            for (int c = 0; c < ROW_BYTES / 16; ++c) st_shared_v4(vb + row * ROW_BYTES + c * 16, 0u, 0u, 0u, 0u);
-          }
+      for (int g = 0; g < GROUPS; ++g) {
+        if (ok && !mbar_wait(smem_u32(&p_ready[g][p_buf]), p_par)) {
+          if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
+          ok = false;
         }
-        fence_proxy_async();
-        __syncwarp();
       }
+      if (!ok) break;
+      GB_PROF(5);
+      // both groups have read this S buffer in full and written their P: first the S product that
+      // takes the buffer over, then this tile's P V
+      if (!ws.done) issue_s();
+      if (!ok) break;
+      tc_fence_after_sync();
       if (lane == 0) {
-        const uint32_t pb = p_s + (j & 1) * P_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < KT / 16; ++ks)
-          mma_bf16(tmem_base + O_COL0 + (j & 1) * HD, smem_desc_sw128(pb + (ks >> 2) * (QROWS * 128) + (ks & 3) * 32),
-                   smem_desc_sw128_mn(vb + ks * 16 * ROW_BYTES), idesc_o, ks > 0);
-        mma_commit(smem_u32(&o_ready[j & 1]));
-        mma_commit(smem_u32(&kv_empty[s]));     // keys and values of the stage have been read
+        for (int g = 0; g < GROUPS; ++g) {
+          const uint64_t dp = dp0 + (uint64_t)((2 * g + p_buf) * (P_BYTES >> 4));
+          const uint64_t dv = dv0 + (uint64_t)(p_stage * (STAGE_BYTES >> 4) + g * (GK * ROW_BYTES >> 4));
+          const uint32_t d = tmem_base + O_COL0 + (2 * g + p_buf) * HD;
+#pragma unroll
+          for (int ks = 0; ks < GK / 16; ++ks) mma_bf16(d, dp + 2 * ks, dv + ks * (16 * ROW_BYTES >> 4), idesc_o, ks > 0);
+        }
+        mma_commit(smem_u32(&o_ready[p_buf]));
+        mma_commit(smem_u32(&kv_empty[p_stage]));     // keys and values of the stage have been read
       }
       __syncwarp();
-      if (j + 2 < n_tiles) issue_s(j + 2);      // its S buffer was read in full before p_ready fired
+      GB_PROF(6);
+      if (++p_stage == STAGES) p_stage = 0;
+      p_par ^= p_buf;         // the phase flips after buffer 1
+      p_buf ^= 1;
+      wp.next_tile(p, q_tiles, total_items);
+      GB_PROF(7);
     }
     if (!ok) abort_s = 1;
+    if (lane == 0) GB_PROF_FLUSH(8, 0);
   } else {
     // -------------------------------------------------------------------- softmax warps
+    // Group g takes keys [g * 64, g * 64 + 64) of every tile: an attention stream of its own
+    // (maximum, denominator, sums), merged with the other group's at the end. Two groups put two
+    // warps on every scheduler, so that one computes while the other waits for tensor memory.
+    const int grp = (warp - 2) >> 2;
     const int quarter = warp & 3;                        // the TMEM lanes this warp may read
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const int row_pos = row < nrows ? pos0 + row / p.g : -1;       // no key is valid for a padding row
-    const int row_start = (row < nrows && p.window > 0) ? max(0, row_pos + 1 - p.window) : 0;
     const float scale_log2 = p.scale_log2;
-    float o_acc[HD];
+    float* xo = reinterpret_cast<float*>(smem_raw + (p_s + 2 * P_BYTES - smem_u32(smem_raw)));
+    bool ok = true;       // false: this thread only keeps the others company at the barriers
+    int gt = 0;           // tiles so far, over all items
+    int stage = 0;        // the current tile's stage of keys and values
+    GB_PROF_DECL;
+    Cursor c;
+    for (c.start(p, q_tiles, total_items); !c.done; c.next_item(p)) {
+      const Item& w = c.w;
+      const int row_pos = row < w.nrows ? w.pos0 + row / p.g : -1;       // no key is valid for a padding row
+      const int row_start = (row < w.nrows && p.window > 0) ? max(0, row_pos + 1 - p.window) : 0;
+      float o_acc[HD];
 #pragma unroll
-    for (int c = 0; c < HD; ++c) o_acc[c] = 0.f;
-    float m = -INFINITY, l = 0.f, corr_saved = 0.f;      // m: running maximum of the raw dot products
-    bool ok = true;
+      for (int ch = 0; ch < HD; ++ch) o_acc[ch] = 0.f;
+      float m = -INFINITY, l = 0.f, corr_saved = 0.f;      // m: running maximum of the raw dot products
 
-    auto fold = [&](int j) {        // o_acc = o_acc * corr_saved + O_tile(j)
-      if (!mbar_wait(smem_u32(&o_ready[j & 1]), (j >> 1) & 1)) {
-        if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
-        ok = false;
-        return;
-      }
-      tc_fence_after_sync();
-#pragma unroll
-      for (int h = 0; h < HD / 32; ++h) {
-        uint32_t v[32];
-        tmem_ld_32(lane_addr + O_COL0 + (j & 1) * HD + h * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) o_acc[h * 32 + c] = fmaf(o_acc[h * 32 + c], corr_saved, __uint_as_float(v[c]));
-      }
-    };
-
-    for (int j = 0; j < n_tiles; ++j) {
-      if (*(volatile int*)&abort_s) { ok = false; break; }
-      if (!mbar_wait(smem_u32(&s_ready[j & 1]), (j >> 1) & 1)) {
-        if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      float s[KT];
-#pragma unroll
-      for (int h = 0; h < KT / 32; ++h) {
-        uint32_t v[32];
-        tmem_ld_32(lane_addr + (j & 1) * KT + h * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) s[h * 32 + c] = __uint_as_float(v[c]);
-      }
-      const int key0 = (tile_begin + j) * KT;
-      // a tile needs no mask if it lies wholly before the first row's position and inside the
-      // last row's window
-      const bool full = key0 + KT - 1 <= pos0 && (p.window <= 0 || key0 >= hi + 1 - p.window);
-      if (!full) {
-#pragma unroll
-        for (int c = 0; c < KT; ++c)
-          if (!(key0 + c >= row_start && key0 + c <= row_pos)) s[c] = -INFINITY;
-      }
-      float m_new = m;
-#pragma unroll
-      for (int c = 0; c < KT; ++c) m_new = fmaxf(m_new, s[c]);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;          // nothing valid yet: avoid inf - inf
-      const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
-      const float neg_m = -m_use * scale_log2;
-      m = m_new;
-      float l_add = 0.f;
-      const uint32_t prow = p_s + (j & 1) * P_BYTES + row * 128;
-#pragma unroll
-      for (int c8 = 0; c8 < KT / 8; ++c8) {
-        float pr[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          pr[e] = fast_exp2(fmaf(s[c8 * 8 + e], scale_log2, neg_m));   // exp2(-inf) = 0 for masked keys
-          l_add += pr[e];
+      auto fold = [&](int t) {        // o_acc = o_acc * corr_saved + O_tile of the tile counted t
+        if (!mbar_wait(smem_u32(&o_ready[t & 1]), (t >> 1) & 1)) {
+          if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
+          ok = false;
+          abort_s = 1;
+          return;
         }
-        // block of 64 keys c8 / 8, 16-byte chunk c8 % 8 of the row, swizzled with the row
-        st_shared_v4(prow + (c8 >> 3) * (QROWS * 128) + (((c8 & 7) ^ (row & 7)) << 4), pack_bf16(pr[0], pr[1]),
-                     pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
-      }
-      l = l * corr + l_add;
-      fence_proxy_async();            // the tensor core reads P through the async proxy
-      tc_fence_before_sync();         // this thread's reads of S are over
-      mbar_arrive(smem_u32(&p_ready[j & 1]));
-      if (j > 0) {
-        fold(j - 1);
-        if (!ok) break;
-      }
-      corr_saved = corr;
-    }
-    if (ok && n_tiles > 0) fold(n_tiles - 1);
-    if (ok && row < nrows) {
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row / p.g) * p.Hq + kvh * p.g + row % p.g) * HD;
+        tc_fence_after_sync();
+        uint32_t v[HD / 32][32];
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
-        uint4 w;
-        w.x = pack_bf16(o_acc[c] * inv, o_acc[c + 1] * inv);
-        w.y = pack_bf16(o_acc[c + 2] * inv, o_acc[c + 3] * inv);
-        w.z = pack_bf16(o_acc[c + 4] * inv, o_acc[c + 5] * inv);
-        w.w = pack_bf16(o_acc[c + 6] * inv, o_acc[c + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + c) = w;
+        for (int h = 0; h < HD / 32; ++h) tmem_ld_32(lane_addr + O_COL0 + (2 * grp + (t & 1)) * HD + h * 32, v[h]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < HD; ++ch) o_acc[ch] = fmaf(o_acc[ch], corr_saved, __uint_as_float(v[ch >> 5][ch & 31]));
+      };
+
+      for (int j = 0; j < w.n_tiles && ok; ++j, ++gt) {
+        if (*(volatile int*)&abort_s) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&s_ready[gt & 1]), (gt >> 1) & 1)) {
+          if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
+          ok = false;
+          abort_s = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        GB_PROF(0);
+        {
+          // Value rows that no row may read hold whatever was there (a page that was not fetched,
+          // the unwritten end of the last page): their probabilities are zero, but zero times a
+          // stray NaN is not. Clear them: half of each group's threads take one of the group's 64
+          // rows each. (The stage has landed: S of this tile was computed from its keys. The
+          // tensor core reads the values only after this thread's arrival below.)
+          const int tile_key0 = (w.tile_begin + j) * KT;
+          if ((tile_key0 < w.lo || tile_key0 + KT - 1 > w.hi) && row < GK) {
+            const int vrow = grp * GK + row, key = tile_key0 + vrow;
+            if (key < w.lo || key > w.hi) {
+              const uint32_t vaddr = kv_s + stage * STAGE_BYTES + K_BYTES + vrow * ROW_BYTES;
+#pragma unroll
+              for (int ch = 0; ch < ROW_BYTES / 16; ++ch) st_shared_v4(vaddr + ch * 16, 0u, 0u, 0u, 0u);
+            }
+          }
+          if (++stage == STAGES) stage = 0;
+        }
+        // the row's 64 scores of this group, one wait for the two loads
+        uint32_t sv[GK / 32][32];
+#pragma unroll
+        for (int h = 0; h < GK / 32; ++h) tmem_ld_32(lane_addr + (2 * (gt & 1) + grp) * GK + h * 32, sv[h]);
+        tmem_ld_wait();
+        GB_PROF(1);
+        auto sc = [&](int ch) -> float& { return reinterpret_cast<float&>(sv[ch >> 5][ch & 31]); };
+        const int key0 = (w.tile_begin + j) * KT + grp * GK;
+        // the keys need no mask if they lie wholly before the first row's position and inside the
+        // last row's window
+        const bool full = key0 + GK - 1 <= w.pos0 && (p.window <= 0 || key0 >= w.hi + 1 - p.window);
+        if (!full) {
+#pragma unroll
+          for (int ch = 0; ch < GK; ++ch)
+            if (!(key0 + ch >= row_start && key0 + ch <= row_pos)) sc(ch) = -INFINITY;
+        }
+        // four independent chains for the maximum and for the sum
+        float mx[4] = {m, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int ch = 0; ch < GK; ch += 8) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) mx[e] = max3(mx[e], sc(ch + e), sc(ch + 4 + e));
+        }
+        const float m_new = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;          // nothing valid yet: avoid inf - inf
+        const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
+        const float neg_m = -m_use * scale_log2;
+        m = m_new;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t prow = p_s + (2 * grp + (gt & 1)) * P_BYTES + row * 128;
+#pragma unroll
+        for (int c8 = 0; c8 < GK / 8; ++c8) {
+          float pr[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            pr[e] = fast_exp2(fmaf(sc(c8 * 8 + e), scale_log2, neg_m));   // exp2(-inf) = 0 for masked keys
+            ls[e & 3] += pr[e];
+          }
+          // 16-byte chunk c8 of the row, swizzled with the row
+          st_shared_v4(prow + ((c8 ^ (row & 7)) << 4), pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]),
+                       pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
+        }
+        l = l * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+        GB_PROF(2);
+        fence_proxy_async();            // the tensor core reads P through the async proxy
+        tc_fence_before_sync();         // this thread's reads of S are over
+        mbar_arrive(smem_u32(&p_ready[grp][gt & 1]));
+        GB_PROF(3);
+        if (j > 0) fold(gt - 1);
+        GB_PROF(4);
+        corr_saved = corr;
       }
+      if (ok) fold(gt - 1);
+      GB_PROF(5);
+      // ---- merge the two groups: the second hands its sums over through its own P buffers
+      // (its last product has been read from them: fold waited for it), [channel][row] floats
+      if (grp == 1 && ok) {
+#pragma unroll
+        for (int ch = 0; ch < HD; ++ch) xo[ch * QROWS + row] = o_acc[ch];
+        other_ml[row][0] = m;
+        other_ml[row][1] = l;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(GROUPS * 128) : "memory");
+      if (grp == 0 && ok && row < w.nrows && !*(volatile int*)&abort_s) {
+        const float m2 = other_ml[row][0], l2 = other_ml[row][1];
+        const float mt = fmaxf(m, m2);
+        const float f1 = m == -INFINITY ? 0.f : fast_exp2((m - mt) * scale_log2);
+        const float f2 = m2 == -INFINITY ? 0.f : fast_exp2((m2 - mt) * scale_log2);
+        const float lt = l * f1 + l2 * f2;
+        const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+        const float a1 = f1 * inv, a2 = f2 * inv;
+        __nv_bfloat16* dst = p.out + ((size_t)(w.q_begin + w.tok0 + row / p.g) * p.Hq + w.kvh * p.g + row % p.g) * HD;
+#pragma unroll
+        for (int ch = 0; ch < HD; ch += 8) {
+          float t[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) t[e] = o_acc[ch + e] * a1 + xo[(ch + e) * QROWS + row] * a2;
+          uint4 wv;
+          wv.x = pack_bf16(t[0], t[1]);
+          wv.y = pack_bf16(t[2], t[3]);
+          wv.z = pack_bf16(t[4], t[5]);
+          wv.w = pack_bf16(t[6], t[7]);
+          *reinterpret_cast<uint4*>(dst + ch) = wv;
+        }
+      }
+      // the second group's next probabilities go where its sums were just read
+      asm volatile("bar.sync 1, %0;" ::"n"(GROUPS * 128) : "memory");
+      GB_PROF(6);
     }
-    if (!ok) abort_s = 1;
+    if (threadIdx.x == 64) GB_PROF_FLUSH(0, gt);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -444,11 +682,28 @@ int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "attention_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((max_q_len + tokens_per_tile - 1) / tokens_per_tile, p.Hkv, R);
+  const int q_tiles = (max_q_len + tokens_per_tile - 1) / tokens_per_tile;
+  const long long total = (long long)q_tiles * p.Hkv * R;
+  if (total > 0x7fffffff) return gb::fail(GB_UNSUPPORTED, "attention_tc: %lld pieces of work", total);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  dim3 grid((unsigned)(total < sms ? total : sms), 1, 1);
   return gb::check_pdl_launch(gb::launch_pdl(attention_tile_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream,
-                                             dim3(1, 1, 1), qm, km, vm, p),
+                                             dim3(1, 1, 1), qm, km, vm, p, q_tiles, (int)total),
                               "attention_tc (tile)");
 }
+
+#ifdef GB_ATTN_PROFILE
+extern "C" __attribute__((visibility("default"))) int gb_attention_prof(unsigned long long* host_out) {
+  if (cudaMemcpyFromSymbol(host_out, g_prof, sizeof(unsigned long long) * 24) != cudaSuccess) return 1;
+  unsigned long long zero[24] = {0};
+  return cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int tile_tc_error_check() {
   int v = 0;
