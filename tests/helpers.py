@@ -29,7 +29,15 @@ TINY_C = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_siz
               vocab_size=331, rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
               max_position_embeddings=192, sliding_window=24)
 
-TINY = {"A": (TINY_A, 0, None), "B": (TINY_B, 1, ("normal_about_one", 0.1)), "C": (TINY_C, 2, None)}
+# head size 64 (the size the tcgen05 prompt attention takes), groups of two, one windowed layer
+TINY_D = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=128, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=320,
+              vocab_size=500, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+              max_position_embeddings=512, sliding_window=160,
+              layer_types=["full_attention", "sliding_attention"])
+
+TINY = {"A": (TINY_A, 0, None), "B": (TINY_B, 1, ("normal_about_one", 0.1)), "C": (TINY_C, 2, None),
+        "D": (TINY_D, 3, None)}
 
 _DIRS = {}
 

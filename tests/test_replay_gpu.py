@@ -19,7 +19,7 @@ def up64(n):
     return (n + 63) // 64 * 64
 
 
-@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")],
+@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B", "C", "D") for d in ("float32", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def run(request):
     name, dtype = request.param
@@ -110,6 +110,26 @@ def test_mixed_requests_reusing_pages(run):
     assert most_live == 4
     for i in range(len(lens)):
         assert_close(np.concatenate(got[i]), refs[i], dtype, f"mixed, request {i}")
+
+
+def test_long_prompt_across_key_tiles(run):
+    """Prompts longer than one 128-key tile of the prompt attention, whole and in portions that end
+    inside, at and just after a tile's edge, then decoded; a window shorter than the prompt."""
+    name, dtype, tr = run
+    if name != "D":
+        pytest.skip("the configuration with room for 300 tokens")
+    toks = random_tokens(name, 300, 41)
+    ref = plain_logits(name, STORE[dtype], toks)
+    out = tr.step([("t", toks, range(300))], end=["t"])
+    assert_close(out, ref, dtype, "whole, 300 tokens")
+    cuts = [127, 1, 2, 126, 33]
+    pos, outs = 0, []
+    for c in cuts:
+        outs.append(tr.step([("u", toks[pos:pos + c], range(c))]))
+        pos += c
+    for i in range(pos, 300):
+        outs.append(tr.step([("u", [toks[i]], [0])], end=["u"] if i == 299 else []))
+    assert_close(np.concatenate(outs), ref, dtype, "portions across tiles, then decoded")
 
 
 def test_every_way_of_cutting_gives_the_same_logits_in_32_bit(run):
