@@ -516,6 +516,127 @@ __device__ __forceinline__ void epilogue_store16<__nv_bfloat16>(__nv_bfloat16* p
   }
 }
 
+// The epilogue of one 128 x BN tile for the thread that owns token `row` (a TMEM lane): taddr is the
+// lane's address of the tile's first column, n0 the tile's first output column (packed row for
+// the SiLU-gate).
+template <int BN, int EPI, typename OT>
+__device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, OT* __restrict__ out, int ldo,
+                                              int rows_m, int rows_n, bool vec, const RopeArgs& ra) {
+  if (EPI == EPI_ROPE) {
+    // This thread holds one token's row: whole heads, so both channels of every rotation pair.
+    const int hd = ra.head_dim, half = hd >> 1;
+    const bool token_ok = row < rows_m;
+    const int pos = token_ok ? ra.positions[row] : 0;
+    const int req = token_ok ? ra.token_req[row] : 0;
+#pragma unroll 1
+    for (int hc = 0; hc < BN && n0 + hc < rows_n; hc += hd) {
+      const int head = (n0 + hc) / hd;
+      const bool rotate = ra.inv_freq != nullptr && head < ra.heads + ra.kv_heads;
+      __nv_bfloat16* dst = token_ok ? rope_destination(ra, row, req, pos, head, 0) : nullptr;
+      const bool split_halves = rotate && !ra.interleaved && half >= 16;
+#pragma unroll 1
+      for (int dd = 0; dd < (split_halves ? half : hd); dd += 16) {
+        uint32_t ra_[16], rb_[16];
+        tmem_ld_16(taddr + hc + dd, ra_);
+        if (split_halves) tmem_ld_16(taddr + hc + half + dd, rb_);
+        tmem_ld_wait();
+        if (!dst) continue;
+        float a[16], b[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          a[j] = __uint_as_float(ra_[j]);
+          b[j] = split_halves ? __uint_as_float(rb_[j]) : 0.f;
+        }
+        if (split_halves) {
+          // channels dd .. dd + 15 pair with half + dd ..
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float sn, cs;
+            sincosf((float)pos * ra.inv_freq[dd + j], &sn, &cs);
+            const float x = a[j], y = b[j];
+            a[j] = x * cs - y * sn;
+            b[j] = x * sn + y * cs;
+          }
+          epilogue_store16<__nv_bfloat16>(dst + dd, a, true);
+          epilogue_store16<__nv_bfloat16>(dst + half + dd, b, true);
+        } else {
+          if (rotate) {
+            // pairs inside the chunk: (2k, 2k + 1), or for a head of 16 channels (k, k + 8)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int ia = ra.interleaved ? 2 * k : k, ib = ra.interleaved ? 2 * k + 1 : k + 8;
+              float sn, cs;
+              sincosf((float)pos * ra.inv_freq[ra.interleaved ? (dd >> 1) + k : k], &sn, &cs);
+              const float x = a[ia], y = a[ib];
+              a[ia] = x * cs - y * sn;
+              a[ib] = x * sn + y * cs;
+            }
+          }
+          epilogue_store16<__nv_bfloat16>(dst + dd, a, true);
+        }
+      }
+    }
+  } else if (EPI == EPI_SWIGLU) {
+    // columns [128 q, 128 q + 64) of the tile are gate values, the next 64 the up values of
+    // the same features: feature = 64 * (packed row / 128) + offset
+#pragma unroll 1
+    for (int q = 0; q < BN / 128; ++q) {
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 16) {
+        uint32_t r0[16], r1[16];
+        tmem_ld_16(taddr + q * 128 + c, r0);
+        tmem_ld_16(taddr + q * 128 + 64 + c, r1);
+        tmem_ld_wait();
+        const int col = (n0 >> 1) + q * 64 + c;      // output feature of the first of 16
+        if (row >= rows_m || col >= rows_n) continue;
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = silu_gate_fast(__uint_as_float(r0[j]), __uint_as_float(r1[j]));
+        OT* p = out + (size_t)row * ldo + col;
+        if (col + 16 <= rows_n) {
+          epilogue_store16<OT>(p, v, vec);
+        } else {
+          for (int j = 0; j < 16 && col + j < rows_n; ++j) store_value<OT>(p + j, v[j]);
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 16) {
+    uint32_t r0[16];
+    tmem_ld_16(taddr + c, r0);
+    tmem_ld_wait();
+    const int col = n0 + c;
+    if (row >= rows_m || col >= rows_n) continue;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]);
+    OT* p = out + (size_t)row * ldo + col;
+    if (col + 16 <= rows_n) {
+      if (EPI == EPI_ACCUMULATE) {
+        if (vec) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 old = reinterpret_cast<const float4*>(p)[i];
+            v[4 * i] += old.x; v[4 * i + 1] += old.y; v[4 * i + 2] += old.z; v[4 * i + 3] += old.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] += gb::to_float<OT>(p[j]);
+        }
+      }
+      epilogue_store16<OT>(p, v, vec);
+    } else {
+      for (int j = 0; j < 16 && col + j < rows_n; ++j) {
+        float x = v[j];
+        if (EPI == EPI_ACCUMULATE) x += gb::to_float<OT>(p[j]);
+        store_value<OT>(p + j, x);
+      }
+    }
+  }
+  }
+}
+
 // EPI_SWIGLU: the weight rows are packed gate/up groups; rows_n counts the output features and the
 // tiles run over the packed rows (twice as many).
 template <int BN, int EPI, typename OT>
@@ -654,119 +775,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
       tc_fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + as * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      if (EPI == EPI_ROPE) {
-        // This thread holds one token's row: whole heads, so both channels of every rotation pair.
-        const int hd = ra.head_dim, half = hd >> 1;
-        const bool token_ok = row < rows_m;
-        const int pos = token_ok ? ra.positions[row] : 0;
-        const int req = token_ok ? ra.token_req[row] : 0;
-#pragma unroll 1
-        for (int hc = 0; hc < BN && n0 + hc < rows_n; hc += hd) {
-          const int head = (n0 + hc) / hd;
-          const bool rotate = ra.inv_freq != nullptr && head < ra.heads + ra.kv_heads;
-          __nv_bfloat16* dst = token_ok ? rope_destination(ra, row, req, pos, head, 0) : nullptr;
-          const bool split_halves = rotate && !ra.interleaved && half >= 16;
-#pragma unroll 1
-          for (int dd = 0; dd < (split_halves ? half : hd); dd += 16) {
-            uint32_t ra_[16], rb_[16];
-            tmem_ld_16(taddr + hc + dd, ra_);
-            if (split_halves) tmem_ld_16(taddr + hc + half + dd, rb_);
-            tmem_ld_wait();
-            if (!dst) continue;
-            float a[16], b[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              a[j] = __uint_as_float(ra_[j]);
-              b[j] = split_halves ? __uint_as_float(rb_[j]) : 0.f;
-            }
-            if (split_halves) {
-              // channels dd .. dd + 15 pair with half + dd ..
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                float sn, cs;
-                sincosf((float)pos * ra.inv_freq[dd + j], &sn, &cs);
-                const float x = a[j], y = b[j];
-                a[j] = x * cs - y * sn;
-                b[j] = x * sn + y * cs;
-              }
-              epilogue_store16<__nv_bfloat16>(dst + dd, a, true);
-              epilogue_store16<__nv_bfloat16>(dst + half + dd, b, true);
-            } else {
-              if (rotate) {
-                // pairs inside the chunk: (2k, 2k + 1), or for a head of 16 channels (k, k + 8)
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                  const int ia = ra.interleaved ? 2 * k : k, ib = ra.interleaved ? 2 * k + 1 : k + 8;
-                  float sn, cs;
-                  sincosf((float)pos * ra.inv_freq[ra.interleaved ? (dd >> 1) + k : k], &sn, &cs);
-                  const float x = a[ia], y = a[ib];
-                  a[ia] = x * cs - y * sn;
-                  a[ib] = x * sn + y * cs;
-                }
-              }
-              epilogue_store16<__nv_bfloat16>(dst + dd, a, true);
-            }
-          }
-        }
-      } else if (EPI == EPI_SWIGLU) {
-        // columns [128 q, 128 q + 64) of the tile are gate values, the next 64 the up values of
-        // the same features: feature = 64 * (packed row / 128) + offset
-#pragma unroll 1
-        for (int q = 0; q < BN / 128; ++q) {
-#pragma unroll 1
-          for (int c = 0; c < 64; c += 16) {
-            uint32_t r0[16], r1[16];
-            tmem_ld_16(taddr + q * 128 + c, r0);
-            tmem_ld_16(taddr + q * 128 + 64 + c, r1);
-            tmem_ld_wait();
-            const int col = (n0 >> 1) + q * 64 + c;      // output feature of the first of 16
-            if (row >= rows_m || col >= rows_n) continue;
-            float v[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_gate_fast(__uint_as_float(r0[j]), __uint_as_float(r1[j]));
-            OT* p = out + (size_t)row * ldo + col;
-            if (col + 16 <= rows_n) {
-              epilogue_store16<OT>(p, v, vec);
-            } else {
-              for (int j = 0; j < 16 && col + j < rows_n; ++j) store_value<OT>(p + j, v[j]);
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        uint32_t r0[16];
-        tmem_ld_16(taddr + c, r0);
-        tmem_ld_wait();
-        const int col = n0 + c;
-        if (row >= rows_m || col >= rows_n) continue;
-        float v[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]);
-        OT* p = out + (size_t)row * ldo + col;
-        if (col + 16 <= rows_n) {
-          if (EPI == EPI_ACCUMULATE) {
-            if (vec) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float4 old = reinterpret_cast<const float4*>(p)[i];
-                v[4 * i] += old.x; v[4 * i + 1] += old.y; v[4 * i + 2] += old.z; v[4 * i + 3] += old.w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] += gb::to_float<OT>(p[j]);
-            }
-          }
-          epilogue_store16<OT>(p, v, vec);
-        } else {
-          for (int j = 0; j < 16 && col + j < rows_n; ++j) {
-            float x = v[j];
-            if (EPI == EPI_ACCUMULATE) x += gb::to_float<OT>(p[j]);
-            store_value<OT>(p + j, x);
-          }
-        }
-      }
-      }
+      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, ra);
       // every read of this accumulator stage has completed: hand it back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
@@ -776,6 +785,166 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// --------------------------------------------------------------------------
+// Many tokens, CTA pairs: two CTAs of a cluster share 256 x 256 tiles. Each CTA loads its 128 token
+// rows and its half (128 rows) of the weight tile; one thread of the even CTA issues products with
+// M = 256 that read both CTAs' shared memory and leave each CTA's 128 rows in its own tensor memory.
+// A CTA thus fetches 32 KB per 64-deep step instead of 48 KB for the same work: the stream of
+// operands from L2, which bounds the single-CTA kernel, is cut by a third. Six stages; the two
+// accumulator stages and the epilogue are as in the single-CTA kernel, each CTA for its own rows.
+// Barriers: `full` lives in the even CTA and counts both CTAs' TMA bytes; `empty` and `acc_full`
+// are completed in both CTAs at once by the issuer's commits; `acc_empty` lives in the even CTA and
+// takes one arrival per epilogue warp of both CTAs.
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGE_BYTES = BM * BK * 2 + (PAIR_BN / 2) * BK * 2;      // 32 KB per CTA
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+
+template <int EPI, typename OT>
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
+                    OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m, int tiles_n) {
+  constexpr int BN = PAIR_BN, STAGES = PAIR_STAGES;
+  constexpr int TMEM_COLS = 2 * BN;               // two accumulator stages
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();         // 0: issues the products
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int num_kb = (K + BK - 1) / BK;
+  const int total_tiles = tiles_m * tiles_n;
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&acc_full[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), 8);      // one arrival per epilogue warp of both CTAs
+    }
+    abort_s = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tensormap(&map_m);
+    prefetch_tensormap(&map_n);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&tmem_base_s), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive_wait();        // both CTAs' barriers exist before either signals the other's
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* aborted = &abort_s;
+  gb::pdl_launch_dependents();
+  gb::pdl_wait();     // the activations, and for an accumulating epilogue the output, come from earlier kernels
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ producer (both CTAs)
+      int s = 0, par = 1, issued = 0;
+      for (int tile = pair; tile < total_tiles && !*aborted; tile += pairs) {
+        const int m0 = (tile % tiles_m) * (2 * BM) + (int)rank * BM;
+        const int n0 = (tile / tiles_m) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[s]), par)) {
+            atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
+            *aborted = 1;
+          }
+          if (*aborted) break;
+          const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);     // the even CTA's barrier
+          const uint32_t base = tiles + s * PAIR_STAGE_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[s]), 2 * PAIR_STAGE_BYTES);
+          tma_load_2d_pair(base, &map_m, bar, kb * BK, m0);
+          tma_load_2d_pair(base + BM * BK * 2, &map_n, bar, kb * BK, n0);
+          ++issued;
+          if (++s == STAGES) s = 0, par ^= 1;
+        }
+      }
+      if (*aborted && issued > 0) {
+        // wind down: the copies in flight (counted on the even CTA's barriers) need microseconds
+        // to land; give them two milliseconds before the CTA's shared memory is given up
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ------------------------------------------------------------ MMA issuer (even CTA)
+      constexpr uint32_t idesc = instr_desc_bf16(2 * BM, BN);
+      const uint64_t da0 = smem_desc_sw128(tiles), db0 = smem_desc_sw128(tiles + BM * BK * 2);
+      int s = 0, par = 0, t = 0;
+      for (int tile = pair; tile < total_tiles && !*aborted; tile += pairs, ++t) {
+        const int as = t & 1;
+        if (!mbar_wait(smem_u32(&acc_empty[as]), ((t >> 1) & 1) ^ 1)) {   // both epilogues have drained this stage
+          atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+          *aborted = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t acc = tmem_base + as * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&full_bar[s]), par)) {
+            atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
+            *aborted = 1;
+          }
+          if (*aborted) break;
+          tc_fence_after_sync();
+          const uint64_t da = da0 + (uint64_t)(s * (PAIR_STAGE_BYTES >> 4)), db = db0 + (uint64_t)(s * (PAIR_STAGE_BYTES >> 4));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) mma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, kb > 0 || k > 0);
+          mma_commit_pair(smem_u32(&empty_bar[s]), 3);      // the stage is free in both CTAs
+          if (++s == STAGES) s = 0, par ^= 1;
+        }
+        mma_commit_pair(smem_u32(&acc_full[as]), 3);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue warps (both CTAs, own rows)
+    const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4)
+    const bool vec = (((uintptr_t)out) & 15) == 0 && ((size_t)ldo * sizeof(OT)) % 16 == 0;
+    const RopeArgs no_rope{};
+    int t = 0;
+    for (int tile = pair; tile < total_tiles; tile += pairs, ++t) {
+      const int as = t & 1;
+      const int m0 = (tile % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (tile / tiles_m) * BN;
+      bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
+      if (!have && lane == 0) {
+        atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+        *aborted = 1;
+      }
+      if (!have || *aborted) break;
+      tc_fence_after_sync();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + as * BN + ((uint32_t)(quarter * 32) << 16);
+      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, no_rope);
+      // every read of this accumulator stage has completed: hand it back to the issuer
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(smem_u32(&acc_empty[as]));
+        else mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[as]), 0));
+      }
+    }
+  }
+  // Neither CTA may leave, or give its tensor memory back, while the other's products or copies may
+  // still touch it.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive_wait();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
 // ------------------------------------------------------------------ host side
@@ -948,6 +1117,25 @@ int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int
                               "gemm_tc (persistent)");
 }
 
+// 256 x 256 tiles on CTA pairs (clusters of two).
+template <int EPI, typename OT>
+int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int tokens, int weight_rows,
+                int out_features, int K, cudaStream_t stream) {
+  auto kernel = gemm_tc_pair_kernel<EPI, OT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
+    if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tiles_m = (tokens + 2 * BM - 1) / (2 * BM), tiles_n = (weight_rows + PAIR_BN - 1) / PAIR_BN;
+  const int total = tiles_m * tiles_n, most = sm_count() / 2;
+  const int pairs = total < most ? total : most;
+  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(2 * pairs), dim3(P_THREADS), PAIR_SMEM_BYTES, stream, dim3(2, 1, 1),
+                                             mm, mn, out, ldo, tokens, out_features, K, tiles_m, tiles_n),
+                              "gemm_tc (pairs)");
+}
+
 // Tile width for many tokens: the one that needs fewer rounds over the SMs (a 256-wide tile costs
 // two 128-wide ones but reads each operand half as often); ties go to the wide tile.
 int pick_tile_width(int rows_m, int rows_n) {
@@ -1010,6 +1198,21 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
     return dispatch_cluster<64>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
+  static const bool pairs_on = [] {
+    const char* v = getenv("GARUDA_B200_PAIRS");
+    return !(v && v[0] == '0');
+  }();
+  if (pairs_on && Mx >= 2 * BM && weight_rows >= PAIR_BN) {
+    // each CTA of a pair loads 128 rows of the weight tile
+    if ((rc = tensor_map_2d(w, weight_rows, K, PAIR_BN / 2, &mn))) return rc;
+    if (epi == EPI_SWIGLU)
+      return launch_pair<EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream);
+    if (epi == EPI_ACCUMULATE)
+      return launch_pair<EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);
+    if (out_dtype == GB_F32)
+      return launch_pair<EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);
+    return launch_pair<EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream);
+  }
   const int width = pick_tile_width(Mx, weight_rows);
   if ((rc = tensor_map_2d(w, weight_rows, K, width, &mn))) return rc;
 #define GB_PERSISTENT(BN_)                                                                                         \
