@@ -483,7 +483,18 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
 // one of two accumulator stages in tensor memory, warps 2-5 drain the other
 // stage (tcgen05.ld, epilogue arithmetic, 16-byte stores), so the epilogue of a
 // tile runs under the matrix product of the next.
-constexpr int P_THREADS = 192;
+// Epilogue warps of the many-token kernels: two per lane quarter, each with half of a tile's columns
+// (twice the loads and stores in flight), except for the rotation's epilogue, whose threads need
+// whole heads and many registers.
+__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == EPI_ROPE ? 4 : 8; }
+__host__ __device__ constexpr int p_threads(int epi) { return 64 + 32 * epilogue_warps(epi); }
+// The columns [begin, end) of a BN-wide tile for the first or second warp of a quarter.
+__device__ __forceinline__ void epilogue_columns(int epi, int bn, int which, int& begin, int& end) {
+  const int unit = epi == EPI_SWIGLU ? 128 : 32;
+  const int mid = epilogue_warps(epi) == 4 ? bn : ((bn / 2 + unit - 1) / unit) * unit;
+  begin = which == 0 ? 0 : mid;
+  end = which == 0 ? mid : bn;
+}
 
 template <typename OT>
 __device__ __forceinline__ void epilogue_store16(OT* p, const float (&v)[16], bool vec);
@@ -516,12 +527,105 @@ __device__ __forceinline__ void epilogue_store16<__nv_bfloat16>(__nv_bfloat16* p
   }
 }
 
+// For the accumulating epilogue of a whole tile: the residual of the warp's first block of 32
+// columns (lane: column, entries: the warp's 32 rows), asked for while the tile's products still run.
+template <int BN, int EPI, typename OT>
+__device__ __forceinline__ void epilogue_prefetch(float (&first)[32], int row, int n0, const OT* __restrict__ out, int ldo,
+                                                  int rows_m, int rows_n, int c_begin) {
+  if (EPI != EPI_ACCUMULATE || n0 + BN > rows_n) return;
+  const int lane = threadIdx.x & 31;
+  const int row0 = row - lane;
+  const int rows_valid = min(32, rows_m - row0);
+  const OT* gbase = out + (size_t)row0 * ldo + n0 + lane + c_begin;
+#pragma unroll
+  for (int rr = 0; rr < 32; ++rr) first[rr] = rr < rows_valid ? gb::to_float<OT>(gbase[(size_t)rr * ldo]) : 0.f;
+}
+
 // The epilogue of one 128 x BN tile for the thread that owns token `row` (a TMEM lane): taddr is the
 // lane's address of the tile's first column, n0 the tile's first output column (packed row for
-// the SiLU-gate).
+// the SiLU-gate), turn this warp's 32 x 33 floats of shared memory. Two warps share a lane
+// quarter: each takes the columns [c_begin, c_end) (multiples of 128); the rotation's epilogue, which
+// needs whole heads, and the paths for ragged tiles are run by the first of them alone.
 template <int BN, int EPI, typename OT>
 __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, OT* __restrict__ out, int ldo,
-                                              int rows_m, int rows_n, bool vec, const RopeArgs& ra) {
+                                              int rows_m, int rows_n, bool vec, const RopeArgs& ra, float* turn,
+                                              int c_begin, int c_end, const float (&first)[32]) {
+  // Whole tiles, the usual case: 32 columns at a time, turned round in shared memory. A thread holds
+  // a row of the accumulator, so stores straight from its registers touch 32 different lines per
+  // instruction; after the turn a warp's instruction covers 32 consecutive columns of one row, and
+  // the residual of all 32 rows is asked for before any of it is used.
+  if ((EPI == EPI_STORE || EPI == EPI_ACCUMULATE) && n0 + BN <= rows_n) {
+    const int lane = threadIdx.x & 31;
+    const int row0 = row - lane;                               // the warp's first row
+    const int rows_valid = min(32, rows_m - row0);             // may be <= 0
+    OT* gbase = out + (size_t)row0 * ldo + n0 + lane;
+    constexpr bool ACC = EPI == EPI_ACCUMULATE;
+    // the residual of a block is asked for one block ahead; the first block's before the tile's
+    // products have finished (first: the caller's prefetch)
+    float old_cur[ACC ? 32 : 1], old_nxt[ACC ? 32 : 1];
+    auto fetch = [&](float (&dst)[ACC ? 32 : 1], int c) {
+      if (ACC) {
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr)
+          dst[ACC ? rr : 0] = rr < rows_valid ? gb::to_float<OT>(gbase[(size_t)rr * ldo + c]) : 0.f;
+      }
+    };
+    if (ACC) {
+#pragma unroll
+      for (int rr = 0; rr < 32; ++rr) old_cur[ACC ? rr : 0] = first[ACC ? rr : 0];
+    }
+    constexpr int BLOCKS = BN / 32 / (epilogue_warps(EPI) / 4);     // blocks of 32 columns per warp
+#pragma unroll
+    for (int k = 0; k < BLOCKS; ++k) {
+      const int c = c_begin + 32 * k;
+      if (c >= c_end) break;
+      uint32_t r[32];
+      tmem_ld_32(taddr + c, r);
+      if (k + 1 < BLOCKS && c + 32 < c_end) fetch(old_nxt, c + 32);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) turn[lane * 33 + j] = __uint_as_float(r[j]);
+      __syncwarp();
+#pragma unroll
+      for (int rr = 0; rr < 32; ++rr) {
+        float v = turn[rr * 33 + lane];
+        if (ACC) v += old_cur[ACC ? rr : 0];
+        if (rr < rows_valid) store_value<OT>(gbase + (size_t)rr * ldo + c, v);
+      }
+      __syncwarp();
+      if (ACC) {
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr) old_cur[ACC ? rr : 0] = old_nxt[ACC ? rr : 0];
+      }
+    }
+    return;
+  }
+  if (EPI == EPI_SWIGLU && vec && (n0 >> 1) + BN / 2 <= rows_n) {
+    // columns [128 q, 128 q + 64) of the tile are gate values, the next 64 the up values of the same
+    // 64 features; 32 features at a time, 16-byte stores from the thread's own row
+    const bool row_ok = row < rows_m;
+    OT* prow = out + (size_t)(row_ok ? row : 0) * ldo + (n0 >> 1);
+#pragma unroll 1
+    for (int q = c_begin / 128; q < c_end / 128; ++q) {
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t g_[32], u_[32];
+        tmem_ld_32(taddr + q * 128 + c, g_);
+        tmem_ld_32(taddr + q * 128 + 64 + c, u_);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = silu_gate_fast(__uint_as_float(g_[h * 16 + j]), __uint_as_float(u_[h * 16 + j]));
+          epilogue_store16<OT>(prow + q * 64 + c + h * 16, v, true);
+        }
+      }
+    }
+    return;
+  }
+  if (c_begin != 0) return;       // what follows runs once per lane quarter
   if (EPI == EPI_ROPE) {
     // This thread holds one token's row: whole heads, so both channels of every rotation pair.
     const int hd = ra.head_dim, half = hd >> 1;
@@ -640,7 +744,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
 // EPI_SWIGLU: the weight rows are packed gate/up groups; rows_n counts the output features and the
 // tiles run over the packed rows (twice as many).
 template <int BN, int EPI, typename OT>
-__global__ void __launch_bounds__(P_THREADS, 1)
+__global__ void __launch_bounds__(p_threads(EPI), 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
                           OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m,
                           int tiles_n, const RopeArgs ra) {
@@ -657,6 +761,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ float turn_buf[epilogue_warps(EPI)][32 * 33];       // per epilogue warp: a 32 x 32 block on its way round
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (K + BK - 1) / BK;
@@ -670,7 +775,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&acc_full[a]), 1);
-      mbar_init(smem_u32(&acc_empty[a]), 4);      // one arrival per epilogue warp
+      mbar_init(smem_u32(&acc_empty[a]), epilogue_warps(EPI));      // one arrival per epilogue warp
     }
     abort_s = 0;
     fence_barrier_init();
@@ -761,11 +866,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
   } else {
     // -------------------------------------------------------------- epilogue warps
     const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4)
+    int c_begin, c_end;
+    epilogue_columns(EPI, BN, (warp - 2) >> 2, c_begin, c_end);
     const bool vec = (((uintptr_t)out) & 15) == 0 && ((size_t)ldo * sizeof(OT)) % 16 == 0;
     int t = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
       const int as = t & 1;
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      float first[32];
+      epilogue_prefetch<BN, EPI, OT>(first, m0 + quarter * 32 + lane, n0, out, ldo, rows_m, rows_n, c_begin);
       bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
       if (!have && lane == 0) {
         atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
@@ -775,7 +884,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
       tc_fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + as * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, ra);
+      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, ra, turn_buf[warp - 2], c_begin, c_end, first);
       // every read of this accumulator stage has completed: hand it back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
@@ -792,21 +901,27 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
 // rows and its half (128 rows) of the weight tile; one thread of the even CTA issues products with
 // M = 256 that read both CTAs' shared memory and leave each CTA's 128 rows in its own tensor memory.
 // A CTA thus fetches 32 KB per 64-deep step instead of 48 KB for the same work: the stream of
-// operands from L2, which bounds the single-CTA kernel, is cut by a third. Six stages; the two
+// operands from L2 is cut by a third. Six (eight) stages; the two
 // accumulator stages and the epilogue are as in the single-CTA kernel, each CTA for its own rows.
 // Barriers: `full` lives in the even CTA and counts both CTAs' TMA bytes; `empty` and `acc_full`
 // are completed in both CTAs at once by the issuer's commits; `acc_empty` lives in the even CTA and
 // takes one arrival per epilogue warp of both CTAs.
-constexpr int PAIR_BN = 256;
-constexpr int PAIR_STAGE_BYTES = BM * BK * 2 + (PAIR_BN / 2) * BK * 2;      // 32 KB per CTA
-constexpr int PAIR_STAGES = 6;
-constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+// BN: the pair's tile width. 256 is what is launched: with 128 the products themselves took nearly
+// twice as long per flop when measured (a pair's product of 128 columns costs about as much as one of
+// 256), which outweighs hiding a lone tile's epilogue under a second tile.
+template <int BN>
+struct PairGeometry {
+  static constexpr int STAGE_BYTES = BM * BK * 2 + (BN / 2) * BK * 2;      // per CTA: 32 KB or 24 KB
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;                // 6 or 8
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+};
 
-template <int EPI, typename OT>
-__global__ void __launch_bounds__(P_THREADS, 1)
+template <int BN, int EPI, typename OT>
+__global__ void __launch_bounds__(p_threads(EPI), 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
                     OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m, int tiles_n) {
-  constexpr int BN = PAIR_BN, STAGES = PAIR_STAGES;
+  using PG = PairGeometry<BN>;
+  constexpr int STAGES = PG::STAGES, PAIR_STAGE_BYTES = PG::STAGE_BYTES;
   constexpr int TMEM_COLS = 2 * BN;               // two accumulator stages
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -815,6 +930,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ float turn_buf[epilogue_warps(EPI)][32 * 33];       // per epilogue warp: a 32 x 32 block on its way round
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();         // 0: issues the products
@@ -830,7 +946,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&acc_full[a]), 1);
-      mbar_init(smem_u32(&acc_empty[a]), 8);      // one arrival per epilogue warp of both CTAs
+      mbar_init(smem_u32(&acc_empty[a]), 2 * epilogue_warps(EPI));      // one arrival per epilogue warp of both CTAs
     }
     abort_s = 0;
     fence_barrier_init();
@@ -914,12 +1030,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
   } else {
     // -------------------------------------------------------------- epilogue warps (both CTAs, own rows)
     const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4)
+    int c_begin, c_end;
+    epilogue_columns(EPI, BN, (warp - 2) >> 2, c_begin, c_end);
     const bool vec = (((uintptr_t)out) & 15) == 0 && ((size_t)ldo * sizeof(OT)) % 16 == 0;
     const RopeArgs no_rope{};
     int t = 0;
     for (int tile = pair; tile < total_tiles; tile += pairs, ++t) {
       const int as = t & 1;
       const int m0 = (tile % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (tile / tiles_m) * BN;
+      float first[32];
+      epilogue_prefetch<BN, EPI, OT>(first, m0 + quarter * 32 + lane, n0, out, ldo, rows_m, rows_n, c_begin);
       bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
       if (!have && lane == 0) {
         atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
@@ -929,7 +1049,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
       tc_fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + as * BN + ((uint32_t)(quarter * 32) << 16);
-      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, no_rope);
+      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, no_rope, turn_buf[warp - 2], c_begin, c_end, first);
       // every read of this accumulator stage has completed: hand it back to the issuer
       tc_fence_before_sync();
       __syncwarp();
@@ -1112,26 +1232,27 @@ int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int
   const int tiles_m = (tokens + BM - 1) / BM, tiles_n = (weight_rows + BN - 1) / BN;
   const int total = tiles_m * tiles_n;
   const int grid = total < sm_count() ? total : sm_count();
-  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(grid), dim3(P_THREADS), G::SMEM_BYTES, stream, dim3(1, 1, 1), mm, mn, out,
+  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(grid), dim3(p_threads(EPI)), G::SMEM_BYTES, stream, dim3(1, 1, 1), mm, mn, out,
                                              ldo, tokens, out_features, K, tiles_m, tiles_n, ra),
                               "gemm_tc (persistent)");
 }
 
-// 256 x 256 tiles on CTA pairs (clusters of two).
-template <int EPI, typename OT>
+// 256 x BN tiles on CTA pairs (clusters of two).
+template <int BN, int EPI, typename OT>
 int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int tokens, int weight_rows,
                 int out_features, int K, cudaStream_t stream) {
-  auto kernel = gemm_tc_pair_kernel<EPI, OT>;
+  using PG = PairGeometry<BN>;
+  auto kernel = gemm_tc_pair_kernel<BN, EPI, OT>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PG::SMEM_BYTES);
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
-  const int tiles_m = (tokens + 2 * BM - 1) / (2 * BM), tiles_n = (weight_rows + PAIR_BN - 1) / PAIR_BN;
+  const int tiles_m = (tokens + 2 * BM - 1) / (2 * BM), tiles_n = (weight_rows + BN - 1) / BN;
   const int total = tiles_m * tiles_n, most = sm_count() / 2;
   const int pairs = total < most ? total : most;
-  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(2 * pairs), dim3(P_THREADS), PAIR_SMEM_BYTES, stream, dim3(2, 1, 1),
+  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(2 * pairs), dim3(p_threads(EPI)), PG::SMEM_BYTES, stream, dim3(2, 1, 1),
                                              mm, mn, out, ldo, tokens, out_features, K, tiles_m, tiles_n),
                               "gemm_tc (pairs)");
 }
@@ -1202,16 +1323,23 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
     const char* v = getenv("GARUDA_B200_PAIRS");
     return !(v && v[0] == '0');
   }();
-  if (pairs_on && Mx >= 2 * BM && weight_rows >= PAIR_BN) {
-    // each CTA of a pair loads 128 rows of the weight tile
-    if ((rc = tensor_map_2d(w, weight_rows, K, PAIR_BN / 2, &mn))) return rc;
-    if (epi == EPI_SWIGLU)
-      return launch_pair<EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream);
-    if (epi == EPI_ACCUMULATE)
-      return launch_pair<EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);
-    if (out_dtype == GB_F32)
-      return launch_pair<EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);
-    return launch_pair<EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream);
+  if (pairs_on && Mx >= 2 * BM && weight_rows >= 256) {
+    // each CTA of a pair loads half of the weight tile's rows
+    if ((rc = tensor_map_2d(w, weight_rows, K, 128, &mn))) return rc;
+#define GB_PAIR(BN_)                                                                                              \
+  do {                                                                                                            \
+    if (epi == EPI_SWIGLU)                                                                                        \
+      return launch_pair<BN_, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, \
+                                                         stream);                                                 \
+    if (epi == EPI_ACCUMULATE)                                                                                    \
+      return launch_pair<BN_, EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);    \
+    if (out_dtype == GB_F32)                                                                                      \
+      return launch_pair<BN_, EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);         \
+    return launch_pair<BN_, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K,    \
+                                                      stream);                                                    \
+  } while (0)
+    GB_PAIR(256);
+#undef GB_PAIR
   }
   const int width = pick_tile_width(Mx, weight_rows);
   if ((rc = tensor_map_2d(w, weight_rows, K, width, &mn))) return rc;
