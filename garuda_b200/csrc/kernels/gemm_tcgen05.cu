@@ -131,7 +131,9 @@ struct Geometry {
   static constexpr int MAX_CLUSTER_RAW = 1 + (SMEM_LIMIT - STATIC_RESERVE - 1024 - PIPE_BYTES - EXTRA) / PARTIAL_BYTES;
   static constexpr int MAX_CLUSTER = !TRANS ? 1 : (MAX_CLUSTER_RAW < 1 ? 1 : MAX_CLUSTER_RAW < 8 ? MAX_CLUSTER_RAW : 8);
   // + slack to align the tiles to 1024 B
-  static constexpr int smem_bytes(int cluster) { return PIPE_BYTES + 1024 + EXTRA + (cluster - 1) * PARTIAL_BYTES; }
+  static constexpr int smem_bytes(int cluster, int stages = STAGES) {
+    return stages * STAGE_BYTES + 1024 + EXTRA + (cluster - 1) * PARTIAL_BYTES;
+  }
   static_assert(PIPE_BYTES + 1024 + EXTRA + STATIC_RESERVE <= SMEM_LIMIT, "tile and tables too large for shared memory");
   static constexpr int SMEM_BYTES = smem_bytes(1);
   static_assert(STAGES >= 2, "tile too large for shared memory");
@@ -162,10 +164,10 @@ template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(C_THREADS, 1)
 gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
                        OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int kb_per_rank,
-                       const RopeArgs ra) {
+                       const RopeArgs ra, const int stages) {
   constexpr bool DUAL_M = false;
   using G = Geometry<BN, false, false, true, rope_table_bytes(EPI, BN)>;
-  constexpr int STAGES = G::STAGES;
+  constexpr int STAGES = G::STAGES;          // the most; `stages` of them are used (fewer: two CTAs fit on an SM)
   constexpr int ACC = G::ACCUMULATORS;
   // With so few columns an MMA is over long before the next one that adds to the same accumulator
   // may start. The four MMAs of a K block therefore go to four accumulators of their own (four
@@ -193,7 +195,8 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // [rank - 1][ACC * BN columns][128 rows] floats: the threads of a warp (consecutive rows) write and
   // read consecutive words, so neither the remote stores nor the leader's loads collide on a bank
-  const uint32_t partials = tiles + G::PIPE_BYTES + rope_table_bytes(EPI, BN);
+  const uint32_t pipe_bytes = (uint32_t)stages * G::STAGE_BYTES;
+  const uint32_t partials = tiles + pipe_bytes + rope_table_bytes(EPI, BN);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -229,7 +232,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
       // The weights are written by no kernel: their first tiles are fetched before waiting for
       // the kernel in front; the tokens' tiles after.
       int issued = 0;
-      const int early = min(STAGES, num_kb);
+      const int early = min(stages, num_kb);
       for (int it = 0; it < early; ++it) {
         const uint32_t bar = smem_u32(&full_bar[it]);
         const uint32_t base = tiles + it * G::STAGE_BYTES;
@@ -244,9 +247,10 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
                     (kb_begin + it) * BK, n0);
         issued = it + 1;
       }
-      for (int it = early; it < num_kb; ++it) {
-        const int s = it % STAGES;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) & 1) ^ 1)) {
+      // the first `early` blocks filled stages 0 .. early - 1 in their first phase
+      int s = early == stages ? 0 : early, par = early == stages ? 0 : 1;
+      for (int it = early; it < num_kb; ++it, s = (s + 1 == stages ? 0 : s + 1), par ^= (s == 0)) {
+        if (!mbar_wait(smem_u32(&empty_bar[s]), par)) {
           atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
           abort_s = 1;
         }
@@ -261,9 +265,9 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
       }
       if (*(volatile int*)&abort_s) {
         // wind down: let the copies already in flight land before the CTA's shared memory is given up
-        for (int it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it) {
+        for (int it = issued > stages ? issued - stages : 0; it < issued; ++it) {
           const unsigned long long t0 = globaltimer_ns();
-          while (!mbar_try_wait(smem_u32(&full_bar[it % STAGES]), (it / STAGES) & 1)) {
+          while (!mbar_try_wait(smem_u32(&full_bar[it % stages]), (it / stages) & 1)) {
             if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
               atomicCAS(&g_error_word, 0, ERR_WAIT_DRAIN);
               break;
@@ -276,9 +280,9 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     if (lane == 0) {
       // -------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
-      for (int it = 0; it < num_kb; ++it) {
-        const int s = it % STAGES;
-        if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) {
+      int s = 0, par = 0;
+      for (int it = 0; it < num_kb; ++it, s = (s + 1 == stages ? 0 : s + 1), par ^= (s == 0)) {
+        if (!mbar_wait(smem_u32(&full_bar[s]), par)) {
           atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
           abort_s = 1;
           break;
@@ -310,7 +314,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     // before the first kernel of a chain starts, so they are read without waiting for the kernel
     // in front. The table is complete for every thread after the first barrier of the loop below.
     constexpr bool ROPE_EARLY = EPI == EPI_ROPE;
-    float (*rope_cs)[64] = reinterpret_cast<float (*)[64]>(smem_raw + (tiles - smem_u32(smem_raw)) + G::PIPE_BYTES);
+    float (*rope_cs)[64] = reinterpret_cast<float (*)[64]>(smem_raw + (tiles - smem_u32(smem_raw)) + pipe_bytes);
     float (*rope_sn)[64] = rope_cs + BN;
     long long* rope_slot = reinterpret_cast<long long*>(rope_sn + BN);   // element offset of the token's row, head 0; -1: no page
     if (ROPE_EARLY && rank == 0) {
@@ -1145,17 +1149,26 @@ int sm_count() {
 // so the CTAs should not outnumber the SMs; clusters of more than six are placed badly.
 // `active[s]`: whether clusters of size s can be resident at all (0: not asked yet, -1: no), kept by the
 // caller per kernel.
-template <typename Kernel, typename SmemFn>
-int pick_cluster_size(Kernel kernel, int* active, SmemFn smem_for, int tiles, int total_kb, int max_cluster) {
-  int best = 1;
+struct ClusterPlan { int split, stages; };
+
+// The cost of a plan in units of one K block's streaming time: a CTA costs about 13.5 blocks of set-up,
+// first-byte latency, reduction and tail besides its own blocks (timeline measurements). Two ways to
+// place the CTAs: one per SM with the full pipeline, or, with a pipeline short enough for two CTAs
+// to share an SM's shared memory, up to two per SM; CTAs that share an SM also share its path to L2:
+// 1.3 to 1.65 times the time of a CTA that has the SM to itself, by how many SMs hold two.
+template <typename Kernel, typename G>
+ClusterPlan pick_cluster_plan(Kernel kernel, int* active, int tiles, int total_kb) {
+  ClusterPlan best{1, G::STAGES};
   double best_cost = 1e30;
   const int sms = sm_count();
-  for (int s = 1; s <= max_cluster && s <= 6 && s <= total_kb; ++s) {
+  static const int force_split = [] { const char* v = getenv("GARUDA_B200_FORCE_SPLIT"); return v ? atoi(v) : 0; }();
+  static const int force_two = [] { const char* v = getenv("GARUDA_B200_FORCE_TWO"); return v ? atoi(v) : -1; }();
+  for (int s = 1; s <= G::MAX_CLUSTER && s <= 6 && s <= total_kb; ++s) {
     if (active[s] == 0) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(1, 148, s);
       cfg.blockDim = dim3(C_THREADS);
-      cfg.dynamicSmemBytes = smem_for(s);
+      cfg.dynamicSmemBytes = G::smem_bytes(s);
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
       attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = s;
@@ -1169,10 +1182,22 @@ int pick_cluster_size(Kernel kernel, int* active, SmemFn smem_for, int tiles, in
       active[s] = n;
     }
     if (active[s] < 1) continue;
+    if (force_split > 0 && s != force_split && force_split <= G::MAX_CLUSTER) continue;
     const int per = (total_kb + s - 1) / s;
-    const int rounds = (tiles * s + sms - 1) / sms;
-    const double cost = rounds * (per + 13.5);
-    if (cost < best_cost) { best_cost = cost; best = s; }
+    const int ctas = tiles * s;
+    // one CTA per SM
+    if (force_two != 1) {
+      const double cost = (double)((ctas + sms - 1) / sms) * (per + 13.5);
+      if (cost < best_cost) { best_cost = cost; best = ClusterPlan{s, G::STAGES}; }
+    }
+    // two per SM: the most stages that let two CTAs (and their 1 KB each of reserve) share 227 KB
+    int st2 = G::STAGES;
+    while (st2 > 2 && 2 * (G::smem_bytes(s, st2) + 2048) > SMEM_LIMIT) --st2;
+    if (force_two != 0 && 2 * (G::smem_bytes(s, st2) + 2048) <= SMEM_LIMIT && ctas > sms) {
+      const double share = 2 * ctas <= 3 * sms ? 1.3 : 1.65;      // measured at 1.2 and 1.8 CTAs per SM
+      const double cost = (double)((ctas + 2 * sms - 1) / (2 * sms)) * (per + 13.5) * share;
+      if (cost < best_cost) { best_cost = cost; best = ClusterPlan{s, st2}; }
+    }
   }
   return best;
 }
@@ -1194,13 +1219,13 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ld
   const int tiles_n = (tokens + BN - 1) / BN, tiles_m = (weight_rows + BM - 1) / BM;
   const int total_kb = (K + BK - 1) / BK;
   static int active[9] = {0};
-  int split = pick_cluster_size(kernel, active, [](int s) { return G::smem_bytes(s); }, tiles_n * tiles_m, total_kb,
-                                G::MAX_CLUSTER);
+  const ClusterPlan plan = pick_cluster_plan<decltype(kernel), G>(kernel, active, tiles_n * tiles_m, total_kb);
+  int split = plan.split;
   const int per = (total_kb + split - 1) / split;
   split = (total_kb + per - 1) / per;            // no rank without K blocks
   return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(tiles_n, tiles_m, split), dim3(C_THREADS),
-                                             G::smem_bytes(split), stream, dim3(1, 1, split), mm, mn, out, ldo, out_features,
-                                             tokens, K, per, ra),
+                                             G::smem_bytes(split, plan.stages), stream, dim3(1, 1, split), mm, mn, out, ldo,
+                                             out_features, tokens, K, per, ra, plan.stages),
                               "gemm_tc (cluster)");
 }
 
