@@ -281,6 +281,29 @@ GB_EXPORT int gb_rope_kv_append(const void* qkv, int in_dtype, int row_stride, v
   });
 }
 
+// out[t][i] = (cos, sin)((float)positions[t] * inv_freq[i]) for i < half: the rotation's angles
+// (garuda/src/simd/mod.rs:196-206) once per step, for every layer's fused epilogue to read.
+__global__ void rope_table_kernel(const int32_t* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ out, int T, int half) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * half) return;
+  const int t = idx / half, i = idx % half;
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+  out[idx] = make_float2(cs, sn);
+}
+
+// A plain launch on purpose: kernels after it that start early (programmatic dependent launch) may
+// read the table before their dependency wait, which is safe only because this kernel gives no
+// early start signal, so that they cannot begin before it has finished.
+GB_EXPORT int gb_rope_table(const int32_t* positions, const float* inv_freq, float* out, int T, int half,
+                            cudaStream_t stream) {
+  if (T <= 0 || half <= 0) return GB_OK;
+  const int n = T * half;
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, inv_freq, reinterpret_cast<float2*>(out), T, half);
+  return gb::check_launch("rope_table");
+}
+
 GB_EXPORT int gb_rope_inplace(float* x, int row_stride, int T, int H, int hd, const int32_t* positions,
                               const float* inv_freq, int interleaved, cudaStream_t stream) {
   if (T <= 0 || H <= 0) return GB_OK;

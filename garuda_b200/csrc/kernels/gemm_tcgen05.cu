@@ -54,7 +54,8 @@ enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROP
 
 // What the query/key/value epilogue needs: the output features are (heads + 2 kv_heads) heads of
 // head_dim; query and key heads are rotated at the token's position (garuda/src/simd/mod.rs:196-206,
-// angle = (float)pos * inv_freq[i] in 32-bit), queries go to q_out, rotated keys and raw values into
+// angle = (float)pos * inv_freq[i] in 32-bit; the cosines and sines are made once per step for all
+// layers by rope_table in elementwise.cu), queries go to q_out, rotated keys and raw values into
 // their pages (garuda/src/llama/mod.rs:784-791). head_dim divides 128, so no head straddles a tile.
 struct RopeArgs {
   __nv_bfloat16* q_out;          // [T, heads, head_dim]
@@ -63,7 +64,7 @@ struct RopeArgs {
   const int32_t* positions;      // [T]
   const int32_t* token_req;      // [T]
   const int32_t* block_table;    // [R, table_width]
-  const float* inv_freq;         // [head_dim / 2], or null: no rotation
+  const float2* cs;              // [T, head_dim / 2] (cos, sin) of every token's angles, or null: no rotation
   int table_width, heads, kv_heads, head_dim, interleaved, page_size;
 };
 
@@ -323,8 +324,10 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
       for (int e = t; e < BN * half; e += 128) {
         const int j = e >> lg, fi = e & (half - 1);
         float sn = 0.f, cs = 1.f;
-        if (ra.inv_freq != nullptr && n0 + j < rows_n)
-          sincosf((float)ra.positions[n0 + j] * ra.inv_freq[fi], &sn, &cs);
+        if (ra.cs != nullptr && n0 + j < rows_n) {
+          const float2 v = ra.cs[(size_t)(n0 + j) * half + fi];
+          cs = v.x, sn = v.y;
+        }
         rope_cs[j][fi] = cs;
         rope_sn[j][fi] = sn;
       }
@@ -437,7 +440,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
             if (row < rows_m) {
               const int hd = ra.head_dim, half = hd >> 1;
               const int head = row / hd, d = row % hd;
-              const bool rotate = ra.inv_freq != nullptr && head < ra.heads + ra.kv_heads;
+              const bool rotate = ra.cs != nullptr && head < ra.heads + ra.kv_heads;
               const bool low = ra.interleaved ? (d & 1) == 0 : d < half;
               const int partner = ra.interleaved ? (row_in_tile ^ 1) : (low ? row_in_tile + half : row_in_tile - half);
               if (ROPE_EARLY) {
@@ -636,10 +639,11 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
     const bool token_ok = row < rows_m;
     const int pos = token_ok ? ra.positions[row] : 0;
     const int req = token_ok ? ra.token_req[row] : 0;
+    const float2* tab = ra.cs + (size_t)(token_ok ? row : 0) * half;      // this token's cosines and sines
 #pragma unroll 1
     for (int hc = 0; hc < BN && n0 + hc < rows_n; hc += hd) {
       const int head = (n0 + hc) / hd;
-      const bool rotate = ra.inv_freq != nullptr && head < ra.heads + ra.kv_heads;
+      const bool rotate = ra.cs != nullptr && head < ra.heads + ra.kv_heads;
       __nv_bfloat16* dst = token_ok ? rope_destination(ra, row, req, pos, head, 0) : nullptr;
       const bool split_halves = rotate && !ra.interleaved && half >= 16;
 #pragma unroll 1
@@ -659,8 +663,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
           // channels dd .. dd + 15 pair with half + dd ..
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            float sn, cs;
-            sincosf((float)pos * ra.inv_freq[dd + j], &sn, &cs);
+            const float2 v = tab[dd + j];
+            const float cs = v.x, sn = v.y;
             const float x = a[j], y = b[j];
             a[j] = x * cs - y * sn;
             b[j] = x * sn + y * cs;
@@ -673,8 +677,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const int ia = ra.interleaved ? 2 * k : k, ib = ra.interleaved ? 2 * k + 1 : k + 8;
-              float sn, cs;
-              sincosf((float)pos * ra.inv_freq[ra.interleaved ? (dd >> 1) + k : k], &sn, &cs);
+              const float2 v = tab[ra.interleaved ? (dd >> 1) + k : k];
+              const float cs = v.x, sn = v.y;
               const float x = a[ia], y = a[ib];
               a[ia] = x * cs - y * sn;
               a[ib] = x * sn + y * cs;
@@ -1387,11 +1391,12 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
 
 // The query/key/value product with the rotation and the cache write in its epilogue:
 // x [Mx, K] times w [(heads + 2 kv_heads) * head_dim, K]^T; rotated queries to q_out [Mx, heads,
-// head_dim], rotated keys and raw values into their pages (all bfloat16). inv_freq null: no rotation.
+// head_dim], rotated keys and raw values into their pages (all bfloat16). cos_sin: [Mx, head_dim / 2, 2]
+// cosines and sines of every token's angles (rope_table in elementwise.cu), or null: no rotation.
 // head_dim must divide 128 (so that no head straddles a tile); returns GB_UNSUPPORTED otherwise.
 GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* q_out, void* k_pool, void* v_pool,
                              const int32_t* positions, const int32_t* token_req, const int32_t* block_table,
-                             int table_width, int heads, int kv_heads, int head_dim, const float* inv_freq,
+                             int table_width, int heads, int kv_heads, int head_dim, const float* cos_sin,
                              int interleaved, int page_size, cudaStream_t stream) {
   const int Nw = (heads + 2 * kv_heads) * head_dim;
   if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
@@ -1402,7 +1407,7 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_qkv: kv heads given without a cache to store them in");
   RopeArgs ra;
   ra.q_out = (__nv_bfloat16*)q_out; ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool;
-  ra.positions = positions; ra.token_req = token_req; ra.block_table = block_table; ra.inv_freq = inv_freq;
+  ra.positions = positions; ra.token_req = token_req; ra.block_table = block_table; ra.cs = reinterpret_cast<const float2*>(cos_sin);
   ra.table_width = table_width; ra.heads = heads; ra.kv_heads = kv_heads; ra.head_dim = head_dim;
   ra.interleaved = interleaved; ra.page_size = page_size;
   CUtensorMap mm, mn;

@@ -76,3 +76,5 @@ class StepContext:
     ws: Workspace
     ops: object
     dtype: torch.dtype
+    # what a step computes once for all its layers (the rotation's cosines and sines), by key
+    step_cache: dict = field(default_factory=dict)

@@ -73,6 +73,7 @@ class CudaOps:
                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                   c_int, c_void_p],
             "gb_rope_inplace": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+            "gb_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
             "gb_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
             "gb_residual_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
             "gb_gemm_simple": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -216,14 +217,34 @@ class CudaOps:
                   and tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim), "qkv_rope_append: pool shape")
             _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "qkv_rope_append: block table")
         _need(positions.dtype == torch.int32 and token_req.dtype == torch.int32, "qkv_rope_append: int32 indices")
-        if self.tc is not None and self.tc.qkv_rope_append(h, w_qkv, q_out, k_pool, v_pool, positions, token_req,
-                                                           block_table, heads, kv_heads, head_dim, rotary,
-                                                           page_size):
+        if self.tc is not None and self.tc.takes_qkv(h, w_qkv, q_out, head_dim):
+            table = None if rotary is None else self.rope_table(ctx, positions, rotary)
+            self.tc.qkv_rope_append(h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table, heads,
+                                    kv_heads, head_dim, table, None if rotary is None else rotary.interleaved,
+                                    page_size)
             return
         qkv = ctx.ws.get("qkv", (T, w_qkv.shape[0]), torch.float32)
         self.linear(h, w_qkv, qkv)
         self.rope_kv_append(qkv, q_out, k_pool, v_pool, positions, token_req, block_table, heads, kv_heads,
                             head_dim, rotary, page_size)
+
+    def rope_table(self, ctx, positions, rotary):
+        """``[T, head_dim / 2, 2]`` cosines and sines of every token's angles, made once per
+        step (kept in the step's context) for every layer's fused projection to read."""
+        half = rotary.head_dim // 2
+        key = ("rope_table", float(rotary.theta), int(rotary.head_dim), positions.data_ptr(), positions.shape[0])
+        cache = getattr(ctx, "step_cache", None)
+        if cache is not None and key in cache:
+            return cache[key]
+        T = positions.shape[0]
+        name = f"rope_table_{rotary.theta}_{rotary.head_dim}"
+        out = ctx.ws.get(name, (T, half, 2), torch.float32)
+        inv = self.inv_freq(rotary.theta, rotary.head_dim)
+        code = self.core.gb_rope_table(positions.data_ptr(), inv.data_ptr(), out.data_ptr(), T, half, self._stream())
+        self._check(self.core, code, "rope_table")
+        if cache is not None:
+            cache[key] = out
+        return out
 
     def rope_kv_append(self, qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
                        heads, kv_heads, head_dim, rotary, page_size):

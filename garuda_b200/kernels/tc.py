@@ -59,25 +59,28 @@ class TensorCoreKernels:
             return False
         return self._gemm(a, w, out, w.shape[0], 1 if accumulate else 0)
 
-    def qkv_rope_append(self, h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
-                        heads, kv_heads, head_dim, rotary, page_size) -> bool:
-        """The query/key/value product with the rotation and the cache write in its
-        epilogue. Takes head sizes that divide 128."""
+    def takes_qkv(self, h, w_qkv, q_out, head_dim) -> bool:
+        """Whether the fused query/key/value product takes these operands (head sizes that
+        divide 128, bfloat16, rows the TMA can address)."""
         M, K = h.shape
-        if (h.dtype != torch.bfloat16 or w_qkv.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16
-                or head_dim % 16 or 128 % head_dim
-                or not self.lib.gb_gemm_tc_supported(h.data_ptr(), w_qkv.data_ptr(), M, w_qkv.shape[0], K)):
-            return False
-        inv = None if rotary is None else self.ops.inv_freq(rotary.theta, head_dim)
+        return (h.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
+                and head_dim % 16 == 0 and 128 % head_dim == 0
+                and bool(self.lib.gb_gemm_tc_supported(h.data_ptr(), w_qkv.data_ptr(), M, w_qkv.shape[0], K)))
+
+    def qkv_rope_append(self, h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
+                        heads, kv_heads, head_dim, cos_sin, interleaved, page_size) -> None:
+        """The query/key/value product with the rotation and the cache write in its
+        epilogue. ``cos_sin``: ``CudaOps.rope_table`` of the step's positions, or None
+        (no rotation)."""
+        M, K = h.shape
         code = self.lib.gb_gemm_tc_qkv(
             h.data_ptr(), w_qkv.data_ptr(), M, K, q_out.data_ptr(),
             None if k_pool is None else k_pool.data_ptr(), None if v_pool is None else v_pool.data_ptr(),
             positions.data_ptr(), token_req.data_ptr(), None if block_table is None else block_table.data_ptr(),
             0 if block_table is None else block_table.shape[1], heads, kv_heads, head_dim,
-            None if inv is None else inv.data_ptr(), 0 if rotary is None else int(rotary.interleaved),
+            None if cos_sin is None else cos_sin.data_ptr(), 0 if not interleaved else 1,
             int(page_size), self.ops._stream())
         self.ops._check(self.lib, code, "gemm_tc_qkv")
-        return True
 
     def linear_swiglu(self, h, w_gate_up, act) -> bool:
         """``w_gate_up``: the packed layout of ``CudaOps.pack_gate_up``."""
