@@ -927,7 +927,8 @@ struct PairGeometry {
 template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(p_threads(EPI), 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
-                    OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m, int tiles_n) {
+                    OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m, int tiles_n,
+                    const RopeArgs ra) {
   using PG = PairGeometry<BN>;
   constexpr int STAGES = PG::STAGES, PAIR_STAGE_BYTES = PG::STAGE_BYTES;
   constexpr int TMEM_COLS = 2 * BN;               // two accumulator stages
@@ -1041,7 +1042,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
     int c_begin, c_end;
     epilogue_columns(EPI, BN, (warp - 2) >> 2, c_begin, c_end);
     const bool vec = (((uintptr_t)out) & 15) == 0 && ((size_t)ldo * sizeof(OT)) % 16 == 0;
-    const RopeArgs no_rope{};
     int t = 0;
     for (int tile = pair; tile < total_tiles; tile += pairs, ++t) {
       const int as = t & 1;
@@ -1057,7 +1057,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
       tc_fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + as * BN + ((uint32_t)(quarter * 32) << 16);
-      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, no_rope, turn_buf[warp - 2], c_begin, c_end, first);
+      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, ra, turn_buf[warp - 2], c_begin, c_end, first);
       // every read of this accumulator stage has completed: hand it back to the issuer
       tc_fence_before_sync();
       __syncwarp();
@@ -1269,7 +1269,7 @@ int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int
 // 256 x BN tiles on CTA pairs (clusters of two).
 template <int BN, int EPI, typename OT>
 int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int tokens, int weight_rows,
-                int out_features, int K, cudaStream_t stream) {
+                int out_features, int K, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
   using PG = PairGeometry<BN>;
   auto kernel = gemm_tc_pair_kernel<BN, EPI, OT>;
   static bool configured = false;
@@ -1282,7 +1282,7 @@ int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, 
   const int total = tiles_m * tiles_n, most = sm_count() / 2;
   const int pairs = total < most ? total : most;
   return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(2 * pairs), dim3(p_threads(EPI)), PG::SMEM_BYTES, stream, dim3(2, 1, 1),
-                                             mm, mn, out, ldo, tokens, out_features, K, tiles_m, tiles_n),
+                                             mm, mn, out, ldo, tokens, out_features, K, tiles_m, tiles_n, ra),
                               "gemm_tc (pairs)");
 }
 
@@ -1422,6 +1422,14 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
     return launch_cluster<64, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Nw, Nw, Mx, K, stream, ra);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
+  static const bool pairs_on = [] {
+    const char* v = getenv("GARUDA_B200_PAIRS");
+    return !(v && v[0] == '0');
+  }();
+  if (pairs_on && Mx >= 2 * BM && Nw >= 256) {
+    if ((rc = tensor_map_2d(w, Nw, K, 128, &mn))) return rc;
+    return launch_pair<256, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Mx, Nw, Nw, K, stream, ra);
+  }
   const int width = pick_tile_width(Mx, Nw);
   if ((rc = tensor_map_2d(w, Nw, K, width, &mn))) return rc;
   if (width == 256) return launch_persistent<256, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Mx, Nw, Nw, K, stream, ra);

@@ -160,7 +160,7 @@ def test_rotate_and_store(ops, interleaved, dtype):
 
 @pytest.mark.parametrize("interleaved", [False, True])
 @pytest.mark.parametrize("Hq,Hkv,hd,d", [(4, 2, 16, 64), (3, 1, 32, 96), (32, 4, 64, 256), (2, 2, 128, 72), (6, 3, 48, 72)])
-@pytest.mark.parametrize("T", [1, 11, 70, 200])
+@pytest.mark.parametrize("T", [1, 11, 70, 200, 300])
 def test_fused_projection_rotation_and_cache_write(ops, interleaved, Hq, Hkv, hd, d, T):
     """The query/key/value product with rotation and page write in its epilogue
     against the plain product followed by the plain rotate-and-store."""
