@@ -79,7 +79,13 @@ __device__ unsigned long long g_prof[24];
 #define GB_PROF(i) do { const long long t = clock64(); pacc[i] += t - pt0; pt0 = t; } while (0)
 #define GB_PROF_FLUSH(base, tiles_done) do { for (int i = 0; i < 8; ++i) if (pacc[i]) atomicAdd(&g_prof[(base) + i], (unsigned long long)pacc[i]); \
     atomicAdd(&g_prof[23], (unsigned long long)(tiles_done)); } while (0)
+// and a trace of CTA 0's events: (time in ns, event number, tile count)
+__device__ unsigned long long g_trace[3 * 8192];
+__device__ unsigned int g_trace_n;
+#define GB_TRACE(ev, tile) do { if (blockIdx.x == 0) { const unsigned int i_ = atomicAdd(&g_trace_n, 1u); if (i_ < 8192) { \
+    g_trace[3 * i_] = globaltimer_ns(); g_trace[3 * i_ + 1] = (ev); g_trace[3 * i_ + 2] = (unsigned long long)(tile); } } } while (0)
 #else
+#define GB_TRACE(ev, tile) do {} while (0)
 #define GB_PROF_DECL do {} while (0)
 #define GB_PROF(i) do {} while (0)
 #define GB_PROF_FLUSH(base, tiles_done) do {} while (0)
@@ -304,6 +310,7 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
             pages[g] = (first <= w.hi && first + p.page_size > w.lo) ? w.table[first >> page_shift] : -1;
             count += pages[g] >= 0;
           }
+          GB_TRACE(30, gt);
           if (gt >= STAGES && !mbar_wait(smem_u32(&kv_empty[s]), par)) {
             atomicCAS(&g_tc_error_word, 0, ERR_WAIT_EMPTY);
             abort_s = 1;
@@ -321,6 +328,7 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
               tma_load_4d(vdst + g * page_bytes, &v_map, bar, 0, 0, w.kvh, pages[g]);
             }
           }
+          GB_TRACE(31, gt);
           if (++stage == STAGES) stage = 0, par ^= 1;
         }
         if (*(volatile int*)&abort_s) break;
@@ -364,7 +372,9 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       GB_PROF(0);
       if (ws.j == 0 && !mbar_wait(smem_u32(&q_full[qb]), (ws.it >> 1) & 1)) ok = false;
       GB_PROF(1);
+      if (lane == 0) GB_TRACE(10, s_buf);
       if (ok && !mbar_wait(smem_u32(&kv_full[s_stage]), s_par)) ok = false;
+      if (lane == 0) GB_TRACE(11, s_buf);
       GB_PROF(2);
       if (!ok) {
         if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_FULL);
@@ -372,14 +382,14 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       }
       tc_fence_after_sync();
       if (lane == 0) {
-        const uint64_t dq = dq0 + (uint64_t)(qb * (Q_BYTES >> 4)), dk = dk0 + (uint64_t)(s_stage * (STAGE_BYTES >> 4));
-        const uint32_t d = tmem_base + s_buf * KT;
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_bf16(d, dq + 2 * k, dk + 2 * k, idesc_s, k > 0);
+        static_assert(HD / 16 == 4 && GK / 16 == 4, "four k steps per product");
+        mma_bf16_x4(tmem_base + s_buf * KT, dq0 + (uint64_t)(qb * (Q_BYTES >> 4)),
+                    dk0 + (uint64_t)(s_stage * (STAGE_BYTES >> 4)), idesc_s, 2, 2);
         mma_commit(smem_u32(&s_ready[s_buf]));
         if (ws.j == ws.n - 1) mma_commit(smem_u32(&q_empty[qb]));   // the item's queries have been read
       }
       __syncwarp();
+      if (lane == 0) GB_TRACE(12, s_buf);
       GB_PROF(3);
       if (++s_stage == STAGES) s_stage = 0, s_par ^= 1;
       s_buf ^= 1;
@@ -399,6 +409,7 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
         }
       }
       if (!ok) break;
+      if (lane == 0) GB_TRACE(13, p_buf);
       GB_PROF(5);
       // both groups have read this S buffer in full and written their P: first the S product that
       // takes the buffer over, then this tile's P V
@@ -408,16 +419,15 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       if (lane == 0) {
 #pragma unroll
         for (int g = 0; g < GROUPS; ++g) {
-          const uint64_t dp = dp0 + (uint64_t)((2 * g + p_buf) * (P_BYTES >> 4));
-          const uint64_t dv = dv0 + (uint64_t)(p_stage * (STAGE_BYTES >> 4) + g * (GK * ROW_BYTES >> 4));
-          const uint32_t d = tmem_base + O_COL0 + (2 * g + p_buf) * HD;
-#pragma unroll
-          for (int ks = 0; ks < GK / 16; ++ks) mma_bf16(d, dp + 2 * ks, dv + ks * (16 * ROW_BYTES >> 4), idesc_o, ks > 0);
+          mma_bf16_x4(tmem_base + O_COL0 + (2 * g + p_buf) * HD, dp0 + (uint64_t)((2 * g + p_buf) * (P_BYTES >> 4)),
+                      dv0 + (uint64_t)(p_stage * (STAGE_BYTES >> 4) + g * (GK * ROW_BYTES >> 4)), idesc_o, 2,
+                      16 * ROW_BYTES >> 4);
         }
         mma_commit(smem_u32(&o_ready[p_buf]));
         mma_commit(smem_u32(&kv_empty[p_stage]));     // keys and values of the stage have been read
       }
       __syncwarp();
+      if (lane == 0) GB_TRACE(14, p_buf);
       GB_PROF(6);
       if (++p_stage == STAGES) p_stage = 0;
       p_par ^= p_buf;         // the phase flips after buffer 1
@@ -477,6 +487,7 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           break;
         }
         tc_fence_after_sync();
+        if ((threadIdx.x & 127) == 64) GB_TRACE(grp * 20 + 0, gt);
         GB_PROF(0);
         {
           // Value rows that no row may read hold whatever was there (a page that was not fetched,
@@ -542,8 +553,10 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
         fence_proxy_async();            // the tensor core reads P through the async proxy
         tc_fence_before_sync();         // this thread's reads of S are over
         mbar_arrive(smem_u32(&p_ready[grp][gt & 1]));
+        if ((threadIdx.x & 127) == 64) GB_TRACE(grp * 20 + 1, gt);
         GB_PROF(3);
         if (j > 0) fold(gt - 1);
+        if ((threadIdx.x & 127) == 64) GB_TRACE(grp * 20 + 2, gt);
         GB_PROF(4);
         corr_saved = corr;
       }
@@ -698,6 +711,12 @@ int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len
 }
 
 #ifdef GB_ATTN_PROFILE
+extern "C" __attribute__((visibility("default"))) int gb_attention_trace(unsigned long long* host_out, unsigned int* n) {
+  if (cudaMemcpyFromSymbol(n, g_trace_n, 4) != cudaSuccess) return 1;
+  if (cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 3 * 8192) != cudaSuccess) return 1;
+  unsigned int zero = 0;
+  return cudaMemcpyToSymbol(g_trace_n, &zero, 4) == cudaSuccess ? 0 : 1;
+}
 extern "C" __attribute__((visibility("default"))) int gb_attention_prof(unsigned long long* host_out) {
   if (cudaMemcpyFromSymbol(host_out, g_prof, sizeof(unsigned long long) * 24) != cudaSuccess) return 1;
   unsigned long long zero[24] = {0};

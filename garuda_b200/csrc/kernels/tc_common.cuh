@@ -233,6 +233,24 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint6
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
       : "memory");
 }
+// Four products in a row onto one accumulator, the first overwriting it: the k steps of a 64-deep
+// block whose operand descriptors advance by a fixed step (in descriptor units of 16 bytes). One
+// predicate set-up for all four, and nothing between them for the issuing thread to wait on.
+__device__ __forceinline__ void mma_bf16_x4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t step_a, uint32_t step_b) {
+  const uint64_t a1 = desc_a + step_a, a2 = desc_a + 2 * step_a, a3 = desc_a + 3 * step_a;
+  const uint64_t b1 = desc_b + step_b, b2 = desc_b + 2 * step_b, b3 = desc_b + 3 * step_b;
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, 0, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %5, %9, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %6, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %7, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %9, p1;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(a1), "l"(a2), "l"(a3), "l"(desc_b), "l"(b1), "l"(b2), "l"(b3), "r"(idesc)
+      : "memory");
+}
 // Makes `bar` complete once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
