@@ -100,10 +100,16 @@ class DecodeGraphs:
     def _capture(self, B: int) -> _Captured:
         r = self.runner
         offs, size = self._layout(B)
-        host = torch.empty(size, dtype=torch.int32).pin_memory()
+        # Two pinned staging buffers in turn, each with an event that tells when its copy to the device
+        # has run: a caller that does not read a step's logits (a prompt's unwanted tokens, a timing
+        # loop) comes back before the copy of the step in front has happened, and must not overwrite
+        # what that copy will read.
+        staging = [torch.empty(size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        host = staging[0]
         dev = torch.zeros(size, dtype=torch.int32, device=r.device)
         cap = _Captured(None, None, host.numpy(), dev, offs)
         cap.pinned = host
+        cap.staging, cap.copied, cap.turn = staging, [None, None], 0
         self._fill(cap, B, [], [])
         dev.copy_(host, non_blocking=True)
         batch = self._batch(cap, B)
@@ -115,6 +121,9 @@ class DecodeGraphs:
         torch.cuda.synchronize(r.device)
         graph = torch.cuda.CUDAGraph()
         before = getattr(r.ops, "launches", 0)
+        # a context of its own: what the run above made "once per step" (the rotation's table) must be
+        # made inside the graph too, or a replay would rotate by the angles of the capture's positions
+        ctx = StepContext(batch=batch, ws=ws, ops=r.ops, dtype=r.dtype)
         with torch.cuda.graph(graph):
             logits = r.model.forward(ctx, caches)
         cap.launches = getattr(r.ops, "launches", 0) - before      # kernels one replay runs
@@ -134,8 +143,16 @@ class DecodeGraphs:
         cap = self.graphs.get(B)
         if cap is None:
             cap = self.graphs[B] = self._capture(B)
+        cap.turn ^= 1
+        cap.pinned = cap.staging[cap.turn]
+        cap.host = cap.pinned.numpy()
+        if cap.copied[cap.turn] is not None:
+            cap.copied[cap.turn].synchronize()      # the copy that last read this buffer has run
         self._fill(cap, B, entries, new_lens)
         cap.dev.copy_(cap.pinned, non_blocking=True)
+        if cap.copied[cap.turn] is None:
+            cap.copied[cap.turn] = torch.cuda.Event()
+        cap.copied[cap.turn].record()
         cap.graph.replay()
         self.replays += 1
         rows = [i for i, e in enumerate(entries) if len(e.want)]

@@ -38,23 +38,31 @@ def random_tensor(seed: int, name: str, shape, init) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))
 
 
-def random_weights(config_dict: dict, seed: int, norm_init=None, store_dtype=torch.float32
-                   ) -> Dict[str, torch.Tensor]:
+def random_weights(config_dict: dict, seed: int, norm_init=None, store_dtype=torch.float32,
+                   scale: Optional[Dict[str, float]] = None) -> Dict[str, torch.Tensor]:
     """CPU tensors for every name the model expects. ``norm_init`` overrides the
-    initialiser of vectors (norm weights), e.g. ``("normal_about_one", 0.1)``."""
+    initialiser of vectors (norm weights), e.g. ``("normal_about_one", 0.1)``.
+    ``scale``: factors for the tensors whose name contains a key, e.g.
+    ``{"q_proj": 8.0, "k_proj": 8.0}``: with N(0, 0.02) weights the attention
+    scores of a small model are so close to zero that every key weighs the same,
+    and a fault in positions, rotation or masking barely moves the logits."""
     _, model = build_model(config_dict)
     out = {}
     for name, ts in model.expected_tensors().items():
         init = tuple(norm_init) if (norm_init is not None and ts.role == "vector") else ts.init
-        out[name] = random_tensor(seed, name, ts.shape, init).to(store_dtype)
+        t = random_tensor(seed, name, ts.shape, init)
+        for key, factor in (scale or {}).items():
+            if key in name:
+                t = t * float(factor)
+        out[name] = t.to(store_dtype)
     return out
 
 
 def write_random_model(model_dir: str, config_dict: dict, seed: int, norm_init=None,
-                       store_dtype=torch.float32) -> str:
+                       store_dtype=torch.float32, scale: Optional[Dict[str, float]] = None) -> str:
     """Create ``model_dir`` with config.json and model.safetensors."""
     os.makedirs(model_dir, exist_ok=True)
-    tensors = random_weights(config_dict, seed, norm_init, store_dtype)
+    tensors = random_weights(config_dict, seed, norm_init, store_dtype, scale)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config_dict, f, indent=2)
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors,

@@ -39,6 +39,11 @@ TINY_D = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_siz
 TINY = {"A": (TINY_A, 0, None), "B": (TINY_B, 1, ("normal_about_one", 0.1)), "C": (TINY_C, 2, None),
         "D": (TINY_D, 3, None)}
 
+# Query and key projections eight times the usual N(0, 0.02): attention scores of the order of one,
+# so that the keys do not all weigh the same and a wrong position, rotation, mask or page shows in
+# the logits (with the plain scale a decode step that rotated by stale angles passed every test).
+SHARPEN = {"q_proj": 8.0, "k_proj": 8.0}
+
 _DIRS = {}
 
 
@@ -50,7 +55,7 @@ def model_dir(name: str, store_dtype=torch.float32) -> str:
     if key not in _DIRS:
         cfg, seed, norm_init = TINY[name]
         d = tempfile.mkdtemp(prefix=f"garuda_tiny_{name}_")
-        write_random_model(d, cfg, seed, norm_init=norm_init, store_dtype=store_dtype)
+        write_random_model(d, cfg, seed, norm_init=norm_init, store_dtype=store_dtype, scale=SHARPEN)
         _DIRS[key] = d
     return _DIRS[key]
 
