@@ -26,7 +26,7 @@ def engines():
     d = tempfile.mkdtemp(prefix="garuda_shape_")
     # 32-bit on disk: the 32-bit engine reads it as it is, the bfloat16 engine rounds it once
     write_random_model(d, SHAPE, seed=5, store_dtype=torch.float32)
-    kw = dict(context=1024, page_size=32, kv_tokens=4096, max_concurrent=8)
+    kw = dict(context=1024, page_size=32, kv_tokens=8192, max_concurrent=64)
     return Engine(d, dtype="float32", **kw), Engine(d, dtype="bfloat16", **kw)
 
 
@@ -90,4 +90,28 @@ def test_batched_requests_agree_with_32_bit(engines):
     for i in range(4):
         e32.runner.end(20 + i)
         e16.runner.end(10 + i)
+    e16.ops.tc.check_errors()
+
+
+def test_forty_requests_decoding_together(engines):
+    """Batches of 17 to 64 tokens take the wider tiles of the few-token product and another plan of
+    the decode attention than batches of a few."""
+    from garuda_b200 import StepEntry
+    e32, e16 = engines
+    rng = np.random.default_rng(6)
+    n = 40
+    lens = [int(x) for x in rng.integers(3, 90, n)]
+    toks = [rng.integers(0, SHAPE["vocab_size"], m).tolist() for m in lens]
+    for eng in (e32, e16):
+        for lo in range(0, n, 8):       # prompts eight at a time
+            eng.step([StepEntry(100 + i, toks[i], []) for i in range(lo, lo + 8)])
+    nxt = [int(x) for x in rng.integers(0, SHAPE["vocab_size"], n)]
+    for step in range(3):
+        r = e32.step([StepEntry(100 + i, [nxt[i]], [0]) for i in range(n)]).clone()
+        o = e16.step([StepEntry(100 + i, [nxt[i]], [0]) for i in range(n)])
+        close(o, r, f"decode step {step} of forty requests")
+        nxt = [int(x) for x in r.argmax(-1).cpu()]
+    for i in range(n):
+        e32.runner.end(100 + i)
+        e16.runner.end(100 + i)
     e16.ops.tc.check_errors()
