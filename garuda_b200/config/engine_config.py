@@ -70,6 +70,7 @@ class RuntimeSection:
     max_batch_tokens: int = 2048  # tokens of one step: decode tokens and prompt portions together
     prefill_chunk: int = 512      # most tokens of one prompt per step (scheduler/mod.rs:319-321)
     cuda_graphs: bool = True      # replay decode steps from captured graphs
+    lookahead: bool = True        # launch the next greedy decode step while this one's tokens travel to the host
     device: int = 0
 
 

@@ -24,7 +24,7 @@ from ..csrc.build import load_host_module
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from ..weights.loader import load_weights
-from .step import StepRunner, StepEntry
+from .step import StepRunner, StepEntry, StepError
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -42,7 +42,7 @@ class Engine:
                  sliding_window: int = 0, page_size: int = 32, kv_tokens: Optional[int] = None,
                  kv_cache_bytes: Optional[int] = None, max_concurrent: int = 4,
                  queue_capacity: int = 256, max_batch_tokens: int = 2048, prefill_chunk: int = 512,
-                 cuda_graphs: bool = True, device: int = 0, ignore_eos: bool = False,
+                 cuda_graphs: bool = True, lookahead: bool = True, device: int = 0, ignore_eos: bool = False,
                  eos_token_id: Optional[int] = None, ops=None):
         if dtype not in _DTYPES:
             raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
@@ -99,6 +99,8 @@ class Engine:
         sc.ignore_eos = bool(ignore_eos)
         self.scheduler = host.Scheduler(sc, self.cache.manager)
         self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda"
+        # launch the next greedy decode step before this step's tokens have reached the host
+        self.lookahead = bool(lookahead) and self.cuda_graphs
         if self.cuda_graphs:
             from .graph import DecodeGraphs
             self.runner.graphs = DecodeGraphs(self.runner, max_concurrent)
@@ -112,6 +114,7 @@ class Engine:
             kv_cache_bytes=kv_bytes or None, max_concurrent=cfg.server.max_concurrent,
             queue_capacity=cfg.server.queue_capacity, max_batch_tokens=cfg.runtime.max_batch_tokens,
             prefill_chunk=cfg.runtime.prefill_chunk, cuda_graphs=cfg.runtime.cuda_graphs,
+            lookahead=cfg.runtime.lookahead,
             device=cfg.runtime.device)
         kwargs.update(overrides)
         return cls(cfg.model.path, **kwargs)
@@ -163,6 +166,7 @@ class Engine:
                     results[i].error = ev.detail
                     live -= 1
 
+        ahead = None      # (ids, Pending): a decode step launched before its plan was made
         while pending or live:
             while pending:
                 i = pending[0]
@@ -182,19 +186,83 @@ class Engine:
             plan = sched.plan()
             handle(plan.events)
             if not plan.entries:
+                ahead = None
                 continue
-            entries = [StepEntry(e.id, e.tokens, (len(e.tokens) - 1,) if e.sample else ())
-                       for e in plan.entries]
             try:
-                logits = self.runner.run(entries)
-                rows = [e for e in plan.entries if e.sample]
-                tokens = self.sampler.sample(logits, [e.temperature for e in rows], [e.top_k for e in rows],
-                                             [e.top_p for e in rows], [e.u for e in rows])
+                collect, ahead = self._run_plan(plan, ahead)
+                tokens = collect()
             except Exception as exc:     # the step failed as a whole: its requests end with the error
+                ahead = None
                 handle(sched.fail(plan, f"{type(exc).__name__}: {exc}"))
                 continue
             handle(sched.complete(plan, tokens))
         return results
+
+    def _run_plan(self, plan, ahead):
+        """Runs a plan's entries and starts drawing their tokens. Returns ``(collect,
+        ahead)``: ``collect()`` waits for the tokens (one per sampled entry, in the plan's
+        order); ``ahead`` is a decode step for the same requests, launched at once with
+        its tokens read on the device from this step's draw, or None.
+
+        Launching ahead keeps the GPU busy while the host waits for this step's tokens,
+        lets the scheduler finish and plan, and prepares the next launch. A step ahead
+        is only launched for greedy decode steps, whose next entries are known but for
+        the tokens. When the plan to come turns out different (a request has finished
+        or was preempted, another has joined), the rows of the step ahead that still
+        fit are used and the plan's other entries run as a step of their own; a row
+        for a request that is gone is dropped (what it wrote to the cache lies in pages
+        that are given back with the request)."""
+        entries = list(plan.entries)
+        have = {}
+        if ahead is not None:
+            gone = set(plan.preempted)
+            have = {rid: k for k, rid in enumerate(ahead[0]) if rid not in gone}
+        matched = [e for e in entries if e.sample and len(e.tokens) == 1 and e.id in have]
+        taken = {e.id for e in matched}
+        rest = [e for e in entries if e.id not in taken]
+        fresh = None
+        if rest:
+            logits = self.runner.run([StepEntry(e.id, e.tokens, (len(e.tokens) - 1,) if e.sample else ())
+                                      for e in rest])
+            rows = [e for e in rest if e.sample]
+            fresh = self.sampler.launch(logits, [e.temperature for e in rows], [e.top_k for e in rows],
+                                        [e.top_p for e in rows], [e.u for e in rows])
+        # where each sampled entry's token will be: ("ahead", row) or ("fresh", row)
+        where, k = [], 0
+        for e in entries:
+            if not e.sample:
+                continue
+            if e.id in taken:
+                where.append((0, have[e.id]))
+            else:
+                where.append((1, k))
+                k += 1
+
+        nxt = None
+        if (self.lookahead and self.runner.graphs is not None
+                and all(e.sample and len(e.tokens) == 1 and e.temperature == 0.0 for e in entries)):
+            try:
+                if not rest and [w[1] for w in where] == list(range(len(ahead[0]))):
+                    dev_tokens = ahead[1].tokens
+                elif not matched:
+                    dev_tokens = fresh.tokens
+                else:
+                    parts = [(ahead[1].tokens if src == 0 else fresh.tokens)[row:row + 1] for src, row in where]
+                    dev_tokens = torch.cat(parts)
+                step = [StepEntry(e.id, (0,), (0,)) for e in entries]
+                logits = self.runner.run(step, device_tokens=dev_tokens)
+                zeros = [0.0] * len(step)
+                nxt = ([e.id for e in entries],
+                       self.sampler.launch(logits, zeros, [0] * len(step), [1.0] * len(step), zeros))
+            except (StepError, self._host.CacheError):
+                nxt = None        # no room (pages, context) to run ahead: the scheduler decides next time
+
+        def collect():
+            a = self.sampler.result(ahead[1]) if matched else []
+            f = self.sampler.result(fresh) if fresh is not None else []
+            return [(a if src == 0 else f)[row] for src, row in where]
+
+        return collect, nxt
 
     def stats(self) -> dict:
         s = self.scheduler.stats()

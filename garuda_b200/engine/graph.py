@@ -138,7 +138,9 @@ class DecodeGraphs:
         return cap.launches if cap is not None else 0
 
     # ------------------------------------------------------------------ run
-    def run(self, entries, new_lens) -> torch.Tensor:
+    def run(self, entries, new_lens, device_tokens=None) -> torch.Tensor:
+        """``device_tokens``: int32 on the device, the entries' tokens in their order, for a step
+        whose tokens the host does not know yet (they come from the step in front)."""
         B = _bucket(len(entries))
         cap = self.graphs.get(B)
         if cap is None:
@@ -153,6 +155,9 @@ class DecodeGraphs:
         if cap.copied[cap.turn] is None:
             cap.copied[cap.turn] = torch.cuda.Event()
         cap.copied[cap.turn].record()
+        if device_tokens is not None:
+            o, _ = cap.offs["token_ids"]
+            cap.dev[o:o + len(entries)].copy_(device_tokens[:len(entries)])
         cap.graph.replay()
         self.replays += 1
         rows = [i for i, e in enumerate(entries) if len(e.want)]

@@ -161,12 +161,17 @@ class StepRunner:
         )
 
     # ------------------------------------------------------------------ run
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], device_tokens=None) -> torch.Tensor:
         """Logits ``[W, vocab]`` (float32, on the device) at the wanted places, in
-        the order of the entries and of their ``want``. Valid until the next step."""
+        the order of the entries and of their ``want``. Valid until the next step.
+        ``device_tokens``: for a step of single tokens that are still on their way from
+        the step in front (int32 on the device, in the entries' order; the entries' own
+        tokens are placeholders then). Only decode steps replayed from graphs take it."""
+        if device_tokens is not None and not (self.graphs is not None and self.graphs.eligible(entries)):
+            raise StepError("tokens on the device are taken by graph-replayed decode steps only")
         new_lens = self._validate_and_reserve(entries)
         if self.graphs is not None and self.graphs.eligible(entries):
-            logits = self.graphs.run(entries, new_lens)
+            logits = self.graphs.run(entries, new_lens, device_tokens)
             tokens = len(entries)
         else:
             batch = self.build_batch(entries, new_lens)

@@ -83,6 +83,33 @@ def test_preemption_on_the_gpu_keeps_the_tokens():
     assert [r.tokens for r in got] == [r.tokens for r in want]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing(dtype):
+    """Greedy decode steps are launched before the tokens of the step in front have reached the
+    host. Requests that end at different times (their own limits, an end-of-sequence token in the
+    middle), more prompts than may run at once, and too few pages: the tokens and the reasons for
+    finishing are those of an engine that launches nothing ahead."""
+    from garuda_b200 import Engine, SamplingParams
+    name = "D"
+    prompts = [random_tokens(name, n, 300 + i) for i, n in enumerate([5, 40, 17, 64, 9, 33, 2])]
+    limits = [7, 30, 12, 25, 40, 3, 18]
+    params = [SamplingParams.greedy(max_tokens=m) for m in limits]
+    kw = dict(dtype=dtype, page_size=16, max_concurrent=3)
+    plain = Engine(model_dir(name), lookahead=False, **kw).generate(prompts, params)
+    # a token that some request produces in the middle of its answer ends it there
+    eos = plain[4].tokens[11]
+    for extra in (dict(), dict(eos_token_id=eos), dict(kv_tokens=160)):
+        want = Engine(model_dir(name), lookahead=False, **kw, **extra).generate(prompts, params)
+        ahead = Engine(model_dir(name), lookahead=True, **kw, **extra)
+        got = ahead.generate(prompts, params)
+        assert [r.tokens for r in got] == [r.tokens for r in want], extra
+        assert [r.finish_reason for r in got] == [r.finish_reason for r in want], extra
+        if "kv_tokens" in extra:
+            assert ahead.stats()["preemptions"] > 0
+        if "eos_token_id" in extra:
+            assert any(r.finish_reason != "length" for r in want)
+
+
 def test_missing_extension_fails_loudly(monkeypatch):
     from garuda_b200.csrc import build
     from garuda_b200.kernels import ops as ops_mod
