@@ -916,7 +916,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
 // takes one arrival per epilogue warp of both CTAs.
 // BN: the pair's tile width. 256 is what is launched: with 128 the products themselves took nearly
 // twice as long per flop when measured (a pair's product of 128 columns costs about as much as one of
-// 256), which outweighs hiding a lone tile's epilogue under a second tile.
+// 256), which outweighs hiding a lone tile's epilogue under a second tile; for the same reason tiles
+// of 384 columns (a 256- and a 128-column product per step), tried for widths where 256-wide tiles
+// need a second, nearly empty round over the pairs, were slower than that second round.
 template <int BN>
 struct PairGeometry {
   static constexpr int STAGE_BYTES = BM * BK * 2 + (BN / 2) * BK * 2;      // per CTA: 32 KB or 24 KB

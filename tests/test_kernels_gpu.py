@@ -122,6 +122,29 @@ def test_tensor_core_gate_up(ops, M, F, K):
     close(out2, ref, 8e-3, "swiglu, unfused")
 
 
+def test_products_with_more_tiles_than_cta_pairs(ops):
+    """2,048 tokens times 2,560 features are 80 tiles of 256 x 256 for 74 CTA pairs: some pairs take
+    a second tile (the other accumulator stage, the persistent loop). Every epilogue at that shape."""
+    M, N, K = 2048, 2560, 192
+    a, w = (torch.randn(M, K) * 0.5).bfloat16(), (torch.randn(N, K) * 0.1).bfloat16()
+    ref = a.float() @ w.float().t()
+    for odt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 8e-3)):
+        out = torch.full((M, N), 5.0, dtype=odt, device="cuda")
+        assert ops.tc.linear(dev(a), dev(w), out, False)
+        close(out, ref, tol, f"store {odt}")
+    base = torch.randn(M, N)
+    acc = dev(base.clone())
+    assert ops.tc.linear(dev(a), dev(w), acc, True)
+    close(acc, base + ref, 1e-5, "accumulate")
+    F = N // 2
+    refs = torch.zeros(M, F)
+    cpu.linear_swiglu(None, a, w, refs)
+    outs = torch.full((M, F), 9.0, dtype=torch.bfloat16, device="cuda")
+    assert ops.tc.linear_swiglu(dev(a), ops.pack_gate_up(dev(w[:F]), dev(w[F:])), outs)
+    close(outs, refs, 8e-3, "swiglu")
+    ops.tc.check_errors()
+
+
 def test_row_pitch_that_tma_cannot_take_uses_the_plain_kernel(ops):
     a, w = torch.randn(5, 20).bfloat16(), torch.randn(12, 20).bfloat16()     # K = 20: 40-byte rows
     out = torch.zeros(5, 12, device="cuda")
@@ -160,12 +183,14 @@ def test_rotate_and_store(ops, interleaved, dtype):
 
 @pytest.mark.parametrize("interleaved", [False, True])
 @pytest.mark.parametrize("Hq,Hkv,hd,d", [(4, 2, 16, 64), (3, 1, 32, 96), (32, 4, 64, 256), (2, 2, 128, 72), (6, 3, 48, 72)])
-@pytest.mark.parametrize("T", [1, 11, 70, 200, 300])
+@pytest.mark.parametrize("T", [1, 11, 70, 200, 300, 2048])
 def test_fused_projection_rotation_and_cache_write(ops, interleaved, Hq, Hkv, hd, d, T):
     """The query/key/value product with rotation and page write in its epilogue
     against the plain product followed by the plain rotate-and-store."""
     from garuda_b200.parts.rotary import RotaryParams
     from garuda_b200.engine.batch import Workspace
+    if T == 2048 and (Hq, hd) != (32, 64):
+        pytest.skip("the 2,048-token case is for the 2,560-feature shape (more tiles than CTA pairs)")
 
     class Ctx:
         ws = Workspace("cuda:0")
