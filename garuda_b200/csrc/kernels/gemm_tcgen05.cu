@@ -50,7 +50,9 @@ constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // many tokens: one CTA per SM, 
 constexpr int SMEM_BUDGET_SMALL = GB_SMEM_BUDGET_SMALL_KB * 1024;   // few tokens: pipeline depth that the stream of weights needs
 constexpr int SMEM_BUDGET_DUAL = 140 * 1024;    // few tokens, gate and up together
 
-enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
+// EPI_ACCUMULATE_NORM: accumulate, and fold in the first half of the norm that follows (RopeArgs::h_out);
+// chosen by the host, a variant of its own so that the plain accumulation's code stays as it is
+enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_ACCUMULATE_NORM = 4 };
 
 // What the query/key/value epilogue needs: the output features are (heads + 2 kv_heads) heads of
 // head_dim; query and key heads are rotated at the token's position (garuda/src/simd/mod.rs:196-206,
@@ -66,6 +68,19 @@ struct RopeArgs {
   const int32_t* block_table;    // [R, table_width]
   const float2* cs;              // [T, head_dim / 2] (cos, sin) of every token's angles, or null: no rotation
   int table_width, heads, kv_heads, head_dim, interleaved, page_size;
+  // An RMS norm folded into the two products around it (garuda/src/simd/mod.rs:166-173,
+  // garuda/src/llama/mod.rs:733-738). The product in front, which adds into the residual stream,
+  // also writes x * weight in bfloat16 (x: the new residual value) and, per tile of 128 features,
+  // the sum of x^2 over the tile for every token. The product behind reads those rows as its
+  // tokens and multiplies its results by 1/sqrt(sum x^2 / width + eps) of their token, which gives
+  // (x * rms * weight) W^T with the sum, the root and the scaling in 32-bit.
+  const float* sums_in;          // consumer: [tiles_in, sums_ld] partial sums of squares, or null
+  int tiles_in;
+  float eps, inv_width;
+  __nv_bfloat16* h_out;          // producer: [T, features] x * weight, or null
+  const float* weight;           // [features]
+  float* sums_out;               // [tiles of 128 features, sums_ld]
+  int sums_ld;                   // tokens
 };
 
 // Where feature `head`, channel d of the token at `pos` (request row `req`) is stored; null if the
@@ -154,6 +169,29 @@ __device__ __forceinline__ float silu_gate_fast(float g, float u) {
   return g * __frcp_rn(1.0f + __expf(-g)) * u;
 }
 
+// Sums each of sixteen values over the lanes of a warp with sixteen shuffles: at every step a
+// lane keeps half of its values and hands the other half to its partner, which keeps those. Lane
+// L ends with the sum of value warp_sum16_index(L) (lanes 2k and 2k + 1 hold the same). The order
+// of the additions is fixed.
+__device__ __forceinline__ int warp_sum16_index(int lane) {
+  return ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+}
+__device__ __forceinline__ float warp_sum16(const float (&v)[16], int lane) {
+  float a8[8], a4[4], a2[2];
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    a8[i] = (b4 ? v[i + 8] : v[i]) + __shfl_xor_sync(0xffffffffu, b4 ? v[i] : v[i + 8], 16);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    a4[i] = (b3 ? a8[i + 4] : a8[i]) + __shfl_xor_sync(0xffffffffu, b3 ? a8[i] : a8[i + 4], 8);
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+    a2[i] = (b2 ? a4[i + 2] : a4[i]) + __shfl_xor_sync(0xffffffffu, b2 ? a4[i] : a4[i + 2], 4);
+  const float a1 = (b1 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, b1 ? a2[0] : a2[1], 2);
+  return a1 + __shfl_xor_sync(0xffffffffu, a1, 1);
+}
+
 constexpr int C_THREADS = 192;   // warp 0: producer, warp 1: MMA issuer, warps 2-5: epilogue
 
 // Few tokens. rows_m / rows_n: valid rows of the MMA-row operand (the weights: output features)
@@ -185,6 +223,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
   __shared__ __align__(8) uint64_t partial_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ float inv_s[BN];       // folded norm: 1/rms of this tile's tokens
 
   GB_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -342,14 +381,33 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         rope_slot[t] = slot;
       }
     }
-    float old[EPI == EPI_ACCUMULATE ? BN : 1];
+    constexpr bool emit = EPI == EPI_ACCUMULATE_NORM;                    // the norm behind this product is folded in
+    constexpr bool ADD = EPI == EPI_ACCUMULATE || emit;
+    float old[ADD ? BN : 1];
+    // each epilogue warp's sum of squares per token, in the pipeline's memory (idle by then; static
+    // shared memory is kept small, so that two CTAs still fit on an SM)
+    float (*red_s)[BN] = reinterpret_cast<float (*)[BN]>(smem_raw + (tiles - smem_u32(smem_raw)));
+    float w_row = 0.f;
     if (rank == 0) {
+      if (emit && row < rows_m) w_row = ra.weight[row];                 // a model constant: no need to wait
       gb::pdl_wait();
-      if (EPI == EPI_ACCUMULATE) {
+      if (ADD) {
         // what is to be added to is fetched while the matrix product runs
 #pragma unroll
         for (int j = 0; j < BN; ++j)
           old[j] = (row < rows_m && n0 + j < rows_n) ? gb::to_float<OT>(out[(size_t)(n0 + j) * ldo + row]) : 0.f;
+      }
+      if (ra.sums_in != nullptr) {
+        // the norm in front of this product: 1/rms of every token, from the partial sums (in tile
+        // order: the same sum whatever else is in the batch)
+        const int t = (int)threadIdx.x - 64;
+        if (t < BN) {
+          float s = 0.f;
+          if (n0 + t < rows_n)
+            for (int i = 0; i < ra.tiles_in; ++i) s += ra.sums_in[(size_t)i * ra.sums_ld + n0 + t];
+          inv_s[t] = rsqrtf(s * ra.inv_width + ra.eps);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     }
     GB_STAMP_E(4);
@@ -415,6 +473,10 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] += src[j * BM];
           }
+          if (ra.sums_in != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] *= inv_s[c + j];
+          }
           if (EPI == EPI_SWIGLU) {
             if (row_in_tile >= 64) {
 #pragma unroll
@@ -464,16 +526,33 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-          } else if (row < rows_m) {
+          } else {
+            float sq[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int col = n0 + c + j;      // token
-              if (col >= rows_n) continue;
+              sq[j] = 0.f;
+              if (row >= rows_m || col >= rows_n) continue;
               float x = v[j];
-              if (EPI == EPI_ACCUMULATE) x += old[EPI == EPI_ACCUMULATE ? c + j : 0];
+              if (ADD) x += old[ADD ? c + j : 0];
               store_value<OT>(out + (size_t)col * ldo + row, x);
+              if (emit) {
+                ra.h_out[(size_t)col * ldo + row] = __float2bfloat16_rn(x * w_row);
+                sq[j] = x * x;
+              }
+            }
+            if (emit) {
+              const float total = warp_sum16(sq, lane);
+              if ((lane & 1) == 0) red_s[quarter][c + warp_sum16_index(lane)] = total;
             }
           }
+        }
+        if (emit) {
+          // this tile's sum of squares for every token: the four warps' parts in a fixed order
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int t = (int)threadIdx.x - 64;
+          if (t < BN && n0 + t < rows_n)
+            ra.sums_out[(size_t)blockIdx.y * ra.sums_ld + n0 + t] = red_s[0][t] + red_s[1][t] + red_s[2][t] + red_s[3][t];
         }
       }
     }
@@ -1238,15 +1317,17 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ld
 // Few tokens: the weights are the MMA-row operand; BN tokens per tile.
 template <int BN>
 int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mn, void* out, int ldo,
-                     int weight_rows, int out_features, int tokens, int K, cudaStream_t stream) {
+                     int weight_rows, int out_features, int tokens, int K, cudaStream_t stream, const RopeArgs& ra) {
   if (epi == EPI_STORE) {
     if (out_dtype == GB_F32)
-      return launch_cluster<BN, EPI_STORE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream);
-    return launch_cluster<BN, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream);
+      return launch_cluster<BN, EPI_STORE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
+    return launch_cluster<BN, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
   }
+  if (epi == EPI_ACCUMULATE && ra.h_out != nullptr)
+    return launch_cluster<BN, EPI_ACCUMULATE_NORM, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
   if (epi == EPI_ACCUMULATE)
-    return launch_cluster<BN, EPI_ACCUMULATE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream);
-  return launch_cluster<BN, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream);
+    return launch_cluster<BN, EPI_ACCUMULATE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
+  return launch_cluster<BN, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
 }
 
 template <int BN, int EPI, typename OT>
@@ -1320,6 +1401,32 @@ GB_EXPORT int gb_tc_error_check() {
   return v;
 }
 
+// An RMS norm folded into the products around it (see RopeArgs). As the consumer: sums_in
+// [tiles_in, sums_ld] and eps, inv_width = 1 / features of the normed vector. As the producer
+// (accumulating products only): h_out [Mx, Nw] bfloat16, weight [Nw] 32-bit, sums_out
+// [gb_gemm_tc_norm_tiles(Mx, Nw), sums_ld]. Unused halves are null.
+struct GbNormFold {
+  const float* sums_in;
+  int tiles_in;
+  float eps, inv_width;
+  void* h_out;
+  const float* weight;
+  float* sums_out;
+  int sums_ld;
+};
+
+namespace {
+void fold_norm(RopeArgs& ra, const GbNormFold* n) {
+  if (n == nullptr) return;
+  ra.sums_in = n->sums_in; ra.tiles_in = n->tiles_in; ra.eps = n->eps; ra.inv_width = n->inv_width;
+  ra.h_out = (__nv_bfloat16*)n->h_out; ra.weight = n->weight; ra.sums_out = n->sums_out; ra.sums_ld = n->sums_ld;
+}
+}  // namespace
+
+// Rows of sums_out that a product of Mx tokens and Nw output features writes when a norm is folded
+// in behind it; 0: this shape does not fold norms.
+GB_EXPORT int gb_gemm_tc_norm_tiles(int Mx, int Nw) { return Mx <= 64 ? (Nw + BM - 1) / BM : 0; }
+
 // Whether gb_gemm_tc takes this problem (else the caller uses the plain kernel).
 GB_EXPORT int gb_gemm_tc_supported(const void* x, const void* w, int Mx, int Nw, int K) {
   if (Mx < 1 || Nw < 1 || K < 8 || K % 8) return 0;
@@ -1331,7 +1438,7 @@ GB_EXPORT int gb_gemm_tc_supported(const void* x, const void* w, int Mx, int Nw,
 // 2: w holds gate and up rows packed in groups of 64 ([128 * ceil(Nw / 64), K], see the head of this
 // file); out[Mx,Nw] (bf16) = silu(x gate^T) * (x up^T).
 GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw, int K, int out_dtype, int epi,
-                         cudaStream_t stream) {
+                         const GbNormFold* norm, cudaStream_t stream) {
   if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: needs K a multiple of 8 and 16-byte aligned operands (K = %d)", K);
   if (epi == EPI_ACCUMULATE && out_dtype != GB_F32)
@@ -1339,15 +1446,21 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   if (epi == EPI_SWIGLU && out_dtype != GB_BF16)
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: the SiLU-gate epilogue writes bfloat16");
   const int weight_rows = epi == EPI_SWIGLU ? 128 * ((Nw + 63) / 64) : Nw;
+  RopeArgs ra{};
+  fold_norm(ra, norm);
+  if (ra.h_out != nullptr && (epi != EPI_ACCUMULATE || gb_gemm_tc_norm_tiles(Mx, Nw) == 0))
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc: no norm can be folded in behind this product (%d tokens, epilogue %d)", Mx, epi);
+  if (ra.sums_in != nullptr && Mx > 64)
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc: no norm can be folded in in front of a product of %d tokens", Mx);
   CUtensorMap mm, mn;
   int rc;
   if (Mx <= 64) {
     const int bn = Mx <= 16 ? 16 : Mx <= 32 ? 32 : 64;
     if ((rc = tensor_map_2d(w, weight_rows, K, BM, &mm))) return rc;
     if ((rc = tensor_map_2d(x, Mx, K, bn, &mn))) return rc;
-    if (bn == 16) return dispatch_cluster<16>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream);
-    if (bn == 32) return dispatch_cluster<32>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream);
-    return dispatch_cluster<64>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream);
+    if (bn == 16) return dispatch_cluster<16>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream, ra);
+    if (bn == 32) return dispatch_cluster<32>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream, ra);
+    return dispatch_cluster<64>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream, ra);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
   static const bool pairs_on = [] {
@@ -1399,7 +1512,7 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
 GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* q_out, void* k_pool, void* v_pool,
                              const int32_t* positions, const int32_t* token_req, const int32_t* block_table,
                              int table_width, int heads, int kv_heads, int head_dim, const float* cos_sin,
-                             int interleaved, int page_size, cudaStream_t stream) {
+                             int interleaved, int page_size, const GbNormFold* norm, cudaStream_t stream) {
   const int Nw = (heads + 2 * kv_heads) * head_dim;
   if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: needs K a multiple of 8 and 16-byte aligned operands (K = %d)", K);
@@ -1407,7 +1520,10 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
     return gb::fail(GB_UNSUPPORTED, "gemm_tc_qkv: head_dim %d does not divide 128", head_dim);
   if (kv_heads > 0 && (!k_pool || !v_pool || !block_table || page_size < 1))
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_qkv: kv heads given without a cache to store them in");
-  RopeArgs ra;
+  RopeArgs ra{};
+  fold_norm(ra, norm);
+  if (ra.h_out != nullptr || (ra.sums_in != nullptr && Mx > 64))
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc_qkv: no norm can be folded into this product (%d tokens)", Mx);
   ra.q_out = (__nv_bfloat16*)q_out; ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool;
   ra.positions = positions; ra.token_req = token_req; ra.block_table = block_table; ra.cs = reinterpret_cast<const float2*>(cos_sin);
   ra.table_width = table_width; ra.heads = heads; ra.kv_heads = kv_heads; ra.head_dim = head_dim;

@@ -78,3 +78,5 @@ class StepContext:
     dtype: torch.dtype
     # what a step computes once for all its layers (the rotation's cosines and sines), by key
     step_cache: dict = field(default_factory=dict)
+    # a part's last product leaves here the norm it folded in (``CudaOps.linear``'s ``emit_norm``)
+    pending_norm: object = None

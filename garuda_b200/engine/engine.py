@@ -124,6 +124,12 @@ class Engine:
         """One step of the step function; see ``StepRunner.run``."""
         return self.runner.run(entries)
 
+    def warm_up(self) -> None:
+        """Captures the decode step's graphs for every batch size now, so that no request
+        waits for a capture later (a capture takes some milliseconds, once per bucket)."""
+        if self.runner.graphs is not None:
+            self.runner.graphs.warm()
+
     # ------------------------------------------------------------------ generate
     def _host_params(self, p: SamplingParams):
         p.validate()

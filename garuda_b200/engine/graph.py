@@ -10,6 +10,7 @@ page, which the kernels skip.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Sequence
 
 import numpy as np
@@ -124,13 +125,31 @@ class DecodeGraphs:
         # a context of its own: what the run above made "once per step" (the rotation's table) must be
         # made inside the graph too, or a replay would rotate by the angles of the capture's positions
         ctx = StepContext(batch=batch, ws=ws, ops=r.ops, dtype=r.dtype)
-        with torch.cuda.graph(graph):
-            logits = r.model.forward(ctx, caches)
+        # No garbage collection in the middle of the capture: garbage that holds device memory or
+        # graphs (an engine that was dropped earlier) would be freed there, and freeing device memory
+        # invalidates a capture. Other threads may use the device meanwhile (thread_local).
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                logits = r.model.forward(ctx, caches)
+        finally:
+            if collecting:
+                gc.enable()
         cap.launches = getattr(r.ops, "launches", 0) - before      # kernels one replay runs
         if hasattr(r.ops, "launches"):
             r.ops.launches = before
         cap.graph, cap.logits, cap.ws = graph, logits, ws
         return cap
+
+    def warm(self) -> None:
+        """Captures every bucket now (a few milliseconds each) rather than at the first step
+        that needs it."""
+        B = 1
+        while B <= self.max_bucket:
+            if B not in self.graphs:
+                self.graphs[B] = self._capture(B)
+            B *= 2
 
     def launches_replayed(self, num_requests: int) -> int:
         """Kernels that one replay for this many requests launches."""

@@ -8,6 +8,7 @@ and contiguity, and launches on torch's current stream.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_void_p, c_int, c_float, c_longlong
 from typing import Optional
 
@@ -40,6 +41,28 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+class PendingNorm:
+    """An RMS norm of which only the first half has run, folded into the product that wrote the
+    residual stream ``x``: ``values`` is ``x * weight`` in bfloat16 and ``sums`` ``[tiles, T]``
+    holds partial sums of ``x^2`` per token. A product that takes it as its tokens multiplies
+    its results by ``1/sqrt(sum / width + eps)`` (32-bit); ``materialize`` runs the norm part
+    on ``x`` the ordinary way instead, for a consumer that cannot."""
+
+    def __init__(self, values, sums, weight, eps, norm, x):
+        self.values, self.sums, self.weight, self.eps, self.norm, self.x = values, sums, weight, float(eps), norm, x
+
+    @property
+    def shape(self):
+        return self.values.shape
+
+    @property
+    def dtype(self):
+        return self.values.dtype
+
+    def materialize(self, ctx):
+        return self.norm.forward(ctx, self.x)
+
+
 class CudaOps:
     """Hand-written sm_100a kernels. ``tensor_cores=False`` keeps every matrix
     product and the attention on the plain 32-bit-arithmetic kernels (the true
@@ -57,6 +80,9 @@ class CudaOps:
         if tensor_cores:
             from .tc import TensorCoreKernels
             self.tc = TensorCoreKernels(self)
+        # whether products fold the norms around them in (``linear``'s ``emit_norm``); the environment
+        # variable is for comparing timings
+        self.folds_norms = self.tc is not None and os.environ.get("GARUDA_B200_FOLD_NORMS", "1") != "0"
         self._inv_freq = {}
         self.launches = 0
         from ..engine.batch import Workspace
@@ -138,8 +164,13 @@ class CudaOps:
             x.data_ptr(), weight.data_ptr(), _tag(weight, "norm weight"), float(eps), out.data_ptr(),
             _tag(out, "rmsnorm out"), _ptr(rows), n, d, self._stream()), "rmsnorm")
 
-    def linear(self, a, w, out, accumulate: bool = False):
-        """``out[M,N] (+)= a[M,K] @ w[N,K]^T``; accumulation is into a 32-bit ``out``."""
+    def linear(self, a, w, out, accumulate: bool = False, ctx=None, emit_norm=None):
+        """``out[M,N] (+)= a[M,K] @ w[N,K]^T``; accumulation is into a 32-bit ``out``.
+
+        ``emit_norm`` (with ``ctx``): the norm part that will be applied to ``out`` next. Where
+        the kernel can, it folds that norm's first half into this product and returns a
+        ``PendingNorm`` to hand to ``qkv_rope_append`` or ``linear_swiglu`` in place of the
+        normed tensor; else it returns None and the norm runs as usual."""
         self._on_device(a, w, out)
         _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "linear: operands must be matrices")
         M, K = a.shape
@@ -147,11 +178,35 @@ class CudaOps:
         _need(w.shape[1] == K and out.shape == (M, N), f"linear: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
         _need(a.dtype == w.dtype, "linear: a and w must have one dtype")
         _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
-        if self.tc is not None and a.dtype == torch.bfloat16 and self.tc.linear(a, w, out, accumulate):
-            return
+        if self.tc is not None and a.dtype == torch.bfloat16:
+            pending = self._pending_for(ctx, emit_norm, out, accumulate)
+            if self.tc.linear(a, w, out, accumulate, emit=pending):
+                return pending
         self._check(self.core, self.core.gb_gemm_simple(
             a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _tag(a, "linear input"),
             _tag(out, "linear output"), int(accumulate), self._stream()), "linear")
+
+    def _pending_for(self, ctx, norm, x, accumulate):
+        """A ``PendingNorm`` with buffers for the product that adds into ``x``, or None."""
+        if norm is None or ctx is None or not accumulate or x.dtype != torch.float32:
+            return None
+        fold = norm.fold() if hasattr(norm, "fold") else None
+        T, d = x.shape
+        tiles = self.tc.norm_tiles(T, d)
+        if fold is None or not tiles:
+            return None
+        weight, eps = fold
+        # two sets of buffers in turn: a block's second norm is pending while the first one's values are
+        # still the operand of no kernel, but never more than two at a time
+        turn = ctx.step_cache.get("pending_turn", 0) ^ 1
+        ctx.step_cache["pending_turn"] = turn
+        values = ctx.ws.get(f"pending_values_{turn}", (T, d), torch.bfloat16)
+        sums = ctx.ws.get(f"pending_sums_{turn}", (tiles, T), torch.float32)
+        return PendingNorm(values, sums, weight, eps, norm, x)
+
+    def normed(self, ctx, h):
+        """``h`` as a tensor: a ``PendingNorm`` is run as the ordinary norm."""
+        return h.materialize(ctx) if isinstance(h, PendingNorm) else h
 
     def pack_gate_up(self, gate, up):
         """The layout ``linear_swiglu`` wants. With the tensor-core kernels: gate and
@@ -176,6 +231,10 @@ class CudaOps:
         """``act[M,F] = silu(h @ gate^T) * (h @ up^T)``, the activation in 32-bit."""
         M, F = act.shape
         group = getattr(w_gate_up, "gb_group", 0)
+        if isinstance(h, PendingNorm):
+            if group == 64 and self.tc is not None and self.tc.linear_swiglu(h.values, w_gate_up, act, pending=h):
+                return
+            h = h.materialize(ctx)
         if (group == 64 and self.tc is not None and h.dtype == torch.bfloat16
                 and self.tc.linear_swiglu(h, w_gate_up, act)):
             return
@@ -208,6 +267,11 @@ class CudaOps:
         not), queries to ``q_out [T, heads, head_dim]``, keys and values into their
         pages. One kernel where the tensor-core product takes the shape, else the
         product in 32-bit followed by ``rope_kv_append``."""
+        pending = h if isinstance(h, PendingNorm) else None
+        if pending is not None:
+            h = pending.values
+            if self.tc is None or not self.tc.takes_qkv(h, w_qkv, q_out, head_dim):
+                h, pending = pending.materialize(ctx), None
         self._on_device(h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table)
         T = h.shape[0]
         _need(w_qkv.shape == ((heads + 2 * kv_heads) * head_dim, h.shape[1]), "qkv_rope_append: weight shape")
@@ -221,7 +285,7 @@ class CudaOps:
             table = None if rotary is None else self.rope_table(ctx, positions, rotary)
             self.tc.qkv_rope_append(h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table, heads,
                                     kv_heads, head_dim, table, None if rotary is None else rotary.interleaved,
-                                    page_size)
+                                    page_size, pending=pending)
             return
         qkv = ctx.ws.get("qkv", (T, w_qkv.shape[0]), torch.float32)
         self.linear(h, w_qkv, qkv)

@@ -18,19 +18,28 @@ _WAIT_NAMES = {1: "an operand tile never arrived (TMA)", 2: "a pipeline stage wa
                5: "a decode attention cluster never delivered its partial results"}
 
 
+class NormFold(ctypes.Structure):
+    """GbNormFold of gemm_tcgen05.cu: an RMS norm folded into the products around it."""
+    _fields_ = [("sums_in", c_void_p), ("tiles_in", c_int), ("eps", c_float), ("inv_width", c_float),
+                ("h_out", c_void_p), ("weight", c_void_p), ("sums_out", c_void_p), ("sums_ld", c_int)]
+
+
 class TensorCoreKernels:
     def __init__(self, ops):
         self.ops = ops
         self.lib = load_kernel_lib("garuda_tc")
         L = self.lib
         L.gb_last_error.restype = ctypes.c_char_p
-        L.gb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        L.gb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                 ctypes.POINTER(NormFold), c_void_p]
         L.gb_gemm_tc.restype = c_int
+        L.gb_gemm_tc_norm_tiles.argtypes = [c_int, c_int]
+        L.gb_gemm_tc_norm_tiles.restype = c_int
         L.gb_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
         L.gb_gemm_tc_supported.restype = c_int
         L.gb_tc_error_check.restype = c_int
         L.gb_gemm_tc_qkv.argtypes = ([c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 6 + [c_int] * 4 + [c_void_p]
-                                     + [c_int, c_int, c_void_p])
+                                     + [c_int, c_int, ctypes.POINTER(NormFold), c_void_p])
         L.gb_gemm_tc_qkv.restype = c_int
         self._attn = {}
 
@@ -44,20 +53,39 @@ class TensorCoreKernels:
             from .ops import KernelError
             raise KernelError("a tensor-core kernel gave up waiting: " + _WAIT_NAMES.get(code, f"code {code}"))
 
-    def _gemm(self, x, w, out, n_out, epi) -> bool:
+    # ------------------------------------------------------------------ folded norms
+    def norm_tiles(self, tokens: int, features: int) -> int:
+        """Rows of partial sums that an accumulating product of this shape writes when the norm
+        behind it is folded in; 0: it folds none."""
+        return int(self.lib.gb_gemm_tc_norm_tiles(tokens, features))
+
+    @staticmethod
+    def _consume(pending):
+        """The kernel's argument for a product whose tokens are a ``PendingNorm``."""
+        if pending is None:
+            return None
+        return NormFold(sums_in=pending.sums.data_ptr(), tiles_in=pending.sums.shape[0], eps=pending.eps,
+                        inv_width=1.0 / pending.values.shape[1], sums_ld=pending.sums.shape[1])
+
+    def _gemm(self, x, w, out, n_out, epi, fold=None) -> bool:
         M, K = x.shape
         if not self.lib.gb_gemm_tc_supported(x.data_ptr(), w.data_ptr(), M, n_out, K):
             return False
         tag = 0 if out.dtype == torch.float32 else 1
         code = self.lib.gb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, n_out, K, tag, epi,
-                                   self.ops._stream())
+                                   None if fold is None else ctypes.byref(fold), self.ops._stream())
         self.ops._check(self.lib, code, "gemm_tc")
         return True
 
-    def linear(self, a, w, out, accumulate) -> bool:
+    def linear(self, a, w, out, accumulate, emit=None) -> bool:
+        """``emit``: a ``PendingNorm`` whose values and sums this accumulating product fills."""
         if w.dtype != torch.bfloat16 or out.dtype not in (torch.float32, torch.bfloat16):
             return False
-        return self._gemm(a, w, out, w.shape[0], 1 if accumulate else 0)
+        fold = None
+        if emit is not None:
+            fold = NormFold(h_out=emit.values.data_ptr(), weight=emit.weight.data_ptr(),
+                            sums_out=emit.sums.data_ptr(), sums_ld=emit.sums.shape[1])
+        return self._gemm(a, w, out, w.shape[0], 1 if accumulate else 0, fold)
 
     def takes_qkv(self, h, w_qkv, q_out, head_dim) -> bool:
         """Whether the fused query/key/value product takes these operands (head sizes that
@@ -68,27 +96,29 @@ class TensorCoreKernels:
                 and bool(self.lib.gb_gemm_tc_supported(h.data_ptr(), w_qkv.data_ptr(), M, w_qkv.shape[0], K)))
 
     def qkv_rope_append(self, h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
-                        heads, kv_heads, head_dim, cos_sin, interleaved, page_size) -> None:
+                        heads, kv_heads, head_dim, cos_sin, interleaved, page_size, pending=None) -> None:
         """The query/key/value product with the rotation and the cache write in its
         epilogue. ``cos_sin``: ``CudaOps.rope_table`` of the step's positions, or None
-        (no rotation)."""
+        (no rotation). ``pending``: the ``PendingNorm`` whose values ``h`` is."""
         M, K = h.shape
+        fold = self._consume(pending)
         code = self.lib.gb_gemm_tc_qkv(
             h.data_ptr(), w_qkv.data_ptr(), M, K, q_out.data_ptr(),
             None if k_pool is None else k_pool.data_ptr(), None if v_pool is None else v_pool.data_ptr(),
             positions.data_ptr(), token_req.data_ptr(), None if block_table is None else block_table.data_ptr(),
             0 if block_table is None else block_table.shape[1], heads, kv_heads, head_dim,
             None if cos_sin is None else cos_sin.data_ptr(), 0 if not interleaved else 1,
-            int(page_size), self.ops._stream())
+            int(page_size), None if fold is None else ctypes.byref(fold), self.ops._stream())
         self.ops._check(self.lib, code, "gemm_tc_qkv")
 
-    def linear_swiglu(self, h, w_gate_up, act) -> bool:
-        """``w_gate_up``: the packed layout of ``CudaOps.pack_gate_up``."""
+    def linear_swiglu(self, h, w_gate_up, act, pending=None) -> bool:
+        """``w_gate_up``: the packed layout of ``CudaOps.pack_gate_up``. ``pending``: the
+        ``PendingNorm`` whose values ``h`` is."""
         F = act.shape[1]
         if (w_gate_up.dtype != torch.bfloat16 or act.dtype != torch.bfloat16
                 or w_gate_up.shape[0] != 128 * ((F + 63) // 64)):
             return False
-        return self._gemm(h, w_gate_up, act, F, 2)
+        return self._gemm(h, w_gate_up, act, F, 2, self._consume(pending))
 
     # ------------------------------------------------------------------ attention
     def _attention_lib(self, head_dim: int):

@@ -119,8 +119,17 @@ class Decoder:
         b, ops, s = ctx.batch, self.ops, self.spec
         x = ctx.ws.get("residual", (b.num_tokens, s.width), torch.float32)
         ops.embedding(self.embedding, b.token_ids, x)
+        # a layer's last product may fold in the first half of the next layer's norm
+        pending = None
         for i, call in enumerate(s.order):
-            self.blocks[call.layer].forward(ctx, x, layer_caches[i])
+            block = self.blocks[call.layer]
+            nxt = self.blocks[s.order[i + 1].layer] if i + 1 < len(s.order) else None
+            takes = getattr(nxt, "takes_pending_norm", None)
+            next_norm = takes(ops) if takes is not None else None
+            if pending is not None or next_norm is not None:
+                pending = block.forward(ctx, x, layer_caches[i], pending=pending, next_norm=next_norm)
+            else:
+                pending = block.forward(ctx, x, layer_caches[i])
         w = b.num_logit_rows
         logits = ctx.ws.get("logits", (w, s.vocab_size), torch.float32)
         if w:

@@ -64,7 +64,12 @@ class PagedAttention(Mixer):
         self.w_o = tensors["o_proj.weight"].contiguous()
 
     # ---- one step ------------------------------------------------------------
-    def forward(self, ctx, h, cache, residual=None):
+    # ``h`` may be a norm that is half done (``CudaOps.qkv_rope_append`` takes it), and the output
+    # product may fold in the first half of the norm that follows (``emit_norm``)
+    takes_pending_norm = True
+    emits_norm = True
+
+    def forward(self, ctx, h, cache, residual=None, emit_norm=None):
         b, ops, ws = ctx.batch, self.ops, ctx.ws
         T = h.shape[0]
         writes = cache.writes and not self.reads_shared_cache
@@ -82,6 +87,8 @@ class PagedAttention(Mixer):
         else:
             # an encoding the fused kernel does not know: let the part change q and k in place
             qkv = ws.get("qkv", (T, cols), torch.float32)
+            if hasattr(ops, "normed"):
+                h = ops.normed(ctx, h)
             ops.linear(h, w_qkv, qkv)
             qv = qkv[:, :self.q_dim].unflatten(1, (self.heads, self.head_dim))
             kv = (qkv[:, self.q_dim:self.q_dim + self.kv_dim].unflatten(1, (self.kv_heads, self.head_dim))
@@ -95,7 +102,10 @@ class PagedAttention(Mixer):
                             self.scale, self.window or 0, cache.page_size,
                             b.num_requests, b.max_q_len, b.max_kv_len, ws=ws, min_q_len=b.min_q_len)
         if residual is not None:
-            ops.linear(out, self.w_o, residual, accumulate=True)
+            if emit_norm is None:
+                ops.linear(out, self.w_o, residual, accumulate=True)
+            else:
+                ctx.pending_norm = ops.linear(out, self.w_o, residual, accumulate=True, ctx=ctx, emit_norm=emit_norm)
             return None
         y = ws.get("mixer_out", (T, self.width), torch.float32)
         ops.linear(out, self.w_o, y)

@@ -42,15 +42,44 @@ class PreNormBlock:
                     (self.feed_forward, s.feed_forward.prefix)]
         return out
 
-    def forward(self, ctx, x, cache):
+    def takes_pending_norm(self, ops):
+        """The norm part that the layer in front may fold into its last product (see
+        ``forward``'s ``pending``), or None."""
+        if getattr(ops, "folds_norms", False) and getattr(self.mixer, "takes_pending_norm", False) \
+                and hasattr(self.mixer_norm, "fold"):
+            return self.mixer_norm
+        return None
+
+    def forward(self, ctx, x, cache, pending=None, next_norm=None):
+        """``pending``: this layer's first norm of ``x``, already half done by the layer in
+        front (a ``PendingNorm``). ``next_norm``: the norm part that the next layer starts with,
+        if that layer takes such a result. Returns the pending norm for the next layer, or None.
+        Parts that know nothing of this are run with the plain norms."""
         ops = ctx.ops
-        h = self.mixer_norm.forward(ctx, x)
-        y = self.mixer.forward(ctx, h, cache, residual=x)
+        folds = getattr(ops, "folds_norms", False)
+        h = pending if pending is not None else self.mixer_norm.forward(ctx, x)
+        ff = self.feed_forward
+        kw = {}
+        if (folds and ff is not None and getattr(self.mixer, "emits_norm", False)
+                and getattr(ff, "takes_pending_norm", False) and hasattr(self.feed_forward_norm, "fold")):
+            kw["emit_norm"] = self.feed_forward_norm
+        ctx.pending_norm = None
+        y = self.mixer.forward(ctx, h, cache, residual=x, **kw)
         if y is not None:
             ops.residual_add(x, y)
-        if self.feed_forward is not None:
-            h2 = self.feed_forward_norm.forward(ctx, x)
-            y2 = self.feed_forward.forward(ctx, h2, residual=x)
+        out = None
+        if ff is not None:
+            h2, ctx.pending_norm = ctx.pending_norm, None
+            if h2 is None:
+                h2 = self.feed_forward_norm.forward(ctx, x)
+            kw = {}
+            if folds and next_norm is not None and getattr(ff, "emits_norm", False):
+                kw["emit_norm"] = next_norm
+            y2 = ff.forward(ctx, h2, residual=x, **kw)
             if y2 is not None:
                 ops.residual_add(x, y2)
-        return x
+            out = ctx.pending_norm
+        elif y is None:
+            out = ctx.pending_norm
+        ctx.pending_norm = None
+        return out

@@ -30,12 +30,21 @@ class SwiGLU(FeedForward):
         self.w_gate_up = ops.pack_gate_up(tensors["gate_proj.weight"], tensors["up_proj.weight"])
         self.w_down = tensors["down_proj.weight"].contiguous()
 
-    def forward(self, ctx, h, residual=None):
+    # ``h`` may be a norm that is half done (``CudaOps.linear_swiglu`` takes it), and the last product
+    # may fold in the first half of the norm that follows (``emit_norm``)
+    takes_pending_norm = True
+    emits_norm = True
+
+    def forward(self, ctx, h, residual=None, emit_norm=None):
         T = h.shape[0]
         act = ctx.ws.get("ffn_act", (T, self.inner), self.dtype)
         self.ops.linear_swiglu(ctx, h, self.w_gate_up, act)
         if residual is not None:
-            self.ops.linear(act, self.w_down, residual, accumulate=True)
+            if emit_norm is None:
+                self.ops.linear(act, self.w_down, residual, accumulate=True)
+            else:
+                ctx.pending_norm = self.ops.linear(act, self.w_down, residual, accumulate=True, ctx=ctx,
+                                                   emit_norm=emit_norm)
             return None
         y = ctx.ws.get("ffn_out", (T, self.width), torch.float32)
         self.ops.linear(act, self.w_down, y)

@@ -28,6 +28,13 @@ class RMSNorm(Norm):
         super().load(tensors, ops, dtype)
         self.weight = tensors["weight"]
 
+    def fold(self):
+        """(weight in 32-bit, eps) for a product that folds this norm in, see
+        ``CudaOps.linear``'s ``emit_norm``."""
+        if getattr(self, "_weight32", None) is None:
+            self._weight32 = self.weight.float().contiguous()
+        return self._weight32, self.eps
+
     def forward(self, ctx, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
                 out_name: str = "normed") -> torch.Tensor:
         n = x.shape[0] if rows is None else rows.shape[0]

@@ -83,6 +83,31 @@ def test_preemption_on_the_gpu_keeps_the_tokens():
     assert [r.tokens for r in got] == [r.tokens for r in want]
 
 
+def test_graphs_captured_ahead_of_time_and_among_dropped_engines():
+    """``warm_up`` captures every batch size's graph before any request; the tokens are those of an
+    engine without graphs. Engines dropped in between leave garbage that holds graphs and device
+    memory: a capture must not be invalidated by its collection."""
+    import gc
+    from garuda_b200 import Engine, SamplingParams
+    name = "A"
+    prompts = [random_tokens(name, n, 500 + n) for n in (3, 21, 9, 14)]
+    params = [SamplingParams.greedy(max_tokens=m) for m in (12, 5, 9, 2)]
+    kw = dict(dtype="bfloat16", page_size=16, max_concurrent=4)
+    want = Engine(model_dir(name, torch.bfloat16), cuda_graphs=False, **kw).generate(prompts, params)
+    for _ in range(3):
+        e = Engine(model_dir(name, torch.bfloat16), **kw)
+        gc.set_threshold(1)           # collect at every allocation: also in the middle of a capture
+        try:
+            e.warm_up()
+        finally:
+            gc.set_threshold(700, 10, 10)
+        assert sorted(e.runner.graphs.graphs) == [1, 2, 4]
+        got = e.generate(prompts, params)
+        assert [r.tokens for r in got] == [r.tokens for r in want]
+        assert e.runner.graphs.replays > 0
+        e.cycle = e                   # garbage that only a collection frees
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_launched_ahead_change_nothing(dtype):
     """Greedy decode steps are launched before the tokens of the step in front have reached the

@@ -122,6 +122,56 @@ def test_tensor_core_gate_up(ops, M, F, K):
     close(out2, ref, 8e-3, "swiglu, unfused")
 
 
+@pytest.mark.parametrize("M", [1, 8, 17, 40, 64])
+@pytest.mark.parametrize("d,K,F", [(200, 72, 176), (1024, 256, 1000)])
+def test_norm_folded_into_the_products_around_it(ops, M, d, K, F):
+    """The product that adds into the residual stream writes x * weight and partial sums of x^2;
+    the products behind it (gate/up; queries, keys and values) scale their results by 1/rms."""
+    from garuda_b200.engine.batch import StepContext, Workspace
+    from garuda_b200.parts.norm import RMSNorm
+    from garuda_b200.parts.rotary import RotaryParams
+    g = torch.Generator().manual_seed(M + d)
+    eps = 1e-3
+    a, w_o = (torch.randn(M, K, generator=g) * 0.5).bfloat16(), (torch.randn(d, K, generator=g) * 0.1).bfloat16()
+    # every token at a scale of its own, so that a 1/rms taken from another token's sums shows
+    x = torch.randn(M, d, generator=g) * (1 + torch.arange(M) % 5).float()[:, None]
+    gamma = (1 + 0.3 * torch.randn(d, generator=g)).bfloat16()
+    norm = RMSNorm(d, eps)
+    norm.load({"weight": dev(gamma)}, ops, torch.bfloat16)
+    ctx = StepContext(batch=None, ws=Workspace("cuda:0"), ops=ops, dtype=torch.bfloat16)
+    res = dev(x.clone())
+    pending = ops.linear(dev(a), dev(w_o), res, accumulate=True, ctx=ctx, emit_norm=norm)
+    assert pending is not None, "this shape folds the norm in"
+    x_new = x + a.float() @ w_o.float().t()
+    close(res, x_new, 1e-5, "residual")
+    close(pending.values, x_new * gamma.float(), 4e-3, "x * weight")
+    torch.testing.assert_close(pending.sums.sum(0).cpu(), (x_new ** 2).sum(1), rtol=1e-4, atol=1e-6)
+    # what the consumers must compute, from the rounded values they read
+    inv = torch.rsqrt((x_new ** 2).mean(1, keepdim=True) + eps)
+    h_ref = pending.values.float().cpu() * inv
+    close(pending.materialize(ctx), x_new * inv * gamma.float(), 8e-3, "the norm run the ordinary way")
+    w = (torch.randn(2 * F, d, generator=g) * 0.2).bfloat16()
+    ref = torch.zeros(M, F)
+    cpu.linear_swiglu(None, h_ref, w.float(), ref)
+    out = torch.full((M, F), 9.0, dtype=torch.bfloat16, device="cuda")
+    ops.linear_swiglu(ctx, pending, ops.pack_gate_up(dev(w[:F]), dev(w[F:])), out)
+    close(out, ref, 8e-3, "gate/up behind a folded norm")
+    Hq, Hkv, hd, page = 4, 2, 32, 8
+    wq = (torch.randn((Hq + 2 * Hkv) * hd, d, generator=g) * 0.2).bfloat16()
+    req = torch.arange(M, dtype=torch.int32)
+    positions = (torch.arange(M, dtype=torch.int32) * 3) % 29
+    table = torch.randperm(M * 4, generator=g).int().view(M, 4)
+    rot = RotaryParams(10000.0, hd, False)
+    k_ref, v_ref = torch.zeros(M * 4, Hkv, page, hd), torch.zeros(M * 4, Hkv, page, hd)
+    q_ref = torch.zeros(M, Hq, hd)
+    cpu.qkv_rope_append(None, h_ref, wq.float(), q_ref, k_ref, v_ref, positions, req, table, Hq, Hkv, hd, rot, page)
+    k = torch.zeros(M * 4, Hkv, page, hd, dtype=torch.bfloat16, device="cuda")
+    v, q = torch.zeros_like(k), torch.zeros(M, Hq, hd, dtype=torch.bfloat16, device="cuda")
+    ops.qkv_rope_append(ctx, pending, dev(wq), q, k, v, dev(positions), dev(req), dev(table), Hq, Hkv, hd, rot, page)
+    close(q, q_ref, 1e-2, "q"), close(k, k_ref, 1e-2, "k"), close(v, v_ref, 1e-2, "v")
+    ops.tc.check_errors()
+
+
 def test_products_with_more_tiles_than_cta_pairs(ops):
     """2,048 tokens times 2,560 features are 80 tiles of 256 x 256 for 74 CTA pairs: some pairs take
     a second tile (the other accumulator stage, the persistent loop). Every epilogue at that shape."""
