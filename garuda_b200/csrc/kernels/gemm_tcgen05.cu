@@ -618,13 +618,22 @@ __device__ __forceinline__ void epilogue_store16<__nv_bfloat16>(__nv_bfloat16* p
 template <int BN, int EPI, typename OT>
 __device__ __forceinline__ void epilogue_prefetch(float (&first)[32], int row, int n0, const OT* __restrict__ out, int ldo,
                                                   int rows_m, int rows_n, int c_begin) {
-  if (EPI != EPI_ACCUMULATE || n0 + BN > rows_n) return;
+  if ((EPI != EPI_ACCUMULATE && EPI != EPI_ACCUMULATE_NORM) || n0 + BN > rows_n) return;
   const int lane = threadIdx.x & 31;
   const int row0 = row - lane;
   const int rows_valid = min(32, rows_m - row0);
   const OT* gbase = out + (size_t)row0 * ldo + n0 + lane + c_begin;
 #pragma unroll
   for (int rr = 0; rr < 32; ++rr) first[rr] = rr < rows_valid ? gb::to_float<OT>(gbase[(size_t)rr * ldo]) : 0.f;
+}
+
+// A norm folded in in front of the product (RopeArgs::sums_in): 1/rms of the thread's token from the
+// partial sums, in their order; 1 without such a norm. Asked for while the tile's products still run.
+__device__ __forceinline__ float epilogue_row_scale(const RopeArgs& ra, int row, int rows_m) {
+  if (ra.sums_in == nullptr || row >= rows_m) return 1.f;
+  float t = 0.f;
+  for (int i = 0; i < ra.tiles_in; ++i) t += ra.sums_in[(size_t)i * ra.sums_ld + row];
+  return rsqrtf(t * ra.inv_width + ra.eps);
 }
 
 // The epilogue of one 128 x BN tile for the thread that owns token `row` (a TMEM lane): taddr is the
@@ -635,20 +644,26 @@ __device__ __forceinline__ void epilogue_prefetch(float (&first)[32], int row, i
 template <int BN, int EPI, typename OT>
 __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, OT* __restrict__ out, int ldo,
                                               int rows_m, int rows_n, bool vec, const RopeArgs& ra, float* turn,
-                                              int c_begin, int c_end, const float (&first)[32]) {
+                                              int c_begin, int c_end, const float (&first)[32], const float inv) {
+  // EMIT: the norm behind this accumulating product is folded in. Every warp writes the sum of squares
+  // of its columns of every token into a row of its own of sums_out (two rows per tile of BN columns).
+  constexpr bool EMIT = EPI == EPI_ACCUMULATE_NORM;
+  const int sums_row = 2 * (n0 / BN) + (c_begin != 0 ? 1 : 0);
   // Whole tiles, the usual case: 32 columns at a time, turned round in shared memory. A thread holds
   // a row of the accumulator, so stores straight from its registers touch 32 different lines per
   // instruction; after the turn a warp's instruction covers 32 consecutive columns of one row, and
   // the residual of all 32 rows is asked for before any of it is used.
-  if ((EPI == EPI_STORE || EPI == EPI_ACCUMULATE) && n0 + BN <= rows_n) {
+  if ((EPI == EPI_STORE || EPI == EPI_ACCUMULATE || EMIT) && n0 + BN <= rows_n) {
     const int lane = threadIdx.x & 31;
     const int row0 = row - lane;                               // the warp's first row
     const int rows_valid = min(32, rows_m - row0);             // may be <= 0
     OT* gbase = out + (size_t)row0 * ldo + n0 + lane;
-    constexpr bool ACC = EPI == EPI_ACCUMULATE;
+    constexpr bool ACC = EPI == EPI_ACCUMULATE || EMIT;
+    float ssq = 0.f;                                           // EMIT: of the token row0 + lane
+    __nv_bfloat16* hbase = EMIT ? ra.h_out + (size_t)row0 * ldo + n0 + lane : nullptr;
     // the residual of a block is asked for one block ahead; the first block's before the tile's
     // products have finished (first: the caller's prefetch)
-    float old_cur[ACC ? 32 : 1], old_nxt[ACC ? 32 : 1];
+    float old_cur[ACC ? 32 : 1];
     auto fetch = [&](float (&dst)[ACC ? 32 : 1], int c) {
       if (ACC) {
 #pragma unroll
@@ -661,29 +676,38 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
       for (int rr = 0; rr < 32; ++rr) old_cur[ACC ? rr : 0] = first[ACC ? rr : 0];
     }
     constexpr int BLOCKS = BN / 32 / (epilogue_warps(EPI) / 4);     // blocks of 32 columns per warp
-#pragma unroll
+    constexpr int UNROLL = ACC ? 1 : BLOCKS;                       // the folded norm's work needs the registers
+#pragma unroll UNROLL
     for (int k = 0; k < BLOCKS; ++k) {
       const int c = c_begin + 32 * k;
       if (c >= c_end) break;
       uint32_t r[32];
       tmem_ld_32(taddr + c, r);
-      if (k + 1 < BLOCKS && c + 32 < c_end) fetch(old_nxt, c + 32);
+      if (ACC && k > 0) fetch(old_cur, c);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) turn[lane * 33 + j] = __uint_as_float(r[j]);
       __syncwarp();
+      const float wv = EMIT ? ra.weight[n0 + c + lane] : 0.f;
 #pragma unroll
       for (int rr = 0; rr < 32; ++rr) {
         float v = turn[rr * 33 + lane];
         if (ACC) v += old_cur[ACC ? rr : 0];
         if (rr < rows_valid) store_value<OT>(gbase + (size_t)rr * ldo + c, v);
+        if (EMIT) {
+          // the squares go back the way the values came: each lane then adds up its own token's
+          if (rr < rows_valid) hbase[(size_t)rr * ldo + c] = __float2bfloat16_rn(v * wv);
+          turn[rr * 33 + lane] = rr < rows_valid ? v * v : 0.f;
+        }
+      }
+      if (EMIT) {
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) ssq += turn[lane * 33 + j];
       }
       __syncwarp();
-      if (ACC) {
-#pragma unroll
-        for (int rr = 0; rr < 32; ++rr) old_cur[ACC ? rr : 0] = old_nxt[ACC ? rr : 0];
-      }
     }
+    if (EMIT && row < rows_m) ra.sums_out[(size_t)sums_row * ra.sums_ld + row] = ssq;
     return;
   }
   if (EPI == EPI_SWIGLU && vec && (n0 >> 1) + BN / 2 <= rows_n) {
@@ -704,14 +728,18 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
         for (int h = 0; h < 2; ++h) {
           float v[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = silu_gate_fast(__uint_as_float(g_[h * 16 + j]), __uint_as_float(u_[h * 16 + j]));
+          for (int j = 0; j < 16; ++j)
+            v[j] = silu_gate_fast(__uint_as_float(g_[h * 16 + j]) * inv, __uint_as_float(u_[h * 16 + j]) * inv);
           epilogue_store16<OT>(prow + q * 64 + c + h * 16, v, true);
         }
       }
     }
     return;
   }
-  if (c_begin != 0) return;       // what follows runs once per lane quarter
+  if (c_begin != 0) {              // what follows runs once per lane quarter
+    if (EMIT && row < rows_m) ra.sums_out[(size_t)sums_row * ra.sums_ld + row] = 0.f;
+    return;
+  }
   if (EPI == EPI_ROPE) {
     // This thread holds one token's row: whole heads, so both channels of every rotation pair.
     const int hd = ra.head_dim, half = hd >> 1;
@@ -735,8 +763,8 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
         float a[16], b[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          a[j] = __uint_as_float(ra_[j]);
-          b[j] = split_halves ? __uint_as_float(rb_[j]) : 0.f;
+          a[j] = __uint_as_float(ra_[j]) * inv;
+          b[j] = split_halves ? __uint_as_float(rb_[j]) * inv : 0.f;
         }
         if (split_halves) {
           // channels dd .. dd + 15 pair with half + dd ..
@@ -782,7 +810,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
         if (row >= rows_m || col >= rows_n) continue;
         float v[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = silu_gate_fast(__uint_as_float(r0[j]), __uint_as_float(r1[j]));
+        for (int j = 0; j < 16; ++j) v[j] = silu_gate_fast(__uint_as_float(r0[j]) * inv, __uint_as_float(r1[j]) * inv);
         OT* p = out + (size_t)row * ldo + col;
         if (col + 16 <= rows_n) {
           epilogue_store16<OT>(p, v, vec);
@@ -792,6 +820,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
       }
     }
   } else {
+  float ssq = 0.f;
 #pragma unroll 1
   for (int c = 0; c < BN; c += 16) {
     uint32_t r0[16];
@@ -801,8 +830,17 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
     if (row >= rows_m || col >= rows_n) continue;
     float v[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]);
+    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]) * inv;
     OT* p = out + (size_t)row * ldo + col;
+    if (EMIT) {
+      for (int j = 0; j < 16 && col + j < rows_n; ++j) {
+        const float x = v[j] + gb::to_float<OT>(p[j]);
+        store_value<OT>(p + j, x);
+        ra.h_out[(size_t)row * ldo + col + j] = __float2bfloat16_rn(x * ra.weight[col + j]);
+        ssq += x * x;
+      }
+      continue;
+    }
     if (col + 16 <= rows_n) {
       if (EPI == EPI_ACCUMULATE) {
         if (vec) {
@@ -825,6 +863,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
       }
     }
   }
+  if (EMIT && row < rows_m) ra.sums_out[(size_t)sums_row * ra.sums_ld + row] = ssq;
   }
 }
 
@@ -962,6 +1001,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       float first[32];
       epilogue_prefetch<BN, EPI, OT>(first, m0 + quarter * 32 + lane, n0, out, ldo, rows_m, rows_n, c_begin);
+      const float inv = epilogue_row_scale(ra, m0 + quarter * 32 + lane, rows_m);
       bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
       if (!have && lane == 0) {
         atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
@@ -971,7 +1011,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
       tc_fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + as * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, ra, turn_buf[warp - 2], c_begin, c_end, first);
+      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, ra, turn_buf[warp - 2], c_begin, c_end, first, inv);
       // every read of this accumulator stage has completed: hand it back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
@@ -1129,6 +1169,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
       const int m0 = (tile % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (tile / tiles_m) * BN;
       float first[32];
       epilogue_prefetch<BN, EPI, OT>(first, m0 + quarter * 32 + lane, n0, out, ldo, rows_m, rows_n, c_begin);
+      const float inv = epilogue_row_scale(ra, m0 + quarter * 32 + lane, rows_m);
       bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
       if (!have && lane == 0) {
         atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
@@ -1138,7 +1179,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
       tc_fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + as * BN + ((uint32_t)(quarter * 32) << 16);
-      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, ra, turn_buf[warp - 2], c_begin, c_end, first);
+      epilogue_tile<BN, EPI, OT>(taddr, row, n0, out, ldo, rows_m, rows_n, vec, ra, turn_buf[warp - 2], c_begin, c_end, first, inv);
       // every read of this accumulator stage has completed: hand it back to the issuer
       tc_fence_before_sync();
       __syncwarp();
@@ -1380,6 +1421,20 @@ int pick_tile_width(int rows_m, int rows_n) {
   return cost(256) <= cost(128) ? 256 : 128;
 }
 
+bool pairs_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("GARUDA_B200_PAIRS");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+// More than 64 tokens: whether CTA pairs take the product, and the tile width over the weight's rows.
+bool many_token_pairs(int tokens, int weight_rows) { return pairs_enabled() && tokens >= 2 * BM && weight_rows >= 256; }
+int many_token_width(int tokens, int weight_rows) {
+  return many_token_pairs(tokens, weight_rows) ? 256 : pick_tile_width(tokens, weight_rows);
+}
+
 }  // namespace
 
 GB_DEFINE_LAST_ERROR()
@@ -1425,7 +1480,11 @@ void fold_norm(RopeArgs& ra, const GbNormFold* n) {
 
 // Rows of sums_out that a product of Mx tokens and Nw output features writes when a norm is folded
 // in behind it; 0: this shape does not fold norms.
-GB_EXPORT int gb_gemm_tc_norm_tiles(int Mx, int Nw) { return Mx <= 64 ? (Nw + BM - 1) / BM : 0; }
+GB_EXPORT int gb_gemm_tc_norm_tiles(int Mx, int Nw) {
+  if (Mx <= 64) return (Nw + BM - 1) / BM;                   // a row per tile of 128 features
+  const int width = many_token_width(Mx, Nw);
+  return 2 * ((Nw + width - 1) / width);                      // a row per epilogue warp of a lane quarter
+}
 
 // Whether gb_gemm_tc takes this problem (else the caller uses the plain kernel).
 GB_EXPORT int gb_gemm_tc_supported(const void* x, const void* w, int Mx, int Nw, int K) {
@@ -1448,10 +1507,8 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   const int weight_rows = epi == EPI_SWIGLU ? 128 * ((Nw + 63) / 64) : Nw;
   RopeArgs ra{};
   fold_norm(ra, norm);
-  if (ra.h_out != nullptr && (epi != EPI_ACCUMULATE || gb_gemm_tc_norm_tiles(Mx, Nw) == 0))
-    return gb::fail(GB_UNSUPPORTED, "gemm_tc: no norm can be folded in behind this product (%d tokens, epilogue %d)", Mx, epi);
-  if (ra.sums_in != nullptr && Mx > 64)
-    return gb::fail(GB_UNSUPPORTED, "gemm_tc: no norm can be folded in in front of a product of %d tokens", Mx);
+  if (ra.h_out != nullptr && epi != EPI_ACCUMULATE)
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc: a norm is folded in behind accumulating products only (epilogue %d)", epi);
   CUtensorMap mm, mn;
   int rc;
   if (Mx <= 64) {
@@ -1463,45 +1520,26 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
     return dispatch_cluster<64>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream, ra);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
-  static const bool pairs_on = [] {
-    const char* v = getenv("GARUDA_B200_PAIRS");
-    return !(v && v[0] == '0');
-  }();
-  if (pairs_on && Mx >= 2 * BM && weight_rows >= 256) {
-    // each CTA of a pair loads half of the weight tile's rows
-    if ((rc = tensor_map_2d(w, weight_rows, K, 128, &mn))) return rc;
-#define GB_PAIR(BN_)                                                                                              \
-  do {                                                                                                            \
-    if (epi == EPI_SWIGLU)                                                                                        \
-      return launch_pair<BN_, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, \
-                                                         stream);                                                 \
-    if (epi == EPI_ACCUMULATE)                                                                                    \
-      return launch_pair<BN_, EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);    \
-    if (out_dtype == GB_F32)                                                                                      \
-      return launch_pair<BN_, EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);         \
-    return launch_pair<BN_, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K,    \
-                                                      stream);                                                    \
+  const bool pairs = many_token_pairs(Mx, weight_rows);
+  const int width = many_token_width(Mx, weight_rows);
+  // CTA pairs: each CTA of a pair loads half of the weight tile's rows
+  if ((rc = tensor_map_2d(w, weight_rows, K, pairs ? 128 : width, &mn))) return rc;
+#define GB_MANY(LAUNCH, BN_)                                                                                          \
+  do {                                                                                                                \
+    if (epi == EPI_SWIGLU)                                                                                            \
+      return LAUNCH<BN_, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
+    if (epi == EPI_ACCUMULATE && ra.h_out != nullptr)                                                                 \
+      return LAUNCH<BN_, EPI_ACCUMULATE_NORM, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);    \
+    if (epi == EPI_ACCUMULATE)                                                                                        \
+      return LAUNCH<BN_, EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);         \
+    if (out_dtype == GB_F32)                                                                                          \
+      return LAUNCH<BN_, EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);              \
+    return LAUNCH<BN_, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
   } while (0)
-    GB_PAIR(256);
-#undef GB_PAIR
-  }
-  const int width = pick_tile_width(Mx, weight_rows);
-  if ((rc = tensor_map_2d(w, weight_rows, K, width, &mn))) return rc;
-#define GB_PERSISTENT(BN_)                                                                                         \
-  do {                                                                                                             \
-    if (epi == EPI_SWIGLU)                                                                                         \
-      return launch_persistent<BN_, EPI_SWIGLU, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows,   \
-                                                               Nw, K, stream);                                     \
-    if (epi == EPI_ACCUMULATE)                                                                                     \
-      return launch_persistent<BN_, EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream); \
-    if (out_dtype == GB_F32)                                                                                       \
-      return launch_persistent<BN_, EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream);    \
-    return launch_persistent<BN_, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw,  \
-                                                            K, stream);                                            \
-  } while (0)
-  if (width == 256) GB_PERSISTENT(256);
-  GB_PERSISTENT(128);
-#undef GB_PERSISTENT
+  if (pairs) GB_MANY(launch_pair, 256);
+  if (width == 256) GB_MANY(launch_persistent, 256);
+  GB_MANY(launch_persistent, 128);
+#undef GB_MANY
 }
 
 // The query/key/value product with the rotation and the cache write in its epilogue:
@@ -1522,8 +1560,8 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_qkv: kv heads given without a cache to store them in");
   RopeArgs ra{};
   fold_norm(ra, norm);
-  if (ra.h_out != nullptr || (ra.sums_in != nullptr && Mx > 64))
-    return gb::fail(GB_UNSUPPORTED, "gemm_tc_qkv: no norm can be folded into this product (%d tokens)", Mx);
+  if (ra.h_out != nullptr)
+    return gb::fail(GB_UNSUPPORTED, "gemm_tc_qkv: no norm can be folded in behind this product");
   ra.q_out = (__nv_bfloat16*)q_out; ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool;
   ra.positions = positions; ra.token_req = token_req; ra.block_table = block_table; ra.cs = reinterpret_cast<const float2*>(cos_sin);
   ra.table_width = table_width; ra.heads = heads; ra.kv_heads = kv_heads; ra.head_dim = head_dim;
@@ -1540,11 +1578,7 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
     return launch_cluster<64, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Nw, Nw, Mx, K, stream, ra);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
-  static const bool pairs_on = [] {
-    const char* v = getenv("GARUDA_B200_PAIRS");
-    return !(v && v[0] == '0');
-  }();
-  if (pairs_on && Mx >= 2 * BM && Nw >= 256) {
+  if (many_token_pairs(Mx, Nw)) {
     if ((rc = tensor_map_2d(w, Nw, K, 128, &mn))) return rc;
     return launch_pair<256, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Mx, Nw, Nw, K, stream, ra);
   }

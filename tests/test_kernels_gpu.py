@@ -122,8 +122,8 @@ def test_tensor_core_gate_up(ops, M, F, K):
     close(out2, ref, 8e-3, "swiglu, unfused")
 
 
-@pytest.mark.parametrize("M", [1, 8, 17, 40, 64])
-@pytest.mark.parametrize("d,K,F", [(200, 72, 176), (1024, 256, 1000)])
+@pytest.mark.parametrize("M", [1, 8, 17, 40, 64, 100, 300, 1100])
+@pytest.mark.parametrize("d,K,F", [(200, 72, 176), (1024, 256, 1000), (2560, 192, 300)])
 def test_norm_folded_into_the_products_around_it(ops, M, d, K, F):
     """The product that adds into the residual stream writes x * weight and partial sums of x^2;
     the products behind it (gate/up; queries, keys and values) scale their results by 1/rms."""
