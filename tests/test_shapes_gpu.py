@@ -115,3 +115,34 @@ def test_forty_requests_decoding_together(engines):
         e32.runner.end(100 + i)
         e16.runner.end(100 + i)
     e16.ops.tc.check_errors()
+
+
+def test_norms_between_products_run_inside_the_products(engines):
+    """With the tensor-core kernels a layer is five launches: the norms between the products are
+    folded into them (only the first layer's first norm and the last norm run as kernels). With the
+    folding switched off the same step launches two more per layer and gives the same logits within
+    rounding. Few tokens (cluster kernel), 65 to 255 (one CTA per tile) and more (CTA pairs)."""
+    from garuda_b200 import StepEntry
+    e32, e16 = engines
+    rng = np.random.default_rng(8)
+    layers = SHAPE["num_hidden_layers"]
+    ops = e16.ops
+    assert ops.folds_norms
+    for n in (5, 64, 150, 400):
+        toks = rng.integers(0, SHAPE["vocab_size"], n).tolist()
+        ref = e32.step([StepEntry(50, toks, [0, n - 1])]).clone()
+        e32.runner.end(50)
+        counts, outs = [], []
+        for fold in (True, False):
+            ops.folds_norms = fold
+            try:
+                before = ops.launches
+                outs.append(e16.step([StepEntry(51, toks, [0, n - 1])]).clone())
+                counts.append(ops.launches - before)
+            finally:
+                ops.folds_norms = True
+                e16.runner.end(51)
+        assert counts[1] - counts[0] == 2 * layers - 1, (n, counts)
+        close(outs[0], ref, f"{n} tokens, norms folded in")
+        close(outs[1], ref, f"{n} tokens, norm kernels")
+    e16.ops.tc.check_errors()
