@@ -27,6 +27,12 @@
 // them in rank order and runs the epilogue. No scratch in global memory, no
 // atomics, and the same sum order every time.
 //
+// An RMS norm that stands between two products is folded into them (EpilogueArgs):
+// the product in front, which adds into the residual stream x, also writes
+// x * weight in bfloat16 and per-token partial sums of x^2; the product behind
+// takes those rows as its tokens and multiplies its results by
+// 1/sqrt(mean(x^2) + eps). No norm kernel, and no second pass over x.
+//
 // Rows outside a matrix are zero-filled by TMA and masked in the epilogue; K
 // need not be a multiple of 64 (the tail is zero-filled) but must be a multiple
 // of 8, because a TMA row pitch is a multiple of 16 bytes.
@@ -50,16 +56,16 @@ constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // many tokens: one CTA per SM, 
 constexpr int SMEM_BUDGET_SMALL = GB_SMEM_BUDGET_SMALL_KB * 1024;   // few tokens: pipeline depth that the stream of weights needs
 constexpr int SMEM_BUDGET_DUAL = 140 * 1024;    // few tokens, gate and up together
 
-// EPI_ACCUMULATE_NORM: accumulate, and fold in the first half of the norm that follows (RopeArgs::h_out);
+// EPI_ACCUMULATE_NORM: accumulate, and fold in the first half of the norm that follows (EpilogueArgs::h_out);
 // chosen by the host, a variant of its own so that the plain accumulation's code stays as it is
 enum Epilogue : int { EPI_STORE = 0, EPI_ACCUMULATE = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_ACCUMULATE_NORM = 4 };
 
-// What the query/key/value epilogue needs: the output features are (heads + 2 kv_heads) heads of
+// What the epilogues need beyond the output pointer. For the query/key/value epilogue: the output features are (heads + 2 kv_heads) heads of
 // head_dim; query and key heads are rotated at the token's position (garuda/src/simd/mod.rs:196-206,
 // angle = (float)pos * inv_freq[i] in 32-bit; the cosines and sines are made once per step for all
 // layers by rope_table in elementwise.cu), queries go to q_out, rotated keys and raw values into
 // their pages (garuda/src/llama/mod.rs:784-791). head_dim divides 128, so no head straddles a tile.
-struct RopeArgs {
+struct EpilogueArgs {
   __nv_bfloat16* q_out;          // [T, heads, head_dim]
   __nv_bfloat16* k_pool;         // [pages, kv_heads, page_size, head_dim]
   __nv_bfloat16* v_pool;
@@ -85,7 +91,7 @@ struct RopeArgs {
 
 // Where feature `head`, channel d of the token at `pos` (request row `req`) is stored; null if the
 // position has no page.
-__device__ __forceinline__ __nv_bfloat16* rope_destination(const RopeArgs& ra, int token, int req, int pos,
+__device__ __forceinline__ __nv_bfloat16* rope_destination(const EpilogueArgs& ra, int token, int req, int pos,
                                                            int head, int d) {
   if (head < ra.heads) return ra.q_out + ((size_t)token * ra.heads + head) * ra.head_dim + d;
   const int page = ra.block_table[(size_t)req * ra.table_width + pos / ra.page_size];
@@ -203,7 +209,7 @@ template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(C_THREADS, 1)
 gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
                        OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int kb_per_rank,
-                       const RopeArgs ra, const int stages) {
+                       const EpilogueArgs ra, const int stages) {
   constexpr bool DUAL_M = false;
   using G = Geometry<BN, false, false, true, rope_table_bytes(EPI, BN)>;
   constexpr int STAGES = G::STAGES;          // the most; `stages` of them are used (fewer: two CTAs fit on an SM)
@@ -627,9 +633,9 @@ __device__ __forceinline__ void epilogue_prefetch(float (&first)[32], int row, i
   for (int rr = 0; rr < 32; ++rr) first[rr] = rr < rows_valid ? gb::to_float<OT>(gbase[(size_t)rr * ldo]) : 0.f;
 }
 
-// A norm folded in in front of the product (RopeArgs::sums_in): 1/rms of the thread's token from the
+// A norm folded in in front of the product (EpilogueArgs::sums_in): 1/rms of the thread's token from the
 // partial sums, in their order; 1 without such a norm. Asked for while the tile's products still run.
-__device__ __forceinline__ float epilogue_row_scale(const RopeArgs& ra, int row, int rows_m) {
+__device__ __forceinline__ float epilogue_row_scale(const EpilogueArgs& ra, int row, int rows_m) {
   if (ra.sums_in == nullptr || row >= rows_m) return 1.f;
   float t = 0.f;
   for (int i = 0; i < ra.tiles_in; ++i) t += ra.sums_in[(size_t)i * ra.sums_ld + row];
@@ -643,7 +649,7 @@ __device__ __forceinline__ float epilogue_row_scale(const RopeArgs& ra, int row,
 // needs whole heads, and the paths for ragged tiles are run by the first of them alone.
 template <int BN, int EPI, typename OT>
 __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, OT* __restrict__ out, int ldo,
-                                              int rows_m, int rows_n, bool vec, const RopeArgs& ra, float* turn,
+                                              int rows_m, int rows_n, bool vec, const EpilogueArgs& ra, float* turn,
                                               int c_begin, int c_end, const float (&first)[32], const float inv) {
   // EMIT: the norm behind this accumulating product is folded in. Every warp writes the sum of squares
   // of its columns of every token into a row of its own of sums_out (two rows per tile of BN columns).
@@ -873,7 +879,7 @@ template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(p_threads(EPI), 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
                           OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m,
-                          int tiles_n, const RopeArgs ra) {
+                          int tiles_n, const EpilogueArgs ra) {
   constexpr bool DUAL = false;
   using G = Geometry<BN, false, false, false>;
   constexpr int STAGES = G::STAGES;
@@ -1049,7 +1055,7 @@ template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(p_threads(EPI), 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
                     OT* __restrict__ out, int ldo, int rows_m, int rows_n, int K, int tiles_m, int tiles_n,
-                    const RopeArgs ra) {
+                    const EpilogueArgs ra) {
   using PG = PairGeometry<BN>;
   constexpr int STAGES = PG::STAGES, PAIR_STAGE_BYTES = PG::STAGE_BYTES;
   constexpr int TMEM_COLS = 2 * BN;               // two accumulator stages
@@ -1332,7 +1338,7 @@ ClusterPlan pick_cluster_plan(Kernel kernel, int* active, int tiles, int total_k
 // twice the output features); out_features: columns of the output.
 template <int BN, int EPI, typename OT>
 int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int weight_rows, int out_features,
-                   int tokens, int K, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
+                   int tokens, int K, cudaStream_t stream, const EpilogueArgs& ra = EpilogueArgs{}) {
   using G = Geometry<BN, false, false, true, rope_table_bytes(EPI, BN)>;
   auto kernel = gemm_tc_cluster_kernel<BN, EPI, OT>;
   static bool configured = false;
@@ -1358,7 +1364,7 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ld
 // Few tokens: the weights are the MMA-row operand; BN tokens per tile.
 template <int BN>
 int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mn, void* out, int ldo,
-                     int weight_rows, int out_features, int tokens, int K, cudaStream_t stream, const RopeArgs& ra) {
+                     int weight_rows, int out_features, int tokens, int K, cudaStream_t stream, const EpilogueArgs& ra) {
   if (epi == EPI_STORE) {
     if (out_dtype == GB_F32)
       return launch_cluster<BN, EPI_STORE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
@@ -1373,7 +1379,7 @@ int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtens
 
 template <int BN, int EPI, typename OT>
 int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int tokens, int weight_rows,
-                      int out_features, int K, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
+                      int out_features, int K, cudaStream_t stream, const EpilogueArgs& ra = EpilogueArgs{}) {
   using G = Geometry<BN, false, false, false>;
   auto kernel = gemm_tc_persistent_kernel<BN, EPI, OT>;
   static bool configured = false;
@@ -1393,7 +1399,7 @@ int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int
 // 256 x BN tiles on CTA pairs (clusters of two).
 template <int BN, int EPI, typename OT>
 int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, int tokens, int weight_rows,
-                int out_features, int K, cudaStream_t stream, const RopeArgs& ra = RopeArgs{}) {
+                int out_features, int K, cudaStream_t stream, const EpilogueArgs& ra = EpilogueArgs{}) {
   using PG = PairGeometry<BN>;
   auto kernel = gemm_tc_pair_kernel<BN, EPI, OT>;
   static bool configured = false;
@@ -1456,7 +1462,7 @@ GB_EXPORT int gb_tc_error_check() {
   return v;
 }
 
-// An RMS norm folded into the products around it (see RopeArgs). As the consumer: sums_in
+// An RMS norm folded into the products around it (see EpilogueArgs). As the consumer: sums_in
 // [tiles_in, sums_ld] and eps, inv_width = 1 / features of the normed vector. As the producer
 // (accumulating products only): h_out [Mx, Nw] bfloat16, weight [Nw] 32-bit, sums_out
 // [gb_gemm_tc_norm_tiles(Mx, Nw), sums_ld]. Unused halves are null.
@@ -1471,7 +1477,7 @@ struct GbNormFold {
 };
 
 namespace {
-void fold_norm(RopeArgs& ra, const GbNormFold* n) {
+void fold_norm(EpilogueArgs& ra, const GbNormFold* n) {
   if (n == nullptr) return;
   ra.sums_in = n->sums_in; ra.tiles_in = n->tiles_in; ra.eps = n->eps; ra.inv_width = n->inv_width;
   ra.h_out = (__nv_bfloat16*)n->h_out; ra.weight = n->weight; ra.sums_out = n->sums_out; ra.sums_ld = n->sums_ld;
@@ -1505,7 +1511,7 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   if (epi == EPI_SWIGLU && out_dtype != GB_BF16)
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: the SiLU-gate epilogue writes bfloat16");
   const int weight_rows = epi == EPI_SWIGLU ? 128 * ((Nw + 63) / 64) : Nw;
-  RopeArgs ra{};
+  EpilogueArgs ra{};
   fold_norm(ra, norm);
   if (ra.h_out != nullptr && epi != EPI_ACCUMULATE)
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: a norm is folded in behind accumulating products only (epilogue %d)", epi);
@@ -1558,7 +1564,7 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
     return gb::fail(GB_UNSUPPORTED, "gemm_tc_qkv: head_dim %d does not divide 128", head_dim);
   if (kv_heads > 0 && (!k_pool || !v_pool || !block_table || page_size < 1))
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_qkv: kv heads given without a cache to store them in");
-  RopeArgs ra{};
+  EpilogueArgs ra{};
   fold_norm(ra, norm);
   if (ra.h_out != nullptr)
     return gb::fail(GB_UNSUPPORTED, "gemm_tc_qkv: no norm can be folded in behind this product");
