@@ -53,9 +53,14 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
+        self._views: Dict[str, tuple] = {}      # name -> (shape, dtype, view): the last view handed out
 
     def get(self, name: str, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """``zero``: the buffer is zeroed when it is created or grown (not on later calls)."""
+        shape = tuple(shape)
+        last = self._views.get(name)
+        if last is not None and last[0] == shape and last[1] is dtype:
+            return last[2]          # the same request as last time (every layer of a step): no new view
         n = 1
         for s in shape:
             n *= int(s)
@@ -67,7 +72,9 @@ class Workspace:
             make = torch.zeros if zero else torch.empty
             buf = make(size, dtype=torch.uint8, device=self.device)
             self._bufs[name] = buf
-        return buf[:nbytes].view(dtype).view(*shape)
+        view = buf[:nbytes].view(dtype).view(*shape)
+        self._views[name] = (shape, dtype, view)
+        return view
 
 
 @dataclass

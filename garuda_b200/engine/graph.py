@@ -131,7 +131,7 @@ class DecodeGraphs:
         collecting = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"), r.ops.on_current_stream():
                 logits = r.model.forward(ctx, caches)
         finally:
             if collecting:

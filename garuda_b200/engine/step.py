@@ -11,6 +11,8 @@ A step runs only the tokens it is given; everything earlier comes from the cache
 """
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -177,7 +179,9 @@ class StepRunner:
             batch = self.build_batch(entries, new_lens)
             ctx = StepContext(batch=batch, ws=self.ws, ops=self.ops, dtype=self.dtype)
             caches = self.cache.layer_caches(batch.block_tables)
-            logits = self.model.forward(ctx, caches)
+            hold = getattr(self.ops, "on_current_stream", None)
+            with (hold() if hold is not None else contextlib.nullcontext()):
+                logits = self.model.forward(ctx, caches)
             tokens = batch.num_tokens
         mgr = self.cache.manager
         for r, n in new_lens:

@@ -7,6 +7,7 @@ and contiguity, and launches on torch's current stream.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from ctypes import c_void_p, c_int, c_float, c_longlong
@@ -84,6 +85,7 @@ class CudaOps:
         # variable is for comparing timings
         self.folds_norms = self.tc is not None and os.environ.get("GARUDA_B200_FOLD_NORMS", "1") != "0"
         self._inv_freq = {}
+        self._held_stream = None
         self.launches = 0
         from ..engine.batch import Workspace
         self.private_ws = Workspace(self.device)   # scratch for calls made outside a step
@@ -116,7 +118,20 @@ class CudaOps:
             fn.restype = c_int
 
     def _stream(self):
+        if self._held_stream is not None:
+            return self._held_stream
         return torch.cuda.current_stream(self.device).cuda_stream
+
+    @contextlib.contextmanager
+    def on_current_stream(self):
+        """Within the block every kernel is launched on the stream that is current now (asked
+        for once, not per launch). The caller must not change the current stream inside."""
+        outer = self._held_stream
+        self._held_stream = torch.cuda.current_stream(self.device).cuda_stream
+        try:
+            yield
+        finally:
+            self._held_stream = outer
 
     def _check(self, lib, code: int, what: str, kernels: int = 1) -> None:
         if code != 0:
@@ -175,7 +190,8 @@ class CudaOps:
         _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "linear: operands must be matrices")
         M, K = a.shape
         N = w.shape[0]
-        _need(w.shape[1] == K and out.shape == (M, N), f"linear: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
+        if not (w.shape[1] == K and out.shape == (M, N)):       # the message is made only when it is needed
+            _need(False, f"linear: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
         _need(a.dtype == w.dtype, "linear: a and w must have one dtype")
         _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
         if self.tc is not None and a.dtype == torch.bfloat16:
