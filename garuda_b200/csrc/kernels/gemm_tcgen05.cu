@@ -1427,6 +1427,20 @@ int pick_tile_width(int rows_m, int rows_n) {
   return cost(256) <= cost(128) ? 256 : 128;
 }
 
+// Up to this many tokens the weights are the MMA's rows and clusters split K (see the head of this file);
+// more tokens than one tile's 64 columns make several column tiles, each of which reads the weights
+// (from L2 after the first). With the TinyLlama layer sizes a step of 65 to 256 tokens took 2.1 to 2.8 ms
+// this way against 2.9 to 3.5 ms with 128-row token tiles, which are too few CTAs to stream the weights;
+// from about 400 tokens on the two are level. The environment variable is for such comparisons.
+int few_token_limit() {
+  static const int limit = [] {
+    const char* v = getenv("GARUDA_B200_FEW_TOKENS");
+    const int n = v ? atoi(v) : 0;
+    return n >= 64 ? n : 256;
+  }();
+  return limit;
+}
+
 bool pairs_enabled() {
   static const bool on = [] {
     const char* v = getenv("GARUDA_B200_PAIRS");
@@ -1436,7 +1450,9 @@ bool pairs_enabled() {
 }
 
 // More than 64 tokens: whether CTA pairs take the product, and the tile width over the weight's rows.
-bool many_token_pairs(int tokens, int weight_rows) { return pairs_enabled() && tokens >= 2 * BM && weight_rows >= 256; }
+// Pairs pay from about a thousand tokens (768: 3.9 ms a step with pairs, 3.4 without; 1,024: 4.4 against 4.5):
+// below that their 256 x 256 tiles are too few for the 74 pairs.
+bool many_token_pairs(int tokens, int weight_rows) { return pairs_enabled() && tokens >= 8 * BM && weight_rows >= 256; }
 int many_token_width(int tokens, int weight_rows) {
   return many_token_pairs(tokens, weight_rows) ? 256 : pick_tile_width(tokens, weight_rows);
 }
@@ -1487,7 +1503,7 @@ void fold_norm(EpilogueArgs& ra, const GbNormFold* n) {
 // Rows of sums_out that a product of Mx tokens and Nw output features writes when a norm is folded
 // in behind it; 0: this shape does not fold norms.
 GB_EXPORT int gb_gemm_tc_norm_tiles(int Mx, int Nw) {
-  if (Mx <= 64) return (Nw + BM - 1) / BM;                   // a row per tile of 128 features
+  if (Mx <= few_token_limit()) return (Nw + BM - 1) / BM;                   // a row per tile of 128 features
   const int width = many_token_width(Mx, Nw);
   return 2 * ((Nw + width - 1) / width);                      // a row per epilogue warp of a lane quarter
 }
@@ -1517,7 +1533,7 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: a norm is folded in behind accumulating products only (epilogue %d)", epi);
   CUtensorMap mm, mn;
   int rc;
-  if (Mx <= 64) {
+  if (Mx <= few_token_limit()) {
     const int bn = Mx <= 16 ? 16 : Mx <= 32 ? 32 : 64;
     if ((rc = tensor_map_2d(w, weight_rows, K, BM, &mm))) return rc;
     if ((rc = tensor_map_2d(x, Mx, K, bn, &mn))) return rc;
@@ -1575,7 +1591,7 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
   CUtensorMap mm, mn;
   int rc;
   __nv_bfloat16* none = nullptr;
-  if (Mx <= 64) {
+  if (Mx <= few_token_limit()) {
     const int bn = Mx <= 16 ? 16 : Mx <= 32 ? 32 : 64;
     if ((rc = tensor_map_2d(w, Nw, K, BM, &mm))) return rc;
     if ((rc = tensor_map_2d(x, Mx, K, bn, &mn))) return rc;
