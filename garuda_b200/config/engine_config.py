@@ -68,7 +68,9 @@ class MemorySection:
 @dataclass
 class RuntimeSection:
     max_batch_tokens: int = 2048  # tokens of one step: decode tokens and prompt portions together
-    prefill_chunk: int = 512      # most tokens of one prompt per step (scheduler/mod.rs:319-321)
+    # most tokens of one prompt per step (scheduler/mod.rs:319-321, where the default is 512: here a
+    # step of 512 tokens runs at 145 tokens/ms, one of 2,048 at 335, so a prompt may fill the step)
+    prefill_chunk: int = 2048
     cuda_graphs: bool = True      # replay decode steps from captured graphs
     lookahead: bool = True        # launch the next greedy decode step while this one's tokens travel to the host
     device: int = 0

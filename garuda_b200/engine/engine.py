@@ -41,7 +41,7 @@ class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", *, context: Optional[int] = None,
                  sliding_window: int = 0, page_size: int = 32, kv_tokens: Optional[int] = None,
                  kv_cache_bytes: Optional[int] = None, max_concurrent: int = 4,
-                 queue_capacity: int = 256, max_batch_tokens: int = 2048, prefill_chunk: int = 512,
+                 queue_capacity: int = 256, max_batch_tokens: int = 2048, prefill_chunk: int = 2048,
                  cuda_graphs: bool = True, lookahead: bool = True, device: int = 0, ignore_eos: bool = False,
                  eos_token_id: Optional[int] = None, ops=None):
         if dtype not in _DTYPES:
