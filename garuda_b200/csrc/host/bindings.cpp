@@ -159,6 +159,7 @@ PYBIND11_MODULE(_garuda_host, m) {
       .def("submit", &Scheduler::submit, py::arg("prompt"), py::arg("params"), py::arg("priority") = 0)
       .def("cancel", &Scheduler::cancel)
       .def("plan", &Scheduler::plan)
+      .def("peek_uniform", &Scheduler::peek_uniform)
       .def("complete", &Scheduler::complete)
       .def("fail", &Scheduler::fail)
       .def("idle", &Scheduler::idle)

@@ -247,6 +247,15 @@ StepPlan Scheduler::plan() {
   return plan;
 }
 
+float Scheduler::peek_uniform(int64_t id) const {
+  for (const auto& r : running_)
+    if (r.id == id) {
+      Rng copy = r.rng;
+      return copy.next_f32();
+    }
+  throw SchedulerError("request " + std::to_string(id) + " is not running");
+}
+
 std::vector<Event> Scheduler::complete(const StepPlan& plan, const std::vector<int32_t>& sampled) {
   std::vector<Event> events;
   size_t wanted = 0;

@@ -119,6 +119,9 @@ class Scheduler {
   void cancel(int64_t id);
   // Decide the next step. Reserves the pages its entries need.
   StepPlan plan();
+  // The uniform draw that the next plan will give a running request's sampling entry (its
+  // generator is not advanced): for a decode step that is launched before that plan is made.
+  float peek_uniform(int64_t id) const;
   // The step ran; `sampled` holds one token per entry with sample == true, in order.
   std::vector<Event> complete(const StepPlan& plan, const std::vector<int32_t>& sampled);
   // The step failed: every request of the plan ends with this error.

@@ -110,6 +110,113 @@ __device__ bool bisect(const float* p, int V, double* sh_d, int* sh_i, Pred pred
   return true;
 }
 
+// top_k of at most LIST_MAX, the usual case: the k most likely tokens are picked out and sorted,
+// and top-p, the total mass and the walk to the drawn point run over that short list exactly as the
+// reference walks its sorted candidates (garuda/src/runtime/mod.rs:109-172), instead of one bisection
+// over the whole vocabulary for each of them.
+constexpr int LIST_MAX = 1024;
+
+// p: the row's probabilities. Ends with the chosen token in *out. Every thread of the block calls it.
+__device__ void sample_from_top_k(const float* p, int V, int k, float tp, float uniform_draw, int32_t* out,
+                                  int* sh_cnt, int* sh_i) {
+  __shared__ unsigned long long keys[LIST_MAX];   // probability bits, then ~token id: descending = by probability, then by id
+  __shared__ int hist[256];
+  const int kk = min(k, V);
+  // the kk-th largest probability by its bit pattern, a byte at a time from the top
+  uint32_t prefix = 0;
+  int remaining = kk;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    const uint32_t mask = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
+    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const uint32_t b = __float_as_uint(p[i]);
+      if ((b & mask) == (prefix & mask)) atomicAdd(&hist[(b >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int above = 0, bin = 255;
+      for (; bin > 0; --bin) {
+        if (above + hist[bin] >= remaining) break;
+        above += hist[bin];
+      }
+      sh_i[0] = bin;
+      sh_i[1] = remaining - above;
+    }
+    __syncthreads();
+    prefix |= (uint32_t)sh_i[0] << shift;
+    remaining = sh_i[1];
+    __syncthreads();
+  }
+  const uint32_t tau_bits = prefix;   // the kk-th largest; `remaining` of those equal to it are wanted
+  const int gt = kk - remaining;
+  // gather: everything above tau in any order (the sort below orders it), and of those equal to tau
+  // the `remaining` lowest token ids, found in order by giving every thread a run of the vocabulary
+  if (threadIdx.x == 0) sh_i[2] = 0;
+  const int chunk = (V + blockDim.x - 1) / blockDim.x;
+  const int lo = min(V, (int)threadIdx.x * chunk), hi = min(V, lo + chunk);
+  int mine = 0;
+  for (int i = lo; i < hi; ++i) mine += (__float_as_uint(p[i]) == tau_bits);
+  sh_cnt[threadIdx.x] = mine;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const uint32_t b = __float_as_uint(p[i]);
+    if (b > tau_bits) keys[atomicAdd(&sh_i[2], 1)] = ((unsigned long long)b << 32) | (0xffffffffu - (uint32_t)i);
+  }
+  int before = 0;
+  for (int t = 0; t < (int)threadIdx.x; ++t) before += sh_cnt[t];
+  for (int i = lo; i < hi && before < remaining; ++i) {
+    if (__float_as_uint(p[i]) == tau_bits) {
+      keys[gt + before] = ((unsigned long long)tau_bits << 32) | (0xffffffffu - (uint32_t)i);
+      ++before;
+    }
+  }
+  // sort descending (bitonic, padded with zeros to a power of two)
+  int size = 1;
+  while (size < kk) size <<= 1;
+  for (int i = kk + threadIdx.x; i < size; i += blockDim.x) keys[i] = 0ull;
+  __syncthreads();
+  for (int span = 2; span <= size; span <<= 1) {
+    for (int step = span >> 1; step > 0; step >>= 1) {
+      for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const int other = i ^ step;
+        if (other > i) {
+          const unsigned long long a = keys[i], b = keys[other];
+          const bool descending = (i & span) == 0;
+          if (descending ? a < b : a > b) { keys[i] = b; keys[other] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (threadIdx.x == 0) {
+    auto prob = [&](int i) { return (double)__uint_as_float((uint32_t)(keys[i] >> 32)); };
+    // n: how many candidates survive top-p (:161-172) within the top k (:144-158)
+    int n = kk;
+    if (tp < 1.0f) {
+      double cum = 0.0;
+      for (int i = 0; i < kk; ++i) {
+        cum += prob(i);
+        if (cum >= (double)tp) { n = i + 1; break; }
+      }
+    }
+    double mass = 0.0;
+    for (int i = 0; i < n; ++i) mass += prob(i);
+    const float total = (float)mass;
+    int j = 1;    // zero mass: the most likely one (:111-115)
+    if (total > 0.f) {
+      const double point = (double)(uniform_draw * total);
+      double cum = 0.0;
+      j = n;
+      for (int i = 0; i < n; ++i) {
+        cum += prob(i);
+        if (cum >= point) { j = i + 1; break; }
+      }
+    }
+    *out = (int32_t)(0xffffffffu - (uint32_t)(keys[j - 1] & 0xffffffffull));
+  }
+}
+
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
@@ -157,6 +264,11 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   const float uniform = 1.0f / (float)V;
   for (int i = threadIdx.x; i < V; i += blockDim.x) p[i] = good ? p[i] * inv : uniform;
   __syncthreads();
+
+  if (top_k[r] > 0 && top_k[r] <= LIST_MAX) {
+    sample_from_top_k(p, V, top_k[r], top_p[r], u[r], out + r, sh_cnt, sh_i);
+    return;
+  }
 
   // n: how many candidates survive top-k (:144-158) and top-p (:161-172)
   int n = V;

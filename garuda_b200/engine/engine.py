@@ -212,8 +212,9 @@ class Engine:
 
         Launching ahead keeps the GPU busy while the host waits for this step's tokens,
         lets the scheduler finish and plan, and prepares the next launch. A step ahead
-        is only launched for greedy decode steps, whose next entries are known but for
-        the tokens. When the plan to come turns out different (a request has finished
+        is only launched for decode steps, whose next entries are known but for the
+        tokens (a sampled entry's uniform draw is the next of its request's generator,
+        which the scheduler lets us look at). When the plan to come turns out different (a request has finished
         or was preempted, another has joined), the rows of the step ahead that still
         fit are used and the plan's other entries run as a step of their own; a row
         for a request that is gone is dropped (what it wrote to the cache lies in pages
@@ -224,6 +225,9 @@ class Engine:
             gone = set(plan.preempted)
             have = {rid: k for k, rid in enumerate(ahead[0]) if rid not in gone}
         matched = [e for e in entries if e.sample and len(e.tokens) == 1 and e.id in have]
+        for e in matched:       # a row of the step ahead was drawn with the uniform that the plan now brings
+            if e.temperature != 0.0 and e.u != ahead[2][e.id]:
+                raise RuntimeError(f"request {e.id}: the step launched ahead drew with {ahead[2][e.id]}, the plan brings {e.u}")
         taken = {e.id for e in matched}
         rest = [e for e in entries if e.id not in taken]
         fresh = None
@@ -246,7 +250,7 @@ class Engine:
 
         nxt = None
         if (self.lookahead and self.runner.graphs is not None
-                and all(e.sample and len(e.tokens) == 1 and e.temperature == 0.0 for e in entries)):
+                and all(e.sample and len(e.tokens) == 1 for e in entries)):
             try:
                 if not rest and [w[1] for w in where] == list(range(len(ahead[0]))):
                     dev_tokens = ahead[1].tokens
@@ -257,9 +261,13 @@ class Engine:
                     dev_tokens = torch.cat(parts)
                 step = [StepEntry(e.id, (0,), (0,)) for e in entries]
                 logits = self.runner.run(step, device_tokens=dev_tokens)
-                zeros = [0.0] * len(step)
+                # a sampled row's uniform draw comes from the request's generator in its fixed order, so
+                # the draw of the step ahead is known now (the scheduler hands it out again with the plan)
+                us = [0.0 if e.temperature == 0.0 else self.scheduler.peek_uniform(e.id) for e in entries]
                 nxt = ([e.id for e in entries],
-                       self.sampler.launch(logits, zeros, [0] * len(step), [1.0] * len(step), zeros))
+                       self.sampler.launch(logits, [e.temperature for e in entries], [e.top_k for e in entries],
+                                           [e.top_p for e in entries], us),
+                       dict(zip((e.id for e in entries), us)))
             except (StepError, self._host.CacheError):
                 nxt = None        # no room (pages, context) to run ahead: the scheduler decides next time
 

@@ -110,8 +110,8 @@ def test_graphs_captured_ahead_of_time_and_among_dropped_engines():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_launched_ahead_change_nothing(dtype):
-    """Greedy decode steps are launched before the tokens of the step in front have reached the
-    host. Requests that end at different times (their own limits, an end-of-sequence token in the
+    """Decode steps, greedy or sampled, are launched before the tokens of the step in front have
+    reached the host. Requests that end at different times (their own limits, an end-of-sequence token in the
     middle), more prompts than may run at once, and too few pages: the tokens and the reasons for
     finishing are those of an engine that launches nothing ahead."""
     from garuda_b200 import Engine, SamplingParams
@@ -119,6 +119,9 @@ def test_steps_launched_ahead_change_nothing(dtype):
     prompts = [random_tokens(name, n, 300 + i) for i, n in enumerate([5, 40, 17, 64, 9, 33, 2])]
     limits = [7, 30, 12, 25, 40, 3, 18]
     params = [SamplingParams.greedy(max_tokens=m) for m in limits]
+    # sampled requests among the greedy ones: their draws come from the requests' own generators
+    for i in (1, 3, 6):
+        params[i] = SamplingParams(temperature=0.9, top_k=50, top_p=0.95, max_tokens=limits[i], seed=40 + i)
     kw = dict(dtype=dtype, page_size=16, max_concurrent=3)
     plain = Engine(model_dir(name), lookahead=False, **kw).generate(prompts, params)
     # a token that some request produces in the middle of its answer ends it there

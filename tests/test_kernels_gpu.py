@@ -445,6 +445,32 @@ def test_argmax_first_maximum_wins(ops):
     assert out.tolist() == want
 
 
+def test_sampling_among_equal_probabilities_goes_by_token_id(ops):
+    """All logits equal: the top k are the k lowest token ids (ties go by id), each with the same
+    probability, and the draw walks them in that order. With far more ties than the kernel's short
+    list of candidates holds."""
+    from tests.plain.sampling_plain import sample as plain_sample
+
+    class FixedU:
+        def __init__(self, u): self.u = u
+        def next_f32(self): return np.float32(self.u)
+
+    V = 5000
+    rows = [(1.0, k, p, u) for k, p in ((40, 1.0), (7, 0.5), (1024, 1.0), (300, 0.02))
+            for u in (0.0, 0.26, 0.5, 0.99)]
+    R = len(rows)
+    logits = torch.full((R, V), 0.25)
+    out = torch.zeros(R, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(R * V, device="cuda")
+    f = lambda i, dt: dev(torch.tensor([r[i] for r in rows], dtype=dt))
+    ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32),
+               out, scratch)
+    got = out.tolist()
+    for i, (temp, k, p, u) in enumerate(rows):
+        want = plain_sample(logits[i].numpy(), temp, k, p, FixedU(u))
+        assert abs(got[i] - want) <= 1 and got[i] < k, (rows[i], got[i], want)    # a draw on a boundary may round either way
+
+
 @pytest.mark.parametrize("V", [50, 331, 32000])
 def test_sampling_follows_the_plain_sampler(ops, V):
     from tests.plain.sampling_plain import sample as plain_sample
@@ -456,7 +482,7 @@ def test_sampling_follows_the_plain_sampler(ops, V):
     g = torch.Generator().manual_seed(V)
     rows = []
     for temp, k, p in ((0.8, 40, 0.95), (1.0, 0, 1.0), (0.5, 5, 1.0), (1.3, 0, 0.7), (0.0, 40, 0.95),
-                       (0.8, 1, 0.95), (2.0, 100, 0.5)):
+                       (0.8, 1, 0.95), (2.0, 100, 0.5), (1.5, 1024, 0.9), (1.5, 1025, 0.9), (1.0, 64, 1.0)):
         for u in (0.0, 0.123, 0.5, 0.77, 0.999):
             rows.append((temp, k, p, u))
     R = len(rows)

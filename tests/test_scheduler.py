@@ -254,3 +254,18 @@ def test_windowed_group_lets_a_long_request_run_in_few_pages():
             break
     assert done is not None and done.kind == Done and done.detail == "length"
     assert s.stats().preemptions == 0
+
+
+def test_the_next_draw_can_be_looked_at_without_taking_it():
+    """A decode step launched before its plan is made needs the uniform that the plan will bring."""
+    s, cache = make()
+    a = s.submit([1], greedy(max_tokens=4, seed=9, temperature=0.8))
+    plan = s.plan()
+    for _ in range(3):
+        ahead = s.peek_uniform(a)
+        assert s.peek_uniform(a) == ahead                   # looking twice takes nothing
+        s.complete(plan, [5])
+        plan = s.plan()
+        assert plan.entries[0].u == ahead
+    with pytest.raises(host.SchedulerError, match="not running"):
+        s.peek_uniform(12345)
