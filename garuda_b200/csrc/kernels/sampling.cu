@@ -54,7 +54,10 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restr
 // subtracting probabilities from u * total until it reaches zero. Survivors are
 // not renormalised.
 //
-// Nothing is sorted here. "The j-th candidate" is found by bisecting on the bit
+// Two ways. With top_k of at most 1,024 (sample_from_top_k below) the k most likely
+// tokens are found by a radix selection on the probabilities' bit patterns, sorted in
+// shared memory, and walked as the reference walks them. Otherwise (no top_k, or a
+// larger one) nothing is sorted: "the j-th candidate" is found by bisecting on the bit
 // pattern of the probability (non-negative floats order like their bits): for a
 // threshold tau one pass gives how many probabilities exceed it, how many equal
 // it, and the sum of those that exceed it. Sums are taken in 64-bit so that
