@@ -123,7 +123,7 @@ constexpr int LIST_MAX = 1024;
 __device__ void sample_from_top_k(const float* p, int V, int k, float tp, float uniform_draw, int32_t* out,
                                   int* sh_cnt, int* sh_i) {
   __shared__ unsigned long long keys[LIST_MAX];   // probability bits, then ~token id: descending = by probability, then by id
-  __shared__ int hist[256];
+  __shared__ int hist[257];                       // bin 256 takes what a pass does not count
   const int kk = min(k, V);
   // the kk-th largest probability by its bit pattern, a byte at a time from the top
   uint32_t prefix = 0;
@@ -132,19 +132,39 @@ __device__ void sample_from_top_k(const float* p, int V, int k, float tp, float 
     const uint32_t mask = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
     if (threadIdx.x < 256) hist[threadIdx.x] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const uint32_t b = __float_as_uint(p[i]);
-      if ((b & mask) == (prefix & mask)) atomicAdd(&hist[(b >> shift) & 255u], 1);
+    // Probabilities crowd into a few bins (most share their exponent), so the lanes of a warp that
+    // hit the same bin add to it once, together.
+    const int padded = (V + 31) & ~31;
+    for (int i = threadIdx.x; i < padded; i += blockDim.x) {
+      const uint32_t b = i < V ? __float_as_uint(p[i]) : 0u;
+      const int bin = (i < V && (b & mask) == (prefix & mask)) ? (int)((b >> shift) & 255u) : 256;
+      const unsigned peers = __match_any_sync(0xffffffffu, bin);
+      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int above = 0, bin = 255;
-      for (; bin > 0; --bin) {
-        if (above + hist[bin] >= remaining) break;
-        above += hist[bin];
+    if (threadIdx.x < 32) {
+      // the bin that holds the `remaining`-th from the top: every lane of the first warp sums eight bins,
+      // a suffix sum over the lanes finds the lane, which then walks its own eight
+      const int lane = threadIdx.x;
+      int mine8 = 0;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) mine8 += hist[8 * lane + q];
+      int suffix = mine8;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(0xffffffffu, suffix, o);
+        if (lane + o < 32) suffix += v;
       }
-      sh_i[0] = bin;
-      sh_i[1] = remaining - above;
+      int above = suffix - mine8;                      // in the bins of the lanes above this one
+      if (above < remaining && remaining <= suffix) {
+        int bin = 8 * lane + 7;
+        for (; bin > 8 * lane; --bin) {
+          if (above + hist[bin] >= remaining) break;
+          above += hist[bin];
+        }
+        sh_i[0] = bin;
+        sh_i[1] = remaining - above;
+      }
     }
     __syncthreads();
     prefix |= (uint32_t)sh_i[0] << shift;
@@ -154,31 +174,56 @@ __device__ void sample_from_top_k(const float* p, int V, int k, float tp, float 
   const uint32_t tau_bits = prefix;   // the kk-th largest; `remaining` of those equal to it are wanted
   const int gt = kk - remaining;
   // gather: everything above tau in any order (the sort below orders it), and of those equal to tau
-  // the `remaining` lowest token ids, found in order by giving every thread a run of the vocabulary
+  // the `remaining` lowest token ids. For these every warp takes a run of the vocabulary and walks it
+  // 32 tokens at a time, so that ranks among the ties follow the token ids.
   if (threadIdx.x == 0) sh_i[2] = 0;
-  const int chunk = (V + blockDim.x - 1) / blockDim.x;
-  const int lo = min(V, (int)threadIdx.x * chunk), hi = min(V, lo + chunk);
-  int mine = 0;
-  for (int i = lo; i < hi; ++i) mine += (__float_as_uint(p[i]) == tau_bits);
-  sh_cnt[threadIdx.x] = mine;
   __syncthreads();
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const uint32_t b = __float_as_uint(p[i]);
-    if (b > tau_bits) keys[atomicAdd(&sh_i[2], 1)] = ((unsigned long long)b << 32) | (0xffffffffu - (uint32_t)i);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int run = ((V + nw - 1) / nw + 31) & ~31;            // tokens per warp, whole walks of 32
+  const int lo = min(V, warp * run), hi = min(V, lo + run);
+  int ties = 0;
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const uint32_t b = i < hi ? __float_as_uint(p[i]) : 0u;
+    if (i < hi && b > tau_bits) keys[atomicAdd(&sh_i[2], 1)] = ((unsigned long long)b << 32) | (0xffffffffu - (uint32_t)i);
+    ties += __popc(__ballot_sync(0xffffffffu, i < hi && b == tau_bits));
   }
-  int before = 0;
-  for (int t = 0; t < (int)threadIdx.x; ++t) before += sh_cnt[t];
-  for (int i = lo; i < hi && before < remaining; ++i) {
-    if (__float_as_uint(p[i]) == tau_bits) {
-      keys[gt + before] = ((unsigned long long)tau_bits << 32) | (0xffffffffu - (uint32_t)i);
-      ++before;
-    }
+  if (lane == 0) sh_cnt[warp] = ties;
+  __syncthreads();
+  int before = 0;                                            // ties in the runs of the warps in front
+  for (int w = 0; w < warp; ++w) before += sh_cnt[w];
+  for (int base = lo; base < hi && before < remaining; base += 32) {
+    const int i = base + lane;
+    const bool tie = i < hi && __float_as_uint(p[i]) == tau_bits;
+    const unsigned votes = __ballot_sync(0xffffffffu, tie);
+    const int rank = before + __popc(votes & ((1u << lane) - 1u));
+    if (tie && rank < remaining) keys[gt + rank] = ((unsigned long long)tau_bits << 32) | (0xffffffffu - (uint32_t)i);
+    before += __popc(votes);
   }
   // sort descending (bitonic, padded with zeros to a power of two)
   int size = 1;
   while (size < kk) size <<= 1;
   for (int i = kk + threadIdx.x; i < size; i += blockDim.x) keys[i] = 0ull;
   __syncthreads();
+  if (size <= 64) {
+    // a short list is sorted by the first warp alone: no block-wide barriers
+    if (threadIdx.x < 32) {
+      for (int span = 2; span <= size; span <<= 1) {
+        for (int step = span >> 1; step > 0; step >>= 1) {
+          for (int i = threadIdx.x; i < size; i += 32) {
+            const int other = i ^ step;
+            if (other > i) {
+              const unsigned long long a = keys[i], b = keys[other];
+              const bool descending = (i & span) == 0;
+              if (descending ? a < b : a > b) { keys[i] = b; keys[other] = a; }
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+    __syncthreads();
+  } else
   for (int span = 2; span <= size; span <<= 1) {
     for (int step = span >> 1; step > 0; step >>= 1) {
       for (int i = threadIdx.x; i < size; i += blockDim.x) {
@@ -223,14 +268,16 @@ __device__ void sample_from_top_k(const float* p, int V, int k, float tp, float 
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
-              const float* __restrict__ u, int32_t* __restrict__ out, float* __restrict__ scratch, int V) {
+              const float* __restrict__ u, int32_t* __restrict__ out, float* __restrict__ scratch, int V,
+              int in_shared) {
+  extern __shared__ float row_shared[];      // in_shared: the row's probabilities live here, not in scratch
   __shared__ double sh_d[32];
   __shared__ int sh_i[64];
   __shared__ float sh_f[32];
   __shared__ int sh_cnt[1024];
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
-  float* p = scratch + (size_t)r * V;
+  float* p = in_shared ? row_shared : scratch + (size_t)r * V;
   const float temp = temperature[r];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   if (temp == 0.f) {  // greedy (:99-107)
@@ -336,6 +383,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
 }  // namespace
 
+
 GB_EXPORT int gb_argmax(const float* logits, int32_t* out, int R, int V, cudaStream_t stream) {
   if (R <= 0) return GB_OK;
   if (V <= 0) return gb::fail(GB_BAD_ARGUMENT, "cannot sample from empty logits");
@@ -343,15 +391,34 @@ GB_EXPORT int gb_argmax(const float* logits, int32_t* out, int R, int V, cudaStr
   return gb::check_launch("argmax");
 }
 
+namespace {
+// A row's probabilities are read a dozen times (hundreds without a small top_k): they are kept in
+// shared memory when the vocabulary fits there (about 50,000 tokens), else in `scratch`.
+int launch_sample(const float* logits, const float* temperature, const int32_t* top_k, const float* top_p,
+                  const float* u, int32_t* out, float* scratch, int R, int V, cudaStream_t stream) {
+  constexpr size_t LIMIT = 200 * 1024;
+  const size_t bytes = (size_t)V * sizeof(float);
+  const bool fits = bytes <= LIMIT;
+  static bool configured = false;
+  if (fits && !configured) {
+    cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LIMIT);
+    if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "sample: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  sample_kernel<<<R, 1024, fits ? bytes : 0, stream>>>(logits, temperature, top_k, top_p, u, out, scratch, V,
+                                                       fits ? 1 : 0);
+  return gb::check_launch("sample");
+}
+}  // namespace
+
 // One token per row of logits [R, V]. Rows with temperature 0 are greedy.
-// scratch: R * V floats of work space (the probabilities).
+// scratch: R * V floats of work space (the probabilities, where a row does not fit in shared memory).
 GB_EXPORT int gb_sample(const float* logits, const float* temperature, const int32_t* top_k,
                         const float* top_p, const float* u, int32_t* out, float* scratch, int R, int V,
                         cudaStream_t stream) {
   if (R <= 0) return GB_OK;
   if (V <= 0) return gb::fail(GB_BAD_ARGUMENT, "cannot sample from empty logits");
-  sample_kernel<<<R, 1024, 0, stream>>>(logits, temperature, top_k, top_p, u, out, scratch, V);
-  return gb::check_launch("sample");
+  return launch_sample(logits, temperature, top_k, top_p, u, out, scratch, R, V, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -396,6 +463,5 @@ GB_EXPORT int gb_sample_noalloc(const float* logits, const float* temperature, c
                       cudaGetErrorString(e));
     g_noalloc_ptr[device] = p;
   }
-  sample_kernel<<<R, 1024, 0, stream>>>(logits, temperature, top_k, top_p, u, out, g_noalloc_ptr[device], V);
-  return gb::check_launch("sample (built-in work space)");
+  return launch_sample(logits, temperature, top_k, top_p, u, out, g_noalloc_ptr[device], R, V, stream);
 }

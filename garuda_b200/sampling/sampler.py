@@ -21,6 +21,7 @@ class Sampler:
         self._scratch = None
         self._staging = {}       # pinned buffers for the tokens' way back, two per size in turn
         self._turn = 0
+        self._params, self._params_turn = {}, 0      # pinned buffers for the rows' sampling parameters
 
     def _host_buffer(self, R: int) -> torch.Tensor:
         self._turn ^= 1
@@ -66,11 +67,29 @@ class Sampler:
         if all(t == 0.0 for t in temperature):
             self.ops.argmax(logits, out)
             return
-        host = np.empty((4, R), dtype=np.float32)
+        if self.device.type == "cuda":
+            # pinned buffers kept and taken in turn (pinning memory anew costs more than the kernel); the
+            # event tells when the copy that last read a buffer has run
+            self._params_turn = (self._params_turn + 1) % 4
+            key = (R, self._params_turn)
+            slot = self._params.get(key)
+            if slot is None:
+                slot = self._params[key] = [torch.empty((4, R), dtype=torch.float32).pin_memory(), None]
+            if slot[1] is not None:
+                slot[1].synchronize()
+            pinned = slot[0]
+            host = pinned.numpy()
+        else:
+            host = np.empty((4, R), dtype=np.float32)
         host[0], host[1], host[2] = temperature, top_p, u
         host[3] = np.asarray(top_k, dtype=np.int32).view(np.float32)
-        params = torch.from_numpy(host)
-        params = params.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else params
+        if self.device.type == "cuda":
+            params = pinned.to(self.device, non_blocking=True)
+            if slot[1] is None:
+                slot[1] = torch.cuda.Event()
+            slot[1].record()
+        else:
+            params = torch.from_numpy(host)
         if self._scratch is None or self._scratch.numel() < R * V:
             self._scratch = torch.empty(R * V, dtype=torch.float32, device=self.device)
         self.ops.sample(logits, params[0], params[3].view(torch.int32), params[1], params[2], out,
