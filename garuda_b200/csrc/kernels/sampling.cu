@@ -3,15 +3,33 @@
 
 namespace {
 
+// f(i, row[i]) for every i < V, each thread's indices in ascending order. Rows that start on a
+// 16-byte boundary are read four values at a time, several loads in flight: with one CTA per row
+// these passes are bound by load latency, not by bandwidth.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int V, F f) {
+  int tail = 0;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int n4 = V >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 8
+    for (int q = threadIdx.x; q < n4; q += blockDim.x) {
+      const float4 v = r4[q];
+      f(4 * q, v.x); f(4 * q + 1, v.y); f(4 * q + 2, v.z); f(4 * q + 3, v.w);
+    }
+    tail = 4 * n4;
+  }
+  for (int i = tail + threadIdx.x; i < V; i += blockDim.x) f(i, row[i]);
+}
+
 // Greedy: the first maximum wins (a strict `>` scan from index 0, :99-107), so
 // among equal values the lowest index is kept, and NaN never wins.
 __device__ int block_argmax(const float* __restrict__ row, int V) {
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
+  for_each_logit(row, V, [&](int i, float v) {
     if (v > best) { best = v; best_i = i; }  // ascending i within a thread: first maximum
-  }
+  });
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int result;
@@ -289,7 +307,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   // softmax(logits / temperature), with the reference's uniform fallbacks
   // (garuda/src/simd/mod.rs:132-158)
   float m = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, row[i] / temp);
+  for_each_logit(row, V, [&](int, float v) { m = fmaxf(m, v / temp); });
   m = gb::warp_max(m);
   if (lane == 0) sh_f[warp] = m;
   __syncthreads();
@@ -297,11 +315,11 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   for (int w = 0; w < nw; ++w) m = fmaxf(m, sh_f[w]);
   const bool finite_max = (m - m) == 0.f;  // neither infinite nor NaN
   double sum = 0.0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float e = finite_max ? expf(row[i] / temp - m) : 1.0f;
+  for_each_logit(row, V, [&](int i, float v) {
+    const float e = finite_max ? expf(v / temp - m) : 1.0f;
     p[i] = e;
     sum += (double)e;
-  }
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   if (lane == 0) sh_d[warp] = sum;
