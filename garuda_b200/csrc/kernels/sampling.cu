@@ -138,8 +138,10 @@ __device__ bool bisect(const float* p, int V, double* sh_d, int* sh_i, Pred pred
 constexpr int LIST_MAX = 1024;
 
 // p: the row's probabilities. Ends with the chosen token in *out. Every thread of the block calls it.
-__device__ void sample_from_top_k(const float* p, int V, int k, float tp, float uniform_draw, int32_t* out,
-                                  int* sh_cnt, int* sh_i) {
+// must_reach: top-p has to be reached within these k (the caller has no top-k of its own and tries the k
+// most likely tokens first); if it is not, nothing is written and false returned, to every thread.
+__device__ bool sample_from_top_k(const float* p, int V, int k, float tp, float uniform_draw, int32_t* out,
+                                  int* sh_cnt, int* sh_i, bool must_reach) {
   __shared__ unsigned long long keys[LIST_MAX];   // probability bits, then ~token id: descending = by probability, then by id
   __shared__ int hist[257];                       // bin 256 takes what a pass does not count
   const int kk = min(k, V);
@@ -191,6 +193,24 @@ __device__ void sample_from_top_k(const float* p, int V, int k, float tp, float 
   }
   const uint32_t tau_bits = prefix;   // the kk-th largest; `remaining` of those equal to it are wanted
   const int gt = kk - remaining;
+  if (must_reach && kk < V) {
+    // Before the list is gathered, sorted and walked: does its mass reach top-p at all? (With a slack
+    // for the order of the additions: a list that only just reaches it is walked and decides itself.)
+    __shared__ double part[32];
+    double above = 0.0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = p[i];
+      if (__float_as_uint(v) > tau_bits) above += (double)v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) above += __shfl_xor_sync(0xffffffffu, above, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = above;
+    __syncthreads();
+    double mass = (double)remaining * (double)__uint_as_float(tau_bits);
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mass += part[w];
+    __syncthreads();
+    if (mass < (double)tp * (1.0 - 1e-6)) return false;
+  }
   // gather: everything above tau in any order (the sort below orders it), and of those equal to tau
   // the `remaining` lowest token ids. For these every warp takes a run of the vocabulary and walks it
   // 32 tokens at a time, so that ranks among the ties follow the token ids.
@@ -259,18 +279,18 @@ __device__ void sample_from_top_k(const float* p, int V, int k, float tp, float 
     auto prob = [&](int i) { return (double)__uint_as_float((uint32_t)(keys[i] >> 32)); };
     // n: how many candidates survive top-p (:161-172) within the top k (:144-158)
     int n = kk;
-    if (tp < 1.0f) {
-      double cum = 0.0;
-      for (int i = 0; i < kk; ++i) {
-        cum += prob(i);
-        if (cum >= (double)tp) { n = i + 1; break; }
-      }
+    bool reached = tp >= 1.0f || kk == V;
+    double mass = 0.0;                         // of the first n
+    for (int i = 0; i < kk; ++i) {
+      mass += prob(i);
+      if (tp < 1.0f && mass >= (double)tp) { n = i + 1; reached = true; break; }
     }
-    double mass = 0.0;
-    for (int i = 0; i < n; ++i) mass += prob(i);
+    sh_i[3] = (must_reach && !reached) ? 0 : 1;
     const float total = (float)mass;
     int j = 1;    // zero mass: the most likely one (:111-115)
-    if (total > 0.f) {
+    if (sh_i[3] == 0) {
+      // top-p reaches beyond this list: the caller goes on without it
+    } else if (total > 0.f) {
       const double point = (double)(uniform_draw * total);
       double cum = 0.0;
       j = n;
@@ -279,8 +299,12 @@ __device__ void sample_from_top_k(const float* p, int V, int k, float tp, float 
         if (cum >= point) { j = i + 1; break; }
       }
     }
-    *out = (int32_t)(0xffffffffu - (uint32_t)(keys[j - 1] & 0xffffffffull));
+    if (sh_i[3] != 0) *out = (int32_t)(0xffffffffu - (uint32_t)(keys[j - 1] & 0xffffffffull));
   }
+  __syncthreads();
+  const bool done = sh_i[3] != 0;
+  __syncthreads();      // before sh_i is used again
+  return done;
 }
 
 __global__ void __launch_bounds__(1024)
@@ -334,9 +358,12 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   __syncthreads();
 
   if (top_k[r] > 0 && top_k[r] <= LIST_MAX) {
-    sample_from_top_k(p, V, top_k[r], top_p[r], u[r], out + r, sh_cnt, sh_i);
+    sample_from_top_k(p, V, top_k[r], top_p[r], u[r], out + r, sh_cnt, sh_i, false);
     return;
   }
+  // top-p alone (or with a top-k beyond the list): nearly always it is reached within the LIST_MAX most
+  // likely tokens, and then those are all that matter
+  if (top_p[r] < 1.0f && sample_from_top_k(p, V, LIST_MAX, top_p[r], u[r], out + r, sh_cnt, sh_i, true)) return;
 
   // n: how many candidates survive top-k (:144-158) and top-p (:161-172)
   int n = V;

@@ -456,7 +456,8 @@ def test_sampling_among_equal_probabilities_goes_by_token_id(ops):
         def next_f32(self): return np.float32(self.u)
 
     V = 5000
-    rows = [(1.0, k, p, u) for k, p in ((40, 1.0), (7, 0.5), (1024, 1.0), (300, 0.02))
+    # top-p alone: reached within the short list (0.1 of 5,000 equal tokens are 500) or far beyond it (2,500)
+    rows = [(1.0, k, p, u) for k, p in ((40, 1.0), (7, 0.5), (1024, 1.0), (300, 0.02), (0, 0.1), (0, 0.5), (2000, 0.3))
             for u in (0.0, 0.26, 0.5, 0.99)]
     R = len(rows)
     logits = torch.full((R, V), 0.25)
@@ -468,7 +469,7 @@ def test_sampling_among_equal_probabilities_goes_by_token_id(ops):
     got = out.tolist()
     for i, (temp, k, p, u) in enumerate(rows):
         want = plain_sample(logits[i].numpy(), temp, k, p, FixedU(u))
-        assert abs(got[i] - want) <= 1 and got[i] < k, (rows[i], got[i], want)    # a draw on a boundary may round either way
+        assert abs(got[i] - want) <= 1 and (k == 0 or got[i] < k), (rows[i], got[i], want)    # a draw on a boundary may round either way
 
 
 @pytest.mark.parametrize("V", [50, 331, 32000])
