@@ -69,11 +69,19 @@ class PagedCache:
 
     # ---- request lifecycle -------------------------------------------------
     def acquire(self, request: int) -> int:
-        """A slot for a new request; its fixed-size state starts at zero."""
-        slot = self.manager.acquire(request)
+        """A slot for a new request. Its fixed-size state is zeroed by the step that runs the
+        request's first token (``reset_states``), so that it makes no difference who took the
+        slot: this call, or a scheduler working on the bookkeeping directly."""
+        return self.manager.acquire(request)
+
+    def reset_states(self, slots: Sequence[int]) -> None:
+        """Fixed-size state of these slots back to zero, in every layer call that keeps some
+        (garuda/src/cache/mod.rs:719-743: a sequence's state starts as zeros)."""
+        if not self.states or not slots:
+            return
         for s in self.states.values():
-            s[slot].zero_()
-        return slot
+            for slot in slots:
+                s[slot].zero_()
 
     def release(self, request: int) -> None:
         self.manager.release(request)

@@ -56,6 +56,8 @@ class ModelSection:
     sliding_window: int = 0       # attention window; 0 attends to the whole context
     seed: int = 0                 # random-weights mode: seed of `garuda init`
     gpu: bool = True              # there is no CPU path: false is refused, not ignored
+    # modules to import before the model is built: they register architectures or parts of their own
+    plugins: list = field(default_factory=list)
 
 
 @dataclass
@@ -113,7 +115,10 @@ class EngineConfig:
                 if key not in names:
                     raise ConfigError(f"unknown key '{key}' in [{section}] (keys: {', '.join(sorted(names))})")
                 default = getattr(target, key)
-                if isinstance(default, bool):
+                if isinstance(default, list):
+                    ok = isinstance(value, list) and all(isinstance(v, str) for v in value)
+                    value = list(value) if ok else value
+                elif isinstance(default, bool):
                     ok = isinstance(value, bool)
                 elif isinstance(default, int):
                     ok = isinstance(value, int) and not isinstance(value, bool)

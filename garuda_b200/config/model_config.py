@@ -53,12 +53,17 @@ class LlamaConfig:
     hidden_act: str = "silu"
     sliding_window: Optional[int] = None
     layer_types: Optional[tuple] = None
-    eos_token_id: Optional[int] = None
+    eos_token_ids: tuple = ()        # config.json gives one id or a list; generation ends on any
     bos_token_id: Optional[int] = None
     torch_dtype: Optional[str] = None
     extra: dict = field(default_factory=dict, compare=False)
 
     # ---- derived ---------------------------------------------------------
+    @property
+    def eos_token_id(self) -> Optional[int]:
+        """The first end-of-sequence id, for callers that want one."""
+        return self.eos_token_ids[0] if self.eos_token_ids else None
+
     @property
     def kv_dim(self) -> int:
         """Width of one stored key or value (garuda/src/llama/mod.rs:468-470)."""
@@ -154,7 +159,7 @@ class LlamaConfig:
             rms_norm_eps=float(eps), rope_theta=float(theta), rope_layout=layout,
             tie_word_embeddings=bool(d.pop("tie_word_embeddings", False)),
             hidden_act=act, sliding_window=window, layer_types=types,
-            eos_token_id=_first_int(d.pop("eos_token_id", None)),
+            eos_token_ids=_int_tuple("eos_token_id", d.pop("eos_token_id", None)),
             bos_token_id=_first_int(d.pop("bos_token_id", None)),
             torch_dtype=d.pop("torch_dtype", d.pop("dtype", None)),
             extra=d,
@@ -164,12 +169,29 @@ class LlamaConfig:
         """The config.json this configuration is read back from."""
         d = asdict(self)
         extra = d.pop("extra")
+        eos = d.pop("eos_token_ids")
+        if eos:
+            d["eos_token_id"] = eos[0] if len(eos) == 1 else list(eos)
         d["architectures"] = [d.pop("architecture")]
         if d["layer_types"] is not None:
             d["layer_types"] = list(d["layer_types"])
         d = {k: v for k, v in d.items() if v is not None}
         d["model_type"] = extra.get("model_type", "llama")
         return d
+
+
+def _int_tuple(key: str, v: Any) -> tuple:
+    """A single id or a list of ids, as a tuple without repeats (order kept)."""
+    if v is None:
+        return ()
+    items = list(v) if isinstance(v, (list, tuple)) else [v]
+    out = []
+    for x in items:
+        if isinstance(x, bool) or not isinstance(x, int) or x < 0:
+            raise ConfigError(f"config.json: '{key}' must be a token id or a list of them, got {v!r}")
+        if x not in out:
+            out.append(x)
+    return tuple(out)
 
 
 def _first_int(v: Any) -> Optional[int]:

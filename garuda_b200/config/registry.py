@@ -20,6 +20,22 @@ def register_architecture(name: str, read_config: Callable, make_spec: Callable)
     _ARCHITECTURES[name] = (read_config, make_spec)
 
 
+def load_plugins(names=None) -> None:
+    """Imports modules that register architectures or parts of their own (each calls
+    ``register_architecture`` / ``register_mixer`` / ... when imported). ``names``: module names;
+    those of the environment variable ``GARUDA_B200_PLUGINS`` (comma separated) are imported as
+    well. The command line's ``--plugin`` and a config.toml's ``[model] plugins`` end up here."""
+    import importlib
+    import os
+    wanted = list(names or [])
+    wanted += [n for n in os.environ.get("GARUDA_B200_PLUGINS", "").split(",") if n.strip()]
+    for name in wanted:
+        try:
+            importlib.import_module(name.strip())
+        except ImportError as e:
+            raise ConfigError(f"plugin module '{name}' cannot be imported: {e}") from None
+
+
 def registered_architectures():
     return sorted(_ARCHITECTURES)
 

@@ -112,6 +112,18 @@ class _Lock:
         self.fh.close()
 
 
+def _drop_older(out_dir: str, prefix: str, keep: str) -> None:
+    """Builds of other versions of the same library (same name, another hash) are deleted, so that
+    the folder does not grow with every change of a source. A process that still has one mapped
+    keeps it until it exits."""
+    for f in os.listdir(out_dir):
+        if f.startswith(prefix) and f.endswith(".so") and os.path.join(out_dir, f) != keep:
+            try:
+                os.remove(os.path.join(out_dir, f))
+            except OSError:
+                pass
+
+
 def nvcc_path() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):
@@ -165,6 +177,7 @@ def kernel_lib_path(name: str) -> str:
                 os.remove(o)
             except OSError:
                 pass
+        _drop_older(out_dir, f"lib{name}.", target)
         _log(f"{name} ready in {time.time() - t0:.0f} s")
     return target
 
@@ -212,6 +225,7 @@ def host_module_path() -> str:
                 os.remove(o)
             except OSError:
                 pass
+        _drop_older(out_dir, "_garuda_host.", target)
         _log(f"host runtime ready in {time.time() - t0:.0f} s")
     return target
 

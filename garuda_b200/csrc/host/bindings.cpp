@@ -108,7 +108,14 @@ PYBIND11_MODULE(_garuda_host, m) {
       .def_readwrite("max_batch_tokens", &SchedulerConfig::max_batch_tokens)
       .def_readwrite("prefill_chunk", &SchedulerConfig::prefill_chunk)
       .def_readwrite("max_context", &SchedulerConfig::max_context)
-      .def_readwrite("eos_token_id", &SchedulerConfig::eos_token_id)
+      .def_readwrite("eos_token_ids", &SchedulerConfig::eos_token_ids)
+      // one id, or -1 for none: the list with that one entry
+      .def_property("eos_token_id",
+                    [](const SchedulerConfig& c) { return c.eos_token_ids.empty() ? -1 : c.eos_token_ids[0]; },
+                    [](SchedulerConfig& c, int32_t id) {
+                      c.eos_token_ids.clear();
+                      if (id >= 0) c.eos_token_ids.push_back(id);
+                    })
       .def_readwrite("vocab_size", &SchedulerConfig::vocab_size)
       .def_readwrite("ignore_eos", &SchedulerConfig::ignore_eos);
 

@@ -279,7 +279,8 @@ std::vector<Event> Scheduler::complete(const StepPlan& plan, const std::vector<i
     ++stats_.tokens_generated;
     // The end-of-sequence token joins the context but is not emitted
     // (garuda/src/runtime/mod.rs:733-738).
-    if (!config_.ignore_eos && config_.eos_token_id >= 0 && tok == config_.eos_token_id) {
+    if (!config_.ignore_eos && std::find(config_.eos_token_ids.begin(), config_.eos_token_ids.end(), tok) !=
+                                   config_.eos_token_ids.end()) {
       finish(r, &events, EventKind::Done, "eos");
       continue;
     }

@@ -61,7 +61,7 @@ struct SchedulerConfig {
   int max_batch_tokens = 2048;  // tokens of one step, decode tokens and prompt portions together
   int prefill_chunk = 512;      // most tokens of one prompt in one step (scheduler/mod.rs:321)
   int max_context = 2048;       // min(configured context, the model's own)
-  int eos_token_id = -1;        // -1: none
+  std::vector<int32_t> eos_token_ids;  // generation ends on any of them; empty: none
   int vocab_size = 0;           // prompts are checked against it at submit; 0: unchecked
   bool ignore_eos = false;
 };

@@ -27,5 +27,7 @@ bool tile_tc_takes(const Params& p, int T, long long pages);
 int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len, cudaStream_t stream);
 // Non-zero if one of its CTAs gave up on a wait since the last call; clears it.
 int tile_tc_error_check();
+// Its kernels' failed waits also write their code to this word of pinned host memory (null: none).
+int tile_tc_set_error_sink(int* host_word);
 
 }  // namespace attn

@@ -26,6 +26,7 @@
 //
 // Compiled per head size: GB_HEAD_DIM (a multiple of 16, at most 128).
 #include "attention_common.cuh"
+#include "error_word.cuh"
 #include "tc_common.cuh"
 
 #ifndef GB_HEAD_DIM
@@ -48,22 +49,6 @@ constexpr int SLOTS = 4;            // key tiles in flight per DECODE CTA: one p
 constexpr int MAX_CLUSTER = 8;      // CTAs that may share one request's keys
 constexpr int RS = HD + 2;          // floats of one row's partial result: sum, then maximum, denominator
 constexpr float LOG2E = 1.4426950408889634f;
-
-__device__ int g_error_word;
-
-// Compiled in with -DGB_TIMELINE only: time stamps per CTA of the decode kernel.
-#ifdef GB_TIMELINE
-__device__ unsigned long long g_timeline[8 * 4096];
-#define GB_STAMP(i)                                                                                   \
-  do {                                                                                                \
-    if (threadIdx.x == 0) {                                                                           \
-      const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
-      if (cta < 4096) g_timeline[8 * cta + (i)] = globaltimer_ns();                                   \
-    }                                                                                                 \
-  } while (0)
-#else
-#define GB_STAMP(i) do {} while (0)
-#endif
 
 using attn::Params;
 
@@ -358,7 +343,6 @@ attention_decode_kernel(const Params p, const int stages) {
   float* parts = reinterpret_cast<float*>(kv + (size_t)stages * 4 * 2 * KT * LD);  // rank 0: [ranks - 1][16][RS]
   __shared__ __align__(8) uint64_t part_bar;
 
-  GB_STAMP(0);
   const int r = blockIdx.z, kvh = blockIdx.y;
   const int rank = blockIdx.x, ranks = gridDim.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -378,7 +362,6 @@ attention_decode_kernel(const Params p, const int stages) {
   }
   __syncthreads();
   if (ranks > 1) cluster_arrive_wait();      // rank 0's barrier is armed before anyone sends to it
-  GB_STAMP(1);
   gb::pdl_launch_dependents();
 
   const int pos0 = kv_len - q_len;                                  // position of the first token
@@ -411,7 +394,6 @@ attention_decode_kernel(const Params p, const int stages) {
   int issued = 0;
   while (issued < stages && issued < mine_n && (tile_begin + warp + 4 * issued + 1) * KT <= pos0) issue(issued++);
   gb::pdl_wait();
-  GB_STAMP(2);
   while (issued < stages) issue(issued++);
 
   // the query fragments of the m16n8k16 A operand, straight from global memory
@@ -438,7 +420,6 @@ attention_decode_kernel(const Params p, const int stages) {
     issue(i + stages);
   }
   cp_async_wait<0>();
-  GB_STAMP(4);
   __syncthreads();            // the slots become the merge buffers
   // ---- the four warps' results into shared memory: [warp][row][RS]
 #pragma unroll
@@ -484,14 +465,12 @@ attention_decode_kernel(const Params p, const int stages) {
       else mine[row * RS + c] = v;
     }
   }
-  GB_STAMP(5);
   if (rank != 0) return;
   if (ranks > 1 && !mbar_wait(smem_u32(&part_bar), 0)) {
-    if (threadIdx.x == 0) atomicCAS(&g_error_word, 0, 1);
+    if (threadIdx.x == 0) gb_err::report(5);
     return;
   }
   __syncthreads();
-  GB_STAMP(6);
   // ---- rank 0: its own rows and the others' [rank - 1][nrows][RS], in rank order
   for (int row = threadIdx.x >> 4; row < nrows; row += THREADS / 16) {
     float f[MAX_CLUSTER], m = mine[row * RS + HD];
@@ -516,7 +495,6 @@ attention_decode_kernel(const Params p, const int stages) {
       dst[c] = __float2bfloat16_rn(acc * inv);
     }
   }
-  GB_STAMP(7);
 }
 
 constexpr int SMEM_TILE = (ROWS_TILE * LD + 2 * 2 * KT * LD) * 2;
@@ -536,23 +514,17 @@ GB_EXPORT int gb_attention_mma_head_dim() { return HD; }
 static long long g_tc_tile_launches = 0;
 GB_EXPORT long long gb_attention_tc_tile_launches() { return g_tc_tile_launches; }
 
-#ifdef GB_TIMELINE
-GB_EXPORT int gb_attention_timeline(unsigned long long* host_out, int ctas) {
-  return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(unsigned long long) * 8 * ctas) == cudaSuccess ? 0 : 1;
-}
-#endif
-
 // Non-zero if a decode CTA gave up waiting for its cluster since the last call; clears it.
 GB_EXPORT int gb_attention_error_check() {
-  int v = 0;
   const int tc = attn::tile_tc_error_check();
-  if (tc != 0) return tc;
-  if (cudaMemcpyFromSymbol(&v, g_error_word, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) {
-    int zero = 0;
-    cudaMemcpyToSymbol(g_error_word, &zero, sizeof(int));
-  }
-  return v;
+  const int own = gb_err::fetch_and_clear();
+  return tc != 0 ? tc : own;
+}
+
+// A word of pinned host memory that a kernel's failed wait also writes its code to (null: none).
+GB_EXPORT int gb_attention_set_error_sink(int* host_word) {
+  const int a = gb_err::set_sink(host_word), b = attn::tile_tc_set_error_sink(host_word);
+  return a != 0 ? a : b;
 }
 
 // q [T, Hq, HD], pools [pages, Hkv, page_size, HD], out [T, Hq*HD], all bfloat16.
@@ -579,14 +551,14 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
   p.table_width = table_width; p.Hq = Hq; p.Hkv = Hkv; p.g = g; p.window = window; p.page_size = page_size;
   p.scale_log2 = scale * LOG2E;
 
-  static bool configured = false;
-  if (!configured) {
+  static gb::OncePerDevice configured;
+  if (configured.needed()) {
     cudaError_t e1 = cudaFuncSetAttribute(attention_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TILE);
     cudaError_t e2 = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           smem_decode(MAX_CLUSTER, MAX_STAGES));
     if (e1 != cudaSuccess || e2 != cudaSuccess)
       return gb::fail(GB_CUDA_ERROR, "attention_mma: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
-    configured = true;
+    configured.done();
   }
   // DECODE requests (a decode token's group, or a very short portion), if the batch can hold any
   if (min_q_len * g <= ROWS_DECODE) {
@@ -599,11 +571,7 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
   }
   // TILE requests: on the tcgen05 kernel where it takes the shape
   if (max_q_len * g > ROWS_DECODE) {
-    static const bool tc_on = [] {
-      const char* v = getenv("GARUDA_B200_ATTN_TC");
-      return !(v && v[0] == '0');
-    }();
-    if (tc_on && attn::tile_tc_takes(p, T, num_pages)) {
+    if (attn::tile_tc_takes(p, T, num_pages)) {
       ++g_tc_tile_launches;
       return attn::launch_tile_tc(p, T, num_pages, R, max_q_len, stream);
     }

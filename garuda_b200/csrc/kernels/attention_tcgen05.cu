@@ -36,6 +36,7 @@
 // Built for head size 64 only (one 128-byte swizzled row per key); other head sizes use the
 // mma.sync kernels.
 #include "attention_common.cuh"
+#include "error_word.cuh"
 #include "tc_common.cuh"
 
 #include <mutex>
@@ -69,27 +70,6 @@ constexpr int O_COL0 = GROUPS * 2 * GK;
 constexpr int THREADS = 64 + GROUPS * 128;
 static_assert(GK == 64 && O_COL0 + GROUPS * 2 * HD <= TMEM_COLS, "tensor memory layout");
 
-__device__ int g_tc_error_word;
-
-// Compiled in with -DGB_ATTN_PROFILE only: where a softmax thread and the MMA issuer spend their
-// cycles, summed over the CTAs (eight counters, then the number of tiles).
-#ifdef GB_ATTN_PROFILE
-__device__ unsigned long long g_prof[24];
-#define GB_PROF_DECL long long pt0 = clock64(), pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define GB_PROF(i) do { const long long t = clock64(); pacc[i] += t - pt0; pt0 = t; } while (0)
-#define GB_PROF_FLUSH(base, tiles_done) do { for (int i = 0; i < 8; ++i) if (pacc[i]) atomicAdd(&g_prof[(base) + i], (unsigned long long)pacc[i]); \
-    atomicAdd(&g_prof[23], (unsigned long long)(tiles_done)); } while (0)
-// and a trace of CTA 0's events: (time in ns, event number, tile count)
-__device__ unsigned long long g_trace[3 * 8192];
-__device__ unsigned int g_trace_n;
-#define GB_TRACE(ev, tile) do { if (blockIdx.x == 0) { const unsigned int i_ = atomicAdd(&g_trace_n, 1u); if (i_ < 8192) { \
-    g_trace[3 * i_] = globaltimer_ns(); g_trace[3 * i_ + 1] = (ev); g_trace[3 * i_ + 2] = (unsigned long long)(tile); } } } while (0)
-#else
-#define GB_TRACE(ev, tile) do {} while (0)
-#define GB_PROF_DECL do {} while (0)
-#define GB_PROF(i) do {} while (0)
-#define GB_PROF_FLUSH(base, tiles_done) do {} while (0)
-#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -293,7 +273,7 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
         const Item& w = c.w;
         const int qb = c.it & 1;
         if (c.it >= 2 && !mbar_wait(smem_u32(&q_empty[qb]), ((c.it >> 1) & 1) ^ 1)) {
-          atomicCAS(&g_tc_error_word, 0, ERR_WAIT_EMPTY);
+          gb_err::report(ERR_WAIT_EMPTY);
           abort_s = 1;
         }
         if (*(volatile int*)&abort_s) break;
@@ -310,9 +290,8 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
             pages[g] = (first <= w.hi && first + p.page_size > w.lo) ? w.table[first >> page_shift] : -1;
             count += pages[g] >= 0;
           }
-          GB_TRACE(30, gt);
           if (gt >= STAGES && !mbar_wait(smem_u32(&kv_empty[s]), par)) {
-            atomicCAS(&g_tc_error_word, 0, ERR_WAIT_EMPTY);
+            gb_err::report(ERR_WAIT_EMPTY);
             abort_s = 1;
           }
           if (*(volatile int*)&abort_s) break;
@@ -328,7 +307,6 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
               tma_load_4d(vdst + g * page_bytes, &v_map, bar, 0, 0, w.kvh, pages[g]);
             }
           }
-          GB_TRACE(31, gt);
           if (++stage == STAGES) stage = 0, par ^= 1;
         }
         if (*(volatile int*)&abort_s) break;
@@ -339,7 +317,7 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           const unsigned long long t0 = globaltimer_ns();
           while (!mbar_try_wait(smem_u32(&kv_full[t % STAGES]), (t / STAGES) & 1)) {
             if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
-              atomicCAS(&g_tc_error_word, 0, ERR_WAIT_DRAIN);
+              gb_err::report(ERR_WAIT_DRAIN);
               break;
             }
           }
@@ -366,18 +344,12 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     int s_stage = 0, s_par = 0, p_stage = 0;       // stage (and its phase) of the S tile, stage of the P V tile
     int s_buf = 0;                                 // S buffer of the S tile
     int p_buf = 0, p_par = 0;                      // buffers of the P V tile and their phase
-    GB_PROF_DECL;
     auto issue_s = [&]() {      // S = Q K^T of the S tile into S buffer s_buf (both groups' columns)
       const int qb = ws.it & 1;
-      GB_PROF(0);
       if (ws.j == 0 && !mbar_wait(smem_u32(&q_full[qb]), (ws.it >> 1) & 1)) ok = false;
-      GB_PROF(1);
-      if (lane == 0) GB_TRACE(10, s_buf);
       if (ok && !mbar_wait(smem_u32(&kv_full[s_stage]), s_par)) ok = false;
-      if (lane == 0) GB_TRACE(11, s_buf);
-      GB_PROF(2);
       if (!ok) {
-        if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_FULL);
+        if (lane == 0) gb_err::report(ERR_WAIT_FULL);
         return;
       }
       tc_fence_after_sync();
@@ -389,28 +361,22 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
         if (ws.j == ws.n - 1) mma_commit(smem_u32(&q_empty[qb]));   // the item's queries have been read
       }
       __syncwarp();
-      if (lane == 0) GB_TRACE(12, s_buf);
-      GB_PROF(3);
       if (++s_stage == STAGES) s_stage = 0, s_par ^= 1;
       s_buf ^= 1;
       ws.next_tile(p, q_tiles, total_items);
-      GB_PROF(4);
     };
     if (!ws.done) issue_s();
     if (ok && !ws.done) issue_s();
     while (ok && !wp.done) {
       if (*(volatile int*)&abort_s) break;
-      GB_PROF(0);
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g) {
         if (ok && !mbar_wait(smem_u32(&p_ready[g][p_buf]), p_par)) {
-          if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
+          if (lane == 0) gb_err::report(ERR_WAIT_ACCUM);
           ok = false;
         }
       }
       if (!ok) break;
-      if (lane == 0) GB_TRACE(13, p_buf);
-      GB_PROF(5);
       // both groups have read this S buffer in full and written their P: first the S product that
       // takes the buffer over, then this tile's P V
       if (!ws.done) issue_s();
@@ -427,16 +393,12 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
         mma_commit(smem_u32(&kv_empty[p_stage]));     // keys and values of the stage have been read
       }
       __syncwarp();
-      if (lane == 0) GB_TRACE(14, p_buf);
-      GB_PROF(6);
       if (++p_stage == STAGES) p_stage = 0;
       p_par ^= p_buf;         // the phase flips after buffer 1
       p_buf ^= 1;
       wp.next_tile(p, q_tiles, total_items);
-      GB_PROF(7);
     }
     if (!ok) abort_s = 1;
-    if (lane == 0) GB_PROF_FLUSH(8, 0);
   } else {
     // -------------------------------------------------------------------- softmax warps
     // Group g takes keys [g * 64, g * 64 + 64) of every tile: an attention stream of its own
@@ -451,7 +413,6 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     bool ok = true;       // false: this thread only keeps the others company at the barriers
     int gt = 0;           // tiles so far, over all items
     int stage = 0;        // the current tile's stage of keys and values
-    GB_PROF_DECL;
     Cursor c;
     for (c.start(p, q_tiles, total_items); !c.done; c.next_item(p)) {
       const Item& w = c.w;
@@ -464,7 +425,7 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
 
       auto fold = [&](int t) {        // o_acc = o_acc * corr_saved + O_tile of the tile counted t
         if (!mbar_wait(smem_u32(&o_ready[t & 1]), (t >> 1) & 1)) {
-          if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
+          if (lane == 0) gb_err::report(ERR_WAIT_ACCUM);
           ok = false;
           abort_s = 1;
           return;
@@ -481,14 +442,12 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       for (int j = 0; j < w.n_tiles && ok; ++j, ++gt) {
         if (*(volatile int*)&abort_s) { ok = false; break; }
         if (!mbar_wait(smem_u32(&s_ready[gt & 1]), (gt >> 1) & 1)) {
-          if (lane == 0) atomicCAS(&g_tc_error_word, 0, ERR_WAIT_ACCUM);
+          if (lane == 0) gb_err::report(ERR_WAIT_ACCUM);
           ok = false;
           abort_s = 1;
           break;
         }
         tc_fence_after_sync();
-        if ((threadIdx.x & 127) == 64) GB_TRACE(grp * 20 + 0, gt);
-        GB_PROF(0);
         {
           // Value rows that no row may read hold whatever was there (a page that was not fetched,
           // the unwritten end of the last page): their probabilities are zero, but zero times a
@@ -511,7 +470,6 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
 #pragma unroll
         for (int h = 0; h < GK / 32; ++h) tmem_ld_32(lane_addr + (2 * (gt & 1) + grp) * GK + h * 32, sv[h]);
         tmem_ld_wait();
-        GB_PROF(1);
         auto sc = [&](int ch) -> float& { return reinterpret_cast<float&>(sv[ch >> 5][ch & 31]); };
         const int key0 = (w.tile_begin + j) * KT + grp * GK;
         // the keys need no mask if they lie wholly before the first row's position and inside the
@@ -549,19 +507,13 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
                        pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
         }
         l = l * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
-        GB_PROF(2);
         fence_proxy_async();            // the tensor core reads P through the async proxy
         tc_fence_before_sync();         // this thread's reads of S are over
         mbar_arrive(smem_u32(&p_ready[grp][gt & 1]));
-        if ((threadIdx.x & 127) == 64) GB_TRACE(grp * 20 + 1, gt);
-        GB_PROF(3);
         if (j > 0) fold(gt - 1);
-        if ((threadIdx.x & 127) == 64) GB_TRACE(grp * 20 + 2, gt);
-        GB_PROF(4);
         corr_saved = corr;
       }
       if (ok) fold(gt - 1);
-      GB_PROF(5);
       // ---- merge the two groups: the second hands its sums over through its own P buffers
       // (its last product has been read from them: fold waited for it), [channel][row] floats
       if (grp == 1 && ok) {
@@ -595,9 +547,7 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       }
       // the second group's next probabilities go where its sums were just read
       asm volatile("bar.sync 1, %0;" ::"n"(GROUPS * 128) : "memory");
-      GB_PROF(6);
     }
-    if (threadIdx.x == 64) GB_PROF_FLUSH(0, gt);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -689,11 +639,11 @@ int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len
   if (rc) return rc;
   rc = tensor_map(p.v_pool, p.page_size, p.Hkv, pages, p.page_size, 1, &vm);
   if (rc) return rc;
-  static bool configured = false;
-  if (!configured) {
+  static gb::OncePerDevice configured;
+  if (configured.needed()) {
     cudaError_t e = cudaFuncSetAttribute(attention_tile_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "attention_tc: %s", cudaGetErrorString(e));
-    configured = true;
+    configured.done();
   }
   const int q_tiles = (max_q_len + tokens_per_tile - 1) / tokens_per_tile;
   const long long total = (long long)q_tiles * p.Hkv * R;
@@ -710,29 +660,8 @@ int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len
                               "attention_tc (tile)");
 }
 
-#ifdef GB_ATTN_PROFILE
-extern "C" __attribute__((visibility("default"))) int gb_attention_trace(unsigned long long* host_out, unsigned int* n) {
-  if (cudaMemcpyFromSymbol(n, g_trace_n, 4) != cudaSuccess) return 1;
-  if (cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 3 * 8192) != cudaSuccess) return 1;
-  unsigned int zero = 0;
-  return cudaMemcpyToSymbol(g_trace_n, &zero, 4) == cudaSuccess ? 0 : 1;
-}
-extern "C" __attribute__((visibility("default"))) int gb_attention_prof(unsigned long long* host_out) {
-  if (cudaMemcpyFromSymbol(host_out, g_prof, sizeof(unsigned long long) * 24) != cudaSuccess) return 1;
-  unsigned long long zero[24] = {0};
-  return cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
-}
-#endif
-
-int tile_tc_error_check() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_tc_error_word, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) {
-    int zero = 0;
-    cudaMemcpyToSymbol(g_tc_error_word, &zero, sizeof(int));
-  }
-  return v;
-}
+int tile_tc_error_check() { return gb_err::fetch_and_clear(); }
+int tile_tc_set_error_sink(int* host_word) { return gb_err::set_sink(host_word); }
 
 }  // namespace attn
 
@@ -744,6 +673,7 @@ int launch_tile_tc(const Params&, int, long long, int, int, cudaStream_t) {
   return gb::fail(GB_UNSUPPORTED, "attention_tc: head size %d", GB_HEAD_DIM);
 }
 int tile_tc_error_check() { return 0; }
+int tile_tc_set_error_sink(int*) { return 0; }
 }  // namespace attn
 
 #endif

@@ -65,6 +65,28 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// A kernel attribute (the dynamic shared memory a kernel may use) belongs to a device: a flag that
+// remembers "set" must be kept per device. `needed()` is true until `done()` has been called with
+// the same device current. Not synchronised: two threads that make a kernel's first call on a
+// device at the same moment both set the attribute, to the same value.
+struct OncePerDevice {
+  static constexpr int MAX_DEVICES = 64;
+  bool set_[MAX_DEVICES] = {};
+  static int device() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MAX_DEVICES) return -1;
+    return d;
+  }
+  bool needed() const {
+    const int d = device();
+    return d < 0 || !set_[d];
+  }
+  void done() {
+    const int d = device();
+    if (d >= 0) set_[d] = true;
+  }
+};
+
 // ---- programmatic dependent launch ----------------------------------------
 // A kernel launched with launch_pdl may start while the kernel before it in the
 // stream is still running. It must call pdl_wait() before it reads anything that

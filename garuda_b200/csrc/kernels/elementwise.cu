@@ -185,11 +185,13 @@ rope_kv_append_kernel(const IT* __restrict__ qkv, int row_stride, OT* __restrict
   }
 }
 
-__global__ void rope_inplace_kernel(float* __restrict__ x, int row_stride, int H, int hd,
+// hd: the rotated width (pairs lie within it); head_stride: the distance between heads, which is
+// larger than hd when only the first channels of every head are rotated.
+__global__ void rope_inplace_kernel(float* __restrict__ x, int row_stride, int head_stride, int H, int hd,
                                     const int32_t* __restrict__ positions,
                                     const float* __restrict__ inv_freq, int interleaved) {
   const int t = blockIdx.x, head = blockIdx.y;
-  float* v = x + (size_t)t * row_stride + (size_t)head * hd;
+  float* v = x + (size_t)t * row_stride + (size_t)head * head_stride;
   const int pos = positions[t];
   const int half = hd >> 1;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -304,12 +306,14 @@ GB_EXPORT int gb_rope_table(const int32_t* positions, const float* inv_freq, flo
   return gb::check_launch("rope_table");
 }
 
-GB_EXPORT int gb_rope_inplace(float* x, int row_stride, int T, int H, int hd, const int32_t* positions,
-                              const float* inv_freq, int interleaved, cudaStream_t stream) {
+GB_EXPORT int gb_rope_inplace(float* x, int row_stride, int head_stride, int T, int H, int hd,
+                              const int32_t* positions, const float* inv_freq, int interleaved,
+                              cudaStream_t stream) {
   if (T <= 0 || H <= 0) return GB_OK;
-  if (hd % 2) return gb::fail(GB_UNSUPPORTED, "rope_inplace: head_dim %d is odd", hd);
+  if (hd % 2) return gb::fail(GB_UNSUPPORTED, "rope_inplace: the rotated width %d is odd", hd);
+  if (head_stride < hd) return gb::fail(GB_BAD_ARGUMENT, "rope_inplace: heads %d apart are narrower than %d", head_stride, hd);
   dim3 grid(T, H);
-  rope_inplace_kernel<<<grid, 32, 0, stream>>>(x, row_stride, H, hd, positions, inv_freq, interleaved);
+  rope_inplace_kernel<<<grid, 32, 0, stream>>>(x, row_stride, head_stride, H, hd, positions, inv_freq, interleaved);
   return gb::check_launch("rope_inplace");
 }
 

@@ -39,6 +39,7 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "error_word.cuh"
 #include "tc_common.cuh"
 
 namespace {
@@ -50,10 +51,7 @@ constexpr int BK = 64;    // bf16 per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int SMEM_LIMIT = 227 * 1024;          // most dynamic shared memory a CTA can have
 constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // many tokens: one CTA per SM, all of it pipeline
-#ifndef GB_SMEM_BUDGET_SMALL_KB
-#define GB_SMEM_BUDGET_SMALL_KB 110
-#endif
-constexpr int SMEM_BUDGET_SMALL = GB_SMEM_BUDGET_SMALL_KB * 1024;   // few tokens: pipeline depth that the stream of weights needs
+constexpr int SMEM_BUDGET_SMALL = 110 * 1024;   // few tokens: pipeline depth that the stream of weights needs
 constexpr int SMEM_BUDGET_DUAL = 140 * 1024;    // few tokens, gate and up together
 
 // EPI_ACCUMULATE_NORM: accumulate, and fold in the first half of the norm that follows (EpilogueArgs::h_out);
@@ -102,30 +100,6 @@ __device__ __forceinline__ __nv_bfloat16* rope_destination(const EpilogueArgs& r
          (((size_t)page * ra.kv_heads + kvh) * ra.page_size + pos % ra.page_size) * ra.head_dim + d;
 }
 
-__device__ int g_error_word;
-
-// Compiled in with -DGB_TIMELINE only: eight time stamps per CTA of the cluster kernel, for finding
-// out where a short kernel spends its time. Slot = linear CTA index.
-#ifdef GB_TIMELINE
-__device__ unsigned long long g_timeline[8 * 4096];
-#define GB_STAMP(i)                                                                                   \
-  do {                                                                                                \
-    if (threadIdx.x == 0) {                                                                           \
-      const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
-      if (cta < 4096) g_timeline[8 * cta + (i)] = globaltimer_ns();                                   \
-    }                                                                                                 \
-  } while (0)
-#define GB_STAMP_E(i)                                                                                 \
-  do {                                                                                                \
-    if (threadIdx.x == 64) {                                                                          \
-      const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                 \
-      if (cta < 4096) g_timeline[8 * cta + (i)] = globaltimer_ns();                                   \
-    }                                                                                                 \
-  } while (0)
-#else
-#define GB_STAMP(i) do {} while (0)
-#define GB_STAMP_E(i) do {} while (0)
-#endif
 
 // Bytes of the rotation's tables in the few-token kernel: cosines and sines [BN tokens][64
 // frequencies] and each token's row in the pools.
@@ -231,7 +205,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
   __shared__ int abort_s;
   __shared__ float inv_s[BN];       // folded norm: 1/rms of this tile's tokens
 
-  GB_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int total_kb = (K + BK - 1) / BK;
@@ -269,7 +242,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
   // Rank 0's barrier is armed before anyone may send to it. This is the only cluster-wide
   // barrier, and it is passed while the kernel in front is still running.
   if (ranks > 1) cluster_arrive_wait();
-  GB_STAMP(1);
   gb::pdl_launch_dependents();
 
   if (warp == 0) {
@@ -287,7 +259,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         tma_load_2d(base, &map_m, bar, k0, m0);
       }
       gb::pdl_wait();
-      GB_STAMP(2);
       for (int it = 0; it < early; ++it) {
         tma_load_2d(tiles + it * G::STAGE_BYTES + G::NUM_M * G::A_BYTES, &map_n, smem_u32(&full_bar[it]),
                     (kb_begin + it) * BK, n0);
@@ -297,7 +268,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
       int s = early == stages ? 0 : early, par = early == stages ? 0 : 1;
       for (int it = early; it < num_kb; ++it, s = (s + 1 == stages ? 0 : s + 1), par ^= (s == 0)) {
         if (!mbar_wait(smem_u32(&empty_bar[s]), par)) {
-          atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
+          gb_err::report(ERR_WAIT_EMPTY);
           abort_s = 1;
         }
         if (*(volatile int*)&abort_s) break;
@@ -315,7 +286,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
           const unsigned long long t0 = globaltimer_ns();
           while (!mbar_try_wait(smem_u32(&full_bar[it % stages]), (it / stages) & 1)) {
             if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
-              atomicCAS(&g_error_word, 0, ERR_WAIT_DRAIN);
+              gb_err::report(ERR_WAIT_DRAIN);
               break;
             }
           }
@@ -329,7 +300,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
       int s = 0, par = 0;
       for (int it = 0; it < num_kb; ++it, s = (s + 1 == stages ? 0 : s + 1), par ^= (s == 0)) {
         if (!mbar_wait(smem_u32(&full_bar[s]), par)) {
-          atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
+          gb_err::report(ERR_WAIT_FULL);
           abort_s = 1;
           break;
         }
@@ -416,12 +387,10 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     }
-    GB_STAMP_E(4);
     bool have = mbar_wait(smem_u32(&accum_bar), 0);
-    if (!have && lane == 0) atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+    if (!have && lane == 0) gb_err::report(ERR_WAIT_ACCUM);
     have = have && !*(volatile int*)&abort_s;
     tc_fence_after_sync();
-    GB_STAMP_E(3);
 
     // 16 columns of this thread's row, summed over the four accumulators
     auto load16 = [&](int col, float (&v)[16]) {
@@ -453,14 +422,12 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
             st_async_f32(remote + (uint32_t)(c + j) * (BM * 4), remote_bar, have ? v[j] : 0.f);
         }
       }
-      GB_STAMP_E(5);
     } else {
       if (ranks > 1) {
         const bool got = mbar_wait(smem_u32(&partial_bar), 0);
-        if (!got && lane == 0) atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+        if (!got && lane == 0) gb_err::report(ERR_WAIT_ACCUM);
         have = have && got;
       }
-      GB_STAMP_E(6);
       if (have) {
         const float* partial = reinterpret_cast<const float*>(smem_raw + (partials - smem_u32(smem_raw))) +
                                row_in_tile;
@@ -566,7 +533,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-  GB_STAMP(7);
 }
 
 // --------------------------------------------------------------------------
@@ -936,7 +902,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) & 1) ^ 1)) {
-            atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
+            gb_err::report(ERR_WAIT_EMPTY);
             *aborted = 1;
           }
           if (*aborted) break;
@@ -953,7 +919,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
           const unsigned long long t0 = globaltimer_ns();
           while (!mbar_try_wait(smem_u32(&full_bar[j % STAGES]), (j / STAGES) & 1)) {
             if (globaltimer_ns() - t0 > 20000000ull) {
-              atomicCAS(&g_error_word, 0, ERR_WAIT_DRAIN);
+              gb_err::report(ERR_WAIT_DRAIN);
               break;
             }
           }
@@ -968,7 +934,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
       for (int tile = blockIdx.x; tile < total_tiles && !*aborted; tile += gridDim.x, ++t) {
         const int as = t & 1;
         if (!mbar_wait(smem_u32(&acc_empty[as]), ((t >> 1) & 1) ^ 1)) {   // the epilogue has drained this stage
-          atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+          gb_err::report(ERR_WAIT_ACCUM);
           *aborted = 1;
           break;
         }
@@ -977,7 +943,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) {
-            atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
+            gb_err::report(ERR_WAIT_FULL);
             *aborted = 1;
           }
           if (*aborted) break;
@@ -1010,7 +976,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
       const float inv = epilogue_row_scale(ra, m0 + quarter * 32 + lane, rows_m);
       bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
       if (!have && lane == 0) {
-        atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+        gb_err::report(ERR_WAIT_ACCUM);
         *aborted = 1;
       }
       if (!have || *aborted) break;
@@ -1112,7 +1078,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
         const int n0 = (tile / tiles_m) * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[s]), par)) {
-            atomicCAS(&g_error_word, 0, ERR_WAIT_EMPTY);
+            gb_err::report(ERR_WAIT_EMPTY);
             *aborted = 1;
           }
           if (*aborted) break;
@@ -1141,7 +1107,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
       for (int tile = pair; tile < total_tiles && !*aborted; tile += pairs, ++t) {
         const int as = t & 1;
         if (!mbar_wait(smem_u32(&acc_empty[as]), ((t >> 1) & 1) ^ 1)) {   // both epilogues have drained this stage
-          atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+          gb_err::report(ERR_WAIT_ACCUM);
           *aborted = 1;
           break;
         }
@@ -1149,7 +1115,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
         const uint32_t acc = tmem_base + as * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&full_bar[s]), par)) {
-            atomicCAS(&g_error_word, 0, ERR_WAIT_FULL);
+            gb_err::report(ERR_WAIT_FULL);
             *aborted = 1;
           }
           if (*aborted) break;
@@ -1178,7 +1144,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
       const float inv = epilogue_row_scale(ra, m0 + quarter * 32 + lane, rows_m);
       bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
       if (!have && lane == 0) {
-        atomicCAS(&g_error_word, 0, ERR_WAIT_ACCUM);
+        gb_err::report(ERR_WAIT_ACCUM);
         *aborted = 1;
       }
       if (!have || *aborted) break;
@@ -1293,8 +1259,6 @@ ClusterPlan pick_cluster_plan(Kernel kernel, int* active, int tiles, int total_k
   ClusterPlan best{1, G::STAGES};
   double best_cost = 1e30;
   const int sms = sm_count();
-  static const int force_split = [] { const char* v = getenv("GARUDA_B200_FORCE_SPLIT"); return v ? atoi(v) : 0; }();
-  static const int force_two = [] { const char* v = getenv("GARUDA_B200_FORCE_TWO"); return v ? atoi(v) : -1; }();
   for (int s = 1; s <= G::MAX_CLUSTER && s <= 6 && s <= total_kb; ++s) {
     if (active[s] == 0) {
       cudaLaunchConfig_t cfg = {};
@@ -1314,18 +1278,17 @@ ClusterPlan pick_cluster_plan(Kernel kernel, int* active, int tiles, int total_k
       active[s] = n;
     }
     if (active[s] < 1) continue;
-    if (force_split > 0 && s != force_split && force_split <= G::MAX_CLUSTER) continue;
     const int per = (total_kb + s - 1) / s;
     const int ctas = tiles * s;
     // one CTA per SM
-    if (force_two != 1) {
+    {
       const double cost = (double)((ctas + sms - 1) / sms) * (per + 13.5);
       if (cost < best_cost) { best_cost = cost; best = ClusterPlan{s, G::STAGES}; }
     }
     // two per SM: the most stages that let two CTAs (and their 1 KB each of reserve) share 227 KB
     int st2 = G::STAGES;
     while (st2 > 2 && 2 * (G::smem_bytes(s, st2) + 2048) > SMEM_LIMIT) --st2;
-    if (force_two != 0 && 2 * (G::smem_bytes(s, st2) + 2048) <= SMEM_LIMIT && ctas > sms) {
+    if (2 * (G::smem_bytes(s, st2) + 2048) <= SMEM_LIMIT && ctas > sms) {
       const double share = 2 * ctas <= 3 * sms ? 1.3 : 1.65;      // measured at 1.2 and 1.8 CTAs per SM
       const double cost = (double)((ctas + 2 * sms - 1) / (2 * sms)) * (per + 13.5) * share;
       if (cost < best_cost) { best_cost = cost; best = ClusterPlan{s, st2}; }
@@ -1341,12 +1304,12 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ld
                    int tokens, int K, cudaStream_t stream, const EpilogueArgs& ra = EpilogueArgs{}) {
   using G = Geometry<BN, false, false, true, rope_table_bytes(EPI, BN)>;
   auto kernel = gemm_tc_cluster_kernel<BN, EPI, OT>;
-  static bool configured = false;
-  if (!configured) {
+  static gb::OncePerDevice configured;
+  if (configured.needed()) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          G::smem_bytes(G::MAX_CLUSTER));
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
-    configured = true;
+    configured.done();
   }
   const int tiles_n = (tokens + BN - 1) / BN, tiles_m = (weight_rows + BM - 1) / BM;
   const int total_kb = (K + BK - 1) / BK;
@@ -1382,11 +1345,11 @@ int launch_persistent(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int
                       int out_features, int K, cudaStream_t stream, const EpilogueArgs& ra = EpilogueArgs{}) {
   using G = Geometry<BN, false, false, false>;
   auto kernel = gemm_tc_persistent_kernel<BN, EPI, OT>;
-  static bool configured = false;
-  if (!configured) {
+  static gb::OncePerDevice configured;
+  if (configured.needed()) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
-    configured = true;
+    configured.done();
   }
   const int tiles_m = (tokens + BM - 1) / BM, tiles_n = (weight_rows + BN - 1) / BN;
   const int total = tiles_m * tiles_n;
@@ -1402,11 +1365,11 @@ int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ldo, 
                 int out_features, int K, cudaStream_t stream, const EpilogueArgs& ra = EpilogueArgs{}) {
   using PG = PairGeometry<BN>;
   auto kernel = gemm_tc_pair_kernel<BN, EPI, OT>;
-  static bool configured = false;
-  if (!configured) {
+  static gb::OncePerDevice configured;
+  if (configured.needed()) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PG::SMEM_BYTES);
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
-    configured = true;
+    configured.done();
   }
   const int tiles_m = (tokens + 2 * BM - 1) / (2 * BM), tiles_n = (weight_rows + BN - 1) / BN;
   const int total = tiles_m * tiles_n, most = sm_count() / 2;
@@ -1431,28 +1394,13 @@ int pick_tile_width(int rows_m, int rows_n) {
 // more tokens than one tile's 64 columns make several column tiles, each of which reads the weights
 // (from L2 after the first). With the TinyLlama layer sizes a step of 65 to 256 tokens took 2.1 to 2.8 ms
 // this way against 2.9 to 3.5 ms with 128-row token tiles, which are too few CTAs to stream the weights;
-// from about 400 tokens on the two are level. The environment variable is for such comparisons.
-int few_token_limit() {
-  static const int limit = [] {
-    const char* v = getenv("GARUDA_B200_FEW_TOKENS");
-    const int n = v ? atoi(v) : 0;
-    return n >= 64 ? n : 256;
-  }();
-  return limit;
-}
-
-bool pairs_enabled() {
-  static const bool on = [] {
-    const char* v = getenv("GARUDA_B200_PAIRS");
-    return !(v && v[0] == '0');
-  }();
-  return on;
-}
+// from about 400 tokens on the two are level.
+constexpr int few_token_limit() { return 256; }
 
 // More than 64 tokens: whether CTA pairs take the product, and the tile width over the weight's rows.
 // Pairs pay from about a thousand tokens (768: 3.9 ms a step with pairs, 3.4 without; 1,024: 4.4 against 4.5):
 // below that their 256 x 256 tiles are too few for the 74 pairs.
-bool many_token_pairs(int tokens, int weight_rows) { return pairs_enabled() && tokens >= 8 * BM && weight_rows >= 256; }
+bool many_token_pairs(int tokens, int weight_rows) { return tokens >= 8 * BM && weight_rows >= 256; }
 int many_token_width(int tokens, int weight_rows) {
   return many_token_pairs(tokens, weight_rows) ? 256 : pick_tile_width(tokens, weight_rows);
 }
@@ -1461,21 +1409,31 @@ int many_token_width(int tokens, int weight_rows) {
 
 GB_DEFINE_LAST_ERROR()
 
-#ifdef GB_TIMELINE
-GB_EXPORT int gb_tc_timeline(unsigned long long* host_out, int ctas) {
-  return cudaMemcpyFromSymbol(host_out, g_timeline, sizeof(unsigned long long) * 8 * ctas) == cudaSuccess ? 0 : 1;
-}
-#endif
-
 // Returns the device error word (0: none) and clears it. Synchronises the device.
-GB_EXPORT int gb_tc_error_check() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_error_word, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) {
-    int zero = 0;
-    cudaMemcpyToSymbol(g_error_word, &zero, sizeof(int));
+GB_EXPORT int gb_tc_error_check() { return gb_err::fetch_and_clear(); }
+
+// A word of pinned host memory that a kernel's failed wait also writes its code to (null: none).
+GB_EXPORT int gb_tc_set_error_sink(int* host_word) { return gb_err::set_sink(host_word); }
+
+namespace {
+// One warp waits, for at most limit_ns, on a barrier that nothing will ever complete.
+__global__ void wait_that_runs_out_kernel(unsigned long long limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
   }
-  return v;
+  __syncthreads();
+  if (threadIdx.x == 0 && !mbar_wait(smem_u32(&bar), 0, limit_ns)) gb_err::report(ERR_WAIT_FULL);
+}
+}  // namespace
+
+// For tests of the error path: launches a kernel whose one wait runs out after limit_us
+// microseconds (at most 100 ms), which then records its code as any product kernel would and returns.
+GB_EXPORT int gb_tc_selftest_wait_runs_out(int limit_us, cudaStream_t stream) {
+  if (limit_us < 1 || limit_us > 100000) return gb::fail(GB_BAD_ARGUMENT, "the limit must be 1 to 100000 us");
+  wait_that_runs_out_kernel<<<1, 32, 0, stream>>>((unsigned long long)limit_us * 1000ull);
+  return gb::check_launch("wait_that_runs_out");
 }
 
 // An RMS norm folded into the products around it (see EpilogueArgs). As the consumer: sums_in

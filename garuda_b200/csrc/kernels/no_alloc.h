@@ -21,7 +21,7 @@
 //  * The first call on a device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current) and remembers it; later
 //    calls on that device only launch. Make that first call before any stream
-//    capture begins.
+//    capture begins, and from one thread: the look-up is not synchronised.
 //  * It calls neither cudaMalloc nor cudaFree nor any routine that allocates.
 //  * All calls share the one array, and it keeps whatever the last call left.
 //    Nothing in it has to start at zero: a call writes every element before it

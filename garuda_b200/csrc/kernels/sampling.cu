@@ -444,11 +444,11 @@ int launch_sample(const float* logits, const float* temperature, const int32_t* 
   constexpr size_t LIMIT = 200 * 1024;
   const size_t bytes = (size_t)V * sizeof(float);
   const bool fits = bytes <= LIMIT;
-  static bool configured = false;
-  if (fits && !configured) {
+  static gb::OncePerDevice configured;
+  if (fits && configured.needed()) {
     cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LIMIT);
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "sample: %s", cudaGetErrorString(e));
-    configured = true;
+    configured.done();
   }
   sample_kernel<<<R, 1024, fits ? bytes : 0, stream>>>(logits, temperature, top_k, top_p, u, out, scratch, V,
                                                        fits ? 1 : 0);

@@ -59,7 +59,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Waits for the phase with the given parity to complete. False after WAIT_LIMIT_NS.
 // The clock is read only once in a few thousand polls: reading it costs far more than a
 // poll, and a waiter that is busy reading the clock wakes up late.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t polls = 0;
@@ -68,7 +69,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if ((++polls & 0xFFFu) == 0) {
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
   return true;

@@ -43,7 +43,7 @@ class Engine:
                  kv_cache_bytes: Optional[int] = None, max_concurrent: int = 4,
                  queue_capacity: int = 256, max_batch_tokens: int = 2048, prefill_chunk: int = 2048,
                  cuda_graphs: bool = True, lookahead: bool = True, device: int = 0, ignore_eos: bool = False,
-                 eos_token_id: Optional[int] = None, ops=None):
+                 eos_token_id: Union[None, int, Sequence[int]] = None, ops=None):
         if dtype not in _DTYPES:
             raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
         self.dtype = _DTYPES[dtype]
@@ -94,8 +94,15 @@ class Engine:
         sc.prefill_chunk = prefill_chunk
         sc.max_context = self.max_context
         sc.vocab_size = spec.vocab_size
-        eos = eos_token_id if eos_token_id is not None else spec.eos_token_id
-        sc.eos_token_id = -1 if eos is None else int(eos)
+        # generation ends on any of the architecture's end tokens (config.json may list several),
+        # or on those given here in their place
+        if eos_token_id is None:
+            eos = tuple(spec.eos_token_ids)
+        elif isinstance(eos_token_id, int):
+            eos = (int(eos_token_id),)
+        else:
+            eos = tuple(int(t) for t in eos_token_id)
+        sc.eos_token_ids = list(eos)
         sc.ignore_eos = bool(ignore_eos)
         self.scheduler = host.Scheduler(sc, self.cache.manager)
         self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda"
@@ -123,6 +130,25 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """One step of the step function; see ``StepRunner.run``."""
         return self.runner.run(entries)
+
+    def check_errors(self) -> None:
+        """Raises ``KernelError`` if a kernel of a step that has finished gave up on a bounded wait
+        (its results are then not to be trusted). Free of copies and synchronisation: it reads a
+        word of pinned host memory that such a kernel writes; call it after waiting for a step's
+        results. ``generate`` and ``replay`` do."""
+        failed = getattr(self.ops, "failed_wait", None)
+        if failed is not None and failed():
+            self.ops.tc.check_errors()       # synchronises, clears, raises with the code's meaning
+
+    def replay(self, trace, out_dir: str, report=None) -> int:
+        """Trace replay through this engine's step function: ``trace`` is a path of a file of
+        steps (one JSON object a line, see ``garuda_b200/engine/replay.py``) or an iterable of such
+        lines; logits of the wanted places go to ``out_dir/<step>.f32``. Returns the number of steps."""
+        from .replay import replay
+        if isinstance(trace, (str, bytes)):
+            with open(trace, "r", encoding="utf-8") as f:
+                return replay(self, f, out_dir, report)
+        return replay(self, trace, out_dir, report)
 
     def warm_up(self) -> None:
         """Captures the decode step's graphs for every batch size now, so that no request
@@ -249,7 +275,7 @@ class Engine:
                 k += 1
 
         nxt = None
-        if (self.lookahead and self.runner.graphs is not None
+        if (self.lookahead and self.runner.graphs is not None and self.model.graph_safe
                 and all(e.sample and len(e.tokens) == 1 for e in entries)):
             try:
                 if not rest and [w[1] for w in where] == list(range(len(ahead[0]))):
@@ -274,6 +300,7 @@ class Engine:
         def collect():
             a = self.sampler.result(ahead[1]) if matched else []
             f = self.sampler.result(fresh) if fresh is not None else []
+            self.check_errors()      # the step's kernels have finished: did one of them give up on a wait?
             return [(a if src == 0 else f)[row] for src, row in where]
 
         return collect, nxt

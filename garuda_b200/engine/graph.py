@@ -39,7 +39,9 @@ class DecodeGraphs:
         self.replays = 0
 
     def eligible(self, entries) -> bool:
-        return len(entries) <= self.max_bucket and all(len(e.tokens) == 1 for e in entries)
+        """A step of single tokens, of a model whose every part may be captured (``graph_safe``)."""
+        return (self.runner.model.graph_safe and len(entries) <= self.max_bucket
+                and all(len(e.tokens) == 1 for e in entries))
 
     # ------------------------------------------------------------------ layout
     def _layout(self, B: int):

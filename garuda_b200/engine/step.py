@@ -47,6 +47,12 @@ class StepRunner:
         self.steps = 0
         self.tokens_run = 0
         self.graphs = None        # DecodeGraphs, when decode steps are replayed from CUDA graphs
+        # pinned staging for the batch's arrays: two buffers in turn, each with an event that tells
+        # when the copy that last read it has run (pinning memory anew for every step costs far more
+        # than the copy)
+        self._staging = [None, None]
+        self._staged = [None, None]
+        self._turn = 0
 
     # ------------------------------------------------------------------ checks
     def _validate_and_reserve(self, entries: Sequence[StepEntry]):
@@ -56,6 +62,7 @@ class StepRunner:
         seen = set()
         wants = []
         fresh = []
+        starting = []          # requests whose first token this step runs
         for e in entries:
             if e.request in seen:
                 raise StepError(f"request {e.request} appears twice in one step")
@@ -76,6 +83,8 @@ class StepRunner:
                                 f"({old} used) of request {e.request}")
             if not known:
                 fresh.append(e.request)
+            if old == 0:
+                starting.append(e.request)
             wants.append((e.request, old + n))
         if len(fresh) > mgr.free_slots:
             raise StepError(f"{len(fresh)} new requests but only {mgr.free_slots} request slots are free")
@@ -94,6 +103,11 @@ class StepRunner:
             for r in fresh:
                 mgr.release(r)
             raise
+        # A request that starts at position 0 starts from zeroed fixed-size state, whoever took its
+        # slot (this runner just now, or a scheduler that admitted it, or readmitted it after it
+        # had been preempted) and whoever held the slot before.
+        if starting and self.cache.states:
+            self.cache.reset_states([mgr.slot(r) for r in starting])
         return wants
 
     # ------------------------------------------------------------------ batch
@@ -110,7 +124,8 @@ class StepRunner:
                         ("tables", G * R * width)):
             offs[name] = (cursor, n)
             cursor += _align(n)
-        host = np.empty(cursor, dtype=np.int32)
+        pinned = self._stage(cursor)
+        host = pinned.numpy()[:cursor] if pinned is not None else np.empty(cursor, dtype=np.int32)
 
         def view(name):
             o, n = offs[name]
@@ -141,11 +156,13 @@ class StepRunner:
         if G:
             mgr.fill_block_tables([e.request for e in entries], tables)
 
-        cpu = torch.from_numpy(host)
-        if self.device.type == "cuda":
-            dev = cpu.pin_memory().to(self.device, non_blocking=True)
+        if pinned is not None:
+            dev = pinned[:cursor].to(self.device, non_blocking=True)
+            if self._staged[self._turn] is None:
+                self._staged[self._turn] = torch.cuda.Event()
+            self._staged[self._turn].record()
         else:
-            dev = cpu.clone()
+            dev = torch.from_numpy(host).clone()
 
         def dview(name):
             o, n = offs[name]
@@ -161,6 +178,23 @@ class StepRunner:
                   "kv_lens": kv_lens, "slots": slots, "logit_rows": logit_rows[:W],
                   "requests": [e.request for e in entries]},
         )
+
+    def _stage(self, n: int):
+        """A pinned int32 buffer of at least ``n`` entries that no copy in flight still reads, or
+        None on a machine without a device."""
+        if self.device.type != "cuda":
+            return None
+        self._turn ^= 1
+        t = self._turn
+        if self._staged[t] is not None:
+            self._staged[t].synchronize()
+        buf = self._staging[t]
+        if buf is None or buf.numel() < n:
+            size = 1024
+            while size < n:
+                size *= 2
+            buf = self._staging[t] = torch.empty(size, dtype=torch.int32).pin_memory()
+        return buf
 
     # ------------------------------------------------------------------ run
     def run(self, entries: Sequence[StepEntry], device_tokens=None) -> torch.Tensor:

@@ -42,6 +42,16 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_ERROR_WORD = None
+
+
+def _error_word() -> torch.Tensor:
+    global _ERROR_WORD
+    if _ERROR_WORD is None:
+        _ERROR_WORD = torch.zeros(4, dtype=torch.int32).pin_memory()
+    return _ERROR_WORD
+
+
 class PendingNorm:
     """An RMS norm of which only the first half has run, folded into the product that wrote the
     residual stream ``x``: ``values`` is ``x * weight`` in bfloat16 and ``sums`` ``[tiles, T]``
@@ -77,18 +87,28 @@ class CudaOps:
         self.device = torch.device(device)
         self.core = load_kernel_lib("garuda_core")
         self._declare_core()
+        # A word of pinned host memory that a kernel whose bounded wait ran out writes its code to (the
+        # device reaches pinned host memory directly); ``failed_wait`` reads it without a copy.
+        # The kernel libraries are loaded once per process, so the word is one per process as well.
+        self.error_word = _error_word()
         self.tc = None
         if tensor_cores:
             from .tc import TensorCoreKernels
             self.tc = TensorCoreKernels(self)
-        # whether products fold the norms around them in (``linear``'s ``emit_norm``); the environment
-        # variable is for comparing timings
-        self.folds_norms = self.tc is not None and os.environ.get("GARUDA_B200_FOLD_NORMS", "1") != "0"
+        # whether products fold the norms around them in (``linear``'s ``emit_norm``); a test flips
+        # it to compare the two ways
+        self.folds_norms = self.tc is not None
         self._inv_freq = {}
         self._held_stream = None
         self.launches = 0
         from ..engine.batch import Workspace
         self.private_ws = Workspace(self.device)   # scratch for calls made outside a step
+
+    def failed_wait(self) -> int:
+        """The code of a bounded wait that ran out in a kernel which has finished by now, or 0.
+        Costs nothing: call it where the host has just waited for a step's results. The full check
+        (``tc.check_errors``) synchronises and clears."""
+        return int(self.error_word[0])
 
     # ------------------------------------------------------------------ plumbing
     def _declare_core(self):
@@ -100,7 +120,7 @@ class CudaOps:
             "gb_rope_kv_append": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                   c_int, c_void_p],
-            "gb_rope_inplace": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+            "gb_rope_inplace": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
             "gb_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
             "gb_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
             "gb_residual_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
@@ -144,16 +164,14 @@ class CudaOps:
                 _need(t.is_cuda, "kernel operands must live on the CUDA device")
 
     # ------------------------------------------------------------------ parts
-    def inv_freq(self, theta: float, head_dim: int) -> torch.Tensor:
-        """``1 / theta^(2i/head_dim)`` in 32-bit (garuda/src/simd/mod.rs:199), once per
-        (theta, head_dim)."""
-        key = (float(theta), int(head_dim))
-        if key not in self._inv_freq:
-            i = np.arange(head_dim // 2, dtype=np.float32)
-            f = np.float32(1.0) / np.power(np.float32(theta), np.float32(2.0) * i / np.float32(head_dim),
-                                           dtype=np.float32)
-            self._inv_freq[key] = torch.from_numpy(f).to(self.device)
-        return self._inv_freq[key]
+    def inv_freq(self, rotary) -> torch.Tensor:
+        """One frequency per pair of the head for a ``RotaryParams``: its own table if it has
+        one, else ``1 / theta^(2i/head_dim)`` in 32-bit (garuda/src/simd/mod.rs:199). Made once
+        per parameter set."""
+        if rotary not in self._inv_freq:
+            from ..parts.rotary import rotary_frequencies
+            self._inv_freq[rotary] = torch.from_numpy(rotary_frequencies(rotary)).to(self.device)
+        return self._inv_freq[rotary]
 
     def embedding(self, table, ids, out):
         self._on_device(table, ids, out)
@@ -312,14 +330,14 @@ class CudaOps:
         """``[T, head_dim / 2, 2]`` cosines and sines of every token's angles, made once per
         step (kept in the step's context) for every layer's fused projection to read."""
         half = rotary.head_dim // 2
-        key = ("rope_table", float(rotary.theta), int(rotary.head_dim), positions.data_ptr(), positions.shape[0])
+        key = ("rope_table", rotary, positions.data_ptr(), positions.shape[0])
         cache = getattr(ctx, "step_cache", None)
         if cache is not None and key in cache:
             return cache[key]
         T = positions.shape[0]
-        name = f"rope_table_{rotary.theta}_{rotary.head_dim}"
+        name = f"rope_table_{rotary.theta}_{rotary.head_dim}_{hash(rotary.inv_freq)}"
         out = ctx.ws.get(name, (T, half, 2), torch.float32)
-        inv = self.inv_freq(rotary.theta, rotary.head_dim)
+        inv = self.inv_freq(rotary)
         code = self.core.gb_rope_table(positions.data_ptr(), inv.data_ptr(), out.data_ptr(), T, half, self._stream())
         self._check(self.core, code, "rope_table")
         if cache is not None:
@@ -346,7 +364,7 @@ class CudaOps:
         inter = 0
         if rotary is not None:
             _need(rotary.head_dim == head_dim, "rope_kv_append: rotary is for another head_dim")
-            inv = self.inv_freq(rotary.theta, head_dim)
+            inv = self.inv_freq(rotary)
             inter = int(rotary.interleaved)
         self._check(self.core, self.core.gb_rope_kv_append(
             qkv.data_ptr(), _tag(qkv, "qkv"), qkv.stride(0), q_out.data_ptr(), _ptr(k_pool), _ptr(v_pool),
@@ -354,15 +372,17 @@ class CudaOps:
             block_table.shape[1] if block_table is not None else 0, T, heads, kv_heads, head_dim,
             _ptr(inv), inter, page_size, self._stream()), "rope_kv_append")
 
-    def rope_inplace(self, x, positions, theta, interleaved):
-        """Rotate ``x [T, H, head_dim]`` (float32, rows may be strided) in place."""
+    def rope_inplace(self, x, positions, rotary):
+        """Rotate ``x [T, H, rotary.head_dim]`` (float32; rows and heads may be strided, so a
+        view of every head's first channels will do) in place."""
         self._on_device(x, positions)
-        _need(x.dtype == torch.float32 and x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == x.shape[2],
-              "rope_inplace: x must be float32 [T, H, hd] with contiguous heads")
+        _need(x.dtype == torch.float32 and x.dim() == 3 and x.stride(2) == 1 and x.stride(1) >= x.shape[2],
+              "rope_inplace: x must be float32 [T, H, width] with unit stride along the width")
         T, H, hd = x.shape
+        _need(hd == rotary.head_dim, "rope_inplace: the view is not as wide as the rotation")
         self._check(self.core, self.core.gb_rope_inplace(
-            x.data_ptr(), x.stride(0), T, H, hd, positions.data_ptr(),
-            self.inv_freq(theta, hd).data_ptr(), int(interleaved), self._stream()), "rope_inplace")
+            x.data_ptr(), x.stride(0), x.stride(1), T, H, hd, positions.data_ptr(),
+            self.inv_freq(rotary).data_ptr(), int(rotary.interleaved), self._stream()), "rope_inplace")
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
                         scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1):

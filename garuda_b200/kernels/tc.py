@@ -38,6 +38,13 @@ class TensorCoreKernels:
         L.gb_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
         L.gb_gemm_tc_supported.restype = c_int
         L.gb_tc_error_check.restype = c_int
+        L.gb_tc_set_error_sink.argtypes = [c_void_p]
+        L.gb_tc_set_error_sink.restype = c_int
+        L.gb_tc_selftest_wait_runs_out.argtypes = [c_int, c_void_p]
+        L.gb_tc_selftest_wait_runs_out.restype = c_int
+        if L.gb_tc_set_error_sink(ops.error_word.data_ptr()):
+            from .ops import KernelError
+            raise KernelError("the tensor-core library could not be given the host's error word")
         L.gb_gemm_tc_qkv.argtypes = ([c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 6 + [c_int] * 4 + [c_void_p]
                                      + [c_int, c_int, ctypes.POINTER(NormFold), c_void_p])
         L.gb_gemm_tc_qkv.restype = c_int
@@ -47,11 +54,18 @@ class TensorCoreKernels:
         """Synchronises, and raises if a kernel gave up on a wait since the last check."""
         code = self.lib.gb_tc_error_check()
         for lib in self._attn.values():
-            if lib.gb_attention_error_check():
-                code = code or 5
+            code = lib.gb_attention_error_check() or code
+        seen, self.ops.error_word[0] = int(self.ops.error_word[0]), 0
+        code = code or seen
         if code:
             from .ops import KernelError
             raise KernelError("a tensor-core kernel gave up waiting: " + _WAIT_NAMES.get(code, f"code {code}"))
+
+    def selftest_wait_runs_out(self, limit_us: int = 1000) -> None:
+        """Launches a kernel whose only wait runs out after ``limit_us`` microseconds and which
+        then records its error code like any product kernel (for tests of the error path)."""
+        self.ops._check(self.lib, self.lib.gb_tc_selftest_wait_runs_out(int(limit_us), self.ops._stream()),
+                        "selftest_wait_runs_out")
 
     # ------------------------------------------------------------------ folded norms
     def norm_tiles(self, tokens: int, features: int) -> int:
@@ -130,6 +144,9 @@ class TensorCoreKernels:
                                              + [c_int] * 6 + [ctypes.c_longlong, c_void_p])
             lib.gb_attention_mma.restype = c_int
             lib.gb_attention_error_check.restype = c_int
+            lib.gb_attention_set_error_sink.argtypes = [c_void_p]
+            lib.gb_attention_set_error_sink.restype = c_int
+            lib.gb_attention_set_error_sink(self.ops.error_word.data_ptr())
             self._attn[head_dim] = lib
         return lib
 

@@ -41,7 +41,14 @@ class ModelSpec:
     final_norm: PartSpec
     head: Optional[str]                  # tensor name of the [vocab, width] head; None: tied
     embedding_init: Tuple = ("normal", 0.02)
-    eos_token_id: Optional[int] = None
+    eos_token_ids: Tuple[int, ...] = ()  # generation ends on any of them (config.json may list several)
+    # names a model folder may hold although the model reads nothing from them (a tied model's
+    # stored copy of its head); anything else the model did not ask for is an error
+    ignored_tensors: Tuple[str, ...] = ()
+
+    @property
+    def eos_token_id(self) -> Optional[int]:
+        return self.eos_token_ids[0] if self.eos_token_ids else None
 
 
 @dataclass(frozen=True)
@@ -84,6 +91,11 @@ class Decoder:
             else:
                 raise TypeError(f"unknown cache need {need!r}")
         self.cache_groups = [CacheGroup(need, tuple(calls)) for need, calls in groups.items()]
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model may be captured in a CUDA graph: every part says so."""
+        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
 
     # ---- tensors ---------------------------------------------------------
     def expected_tensors(self) -> Dict[str, TensorSpec]:

@@ -43,7 +43,8 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
         final_norm=PartSpec("rms", dict(width=cfg.hidden_size, eps=cfg.rms_norm_eps,
                                         weight_init=norm_init), prefix="model.norm."),
         head=None if cfg.tie_word_embeddings else "lm_head.weight",
-        embedding_init=("normal", std), eos_token_id=cfg.eos_token_id,
+        embedding_init=("normal", std), eos_token_ids=cfg.eos_token_ids,
+        ignored_tensors=("lm_head.weight",) if cfg.tie_word_embeddings else (),
     )
 
 

@@ -48,14 +48,21 @@ class PagedAttention(Mixer):
         if not self.reads_shared_cache:
             t["k_proj.weight"] = TensorSpec((self.kv_dim, self.width), init=init)
             t["v_proj.weight"] = TensorSpec((self.kv_dim, self.width), init=init)
+        # a position encoding with tensors of its own (a learned table) keeps them under "position."
+        for local, ts in self.position.tensors().items():
+            t["position." + local] = ts
         return t
+
+    @property
+    def graph_safe(self):
+        return self.position.graph_safe
 
     def cache_need(self):
         return PagedKV(self.kv_heads, self.head_dim, self.window)
 
     def load(self, tensors, ops, dtype):
         super().load(tensors, ops, dtype)
-        self.position.load({}, ops, dtype)
+        self.position.load({local: tensors["position." + local] for local in self.position.tensors()}, ops, dtype)
         if self.reads_shared_cache:
             self.w_qkv = tensors["q_proj.weight"].contiguous()
         else:

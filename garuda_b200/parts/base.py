@@ -81,6 +81,13 @@ class LayerCache:
 class Part:
     """Common behaviour: tensors by local name, bound once after loading."""
 
+    #: Whether a decode step through this part may be captured in a CUDA graph and replayed: every
+    #: launch must read the batch from the device arrays of ``ctx.batch`` only (a replayed step has
+    #: no host copies, ``ctx.batch.host`` is empty), launch the same kernels whatever the batch
+    #: holds, and allocate nothing. The built-in parts say True; a part that says nothing is run
+    #: kernel by kernel.
+    graph_safe = False
+
     def tensors(self) -> Dict[str, TensorSpec]:
         return {}
 

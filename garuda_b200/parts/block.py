@@ -50,6 +50,23 @@ class PreNormBlock:
             return self.mixer_norm
         return None
 
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part, _ in self.parts())
+
+    @staticmethod
+    def _take_pending(ctx, x, added_in_place):
+        """The one place where a folded norm changes hands: what the part that just ran left in
+        ``ctx.pending_norm`` is taken out (the field is empty afterwards) and checked to be the
+        norm of this block's residual stream. A part that returned its output instead of adding
+        it in cannot have folded a norm of the sum; whatever it left is dropped."""
+        p, ctx.pending_norm = ctx.pending_norm, None
+        if p is None or not added_in_place:
+            return None
+        if p.x.data_ptr() != x.data_ptr() or tuple(p.x.shape) != tuple(x.shape):
+            raise RuntimeError("a folded norm was left behind that is not of this block's residual stream")
+        return p
+
     def forward(self, ctx, x, cache, pending=None, next_norm=None):
         """``pending``: this layer's first norm of ``x``, already half done by the layer in
         front (a ``PendingNorm``). ``next_norm``: the norm part that the next layer starts with,
@@ -63,23 +80,20 @@ class PreNormBlock:
         if (folds and ff is not None and getattr(self.mixer, "emits_norm", False)
                 and getattr(ff, "takes_pending_norm", False) and hasattr(self.feed_forward_norm, "fold")):
             kw["emit_norm"] = self.feed_forward_norm
+        elif folds and ff is None and next_norm is not None and getattr(self.mixer, "emits_norm", False):
+            kw["emit_norm"] = next_norm
         ctx.pending_norm = None
         y = self.mixer.forward(ctx, h, cache, residual=x, **kw)
         if y is not None:
             ops.residual_add(x, y)
-        out = None
-        if ff is not None:
-            h2, ctx.pending_norm = ctx.pending_norm, None
-            if h2 is None:
-                h2 = self.feed_forward_norm.forward(ctx, x)
-            kw = {}
-            if folds and next_norm is not None and getattr(ff, "emits_norm", False):
-                kw["emit_norm"] = next_norm
-            y2 = ff.forward(ctx, h2, residual=x, **kw)
-            if y2 is not None:
-                ops.residual_add(x, y2)
-            out = ctx.pending_norm
-        elif y is None:
-            out = ctx.pending_norm
-        ctx.pending_norm = None
-        return out
+        out = self._take_pending(ctx, x, y is None and "emit_norm" in kw)
+        if ff is None:
+            return out
+        h2 = out if out is not None else self.feed_forward_norm.forward(ctx, x)
+        kw = {}
+        if folds and next_norm is not None and getattr(ff, "emits_norm", False):
+            kw["emit_norm"] = next_norm
+        y2 = ff.forward(ctx, h2, residual=x, **kw)
+        if y2 is not None:
+            ops.residual_add(x, y2)
+        return self._take_pending(ctx, x, y2 is None and "emit_norm" in kw)

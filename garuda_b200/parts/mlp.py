@@ -15,6 +15,8 @@ from .base import FeedForward, TensorSpec, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, width: int, inner: int, init_std: float = 0.02):
         self.width, self.inner = int(width), int(inner)
         self.init_std = float(init_std)

@@ -16,6 +16,8 @@ from .base import Norm, TensorSpec, register_norm
 
 @register_norm("rms")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, width: int, eps: float, weight_init=("ones",)):
         self.width = int(width)
         self.eps = float(eps)

@@ -56,10 +56,10 @@ def check_folder(model, folder: SafetensorsFolder, tied_ok: bool = True):
     expected = model.expected_tensors()
     have = folder.entries
     missing = [n for n in expected if n not in have]
-    unexpected = [n for n in have if n not in expected]
-    # a tied model may still carry a copy of the head; it is the embedding table and is not read
-    if model.spec.head is None and tied_ok:
-        unexpected = [n for n in unexpected if n != "lm_head.weight"]
+    # what the architecture says a folder may carry unread (a tied model's copy of its head, which
+    # is the embedding table) is not unexpected
+    ignored = set(getattr(model.spec, "ignored_tensors", ())) if tied_ok else set()
+    unexpected = [n for n in have if n not in expected and n not in ignored]
     wrong, other = [], []
     for n, ts in expected.items():
         if n in have:

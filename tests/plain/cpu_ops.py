@@ -62,11 +62,17 @@ class CpuOps:
         x += y.float()
 
     # garuda/src/simd/mod.rs:196-206
-    def _rotate(self, v, positions, theta, interleaved):
+    def _rotate(self, v, positions, rotary):
+        """``rotary``: anything with ``theta``, ``interleaved`` and ``inv_freq`` (one frequency per
+        pair in place of the formula, or None)."""
         hd = v.shape[-1]
-        i = np.arange(hd // 2, dtype=np.float32)
-        inv = torch.from_numpy(np.float32(1.0) / np.power(np.float32(theta), np.float32(2.0) * i / np.float32(hd),
-                                                          dtype=np.float32))
+        interleaved = rotary.interleaved
+        if getattr(rotary, "inv_freq", None) is not None:
+            inv = torch.tensor(list(rotary.inv_freq), dtype=torch.float32)
+        else:
+            i = np.arange(hd // 2, dtype=np.float32)
+            inv = torch.from_numpy(np.float32(1.0) / np.power(np.float32(rotary.theta),
+                                                              np.float32(2.0) * i / np.float32(hd), dtype=np.float32))
         ang = positions.float()[:, None] * inv[None, :]
         s, c = torch.sin(ang)[:, None, :], torch.cos(ang)[:, None, :]
         out = torch.empty_like(v)
@@ -80,8 +86,8 @@ class CpuOps:
             out[..., hd // 2:] = a * s + b * c
         return out
 
-    def rope_inplace(self, x, positions, theta, interleaved):
-        x.copy_(self._rotate(x.clone(), positions, theta, interleaved))
+    def rope_inplace(self, x, positions, rotary):
+        x.copy_(self._rotate(x.clone(), positions, rotary))
 
     # garuda/src/llama/mod.rs:743-757 (the projections), then rotate and store
     def qkv_rope_append(self, ctx, h, w_qkv, q_out, k_pool, v_pool, positions, token_req, block_table,
@@ -97,14 +103,14 @@ class CpuOps:
         x = qkv.float()
         q = x[:, : heads * head_dim].reshape(T, heads, head_dim)
         if rotary is not None:
-            q = self._rotate(q, positions, rotary.theta, rotary.interleaved)
+            q = self._rotate(q, positions, rotary)
         q_out.copy_(q.to(q_out.dtype))
         if not kv_heads:
             return
         k = x[:, heads * head_dim: (heads + kv_heads) * head_dim].reshape(T, kv_heads, head_dim)
         v = x[:, (heads + kv_heads) * head_dim:].reshape(T, kv_heads, head_dim)
         if rotary is not None:
-            k = self._rotate(k, positions, rotary.theta, rotary.interleaved)
+            k = self._rotate(k, positions, rotary)
         for t in range(T):
             pos = int(positions[t])
             page = int(block_table[int(token_req[t]), pos // page_size])

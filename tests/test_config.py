@@ -103,3 +103,19 @@ def test_engine_config_refuses(tmp_path, text, match):
     p.write_text(text)
     with pytest.raises(ConfigError, match=match):
         EngineConfig.load(str(p))
+
+
+def test_end_of_sequence_ids_may_be_one_or_a_list():
+    from garuda_b200.config.model_config import LlamaConfig, ConfigError
+    from garuda_b200.models.llama import llama_spec
+    from tests.helpers import TINY_A
+    assert LlamaConfig.from_dict(TINY_A).eos_token_ids == ()
+    one = LlamaConfig.from_dict(dict(TINY_A, eos_token_id=2))
+    assert one.eos_token_ids == (2,) and one.eos_token_id == 2 and one.to_dict()["eos_token_id"] == 2
+    three = LlamaConfig.from_dict(dict(TINY_A, eos_token_id=[201, 208, 209, 208]))
+    assert three.eos_token_ids == (201, 208, 209) and three.eos_token_id == 201
+    assert three.to_dict()["eos_token_id"] == [201, 208, 209]
+    assert LlamaConfig.from_dict(three.to_dict()) == three
+    assert llama_spec(three).eos_token_ids == (201, 208, 209)
+    with pytest.raises(ConfigError, match="eos_token_id"):
+        LlamaConfig.from_dict(dict(TINY_A, eos_token_id=[1, "x"]))

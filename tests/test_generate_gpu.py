@@ -253,7 +253,7 @@ def test_a_toy_mixer_with_state_of_its_own_can_be_registered_built_and_stepped()
     from garuda_b200.kernels import CudaOps
     from garuda_b200.weights.random_init import random_tensor
 
-    @register_mixer("toy_running_mean")
+    @register_mixer("toy_running_mean_local")
     class RunningMean(Mixer):
         def __init__(self, width):
             self.width = width
@@ -289,7 +289,7 @@ def test_a_toy_mixer_with_state_of_its_own_can_be_registered_built_and_stepped()
     norm = lambda p: PartSpec("rms", dict(width=d, eps=1e-5), prefix=p)
     ff = lambda l: PartSpec("swiglu", dict(width=d, inner=96), prefix=f"layers.{l}.ff.")
     layers = [BlockSpec(attn(0), ff(0), norm("layers.0.n1."), norm("layers.0.n2.")),
-              BlockSpec(PartSpec("toy_running_mean", dict(width=d), prefix="layers.1.toy."), ff(1),
+              BlockSpec(PartSpec("toy_running_mean_local", dict(width=d), prefix="layers.1.toy."), ff(1),
                         norm("layers.1.n1."), norm("layers.1.n2.")),
               BlockSpec(attn(2), None, norm("layers.2.n1."), None)]
     # the run order names layer 0 twice, and its second call reads the first call's cache
@@ -320,7 +320,7 @@ def test_a_toy_mixer_with_state_of_its_own_can_be_registered_built_and_stepped()
     for i in range(2):
         cut = np.concatenate(got[i])
         assert np.abs(cut - whole[i]).max() <= 2e-5 * np.abs(whole[i]).max()
-    # the state slot is zeroed when a new request takes it
+    # a request that starts in a slot another one has used starts from zeroed state
     runner.end(10), runner.end(11)
     again = runner.run([StepEntry(12, toks[0], range(40))]).cpu().numpy()
     assert np.abs(again - whole[0]).max() <= 2e-5 * np.abs(whole[0]).max()

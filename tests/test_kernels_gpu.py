@@ -225,10 +225,18 @@ def test_rotate_and_store(ops, interleaved, dtype):
     # rotation in place, for position encodings that are applied outside the fused kernel
     x = torch.randn(T, Hq, hd)
     ref = x.clone()
-    cpu.rope_inplace(ref, positions, 500000.0, interleaved)
+    cpu.rope_inplace(ref, positions, rot)
     xd = dev(x)
-    ops.rope_inplace(xd, dev(positions), 500000.0, interleaved)
+    ops.rope_inplace(xd, dev(positions), rot)
     close(xd, ref, 2e-6, "in place")
+    # the first 32 channels of every head only, at frequencies of its own
+    narrow = RotaryParams(1.0, 32, interleaved, tuple(0.5 ** i for i in range(16)))
+    ref = x.clone()
+    cpu.rope_inplace(ref[..., :32], positions, narrow)
+    xd = dev(x)
+    ops.rope_inplace(xd[..., :32], dev(positions), narrow)
+    close(xd, ref, 2e-6, "in place, narrow")
+    assert torch.equal(xd[..., 32:].cpu(), x[..., 32:])
 
 
 @pytest.mark.parametrize("interleaved", [False, True])
@@ -472,47 +480,19 @@ def test_sampling_among_equal_probabilities_goes_by_token_id(ops):
         assert abs(got[i] - want) <= 1 and (k == 0 or got[i] < k), (rows[i], got[i], want)    # a draw on a boundary may round either way
 
 
-@pytest.mark.parametrize("V", [50, 331, 32000])
+@pytest.mark.parametrize("V", [50, 331, 32000, 128256])
 def test_sampling_follows_the_plain_sampler(ops, V):
-    from tests.plain.sampling_plain import sample as plain_sample
-
-    class FixedU:
-        def __init__(self, u): self.u = u
-        def next_f32(self): return np.float32(self.u)
-
-    g = torch.Generator().manual_seed(V)
-    rows = []
-    for temp, k, p in ((0.8, 40, 0.95), (1.0, 0, 1.0), (0.5, 5, 1.0), (1.3, 0, 0.7), (0.0, 40, 0.95),
-                       (0.8, 1, 0.95), (2.0, 100, 0.5), (1.5, 1024, 0.9), (1.5, 1025, 0.9), (1.0, 64, 1.0)):
-        for u in (0.0, 0.123, 0.5, 0.77, 0.999):
-            rows.append((temp, k, p, u))
+    """At 128,256 entries a row's probabilities no longer fit in shared memory: the kernel keeps
+    them in the caller's scratch instead (another branch of it, and the one a Llama-3 vocabulary takes)."""
+    from tests.helpers import sampling_rows, assert_tokens_follow_the_plain_sampler
+    rows = sampling_rows(few=V > 50000)
     R = len(rows)
+    g = torch.Generator().manual_seed(V)
     logits = torch.randn(R, V, generator=g) * 2
     logits[3, 5] = logits[3, 9] = logits[3].max() + 1          # ties among the most likely
     out = torch.zeros(R, dtype=torch.int32, device="cuda")
-    scratch = torch.zeros(R * V, device="cuda")
+    scratch = torch.full((R * V,), float("nan"), device="cuda")   # nothing in it may be read before it is written
     f = lambda i, dt: dev(torch.tensor([r[i] for r in rows], dtype=dt))
     ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32),
                out, scratch)
-    got = out.tolist()
-    from tests.plain.sampling_plain import candidates
-    for i, (temp, k, p, u) in enumerate(rows):
-        want = plain_sample(logits[i].numpy(), temp, k, p, FixedU(u))
-        if got[i] == want:
-            continue
-        # The reference walks the sorted candidates subtracting 32-bit probabilities one by one; the
-        # kernel sums in another order. Over tens of thousands of terms the two running sums differ in
-        # their last bits, and a draw that lands within that rounding of a boundary between two
-        # candidates may fall on either side. Anything further from the boundary is a fault.
-        assert temp > 0
-        cand = candidates(logits[i].numpy(), temp, k, p)
-        ids = [t for t, _ in cand]
-        cum = np.cumsum(np.array([float(pr) for _, pr in cand], dtype=np.float64))
-        point = float(u) * cum[-1]
-        assert got[i] in ids, f"row {i}: token {got[i]} is not among the candidates"
-        j = ids.index(got[i])
-        lo = cum[j - 1] if j else 0.0
-        slack = 16 * np.sqrt(len(cand)) * np.finfo(np.float32).eps * cum[-1]
-        assert lo - slack <= point <= cum[j] + slack, (
-            f"row {i}: temperature {temp}, top_k {k}, top_p {p}, u {u}: token {got[i]} covers "
-            f"[{lo}, {cum[j]}], the draw is {point} (plain sampler: {want})")
+    assert_tokens_follow_the_plain_sampler(rows, logits, out.tolist())

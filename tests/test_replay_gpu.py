@@ -19,7 +19,7 @@ def up64(n):
     return (n + 63) // 64 * 64
 
 
-@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B", "C", "D") for d in ("float32", "bfloat16")],
+@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B", "C", "D", "E", "Ai", "Bh") for d in ("float32", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def run(request):
     name, dtype = request.param
@@ -36,7 +36,7 @@ def test_whole(run):
     for n, seed in ((1, 1), (2, 2), (17, 3), (100, 4)):
         toks = random_tokens(name, n, seed)
         out = tr.step([("w", toks, range(n))], end=["w"])
-        assert_close(out, plain_logits(name, STORE[dtype], toks), dtype, f"whole, {n} tokens")
+        assert_close(out, plain_logits(name, STORE[dtype], toks), dtype, f"whole, {n} tokens", config=name)
 
 
 def test_last_32_tokens_one_by_one(run):
@@ -46,7 +46,7 @@ def test_last_32_tokens_one_by_one(run):
     outs = [tr.step([("d", toks[:78], [77])])]
     for i in range(78, 110):
         outs.append(tr.step([("d", [toks[i]], [0])], end=["d"] if i == 109 else []))
-    assert_close(np.concatenate(outs), ref[77:], dtype, "decode after a prompt")
+    assert_close(np.concatenate(outs), ref[77:], dtype, "decode after a prompt", config=name)
 
 
 def test_first_tokens_and_long_decoding(run):
@@ -58,8 +58,8 @@ def test_first_tokens_and_long_decoding(run):
     for i, t in enumerate(toks):
         outs.append(tr.step([("l", [t], [0])], end=["l"] if i == 99 else []))
     got = np.concatenate(outs)
-    assert_close(got[:4], ref[:4], dtype, "first tokens")
-    assert_close(got, ref, dtype, "long decoding")
+    assert_close(got[:4], ref[:4], dtype, "first tokens", config=name)
+    assert_close(got, ref, dtype, "long decoding", config=name)
 
 
 def test_portions_of_changing_size(run):
@@ -72,7 +72,7 @@ def test_portions_of_changing_size(run):
     for i, c in enumerate(cuts):
         outs.append(tr.step([("p", toks[pos:pos + c], range(c))], end=["p"] if i == len(cuts) - 1 else []))
         pos += c
-    assert_close(np.concatenate(outs), ref, dtype, "portions")
+    assert_close(np.concatenate(outs), ref, dtype, "portions", config=name)
 
 
 def test_mixed_requests_reusing_pages(run):
@@ -109,7 +109,7 @@ def test_mixed_requests_reusing_pages(run):
                 live.remove(i)
     assert most_live == 4
     for i in range(len(lens)):
-        assert_close(np.concatenate(got[i]), refs[i], dtype, f"mixed, request {i}")
+        assert_close(np.concatenate(got[i]), refs[i], dtype, f"mixed, request {i}", config=name)
 
 
 def test_long_prompt_across_key_tiles(run):
@@ -121,7 +121,7 @@ def test_long_prompt_across_key_tiles(run):
     toks = random_tokens(name, 300, 41)
     ref = plain_logits(name, STORE[dtype], toks)
     out = tr.step([("t", toks, range(300))], end=["t"])
-    assert_close(out, ref, dtype, "whole, 300 tokens")
+    assert_close(out, ref, dtype, "whole, 300 tokens", config=name)
     cuts = [127, 1, 2, 126, 33]
     pos, outs = 0, []
     for c in cuts:
@@ -129,7 +129,7 @@ def test_long_prompt_across_key_tiles(run):
         pos += c
     for i in range(pos, 300):
         outs.append(tr.step([("u", [toks[i]], [0])], end=["u"] if i == 299 else []))
-    assert_close(np.concatenate(outs), ref, dtype, "portions across tiles, then decoded")
+    assert_close(np.concatenate(outs), ref, dtype, "portions across tiles, then decoded", config=name)
 
 
 def test_every_way_of_cutting_gives_the_same_logits_in_32_bit(run):
@@ -153,5 +153,5 @@ def test_decode_without_graphs_matches():
     ref = plain_logits(name, STORE[dtype], toks)
     outs = [tr.step([("d", toks[:40], [39])])]
     outs += [tr.step([("d", [t], [0])]) for t in toks[40:]]
-    assert_close(np.concatenate(outs), ref[39:], dtype, "decode, kernel by kernel")
+    assert_close(np.concatenate(outs), ref[39:], dtype, "decode, kernel by kernel", config=name)
     assert tr.close() == 0

@@ -269,3 +269,32 @@ def test_the_next_draw_can_be_looked_at_without_taking_it():
         assert plan.entries[0].u == ahead
     with pytest.raises(host.SchedulerError, match="not running"):
         s.peek_uniform(12345)
+
+
+def test_any_of_several_end_tokens_finishes_a_request():
+    """config.json may list several end-of-sequence ids (current Llama checkpoints list three):
+    each of them ends a request, joins the context and is not emitted
+    (garuda/src/runtime/mod.rs:733-738)."""
+    s, cache = make()
+    s_cfg = host.SchedulerConfig()
+    assert s_cfg.eos_token_id == -1 and s_cfg.eos_token_ids == []
+    s_cfg.eos_token_id = 5
+    assert s_cfg.eos_token_ids == [5]
+    cache = host.CacheManager([host.GroupConfig(64, 0)], 4, 4, 64)
+    c = host.SchedulerConfig()
+    c.max_concurrent, c.queue_capacity, c.max_batch_tokens, c.prefill_chunk = 4, 8, 32, 16
+    c.max_context, c.vocab_size = 64, 100
+    c.eos_token_ids = [90, 91, 92]
+    s = host.Scheduler(c, cache)
+    ids = [s.submit([1, 2, 3], greedy(max_tokens=6)) for _ in range(3)]
+    plan = s.plan()
+    s.complete(plan, [7, 7, 7])
+    plan = s.plan()
+    ev = s.complete(plan, [92, 7, 91])
+    done = {e.id: e.detail for e in ev if e.kind == Done}
+    assert done == {ids[0]: "eos", ids[2]: "eos"}
+    assert [e.token for e in ev if e.kind == Token] == [7]        # the end tokens are not emitted
+    plan = s.plan()
+    ev = s.complete(plan, [90])
+    assert [(e.id, e.detail) for e in ev if e.kind == Done] == [(ids[1], "eos")]
+    assert s.idle() and cache.free_pages(0) == 64
