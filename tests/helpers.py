@@ -62,7 +62,7 @@ def sharpen_for(hidden_size: int) -> dict:
     sum over ``hidden_size`` inputs per channel, so the factor falls with the root of the width).
     Much sharper than that and the softmax turns the bfloat16 rounding of a score into a large change
     of the result, which says nothing about the kernels."""
-    f = max(1.0, 64.0 / float(hidden_size) ** 0.5)
+    f = min(8.0, max(1.0, 64.0 / float(hidden_size) ** 0.5))
     return {"q_proj": f, "k_proj": f}
 
 _DIRS = {}
@@ -76,8 +76,7 @@ def model_dir(name: str, store_dtype=torch.float32) -> str:
     if key not in _DIRS:
         cfg, seed, norm_init = TINY[name]
         d = tempfile.mkdtemp(prefix=f"garuda_tiny_{name}_")
-        # the configurations that have been here longest keep their factor of 8 whatever their width
-        scale = SHARPEN if cfg["hidden_size"] <= 128 else sharpen_for(cfg["hidden_size"])
+        scale = sharpen_for(cfg["hidden_size"])
         write_random_model(d, cfg, seed, norm_init=norm_init, store_dtype=store_dtype, scale=scale)
         _DIRS[key] = d
     return _DIRS[key]
