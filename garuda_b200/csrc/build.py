@@ -139,7 +139,7 @@ def attention_lib_name(head_dim: int) -> str:
 
 def _lib_recipe(name: str):
     if name.startswith("garuda_attn_hd"):
-        return ["attention_mma.cu", "attention_tcgen05.cu"], [f"-DGB_HEAD_DIM={int(name[len('garuda_attn_hd'):])}"]
+        return ["attention_mma.cu", "attention_tcgen05.cu", "attention_decode_tma.cu"], [f"-DGB_HEAD_DIM={int(name[len('garuda_attn_hd'):])}"]
     return KERNEL_LIBS[name], []
 
 

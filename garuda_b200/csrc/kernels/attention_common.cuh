@@ -30,4 +30,16 @@ int tile_tc_error_check();
 // Its kernels' failed waits also write their code to this word of pinned host memory (null: none).
 int tile_tc_set_error_sink(int* host_word);
 
+// The decode kernel that brings keys and values in by TMA (attention_decode_tma.cu; head sizes 64 and
+// 128, pages of 8 to 128 keys). `ranks`: CTAs that share one request's keys, as a thread-block cluster
+// (`cluster`) or independently; more than one independent CTA need `decode_tma_scratch_bytes` of
+// scratch whose first 64 KB are zero before the first launch.
+bool decode_tma_takes(const Params& p, long long pages);
+int decode_tma_max_ranks(bool cluster);
+long long decode_tma_scratch_bytes(int R, int kv_heads, int ranks);
+int launch_decode_tma(const Params& p, long long pages, int R, int ranks, bool cluster, void* scratch,
+                      long long scratch_bytes, cudaStream_t stream);
+int decode_tma_error_check();
+int decode_tma_set_error_sink(int* host_word);
+
 }  // namespace attn

@@ -27,6 +27,7 @@
 // Compiled per head size: GB_HEAD_DIM (a multiple of 16, at most 128).
 #include "attention_common.cuh"
 #include "error_word.cuh"
+#include "attention_mma_core.cuh"
 #include "tc_common.cuh"
 
 #ifndef GB_HEAD_DIM
@@ -36,10 +37,10 @@
 namespace {
 
 using namespace tc;
+using namespace attn_mma;
 
 constexpr int HD = GB_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head_dim must be a multiple of 16 up to 128");
-constexpr int KT = 64;              // keys per tile
 constexpr int PAD = 8;              // bf16 of padding per shared-memory row (16 bytes)
 constexpr int LD = HD + PAD;        // shared-memory row length in bf16
 constexpr int THREADS = 128;
@@ -60,35 +61,6 @@ __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool v
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-      "{%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// 2^x on the special-function unit (about 2^-22 relative error; the result feeds a bfloat16 operand
-// and 32-bit sums). -inf gives 0.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // One warp copies NR key rows (keys first_key ..., shared-memory rows first_row ...) of one kv head,
 // keys and values, 16 bytes per copy. Consecutive lanes copy consecutive chunks, so that one
@@ -151,110 +123,6 @@ __device__ __forceinline__ void load_queries(__nv_bfloat16* qs, const Params& p,
   }
 }
 
-// One warp's running state over the keys it has seen: 16 query rows, of which a thread holds the
-// two rows lane / 4 and lane / 4 + 8.
-struct WarpState {
-  float o[HD / 8][4];
-  float m[2], l[2];
-  __device__ __forceinline__ void reset() {
-#pragma unroll
-    for (int n = 0; n < HD / 8; ++n)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
-    m[0] = m[1] = -INFINITY;
-    l[0] = l[1] = 0.f;
-  }
-};
-
-// One tile of 64 keys for one warp's 16 rows: S = Q K^T, scale and mask, running softmax in
-// 32-bit, O += P V. qf: the warp's query fragments; key0: position of the tile's first key;
-// row_pos / row_start: last and first key each of the thread's two rows may read; full: every key
-// of the tile is inside every row's range (no mask needed). The running maximum st.m is kept
-// unscaled (a raw dot product); the merges scale it.
-__device__ __forceinline__ void process_tile(WarpState& st, const uint32_t (&qf)[HD / 16][4],
-                                             const __nv_bfloat16* ks, const __nv_bfloat16* vs, int key0,
-                                             const int (&row_pos)[2], const int (&row_start)[2], float scale_log2,
-                                             bool full) {
-  const int lane = threadIdx.x & 31;
-  float s[8][4];
-#pragma unroll
-  for (int n = 0; n < 8; ++n)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
-#pragma unroll
-  for (int kk = 0; kk < HD / 16; ++kk) {
-#pragma unroll
-    for (int n2 = 0; n2 < 4; ++n2) {
-      uint32_t b[4];
-      const int key = n2 * 16 + (lane % 8) + (lane / 16) * 8;
-      ldmatrix_x4(b, ks + key * LD + kk * 16 + ((lane / 8) % 2) * 8);
-      mma_16816(s[2 * n2], qf[kk], b[0], b[1]);
-      mma_16816(s[2 * n2 + 1], qf[kk], b[2], b[3]);
-    }
-  }
-  // Mask (only where the tile is not wholly inside every row's range), then the running maximum of
-  // the raw dot products: the scale is positive, so it can wait until the exponent, where
-  // exp2(s * scale_log2 - m * scale_log2) is one multiply-add and one special-function op.
-  float m_new[2] = {st.m[0], st.m[1]};
-  if (!full) {
-#pragma unroll
-    for (int n = 0; n < 8; ++n)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const int j = key0 + n * 8 + (lane % 4) * 2 + (e & 1);
-        if (!(j >= row_start[i] && j <= row_pos[i])) s[n][e] = -INFINITY;
-      }
-  }
-#pragma unroll
-  for (int n = 0; n < 8; ++n)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], s[n][e]);
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
-    m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
-  }
-  float corr[2], neg_m[2], l_add[2] = {0.f, 0.f};
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const float m_use = m_new[i] == -INFINITY ? 0.f : m_new[i];     // nothing valid yet: avoid inf - inf
-    corr[i] = st.m[i] == -INFINITY ? 0.f : fast_exp2((st.m[i] - m_use) * scale_log2);
-    neg_m[i] = -m_use * scale_log2;
-    st.m[i] = m_new[i];
-  }
-  uint32_t pf[4][4];
-#pragma unroll
-  for (int n = 0; n < 8; ++n) {
-    float pr[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      pr[e] = fast_exp2(fmaf(s[n][e], scale_log2, neg_m[e >> 1]));   // exp2(-inf) = 0 for masked keys
-      l_add[e >> 1] += pr[e];
-    }
-    pf[n / 2][(n % 2) * 2 + 0] = pack_bf16(pr[0], pr[1]);
-    pf[n / 2][(n % 2) * 2 + 1] = pack_bf16(pr[2], pr[3]);
-  }
-#pragma unroll
-  for (int i = 0; i < 2; ++i) st.l[i] = st.l[i] * corr[i] + l_add[i];
-#pragma unroll
-  for (int n = 0; n < HD / 8; ++n) {
-    st.o[n][0] *= corr[0]; st.o[n][1] *= corr[0];
-    st.o[n][2] *= corr[1]; st.o[n][3] *= corr[1];
-  }
-#pragma unroll
-  for (int kk = 0; kk < 4; ++kk) {
-#pragma unroll
-    for (int n2 = 0; n2 < HD / 16; ++n2) {
-      uint32_t b[4];
-      const int key = kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8;
-      ldmatrix_x4_trans(b, vs + key * LD + n2 * 16 + (lane / 16) * 8);
-      mma_16816(st.o[2 * n2], pf[kk], b[0], b[1]);
-      mma_16816(st.o[2 * n2 + 1], pf[kk], b[2], b[3]);
-    }
-  }
-}
-
 // ------------------------------------------------------------------ TILE (prompt portions)
 __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 1)
 attention_tile_kernel(const Params p) {
@@ -290,7 +158,7 @@ attention_tile_kernel(const Params p) {
     row_pos[i] = row < nrows ? pos0 + row / p.g : -1;      // no key is valid for a padding row
     row_start[i] = (row < nrows && p.window > 0) ? max(0, row_pos[i] + 1 - p.window) : 0;
   }
-  WarpState st;
+  WarpState<HD> st;
   st.reset();
   uint32_t qf[HD / 16][4];
   for (int tile = tile_begin; tile < tile_end; ++tile) {
@@ -312,7 +180,7 @@ attention_tile_kernel(const Params p) {
     // a tile needs no mask if it lies wholly before the first row's position and inside the last
     // row's window
     const bool full = (tile + 1) * KT - 1 <= pos0 && (p.window <= 0 || tile * KT >= hi + 1 - p.window);
-    process_tile(st, qf, ks, vs, tile * KT, row_pos, row_start, p.scale_log2, full);
+    process_tile<HD>(st, qf, PaddedTile<HD, LD>{ks}, PaddedTile<HD, LD>{vs}, tile * KT, row_pos, row_start, p.scale_log2, full);
     __syncthreads();  // the stage may be overwritten by the next iteration's loads
   }
   cp_async_wait<0>();
@@ -409,13 +277,13 @@ attention_decode_kernel(const Params p, const int stages) {
       qf[kk][e] = row < nrows ? *reinterpret_cast<const uint32_t*>(src + kk * 16) : 0u;
   }
 
-  WarpState st;
+  WarpState<HD> st;
   st.reset();
   for (int i = 0; i < mine_n; ++i) {
     if (stages == 1) cp_async_wait<0>(); else cp_async_wait<1>();
     __syncwarp();
     const __nv_bfloat16* ks = ring + (size_t)(i % stages) * 2 * KT * LD;
-    process_tile(st, qf, ks, ks + KT * LD, (tile_begin + warp + 4 * i) * KT, row_pos, row_start, p.scale_log2, false);
+    process_tile<HD>(st, qf, PaddedTile<HD, LD>{ks}, PaddedTile<HD, LD>{ks + KT * LD}, (tile_begin + warp + 4 * i) * KT, row_pos, row_start, p.scale_log2, false);
     __syncwarp();             // every lane is done with the slot before it is filled again
     issue(i + stages);
   }
@@ -510,21 +378,30 @@ GB_DEFINE_LAST_ERROR()
 
 GB_EXPORT int gb_attention_mma_head_dim() { return HD; }
 
-// How often prompt portions went to the tcgen05 kernel (for tests and launch counts).
-static long long g_tc_tile_launches = 0;
+// Scratch that gb_attention_mma wants for `splits` CTAs per decode request (0: none).
+GB_EXPORT long long gb_attention_scratch_bytes(int R, int kv_heads, int splits) {
+  return attn::decode_tma_scratch_bytes(R, kv_heads, splits);
+}
+
+// How often prompt portions went to the tcgen05 kernel, and decode requests to the kernel that copies
+// pages by TMA (for tests and launch counts).
+static long long g_tc_tile_launches = 0, g_decode_tma_launches = 0;
 GB_EXPORT long long gb_attention_tc_tile_launches() { return g_tc_tile_launches; }
+GB_EXPORT long long gb_attention_decode_tma_launches() { return g_decode_tma_launches; }
 
 // Non-zero if a decode CTA gave up waiting for its cluster since the last call; clears it.
 GB_EXPORT int gb_attention_error_check() {
   const int tc = attn::tile_tc_error_check();
+  const int tma = attn::decode_tma_error_check();
   const int own = gb_err::fetch_and_clear();
-  return tc != 0 ? tc : own;
+  return tc != 0 ? tc : (tma != 0 ? tma : own);
 }
 
 // A word of pinned host memory that a kernel's failed wait also writes its code to (null: none).
 GB_EXPORT int gb_attention_set_error_sink(int* host_word) {
   const int a = gb_err::set_sink(host_word), b = attn::tile_tc_set_error_sink(host_word);
-  return a != 0 ? a : b;
+  const int c = attn::decode_tma_set_error_sink(host_word);
+  return a != 0 ? a : (b != 0 ? b : c);
 }
 
 // q [T, Hq, HD], pools [pages, Hkv, page_size, HD], out [T, Hq*HD], all bfloat16.
@@ -532,18 +409,23 @@ GB_EXPORT int gb_attention_set_error_sink(int* host_word) {
 // per warp of the decode kernel (2: the next tile is fetched while one is computed; clamped to what
 // shared memory holds for this head size).
 // max_q_len and min_q_len (over the batch's requests) decide which kernels are launched; num_pages:
-// pages in each pool.
+// pages in each pool. cluster_merge: for the decode kernel that copies by TMA, whether the CTAs that share
+// a request are a thread-block cluster (no scratch) or independent. scratch: work space for the decode kernel that copies by TMA when several CTAs
+// share a request (gb_attention_scratch_bytes of it; its first 64 KB zero before the first call, and
+// the same memory from call to call, or zeroed again); may be null.
 GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                const int32_t* block_table, int table_width, const int32_t* cu_q,
                                const int32_t* kv_lens, int T, int R, int Hq, int Hkv, float scale, int window,
                                int page_size, int max_q_len, int min_q_len, int num_splits, int stages,
-                               long long num_pages, cudaStream_t stream) {
+                               long long num_pages, int cluster_merge, void* scratch, long long scratch_bytes,
+                               cudaStream_t stream) {
   if (T <= 0 || R <= 0) return GB_OK;
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "attention: %d query heads for %d kv heads", Hq, Hkv);
   const int g = Hq / Hkv;
   if (g > ROWS_TILE) return gb::fail(GB_UNSUPPORTED, "attention_mma: a group of %d query heads per kv head", g);
   // the running maximum is taken before the scale is applied, which needs the scale to be positive
   if (!(scale > 0.f)) return gb::fail(GB_UNSUPPORTED, "attention_mma: scale %g is not positive", (double)scale);
+  const int tma_splits = num_splits;
   num_splits = num_splits < 1 ? 1 : (num_splits > MAX_CLUSTER ? MAX_CLUSTER : num_splits);
   Params p;
   p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
@@ -561,7 +443,11 @@ GB_EXPORT int gb_attention_mma(const void* q, const void* k_pool, const void* v_
     configured.done();
   }
   // DECODE requests (a decode token's group, or a very short portion), if the batch can hold any
-  if (min_q_len * g <= ROWS_DECODE) {
+  if (min_q_len * g <= ROWS_DECODE && attn::decode_tma_takes(p, num_pages)) {
+    int rc = attn::launch_decode_tma(p, num_pages, R, tma_splits, cluster_merge != 0, scratch, scratch_bytes, stream);
+    if (rc) return rc;
+    ++g_decode_tma_launches;
+  } else if (min_q_len * g <= ROWS_DECODE) {
     stages = stages < 1 ? 1 : (stages > MAX_STAGES ? MAX_STAGES : stages);
     int rc = gb::check_pdl_launch(gb::launch_pdl(attention_decode_kernel, dim3(num_splits, Hkv, R), dim3(THREADS),
                                                  smem_decode(num_splits, stages), stream, dim3(num_splits, 1, 1), p,

@@ -85,7 +85,26 @@ struct EpilogueArgs {
   const float* weight;           // [features]
   float* sums_out;               // [tiles of 128 features, sums_ld]
   int sums_ld;                   // tokens
+  // The weights that the kernel after this one will stream (or null): while this kernel waits out its
+  // chain of latencies (activations, products, reduction, epilogue) the memory system is idle, so its
+  // CTAs ask for those weights to be brought into L2 meanwhile, each a slice.
+  const uint8_t* next_stream;
+  long long next_bytes;
 };
+
+// This CTA's slice of `bytes` at `base` into L2 (cta of ctas; 16-byte granules), by one thread.
+__device__ __forceinline__ void prefetch_slice_l2(const uint8_t* base, long long bytes, int cta, int ctas) {
+  if (base == nullptr || bytes <= 0) return;
+  const long long granules = bytes >> 4;
+  const long long per = (granules + ctas - 1) / ctas;
+  long long begin = per * cta, end = begin + per;
+  if (end > granules) end = granules;
+  constexpr long long CHUNK = 4096;        // granules per instruction: 64 KB
+  for (long long g = begin; g < end; g += CHUNK) {
+    const uint32_t size = (uint32_t)(((end - g) < CHUNK ? (end - g) : CHUNK) << 4);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + (g << 4)), "r"(size) : "memory");
+  }
+}
 
 // Where feature `head`, channel d of the token at `pos` (request row `req`) is stored; null if the
 // position has no page.
@@ -280,6 +299,10 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         tma_load_2d(base + G::NUM_M * G::A_BYTES, &map_n, bar, k0, n0);
         issued = it + 1;
       }
+      // everything of this CTA's own stream has been asked for: now the next kernel's weights
+      prefetch_slice_l2(ra.next_stream, ra.next_bytes,
+                        (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)),
+                        (int)(gridDim.x * gridDim.y * gridDim.z));
       if (*(volatile int*)&abort_s) {
         // wind down: let the copies already in flight land before the CTA's shared memory is given up
         for (int it = issued > stages ? issued - stages : 0; it < issued; ++it) {
@@ -1451,12 +1474,31 @@ struct GbNormFold {
 };
 
 namespace {
+thread_local const void* g_next_stream = nullptr;
+thread_local long long g_next_bytes = 0;
+// the hint is for one launch: taken and cleared
+void take_next_stream(EpilogueArgs& ra) {
+  ra.next_stream = (const uint8_t*)g_next_stream;
+  ra.next_bytes = g_next_bytes;
+  g_next_stream = nullptr;
+  g_next_bytes = 0;
+}
 void fold_norm(EpilogueArgs& ra, const GbNormFold* n) {
   if (n == nullptr) return;
   ra.sums_in = n->sums_in; ra.tiles_in = n->tiles_in; ra.eps = n->eps; ra.inv_width = n->inv_width;
   ra.h_out = (__nv_bfloat16*)n->h_out; ra.weight = n->weight; ra.sums_out = n->sums_out; ra.sums_ld = n->sums_ld;
 }
 }  // namespace
+
+// A hint for the calling thread's next product: the weights (16-byte aligned) that the kernel after
+// it will stream, which its CTAs then ask to be brought into L2 while they wait out their own
+// latencies. Only the few-token kernels act on it. Null or 0 bytes: no hint.
+GB_EXPORT int gb_tc_hint_next_stream(const void* weights, long long bytes) {
+  if (((uintptr_t)weights & 15) != 0) return gb::fail(GB_BAD_ARGUMENT, "the hinted weights are not 16-byte aligned");
+  g_next_stream = bytes > 0 ? weights : nullptr;
+  g_next_bytes = bytes > 0 ? bytes : 0;
+  return GB_OK;
+}
 
 // Rows of sums_out that a product of Mx tokens and Nw output features writes when a norm is folded
 // in behind it; 0: this shape does not fold norms.
@@ -1487,6 +1529,7 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   const int weight_rows = epi == EPI_SWIGLU ? 128 * ((Nw + 63) / 64) : Nw;
   EpilogueArgs ra{};
   fold_norm(ra, norm);
+  take_next_stream(ra);
   if (ra.h_out != nullptr && epi != EPI_ACCUMULATE)
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: a norm is folded in behind accumulating products only (epilogue %d)", epi);
   CUtensorMap mm, mn;
@@ -1540,6 +1583,7 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc_qkv: kv heads given without a cache to store them in");
   EpilogueArgs ra{};
   fold_norm(ra, norm);
+  take_next_stream(ra);
   if (ra.h_out != nullptr)
     return gb::fail(GB_UNSUPPORTED, "gemm_tc_qkv: no norm can be folded in behind this product");
   ra.q_out = (__nv_bfloat16*)q_out; ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool;

@@ -119,9 +119,16 @@ class DecodeGraphs:
         ws = Workspace(r.device)
         ctx = StepContext(batch=batch, ws=ws, ops=r.ops, dtype=r.dtype)
         caches = r.cache.layer_caches(batch.block_tables)
-        # once outside the capture: tables and scratch that are made on first use
+        # once outside the capture: tables and scratch that are made on first use. The kernel set notes
+        # meanwhile which weights the step streams, in order, and tells every product of the captured
+        # run what comes behind it.
+        tc = getattr(r.ops, "tc", None)
+        if tc is not None:
+            tc.record_streams()
         r.model.forward(ctx, caches)
         torch.cuda.synchronize(r.device)
+        if tc is not None:
+            tc.hint_streams()
         graph = torch.cuda.CUDAGraph()
         before = getattr(r.ops, "launches", 0)
         # a context of its own: what the run above made "once per step" (the rotation's table) must be
@@ -138,6 +145,8 @@ class DecodeGraphs:
         finally:
             if collecting:
                 gc.enable()
+            if tc is not None:
+                tc.forget_streams()
         cap.launches = getattr(r.ops, "launches", 0) - before      # kernels one replay runs
         if hasattr(r.ops, "launches"):
             r.ops.launches = before

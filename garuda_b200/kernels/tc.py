@@ -48,7 +48,15 @@ class TensorCoreKernels:
         L.gb_gemm_tc_qkv.argtypes = ([c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 6 + [c_int] * 4 + [c_void_p]
                                      + [c_int, c_int, ctypes.POINTER(NormFold), c_void_p])
         L.gb_gemm_tc_qkv.restype = c_int
+        L.gb_tc_hint_next_stream.argtypes = [c_void_p, ctypes.c_longlong]
+        L.gb_tc_hint_next_stream.restype = c_int
         self._attn = {}
+        # The weights that the products of a step stream, in launch order: recorded during one run
+        # (``record_streams``) and replayed as hints during the next (``hint_streams``), so that every
+        # few-token product asks for the weights of the product behind it to be brought into L2 while
+        # it waits out its own latencies. Used when a decode step is captured into a graph.
+        self._recording = None
+        self._plan, self._plan_at = None, 0
 
     def check_errors(self) -> None:
         """Synchronises, and raises if a kernel gave up on a wait since the last check."""
@@ -81,10 +89,37 @@ class TensorCoreKernels:
         return NormFold(sums_in=pending.sums.data_ptr(), tiles_in=pending.sums.shape[0], eps=pending.eps,
                         inv_width=1.0 / pending.values.shape[1], sums_ld=pending.sums.shape[1])
 
+    # ------------------------------------------------------------------ hints of the stream to come
+    HINT_LIMIT = 48 << 20        # no more than L2 can keep beside what is in use
+
+    def record_streams(self):
+        """Start noting which weights the step's products stream, in order."""
+        self._recording, self._plan = [], None
+
+    def hint_streams(self):
+        """The products of the next run of the same step are told what comes behind them."""
+        self._plan, self._plan_at, self._recording = self._recording, 0, None
+
+    def forget_streams(self):
+        self._plan = self._recording = None
+
+    def _stream(self, w):
+        """Called once per product, before its launch."""
+        if self._recording is not None:
+            self._recording.append((w.data_ptr(), w.numel() * w.element_size()))
+        elif self._plan is not None:
+            i, self._plan_at = self._plan_at, self._plan_at + 1
+            if i < len(self._plan) and self._plan[i][0] == w.data_ptr() and i + 1 < len(self._plan):
+                ptr, nbytes = self._plan[i + 1]
+                self.lib.gb_tc_hint_next_stream(ptr, min(nbytes, self.HINT_LIMIT) & ~15)
+            elif i >= len(self._plan) or self._plan[i][0] != w.data_ptr():
+                self._plan = None          # another step than the one that was recorded
+
     def _gemm(self, x, w, out, n_out, epi, fold=None) -> bool:
         M, K = x.shape
         if not self.lib.gb_gemm_tc_supported(x.data_ptr(), w.data_ptr(), M, n_out, K):
             return False
+        self._stream(w)
         tag = 0 if out.dtype == torch.float32 else 1
         code = self.lib.gb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, n_out, K, tag, epi,
                                    None if fold is None else ctypes.byref(fold), self.ops._stream())
@@ -116,6 +151,7 @@ class TensorCoreKernels:
         (no rotation). ``pending``: the ``PendingNorm`` whose values ``h`` is."""
         M, K = h.shape
         fold = self._consume(pending)
+        self._stream(w_qkv)
         code = self.lib.gb_gemm_tc_qkv(
             h.data_ptr(), w_qkv.data_ptr(), M, K, q_out.data_ptr(),
             None if k_pool is None else k_pool.data_ptr(), None if v_pool is None else v_pool.data_ptr(),
@@ -141,7 +177,9 @@ class TensorCoreKernels:
             lib = load_kernel_lib(attention_lib_name(head_dim))
             lib.gb_last_error.restype = ctypes.c_char_p
             lib.gb_attention_mma.argtypes = ([c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 4 + [c_float]
-                                             + [c_int] * 6 + [ctypes.c_longlong, c_void_p])
+                                             + [c_int] * 6 + [ctypes.c_longlong, c_int, c_void_p, ctypes.c_longlong, c_void_p])
+            lib.gb_attention_scratch_bytes.argtypes = [c_int, c_int, c_int]
+            lib.gb_attention_scratch_bytes.restype = ctypes.c_longlong
             lib.gb_attention_mma.restype = c_int
             lib.gb_attention_error_check.restype = c_int
             lib.gb_attention_set_error_sink.argtypes = [c_void_p]
@@ -151,21 +189,40 @@ class TensorCoreKernels:
         return lib
 
     @staticmethod
-    def attention_plan(num_requests: int, kv_heads: int, max_kv_len: int):
-        """(CTAs that share one decode request's keys, slots per warp), from timings
-        at 1 to 64 requests: about two CTAs per SM; no warp without a tile where
-        that can be avoided; clusters above four only while the whole grid stays
-        under 64 CTAs (larger clusters are placed late and merge longer); a second
-        slot per warp, so that the next tile is fetched while one is computed, only
-        while every CTA has an SM to itself (two slots take most of its shared
-        memory)."""
-        tiles = max((max_kv_len + 63) // 64, 1)
+    def attention_plan(num_requests: int, kv_heads: int, max_kv_len: int, head_dim: int = 0):
+        """(CTAs that share one decode request's keys, slots per warp of the kernel with per-thread
+        copies, whether those CTAs are a thread-block cluster), from timings at 1 to 64 requests and
+        contexts of 512 to 8,192.
+
+        The kernel that copies pages by TMA (head sizes 64 and 128). A few requests: a cluster per
+        (request, kv head), as many CTAs as the SMs take one each, every CTA with at least 8 tiles
+        of 32 keys, clusters above four only while the whole grid stays within 64 CTAs (larger ones
+        are placed late). When that would leave clusters of under four (many requests, or many kv
+        heads): independent CTAs that merge through scratch memory, about 256 in all, each with at
+        least 16 tiles, at most 16 per request.
+
+        The kernel with per-thread copies (other head sizes; clusters): about two CTAs per SM; no warp
+        without a tile where that can be avoided; clusters above four only while the whole grid stays
+        under 64 CTAs; a second slot per warp, so that the next tile is fetched while one is computed,
+        only while every CTA has an SM to itself."""
         pairs = max(num_requests * kv_heads, 1)
+        if head_dim in (64, 128):
+            tiles = max((max_kv_len + 31) // 32, 1)
+            c = min(148 // pairs, tiles // 8, 8 if head_dim == 64 else 4)
+            if c > 4 and pairs * c > 64:
+                c = 4
+            independent = max(1, min(256 // pairs, tiles // 16, 16))
+            # clusters, unless they would be under four CTAs or independent CTAs would put twice as many
+            # SMs to work (one request with a context of thousands of keys and heads of 128)
+            if c >= 4 and independent < 2 * c:
+                return c, 1, True
+            return independent, 1, False
+        tiles = max((max_kv_len + 63) // 64, 1)
         splits = max(1, min(2 * 148 // pairs, -(-tiles // 4), 8))
         if splits > 4 and pairs * 4 >= 64:
             splits = 4
         stages = 2 if tiles > 4 * splits and pairs * splits <= 148 else 1
-        return splits, stages
+        return splits, stages, True
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale,
                         window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1) -> bool:
@@ -176,11 +233,18 @@ class TensorCoreKernels:
         lib = self._attention_lib(hd)
         g = Hq // Hkv
         has_decode = min_q_len * g <= 16
-        splits, stages = self.attention_plan(num_requests, Hkv, max_kv_len) if has_decode else (1, 1)
+        splits, stages, cluster = self.attention_plan(num_requests, Hkv, max_kv_len, hd) if has_decode else (1, 1, True)
+        # work space for the partial results of CTAs that share a request's keys; zeroed when it is made
+        # (its counters), and every launch leaves the counters at zero
+        need = int(lib.gb_attention_scratch_bytes(num_requests, Hkv, splits)) if has_decode and not cluster else 0
+        scratch = None
+        if need:
+            scratch = (ws if ws is not None else self.ops.private_ws).get("attention_partials", (need,), torch.uint8, zero=True)
         code = lib.gb_attention_mma(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), T, num_requests, Hq, Hkv, float(scale),
             int(window), int(page_size), int(max_q_len), int(min_q_len), int(splits), int(stages),
-            int(k_pool.shape[0]), self.ops._stream())
+            int(k_pool.shape[0]), int(cluster), None if scratch is None else scratch.data_ptr(), need,
+            self.ops._stream())
         self.ops._check(lib, code, "attention_mma", (1 if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
         return True

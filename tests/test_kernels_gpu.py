@@ -371,6 +371,80 @@ def test_attention_tcgen05_prompt_portions(ops, Hq, Hkv, hd, page, reqs, window)
     close(out, ref, 1e-2, "tcgen05 attention")
 
 
+DECODE_TMA_CASES = [
+    # Hq, Hkv, hd, page, [(keys, new tokens)], window
+    (32, 4, 64, 32, [(2048, 1), (1, 1), (64, 1), (65, 1), (700, 2), (1333, 1)], 0),     # groups of 8; tile edges; two tokens
+    (32, 4, 64, 16, [(900, 1), (130, 1), (511, 1)], 200),                               # a window; pages of 16
+    (8, 8, 64, 8, [(300, 1), (77, 3), (1000, 1)], 0),                                   # no groups; pages of 8
+    (32, 32, 128, 32, [(1500, 1), (200, 1)], 0),                                        # heads of 128, each with its own kv head
+    (32, 8, 128, 64, [(4000, 1), (129, 2), (640, 1)], 0),                               # heads of 128 in groups of 4; pages of 64
+    (16, 4, 128, 16, [(777, 1), (33, 4)], 96),                                          # heads of 128, a window
+]
+
+
+@pytest.mark.parametrize("ranks,cluster", [(1, 0), (2, 0), (3, 0), (4, 0), (8, 0), (16, 0), (2, 1), (3, 1), (4, 1), (8, 1)])
+@pytest.mark.parametrize("Hq,Hkv,hd,page,reqs,window", DECODE_TMA_CASES)
+def test_attention_decode_with_tma_page_copies(ops, Hq, Hkv, hd, page, reqs, window, ranks, cluster):
+    """The decode kernel that fetches pages by TMA, with every way of splitting a request's keys
+    over several CTAs, independent ones that merge through scratch memory and thread-block clusters
+    that merge through shared memory. Every cache slot that no query may read holds NaN (beyond a
+    request's length, another request's page, before a window's start), pages that a window has
+    passed are given back (-1 in the block table), and the table's tail is -1 as well."""
+    q, k, v, bt, cu, kvl, treq, ref = _attention_case(Hq, Hkv, hd, page, reqs, window, torch.bfloat16, seed=ranks + 20 * cluster)
+    used = torch.zeros(k.shape[0], page, dtype=torch.bool)
+    bt = bt.clone()
+    for i, (kv, ql) in enumerate(reqs):
+        first = max(0, kv - ql + 1 - window) if window else 0          # the first key that the first new token reads
+        for j in range(first, kv):
+            used[int(bt[i, j // page]), j % page] = True
+        bt[i, :first // page] = -1                                      # pages wholly before it were given back
+    k = k.clone(); v = v.clone()
+    k.transpose(1, 2)[~used] = float("nan")
+    v.transpose(1, 2)[~used] = float("nan")
+    lib = ops.tc._attention_lib(hd)
+    T = q.shape[0]
+    out = torch.full(ref.shape, float("nan"), dtype=torch.bfloat16, device="cuda")
+    qd, kd, vd, btd, cud, kvd = dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl)
+    if cluster and ranks > (8 if hd == 64 else 4):
+        pytest.skip("more CTAs than a cluster of this head size holds")
+    need = 0 if cluster else lib.gb_attention_scratch_bytes(len(reqs), Hkv, ranks)
+    assert (need == 0) == (ranks == 1 or cluster == 1)
+    scratch = torch.zeros(max(need, 16), dtype=torch.uint8, device="cuda")
+    for again in range(2):      # a second launch finds the counters as the first one left them
+        out.fill_(float("nan"))
+        rc = lib.gb_attention_mma(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), btd.data_ptr(), bt.shape[1],
+                                  cud.data_ptr(), kvd.data_ptr(), T, len(reqs), Hq, Hkv, hd ** -0.5, window, page,
+                                  max(x for _, x in reqs), min(x for _, x in reqs), ranks, 1, k.shape[0], cluster,
+                                  scratch.data_ptr(), need, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, lib.gb_last_error().decode()
+        torch.cuda.synchronize()
+        assert int(scratch[:65536].view(torch.int32).abs().sum()) == 0 or need == 0
+    ops.tc.check_errors()
+    lib.gb_attention_decode_tma_launches.restype = ctypes.c_longlong
+    assert lib.gb_attention_decode_tma_launches() > 0, "the TMA kernel did not take the shape"
+    close(out, ref, 1e-2, f"decode attention by TMA, {ranks} CTAs per request")
+    assert lib.gb_attention_scratch_bytes(len(reqs), Hkv, 1) == 0
+
+
+def test_attention_decode_with_tma_far_key(ops):
+    """One early key stands out among two thousand: whichever CTA and warp of the cluster holds its
+    tile, its weight must survive both merges."""
+    Hq, Hkv, hd, page = 32, 4, 64, 32
+    for far in (3, 700, 2046):
+        q, k, v, bt, cu, kvl, treq, _ = _attention_case(Hq, Hkv, hd, page, [(2047, 1), (500, 1)], 0, torch.bfloat16, seed=far)
+        head = 13                                            # reads kv head 1
+        pg = int(bt[0, far // page])
+        k[pg, 1, far % page] = (q[0, head].float() * 4).bfloat16()
+        v[pg, 1, far % page] = 50.0
+        ref = torch.zeros(2, Hq * hd)
+        cpu.paged_attention(q.float(), k.float(), v.float(), bt, cu, kvl, treq, ref, hd ** -0.5, 0, page, 2, 0, 0)
+        assert ref[0, head * hd:(head + 1) * hd].mean() > 40
+        out = torch.zeros(ref.shape, dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5, 0, page, 2,
+                            1, 2047, min_q_len=1)
+        close(out, ref, 1e-2, f"far key at {far}, decode by TMA")
+
+
 def test_attention_tcgen05_far_key(ops):
     """One early key stands out for one late query row of a long portion."""
     Hq, Hkv, hd, page = 8, 2, 64, 32
