@@ -100,6 +100,30 @@ def test_tensor_core_product(ops, M, N, K):
     ops.tc.check_errors()
 
 
+@pytest.mark.parametrize("M", [1, 5, 16, 33, 64, 100, 256])
+@pytest.mark.parametrize("N,K", [(2048, 2048), (2560, 2048), (2048, 5632), (640, 4096)])
+def test_few_token_products_at_layer_sizes_give_the_same_bits_every_time(ops, M, N, K):
+    """Layer-sized shapes, so that clusters of several CTAs split K (the leading CTA adds up the partial
+    sums in rank order); twice in a row, which must give the same bits."""
+    g = torch.Generator().manual_seed(M + N + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    ref = a.float() @ w.float().t()
+    base = torch.randn(M, N, generator=g)
+    outs = []
+    for again in range(2):
+        out = torch.full((M, N), 5.0, dtype=torch.float32, device="cuda")
+        assert ops.tc.linear(dev(a), dev(w), out, False)
+        acc = dev(base.clone())
+        assert ops.tc.linear(dev(a), dev(w), acc, True)
+        torch.cuda.synchronize()
+        outs.append((out.cpu(), acc.cpu()))
+    close(outs[0][0], ref, 2e-5, "store")
+    close(outs[0][1], base + ref, 2e-5, "accumulate")
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    ops.tc.check_errors()
+
+
 @pytest.mark.parametrize("M", [1, 9, 33, 64, 100, 257])
 @pytest.mark.parametrize("F,K", [(176, 64), (200, 72), (1000, 256)])
 def test_tensor_core_gate_up(ops, M, F, K):
