@@ -36,15 +36,14 @@
 // Rows outside a matrix are zero-filled by TMA and masked in the epilogue; K
 // need not be a multiple of 64 (the tail is zero-filled) but must be a multiple
 // of 8, because a TMA row pitch is a multiple of 16 bytes.
-#include <mutex>
-#include <unordered_map>
-
 #include "error_word.cuh"
 #include "tc_common.cuh"
+#include "tc_host.cuh"
 
 namespace {
 
 using namespace tc;
+using namespace tc_host;
 
 constexpr int BM = 128;   // MMA rows per CTA
 constexpr int BK = 64;    // bf16 per 128-byte swizzled row
@@ -1193,77 +1192,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return (EncodeTiledFn)p;
-  }();
-  return fn;
-}
-
-struct MapKey {
-  const void* ptr;
-  long long rows, cols;
-  int box_rows;
-  bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
-  }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^
-           (std::hash<long long>()(k.cols) * 131) ^ (size_t)k.box_rows * 7919;
-  }
-};
-
-// A [rows, cols] bf16 row-major matrix seen through boxes of box_rows x 64, 128-byte swizzle.
-int tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
-  static std::mutex mu;
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  MapKey key{ptr, rows, cols, box_rows};
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = cache.find(key);
-  if (it != cache.end()) {
-    *out = it->second;
-    return GB_OK;
-  }
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return gb::fail(GB_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUtensorMap m;
-  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return gb::fail(GB_CUDA_ERROR, "cuTensorMapEncodeTiled failed with code %d for a %lld x %lld matrix", (int)r,
-                    rows, cols);
-  if (cache.size() > 4096) cache.clear();
-  cache.emplace(key, m);
-  *out = m;
-  return GB_OK;
-}
-
-int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v;
-  }();
-  return n;
-}
-
 // How many CTAs of a cluster share K. Measured on B200 (2048- to 5632-wide layers, 8 tokens): a CTA
 // costs about 3.5 us before and after its stream of K blocks and streams one 16 KB block in about
 // 0.26 us, so the fixed part weighs as much as 13 blocks; two CTAs on one SM halve each other's rate,
