@@ -112,7 +112,10 @@ def random_tokens(name: str, n: int, seed: int):
 # products and the cache are rounded to 8 bits of mantissa; how much of that reaches the logits
 # depends on depth and widths). A configuration without an entry takes the widest.
 TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
-TOL_BF16 = {}
+# observed on a B200 (GARUDA_B200_RECORD_ERRORS, see tests/conftest.py), times three, at most the widest:
+# A 0.0053, Ai 0.0064, B 0.0062, Bh 0.0057, C 0.0090, D 0.0092, E 0.0069, toy 0.0083; two layers at the
+# TinyLlama, Llama-2-7B and Llama-3-8B widths 0.0147, 0.0137, 0.0115 (32-bit: at most 2.4e-6 and 7.9e-6)
+TOL_BF16 = {"A": 0.016, "Ai": 0.02, "B": 0.019, "Bh": 0.017, "E": 0.021}
 
 OBSERVED = {}        # (configuration, dtype) -> largest difference seen, as a fraction of the largest logit
 

@@ -10,7 +10,8 @@ import numpy as np
 import pytest
 import torch
 
-from tests.helpers import TINY, ROOT, model_dir, plain_logits, random_tokens, assert_close, folder_weights, TOL
+from tests.helpers import (TINY, ROOT, model_dir, plain_logits, random_tokens, assert_close, folder_weights, TOL,
+                           tolerance)
 from tests.plain import llama_plain
 from tests.plain.cpu_ops import CpuOps
 
@@ -50,7 +51,9 @@ def test_greedy_generation_bfloat16(name):
         logits = llama_plain.forward(cfg, w, list(p) + r.tokens)
         for i, tok in enumerate(r.tokens):
             row = logits[len(p) - 1 + i]
-            assert row[tok] >= row.max() - 2 * TOL["bfloat16"] * np.abs(row).max()
+            # the engine's logit of the token it chose is its largest, and both that logit and the
+            # plain model's are within the configuration's tolerance of each other
+            assert row[tok] >= row.max() - 2 * tolerance("bfloat16", name) * np.abs(row).max()
     e.ops.tc.check_errors()
 
 
