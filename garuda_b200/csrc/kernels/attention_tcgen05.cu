@@ -1,7 +1,8 @@
 // Causal grouped-query attention over the paged cache for prompt portions on the
 // fifth-generation tensor cores: both matrix products of a tile are tcgen05.mma with
 // accumulators in tensor memory, operands arrive by TMA, the softmax runs in 32-bit in
-// registers between them.
+// registers between them, and the probabilities go back into tensor memory, where the second
+// product reads them.
 //
 // garuda/src/llama/mod.rs:793-818: s_j = dot(q, K_j) * scale over keys [start, pos],
 // softmax with the maximum subtracted, sum of p_j V_j; query head h reads kv head h / g;
@@ -13,63 +14,87 @@
 // short ones mix), keeping its tensor memory and barriers; the queries and first keys of the next
 // piece arrive, and its first S products run, while the last tiles of the one before are in the
 // softmax.
-//   warp 0   one lane: TMA. The query tile (a 3-D box [tokens][group][64], two buffers); per key
-//            tile one 4-D box per page for keys and for values, four stages.
-//   warp 1   one lane: S = Q K^T for the tile two ahead into one of two S buffers in tensor memory
-//            (128 columns), then O_tile = P V of the tile whose softmax just ended into one of two O
-//            buffers per group (64 columns each). V is read as it lies in the cache, keys along
-//            the rows (an MN-major operand). This warp is the one the tensor cores wait for, so it
-//            steps counters instead of dividing, advances descriptors made once, and learns the
-//            pieces' lengths 32 at a time from its lanes.
+//   warp 0   TMA. The query tile (3-D boxes [tokens][group][64], two buffers); per key tile one
+//            4-D box per page and block of 64 channels, keys and values in rings of their own
+//            (keys are needed two tiles before their values). The lanes look up the pages of
+//            several tiles in one round trip and issue one page's copies each.
+//   warp 1   one lane: O += P V of the tile whose softmax just ended (P from tensor memory, V as
+//            it lies in the cache, keys along the rows: an MN-major operand), one accumulator per
+//            group for the whole piece; then S = Q K^T for the tile two ahead into the S buffer
+//            that this tile's P has just been read from. This warp is the one the tensor cores
+//            wait for, so it steps counters instead of dividing, advances descriptors made once,
+//            and learns the pieces' lengths 32 at a time from its lanes.
 //   warps 2-9  two groups of 128 threads; a thread owns a query row and its group's 64 keys of
 //            every tile, an attention stream of its own: reads its 64 scores from tensor memory,
-//            masks (only on tiles that touch a row's limits), running maximum, exp2 with the
-//            scale folded in, writes P in bfloat16 into shared memory in the layout the second
-//            product reads (128-byte swizzle), and adds the previous tile's O_tile, rescaled, to
-//            its 64 sums in registers. At the end of a piece the two groups' streams are merged.
-//            They also clear the value rows no query may read (a stray NaN times a zero
-//            probability would spoil a sum).
+//            masks (only on tiles that touch a row's limits), exp2 with the scale folded in
+//            against a reference maximum, writes P in bfloat16 over the first half of the scores
+//            it has read. The reference maximum follows the running maximum only when that has
+//            grown by more than 2^8 for some row of the warp; only then is the accumulator in
+//            tensor memory rescaled (read, multiplied, written back). The result is the same
+//            quotient, and probabilities stay below 2^8. At the end of a piece the two groups'
+//            streams are merged, each group writing half of the channels. The groups also clear
+//            the value rows no query may read (a stray NaN times a zero probability would
+//            spoil a sum), and one of their threads tells the TMA warp which stages the tensor
+//            core has finished with (a commit costs the issuing thread as much as two products).
+// Tensor memory (512 columns): two S buffers of 128 columns (group g's scores, then its
+// probabilities, at g * 64), and one accumulator of `head size` columns per group.
 // Measured on this hardware: a product with fewer than 128 columns costs as much as one with 128
 // (about 70 cycles for M = 128, K = 16), which is why S is one 128-column product for both groups.
 // Every wait is bounded; a wait that runs out sets the error word and the CTA winds down.
 //
-// Built for head size 64 only (one 128-byte swizzled row per key); other head sizes use the
-// mma.sync kernels.
+// Built for head sizes 64 and 128 (one or two 128-byte swizzled rows per key); other head sizes use
+// the mma.sync kernels.
 #include "attention_common.cuh"
 #include "error_word.cuh"
 #include "tc_common.cuh"
-
-#include <mutex>
-#include <unordered_map>
+#include "tc_host.cuh"
 
 #ifndef GB_HEAD_DIM
 #define GB_HEAD_DIM 64
 #endif
 
-#if GB_HEAD_DIM == 64
+#if GB_HEAD_DIM == 64 || GB_HEAD_DIM == 128
 
 namespace {
 
 using namespace tc;
 using attn::Params;
 
-constexpr int HD = 64;
+constexpr int HD = GB_HEAD_DIM;
+constexpr int BLOCKS = HD / 64;     // blocks of 64 channels: one swizzled 128-byte row each
 constexpr int QROWS = 128;          // query rows per CTA
 constexpr int KT = 128;             // keys per tile
 constexpr int GROUPS = 2;           // softmax groups: each walks its own half of every key tile
 constexpr int GK = KT / GROUPS;     // keys per group and tile
-constexpr int STAGES = 4;
-constexpr int ROW_BYTES = HD * 2;   // 128: one swizzled row
-constexpr int Q_BYTES = QROWS * ROW_BYTES;
-constexpr int K_BYTES = KT * ROW_BYTES, V_BYTES = K_BYTES;
-constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
-constexpr int P_BYTES = QROWS * GK * 2;             // one group's probabilities of a tile: [128 rows][128 bytes]
-constexpr int SMEM_BYTES = 1024 + 2 * Q_BYTES + STAGES * STAGE_BYTES + GROUPS * 2 * P_BYTES;
-constexpr int TMEM_COLS = 512;                      // S: 2 buffers x 2 groups x 64 columns; O: 2 groups x 2 buffers x 64
-constexpr int O_COL0 = GROUPS * 2 * GK;
+constexpr int ROW_BYTES = 128;      // one swizzled row: 64 channels
+constexpr int BLOCK_BYTES = 128 * ROW_BYTES;        // 128 rows (queries or keys) of one block of channels
+constexpr int Q_BYTES = BLOCKS * BLOCK_BYTES, K_BYTES = Q_BYTES, V_BYTES = Q_BYTES;
+constexpr int K_STAGES = HD == 64 ? 4 : 2;          // keys live from their S product's issue to its end
+constexpr int V_STAGES = HD == 64 ? 5 : 3;          // values until P V, two tiles later
+constexpr int TILE_BYTES = 2 * Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int S_BUFS = 2;                           // S buffers: the S products run this many tiles ahead
+constexpr int O_COL0 = S_BUFS * KT;                 // behind the S buffers
+// Who tells the TMA warp that a stage of keys is free: with few stages the tensor core itself, as
+// soon as the S product has ended (a commit costs the issuing thread as much as two products);
+// with more, a softmax thread once it has seen the S buffer.
+constexpr bool KEYS_FREED_BY_COMMIT = K_STAGES < S_BUFS + 1;
 constexpr int THREADS = 64 + GROUPS * 128;
-static_assert(GK == 64 && O_COL0 + GROUPS * 2 * HD <= TMEM_COLS, "tensor memory layout");
+constexpr float RESCALE_ABOVE = 8.f;                // in powers of two
+static_assert(GK == 64 && O_COL0 + GROUPS * HD <= TMEM_COLS, "tensor memory layout");
+constexpr int CH = HD / GROUPS;     // channels that a group writes out in the merge
+constexpr int ML_BUFS = HD == 64 ? 2 : 1;   // copies of the groups' maxima and denominators (shared memory is short with head size 128)
 
+// Barriers and the like, behind the tiles in dynamic shared memory.
+struct Misc {
+  uint64_t q_full[2], q_empty[2], k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
+  uint64_t s_ready[S_BUFS], p_ready[S_BUFS], o_ready;
+  uint32_t tmem_base;
+  int abort;
+  float2 ml[ML_BUFS][GROUPS][QROWS];     // the groups' reference maxima and denominators, for the merge
+};
+constexpr int SMEM_BYTES = TILE_BYTES + (int)sizeof(Misc);
+static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA");
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -156,9 +181,6 @@ struct Cursor {
     item = cta_item(++round), ++it, j = 0;
     seek(p);
   }
-  __device__ __forceinline__ void next_tile(const Params& p) {
-    if (++j >= w.n_tiles) next_item(p);
-  }
 };
 
 // The same walk for the warp that issues the matrix products: it needs nothing of an item but its
@@ -215,34 +237,37 @@ __global__ void __launch_bounds__(THREADS, 1)
 attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                          const __grid_constant__ CUtensorMap v_map, const Params p, const int q_tiles,
                          const int total_items) {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_full[2], q_empty[2], kv_full[STAGES], kv_empty[STAGES];
-  __shared__ __align__(8) uint64_t s_ready[2], p_ready[GROUPS][2], o_ready[2];   // s and o: one for both groups (a commit costs the issuer about as much as a product)
-  __shared__ float other_ml[QROWS][2];      // the second group's maximum and denominator, for the merge
-  __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_s;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  Misc& mc = *reinterpret_cast<Misc*>(smem_raw + TILE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_s = tiles;                                      // two query buffers
-  const uint32_t kv_s = tiles + 2 * Q_BYTES;                       // stage s: K at kv_s + s * STAGE_BYTES, V after it
-  const uint32_t p_s = kv_s + STAGES * STAGE_BYTES;                // group g, buffer b at p_s + (2 g + b) * P_BYTES
+  const uint32_t q_s = smem_u32(smem_raw);                         // two query buffers
+  const uint32_t k_s = q_s + 2 * Q_BYTES;                          // key stage s at k_s + s * K_BYTES
+  const uint32_t v_s = k_s + K_STAGES * K_BYTES;                   // value stage s at v_s + s * V_BYTES
+  if ((q_s & 1023u) != 0) {                                        // the swizzle needs it; never seen
+    if (threadIdx.x == 0) gb_err::report(ERR_WAIT_DRAIN);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&q_full[b]), 1);
-      mbar_init(smem_u32(&q_empty[b]), 1);
+      mbar_init(smem_u32(&mc.q_full[b]), 1);
+      mbar_init(smem_u32(&mc.q_empty[b]), 1);
     }
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&kv_full[s]), 1);
-      mbar_init(smem_u32(&kv_empty[s]), 1);
+    for (int b = 0; b < S_BUFS; ++b) {
+      mbar_init(smem_u32(&mc.s_ready[b]), 1);
+      mbar_init(smem_u32(&mc.p_ready[b]), GROUPS * 128);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&s_ready[b]), 1);
-      mbar_init(smem_u32(&o_ready[b]), 1);
-      for (int g = 0; g < GROUPS; ++g) mbar_init(smem_u32(&p_ready[g][b]), 128);
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(smem_u32(&mc.k_full[s]), 1);
+      mbar_init(smem_u32(&mc.k_empty[s]), 1);
     }
-    abort_s = 0;
+    for (int s = 0; s < V_STAGES; ++s) {
+      mbar_init(smem_u32(&mc.v_full[s]), 1);
+      mbar_init(smem_u32(&mc.v_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&mc.o_ready), 1);
+    mc.abort = 0;
     fence_barrier_init();
     fence_proxy_async();
     prefetch_tensormap(&q_map);
@@ -250,79 +275,123 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     prefetch_tensormap(&v_map);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
+    tmem_alloc(smem_u32(&mc.tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t tmem_base = mc.tmem_base;
+  volatile int* abort_s = &mc.abort;
   gb::pdl_launch_dependents();
   gb::pdl_wait();      // queries and this step's keys and values come from the kernel in front
 
   if (warp == 0) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ TMA
-      const int page_shift = __ffs(p.page_size) - 1;         // pages are a power of two of keys
-      const int pages_per_tile = KT >> page_shift;
-      const uint32_t page_bytes = (uint32_t)p.page_size * ROW_BYTES;
-      int gt = 0;               // tiles so far, over all items
-      int stage = 0, par = 1;   // the stage to fill and the phase of its "empty" barrier to wait for
-      Cursor c;
-      for (c.start(p, q_tiles, total_items); !c.done; c.next_item(p)) {
-        const Item& w = c.w;
-        const int qb = c.it & 1;
-        if (c.it >= 2 && !mbar_wait(smem_u32(&q_empty[qb]), ((c.it >> 1) & 1) ^ 1)) {
+    // ------------------------------------------------------------------ TMA
+    // The whole warp: its lanes look up the pages of the next 32 / pages_per_tile tiles in one
+    // round trip (a lookup per tile by one thread, each waited for, was what the kernel's pace
+    // hung on); for a tile, lane g issues the copies of the tile's g-th page; lane 0 waits for
+    // the stages and tells their barriers how many bytes to expect.
+    const int page_shift = __ffs(p.page_size) - 1;         // pages are a power of two of keys
+    const int pages_per_tile = KT >> page_shift;           // 1 to 16
+    const int tiles_per_batch = 32 / pages_per_tile;
+    const uint32_t page_bytes = (uint32_t)p.page_size * ROW_BYTES;     // of one block of channels
+    int gt = 0;                       // tiles so far, over all items
+    int ks = 0, kpar = 1;             // the key stage to fill and the phase of its "empty" barrier to wait for
+    int vs = 0, vpar = 1;             // the same for values
+    bool ok = true;
+    Cursor c;
+    for (c.start(p, q_tiles, total_items); !c.done && ok; c.next_item(p)) {
+      const Item& w = c.w;
+      const int qb = c.it & 1;
+      if (lane == 0) {
+        if (c.it >= 2 && !mbar_wait(smem_u32(&mc.q_empty[qb]), ((c.it >> 1) & 1) ^ 1)) {
           gb_err::report(ERR_WAIT_EMPTY);
-          abort_s = 1;
+          *abort_s = 1;
         }
-        if (*(volatile int*)&abort_s) break;
-        mbar_arrive_expect_tx(smem_u32(&q_full[qb]), Q_BYTES);
-        tma_load_3d(q_s + qb * Q_BYTES, &q_map, smem_u32(&q_full[qb]), 0, w.kvh * p.g, w.q_begin + w.tok0);
-        for (int j = 0; j < w.n_tiles; ++j, ++gt) {
-          const int s = stage;
-          const int key0 = (w.tile_begin + j) * KT;
-          // pages that hold a key some row reads, and exist; looked up before waiting for the
-          // stage, so that the table's latency passes during the wait
-          int pages[16], count = 0;
-          for (int g = 0; g < pages_per_tile; ++g) {
-            const int first = key0 + g * p.page_size;
-            pages[g] = (first <= w.hi && first + p.page_size > w.lo) ? w.table[first >> page_shift] : -1;
-            count += pages[g] >= 0;
-          }
-          if (gt >= STAGES && !mbar_wait(smem_u32(&kv_empty[s]), par)) {
-            gb_err::report(ERR_WAIT_EMPTY);
-            abort_s = 1;
-          }
-          if (*(volatile int*)&abort_s) break;
-          const uint32_t bar = smem_u32(&kv_full[s]);
-          const uint32_t kdst = kv_s + s * STAGE_BYTES, vdst = kdst + K_BYTES;
-          if (count == 0) {
-            mbar_arrive(bar);
-          } else {
-            mbar_arrive_expect_tx(bar, 2u * count * page_bytes);
-            for (int g = 0; g < pages_per_tile; ++g) {
-              if (pages[g] < 0) continue;
-              tma_load_4d(kdst + g * page_bytes, &k_map, bar, 0, 0, w.kvh, pages[g]);
-              tma_load_4d(vdst + g * page_bytes, &v_map, bar, 0, 0, w.kvh, pages[g]);
-            }
-          }
-          if (++stage == STAGES) stage = 0, par ^= 1;
+        if (!*abort_s) {
+          mbar_arrive_expect_tx(smem_u32(&mc.q_full[qb]), Q_BYTES);
+#pragma unroll
+          for (int h = 0; h < BLOCKS; ++h)
+            tma_load_3d(q_s + qb * Q_BYTES + h * BLOCK_BYTES, &q_map, smem_u32(&mc.q_full[qb]), h * 64, w.kvh * p.g,
+                        w.q_begin + w.tok0);
         }
-        if (*(volatile int*)&abort_s) break;
       }
-      if (*(volatile int*)&abort_s) {
-        // wind down: let the copies in flight land before the CTA's shared memory is given up
-        for (int t = gt > STAGES ? gt - STAGES : 0; t < gt; ++t) {
+      int entry = -1;       // this lane's page of the batch: tile lane / pages_per_tile, page lane % pages_per_tile
+      for (int j = 0; j < w.n_tiles && ok; ++j, ++gt) {
+        const int jb = j % tiles_per_batch;
+        if (jb == 0) {
+          // pages that hold a key some row reads, and exist
+          const int first = (w.tile_begin + j) * KT + lane * p.page_size;
+          entry = (first <= w.hi && first + p.page_size > w.lo) ? w.table[first >> page_shift] : -1;
+        }
+        const int page = __shfl_sync(0xffffffffu, entry, (jb * pages_per_tile + lane) & 31);
+        const bool mine = lane < pages_per_tile && page >= 0;
+        const int count = __popc(__ballot_sync(0xffffffffu, mine));
+        // keys first: their product runs two tiles before the values' one
+        if (lane == 0) {
+          if (gt >= K_STAGES && !mbar_wait(smem_u32(&mc.k_empty[ks]), kpar)) {
+            gb_err::report(ERR_WAIT_EMPTY);
+            *abort_s = 1;
+          }
+          if (!*abort_s) {
+            if (count == 0) mbar_arrive(smem_u32(&mc.k_full[ks]));
+            else mbar_arrive_expect_tx(smem_u32(&mc.k_full[ks]), (uint32_t)BLOCKS * count * page_bytes);
+          }
+        }
+        __syncwarp();
+        if (*abort_s) { ok = false; break; }
+        if (mine) {
+#pragma unroll
+          for (int h = 0; h < BLOCKS; ++h)
+            tma_load_4d(k_s + ks * K_BYTES + h * BLOCK_BYTES + lane * page_bytes, &k_map, smem_u32(&mc.k_full[ks]), h * 64, 0,
+                        w.kvh, page);
+        }
+        if (lane == 0) {
+          if (gt >= V_STAGES && !mbar_wait(smem_u32(&mc.v_empty[vs]), vpar)) {
+            gb_err::report(ERR_WAIT_EMPTY);
+            *abort_s = 1;
+          }
+          if (!*abort_s) {
+            if (count == 0) mbar_arrive(smem_u32(&mc.v_full[vs]));
+            else mbar_arrive_expect_tx(smem_u32(&mc.v_full[vs]), (uint32_t)BLOCKS * count * page_bytes);
+          }
+        }
+        __syncwarp();
+        if (*abort_s) {
+          ++gt;       // this tile's keys are in flight
+          ok = false;
+          break;
+        }
+        if (mine) {
+#pragma unroll
+          for (int h = 0; h < BLOCKS; ++h)
+            tma_load_4d(v_s + vs * V_BYTES + h * BLOCK_BYTES + lane * page_bytes, &v_map, smem_u32(&mc.v_full[vs]), h * 64, 0,
+                        w.kvh, page);
+        }
+        if (++ks == K_STAGES) ks = 0, kpar ^= 1;
+        if (++vs == V_STAGES) vs = 0, vpar ^= 1;
+      }
+      __syncwarp();
+      if (*abort_s) ok = false;
+    }
+    if (*abort_s && lane == 0) {
+      // wind down: let the copies in flight land before the CTA's shared memory is given up.
+      // (A tile counted in gt whose values were not asked for has a barrier that nothing
+      // completes; its wait runs out after 20 ms.)
+      auto drain = [&](uint64_t* bars, int stages) {
+        for (int t = gt > stages ? gt - stages : 0; t < gt; ++t) {
           const unsigned long long t0 = globaltimer_ns();
-          while (!mbar_try_wait(smem_u32(&kv_full[t % STAGES]), (t / STAGES) & 1)) {
+          while (!mbar_try_wait(smem_u32(&bars[t % stages]), (t / stages) & 1)) {
             if (globaltimer_ns() - t0 > 20000000ull) {  // 20 ms
               gb_err::report(ERR_WAIT_DRAIN);
               break;
             }
           }
         }
-      }
+      };
+      drain(mc.k_full, K_STAGES);
+      drain(mc.v_full, V_STAGES);
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------------- MMA issuer
@@ -331,147 +400,163 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     // and buffer counters are stepped, not divided; descriptors are made once and advanced. On
     // this hardware a product with fewer than 128 columns takes as long as one with 128 (about
     // 70 cycles for M = 128, K = 16), so S is computed for both groups at once (their S buffers
-    // lie side by side). After a tile's softmax the S product two tiles ahead goes first: the
-    // softmax warps wait for it next, for P V only a tile later.
+    // lie side by side). After a tile's softmax its P V goes first: it reads the probabilities
+    // from the S buffer that the S product two tiles ahead then overwrites (products run in the
+    // order of their issue).
     constexpr uint32_t idesc_s = instr_desc_bf16(QROWS, KT);
     constexpr uint32_t idesc_o = instr_desc_bf16(QROWS, HD) | INSTR_B_MN_MAJOR;
-    const uint64_t dq0 = smem_desc_sw128(q_s), dk0 = smem_desc_sw128(kv_s), dv0 = smem_desc_sw128_mn(kv_s + K_BYTES),
-                   dp0 = smem_desc_sw128(p_s);
+    const uint64_t dq0 = smem_desc_sw128(q_s), dk0 = smem_desc_sw128(k_s),
+                   dv0 = smem_desc_sw128_mn(v_s, BLOCKS > 1 ? BLOCK_BYTES : 16);
     bool ok = true;
     TileWalk ws, wp;               // the S products' tile, the P V products' tile
     ws.start(p, q_tiles, total_items);
     wp = ws;
-    int s_stage = 0, s_par = 0, p_stage = 0;       // stage (and its phase) of the S tile, stage of the P V tile
+    int k_stage = 0, k_par = 0;                    // key stage (and its phase) of the S tile
+    int v_stage = 0, v_par = 0;                    // value stage of the P V tile
     int s_buf = 0;                                 // S buffer of the S tile
-    int p_buf = 0, p_par = 0;                      // buffers of the P V tile and their phase
+    int p_buf = 0, p_par = 0;                      // buffer of the P V tile and its phase
     auto issue_s = [&]() {      // S = Q K^T of the S tile into S buffer s_buf (both groups' columns)
       const int qb = ws.it & 1;
-      if (ws.j == 0 && !mbar_wait(smem_u32(&q_full[qb]), (ws.it >> 1) & 1)) ok = false;
-      if (ok && !mbar_wait(smem_u32(&kv_full[s_stage]), s_par)) ok = false;
+      if (ws.j == 0 && !mbar_wait(smem_u32(&mc.q_full[qb]), (ws.it >> 1) & 1)) ok = false;
+      if (ok && !mbar_wait(smem_u32(&mc.k_full[k_stage]), k_par)) ok = false;
       if (!ok) {
         if (lane == 0) gb_err::report(ERR_WAIT_FULL);
         return;
       }
       tc_fence_after_sync();
       if (lane == 0) {
-        static_assert(HD / 16 == 4 && GK / 16 == 4, "four k steps per product");
-        mma_bf16_x4(tmem_base + s_buf * KT, dq0 + (uint64_t)(qb * (Q_BYTES >> 4)),
-                    dk0 + (uint64_t)(s_stage * (STAGE_BYTES >> 4)), idesc_s, 2, 2);
-        mma_commit(smem_u32(&s_ready[s_buf]));
-        if (ws.j == ws.n - 1) mma_commit(smem_u32(&q_empty[qb]));   // the item's queries have been read
+#pragma unroll
+        for (int h = 0; h < BLOCKS; ++h)
+          mma_bf16_x4(tmem_base + s_buf * KT, dq0 + (uint64_t)(qb * (Q_BYTES >> 4) + h * (BLOCK_BYTES >> 4)),
+                      dk0 + (uint64_t)(k_stage * (K_BYTES >> 4) + h * (BLOCK_BYTES >> 4)), idesc_s, 2, 2, h > 0);
+        mma_commit(smem_u32(&mc.s_ready[s_buf]));      // the softmax warps pass it on to the queries' "empty" barrier
+        if (KEYS_FREED_BY_COMMIT) mma_commit(smem_u32(&mc.k_empty[k_stage]));
       }
       __syncwarp();
-      if (++s_stage == STAGES) s_stage = 0, s_par ^= 1;
-      s_buf ^= 1;
+      if (++k_stage == K_STAGES) k_stage = 0, k_par ^= 1;
+      if (++s_buf == S_BUFS) s_buf = 0;
       ws.next_tile(p, q_tiles, total_items);
     };
-    if (!ws.done) issue_s();
-    if (ok && !ws.done) issue_s();
+#pragma unroll 1
+    for (int b = 0; b < S_BUFS; ++b)
+      if (ok && !ws.done) issue_s();
     while (ok && !wp.done) {
-      if (*(volatile int*)&abort_s) break;
-#pragma unroll
-      for (int g = 0; g < GROUPS; ++g) {
-        if (ok && !mbar_wait(smem_u32(&p_ready[g][p_buf]), p_par)) {
-          if (lane == 0) gb_err::report(ERR_WAIT_ACCUM);
-          ok = false;
-        }
+      if (*abort_s) break;
+      if (ok && !mbar_wait(smem_u32(&mc.p_ready[p_buf]), p_par)) {
+        if (lane == 0) gb_err::report(ERR_WAIT_ACCUM);
+        ok = false;
       }
-      if (!ok) break;
-      // both groups have read this S buffer in full and written their P: first the S product that
-      // takes the buffer over, then this tile's P V
-      if (!ws.done) issue_s();
+      if (ok && !mbar_wait(smem_u32(&mc.v_full[v_stage]), v_par)) {
+        if (lane == 0) gb_err::report(ERR_WAIT_FULL);
+        ok = false;
+      }
       if (!ok) break;
       tc_fence_after_sync();
       if (lane == 0) {
 #pragma unroll
-        for (int g = 0; g < GROUPS; ++g) {
-          mma_bf16_x4(tmem_base + O_COL0 + (2 * g + p_buf) * HD, dp0 + (uint64_t)((2 * g + p_buf) * (P_BYTES >> 4)),
-                      dv0 + (uint64_t)(p_stage * (STAGE_BYTES >> 4) + g * (GK * ROW_BYTES >> 4)), idesc_o, 2,
-                      16 * ROW_BYTES >> 4);
-        }
-        mma_commit(smem_u32(&o_ready[p_buf]));
-        mma_commit(smem_u32(&kv_empty[p_stage]));     // keys and values of the stage have been read
+        for (int g = 0; g < GROUPS; ++g)
+          mma_bf16_ts<GK / 16>(tmem_base + O_COL0 + g * HD, tmem_base + p_buf * KT + g * GK,
+                         dv0 + (uint64_t)(v_stage * (V_BYTES >> 4) + g * (GK * ROW_BYTES >> 4)), idesc_o,
+                         16 * ROW_BYTES >> 4, wp.j > 0);
+        mma_commit(smem_u32(&mc.o_ready));             // the softmax warps pass it on to the values' "empty" barrier
       }
       __syncwarp();
-      if (++p_stage == STAGES) p_stage = 0;
-      p_par ^= p_buf;         // the phase flips after buffer 1
-      p_buf ^= 1;
+      // both groups have read this S buffer in full, and the products above read their P from it
+      // before the next one writes: the S product two tiles ahead takes the buffer over
+      if (!ws.done) issue_s();
+      if (!ok) break;
+      if (++v_stage == V_STAGES) v_stage = 0, v_par ^= 1;
+      if (++p_buf == S_BUFS) p_buf = 0, p_par ^= 1;
       wp.next_tile(p, q_tiles, total_items);
     }
-    if (!ok) abort_s = 1;
+    if (!ok) *abort_s = 1;
   } else {
     // -------------------------------------------------------------------- softmax warps
     // Group g takes keys [g * 64, g * 64 + 64) of every tile: an attention stream of its own
-    // (maximum, denominator, sums), merged with the other group's at the end. Two groups put two
-    // warps on every scheduler, so that one computes while the other waits for tensor memory.
+    // (reference maximum, denominator, accumulator), merged with the other group's at the end.
+    // Two groups put two warps on every scheduler, so that one computes while the other waits
+    // for tensor memory.
     const int grp = (warp - 2) >> 2;
     const int quarter = warp & 3;                        // the TMEM lanes this warp may read
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t o_mine = lane_addr + O_COL0 + grp * HD;
     const float scale_log2 = p.scale_log2;
-    float* xo = reinterpret_cast<float*>(smem_raw + (p_s + 2 * P_BYTES - smem_u32(smem_raw)));
     bool ok = true;       // false: this thread only keeps the others company at the barriers
     int gt = 0;           // tiles so far, over all items
-    int stage = 0;        // the current tile's stage of keys and values
+    int sb = 0, sph = 0;          // the current tile's S buffer and the phase of its barriers
+    int kstage = 0;               // the current tile's stage of keys
+    int vstage = 0, vpar = 0;     // the current tile's stage of values and its phase
+    int vprev = 0;                // the stage of the tile before
+    const bool passes_on = threadIdx.x == 64;      // one thread tells the TMA warp what the tensor core has finished with
     Cursor c;
     for (c.start(p, q_tiles, total_items); !c.done; c.next_item(p)) {
       const Item& w = c.w;
       const int row_pos = row < w.nrows ? w.pos0 + row / p.g : -1;       // no key is valid for a padding row
       const int row_start = (row < w.nrows && p.window > 0) ? max(0, row_pos + 1 - p.window) : 0;
-      float o_acc[HD];
-#pragma unroll
-      for (int ch = 0; ch < HD; ++ch) o_acc[ch] = 0.f;
-      float m = -INFINITY, l = 0.f, corr_saved = 0.f;      // m: running maximum of the raw dot products
+      float m = -INFINITY, l = 0.f;      // m: the reference maximum of the raw dot products
 
-      auto fold = [&](int t) {        // o_acc = o_acc * corr_saved + O_tile of the tile counted t
-        if (!mbar_wait(smem_u32(&o_ready[t & 1]), (t >> 1) & 1)) {
+      // waits until the P V products of the tile counted t have ended
+      auto wait_o = [&](int t) {
+        if (!mbar_wait(smem_u32(&mc.o_ready), t & 1)) {
           if (lane == 0) gb_err::report(ERR_WAIT_ACCUM);
           ok = false;
-          abort_s = 1;
-          return;
+          *abort_s = 1;
         }
         tc_fence_after_sync();
-        uint32_t v[HD / 32][32];
-#pragma unroll
-        for (int h = 0; h < HD / 32; ++h) tmem_ld_32(lane_addr + O_COL0 + (2 * grp + (t & 1)) * HD + h * 32, v[h]);
-        tmem_ld_wait();
-#pragma unroll
-        for (int ch = 0; ch < HD; ++ch) o_acc[ch] = fmaf(o_acc[ch], corr_saved, __uint_as_float(v[ch >> 5][ch & 31]));
       };
 
       for (int j = 0; j < w.n_tiles && ok; ++j, ++gt) {
-        if (*(volatile int*)&abort_s) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&s_ready[gt & 1]), (gt >> 1) & 1)) {
+        if (*abort_s) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&mc.s_ready[sb]), sph)) {
           if (lane == 0) gb_err::report(ERR_WAIT_ACCUM);
           ok = false;
-          abort_s = 1;
+          *abort_s = 1;
           break;
         }
         tc_fence_after_sync();
-        {
-          // Value rows that no row may read hold whatever was there (a page that was not fetched,
-          // the unwritten end of the last page): their probabilities are zero, but zero times a
-          // stray NaN is not. Clear them: half of each group's threads take one of the group's 64
-          // rows each. (The stage has landed: S of this tile was computed from its keys. The
-          // tensor core reads the values only after this thread's arrival below.)
-          const int tile_key0 = (w.tile_begin + j) * KT;
-          if ((tile_key0 < w.lo || tile_key0 + KT - 1 > w.hi) && row < GK) {
-            const int vrow = grp * GK + row, key = tile_key0 + vrow;
-            if (key < w.lo || key > w.hi) {
-              const uint32_t vaddr = kv_s + stage * STAGE_BYTES + K_BYTES + vrow * ROW_BYTES;
-#pragma unroll
-              for (int ch = 0; ch < ROW_BYTES / 16; ++ch) st_shared_v4(vaddr + ch * 16, 0u, 0u, 0u, 0u);
-            }
-          }
-          if (++stage == STAGES) stage = 0;
+        if (passes_on) {      // S of this tile is complete: its keys have been read, and after an item's last tile its queries
+          if (!KEYS_FREED_BY_COMMIT) mbar_arrive(smem_u32(&mc.k_empty[kstage]));
+          if (j == w.n_tiles - 1) mbar_arrive(smem_u32(&mc.q_empty[c.it & 1]));
         }
+        if (++kstage == K_STAGES) kstage = 0;
+        const uint32_t s_addr = lane_addr + sb * KT + grp * GK;
         // the row's 64 scores of this group, one wait for the two loads
         uint32_t sv[GK / 32][32];
 #pragma unroll
-        for (int h = 0; h < GK / 32; ++h) tmem_ld_32(lane_addr + (2 * (gt & 1) + grp) * GK + h * 32, sv[h]);
+        for (int h = 0; h < GK / 32; ++h) tmem_ld_32(s_addr + h * 32, sv[h]);
+        const int tile_key0 = (w.tile_begin + j) * KT;
+        const bool edge = tile_key0 < w.lo || tile_key0 + KT - 1 > w.hi;
+        if (edge) {
+          // Value rows that no row may read hold whatever was there (a page that was not fetched,
+          // the unwritten end of the last page): their probabilities are zero, but zero times a
+          // stray NaN is not. Clear them, once the stage's copies have landed: half of each
+          // group's threads take one of the group's 64 rows each. (The tensor core reads the
+          // values only after this thread's arrival below.)
+          if (!mbar_wait(smem_u32(&mc.v_full[vstage]), vpar)) {
+            if (lane == 0) gb_err::report(ERR_WAIT_FULL);
+            ok = false;
+            *abort_s = 1;
+          }
+          if (ok && row < GK) {
+            const int vrow = grp * GK + row, key = tile_key0 + vrow;
+            if (key < w.lo || key > w.hi) {
+#pragma unroll
+              for (int h = 0; h < BLOCKS; ++h) {
+                const uint32_t vaddr = v_s + vstage * V_BYTES + h * BLOCK_BYTES + vrow * ROW_BYTES;
+#pragma unroll
+                for (int ch = 0; ch < ROW_BYTES / 16; ++ch) st_shared_v4(vaddr + ch * 16, 0u, 0u, 0u, 0u);
+              }
+            }
+          }
+          fence_proxy_async();            // the tensor core reads the values through the async proxy
+        }
+        const int vcur = vstage;
+        if (++vstage == V_STAGES) vstage = 0, vpar ^= 1;
         tmem_ld_wait();
+        if (!ok) break;
         auto sc = [&](int ch) -> float& { return reinterpret_cast<float&>(sv[ch >> 5][ch & 31]); };
-        const int key0 = (w.tile_begin + j) * KT + grp * GK;
+        const int key0 = tile_key0 + grp * GK;
         // the keys need no mask if they lie wholly before the first row's position and inside the
         // last row's window
         const bool full = key0 + GK - 1 <= w.pos0 && (p.window <= 0 || key0 >= w.hi + 1 - p.window);
@@ -488,65 +573,108 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
           for (int e = 0; e < 4; ++e) mx[e] = max3(mx[e], sc(ch + e), sc(ch + 4 + e));
         }
         const float m_new = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;          // nothing valid yet: avoid inf - inf
-        const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
-        const float neg_m = -m_use * scale_log2;
-        m = m_new;
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint32_t prow = p_s + (2 * grp + (gt & 1)) * P_BYTES + row * 128;
+        // The reference maximum moves only if some row of the warp has outgrown it by more than
+        // 2^8; then the warp rescales what it has accumulated (the loads and stores of tensor
+        // memory are the whole warp's). A row that has seen no valid key yet has nothing to rescale.
+        const bool grown = m != -INFINITY && (m_new - m) * scale_log2 > RESCALE_ABOVE;
+        bool waited = false;
+        if (j > 0 && __any_sync(0xffffffffu, grown)) {
+          wait_o(gt - 1);
+          waited = true;
+          if (!ok) break;
+          const float corr = m == -INFINITY ? 1.f : fast_exp2((m - m_new) * scale_log2);
 #pragma unroll
-        for (int c8 = 0; c8 < GK / 8; ++c8) {
-          float pr[8];
+          for (int h = 0; h < HD / 32; ++h) {
+            uint32_t v[32];
+            tmem_ld_32(o_mine + h * 32, v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            pr[e] = fast_exp2(fmaf(sc(c8 * 8 + e), scale_log2, neg_m));   // exp2(-inf) = 0 for masked keys
-            ls[e & 3] += pr[e];
+            for (int ch = 0; ch < 32; ++ch) v[ch] = __float_as_uint(__uint_as_float(v[ch]) * corr);
+            tmem_st_32(o_mine + h * 32, v);
           }
-          // 16-byte chunk c8 of the row, swizzled with the row
-          st_shared_v4(prow + ((c8 ^ (row & 7)) << 4), pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]),
-                       pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
+          l *= corr;
+          m = m_new;
+        } else if (m == -INFINITY) {
+          m = m_new;
         }
-        l = l * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
-        fence_proxy_async();            // the tensor core reads P through the async proxy
-        tc_fence_before_sync();         // this thread's reads of S are over
-        mbar_arrive(smem_u32(&p_ready[grp][gt & 1]));
-        if (j > 0) fold(gt - 1);
-        corr_saved = corr;
-      }
-      if (ok) fold(gt - 1);
-      // ---- merge the two groups: the second hands its sums over through its own P buffers
-      // (its last product has been read from them: fold waited for it), [channel][row] floats
-      if (grp == 1 && ok) {
+        const float neg_m = m == -INFINITY ? 0.f : -m * scale_log2;       // nothing valid yet: avoid inf - inf
+        // All exponentials first, in place (the unit that computes them takes a warp's instruction
+        // every eight cycles; the multiply-adds in front fit in between), then sums and packing.
 #pragma unroll
-        for (int ch = 0; ch < HD; ++ch) xo[ch * QROWS + row] = o_acc[ch];
-        other_ml[row][0] = m;
-        other_ml[row][1] = l;
+        for (int ch = 0; ch < GK; ++ch) {
+          sc(ch) = fast_exp2(fmaf(sc(ch), scale_log2, neg_m));   // exp2(-inf) = 0 for masked keys
+        }
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[GK / 2];
+#pragma unroll
+        for (int ch = 0; ch < GK; ch += 2) {
+          ls[(ch >> 1) & 3] += sc(ch) + sc(ch + 1);
+          pk[ch >> 1] = pack_bf16(sc(ch), sc(ch + 1));
+        }
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        tmem_st(s_addr, pk);            // over the first half of the scores just read
+        tmem_st_wait();
+        if (j > 0 && !waited) wait_o(gt - 1);      // every phase of the barrier is seen, in order
+        tc_fence_before_sync();         // this thread's accesses to tensor memory are over
+        mbar_arrive(smem_u32(&mc.p_ready[sb]));
+        if (passes_on && j > 0) mbar_arrive(smem_u32(&mc.v_empty[vprev]));      // the tile before: its P V has ended
+        vprev = vcur;
+        if (++sb == S_BUFS) sb = 0, sph ^= 1;
       }
+      if (ok && w.n_tiles > 0) {
+        wait_o(gt - 1);
+        if (passes_on && ok) mbar_arrive(smem_u32(&mc.v_empty[vprev]));
+      }
+      // ---- merge the groups: each writes its share of the channels, summed over all accumulators
+      const int mb = ML_BUFS == 2 ? (c.it & 1) : 0;
+      mc.ml[mb][grp][row] = make_float2(m, l);
+      tc_fence_before_sync();
       asm volatile("bar.sync 1, %0;" ::"n"(GROUPS * 128) : "memory");
-      if (grp == 0 && ok && row < w.nrows && !*(volatile int*)&abort_s) {
-        const float m2 = other_ml[row][0], l2 = other_ml[row][1];
-        const float mt = fmaxf(m, m2);
-        const float f1 = m == -INFINITY ? 0.f : fast_exp2((m - mt) * scale_log2);
-        const float f2 = m2 == -INFINITY ? 0.f : fast_exp2((m2 - mt) * scale_log2);
-        const float lt = l * f1 + l2 * f2;
+      tc_fence_after_sync();
+      if (ok && !*abort_s) {
+        float a[GROUPS];
+        float mt = -INFINITY, lt = 0.f;
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) mt = fmaxf(mt, mc.ml[mb][g][row].x);
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+          const float2 x = mc.ml[mb][g][row];
+          a[g] = x.x == -INFINITY ? 0.f : fast_exp2((x.x - mt) * scale_log2);
+          lt += x.y * a[g];
+        }
         const float inv = lt > 0.f ? 1.0f / lt : 0.f;
-        const float a1 = f1 * inv, a2 = f2 * inv;
-        __nv_bfloat16* dst = p.out + ((size_t)(w.q_begin + w.tok0 + row / p.g) * p.Hq + w.kvh * p.g + row % p.g) * HD;
+        __nv_bfloat16* dst = p.out + ((size_t)(w.q_begin + w.tok0 + row / p.g) * p.Hq + w.kvh * p.g + row % p.g) * HD + grp * CH;
 #pragma unroll
-        for (int ch = 0; ch < HD; ch += 8) {
-          float t[8];
+        for (int h = 0; h < CH / 16; ++h) {
+          float t[16];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) t[e] = o_acc[ch + e] * a1 + xo[(ch + e) * QROWS + row] * a2;
-          uint4 wv;
-          wv.x = pack_bf16(t[0], t[1]);
-          wv.y = pack_bf16(t[2], t[3]);
-          wv.z = pack_bf16(t[4], t[5]);
-          wv.w = pack_bf16(t[6], t[7]);
-          *reinterpret_cast<uint4*>(dst + ch) = wv;
+          for (int e = 0; e < 16; ++e) t[e] = 0.f;
+#pragma unroll
+          for (int g = 0; g < GROUPS; g += 2) {      // two accumulators at a time (registers)
+            uint32_t v[2][16];
+            tmem_ld_16(lane_addr + O_COL0 + g * HD + grp * CH + h * 16, v[0]);
+            tmem_ld_16(lane_addr + O_COL0 + (g + 1) * HD + grp * CH + h * 16, v[1]);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {      // a stream without a valid key has an accumulator that means nothing
+              t[e] += a[g] > 0.f ? __uint_as_float(v[0][e]) * (a[g] * inv) : 0.f;
+              t[e] += a[g + 1] > 0.f ? __uint_as_float(v[1][e]) * (a[g + 1] * inv) : 0.f;
+            }
+          }
+          if (row < w.nrows) {
+            uint4 w0, w1;
+            w0.x = pack_bf16(t[0], t[1]), w0.y = pack_bf16(t[2], t[3]), w0.z = pack_bf16(t[4], t[5]), w0.w = pack_bf16(t[6], t[7]);
+            w1.x = pack_bf16(t[8], t[9]), w1.y = pack_bf16(t[10], t[11]), w1.z = pack_bf16(t[12], t[13]), w1.w = pack_bf16(t[14], t[15]);
+            *reinterpret_cast<uint4*>(dst + h * 16) = w0;
+            *reinterpret_cast<uint4*>(dst + h * 16 + 8) = w1;
+          }
         }
       }
-      // the second group's next probabilities go where its sums were just read
-      asm volatile("bar.sync 1, %0;" ::"n"(GROUPS * 128) : "memory");
+      // The next item's first P V overwrites the accumulators; it is issued only after all groups
+      // have arrived for that tile, that is after all are through here. With one copy of `ml` a
+      // group must not write the next item's values while another still reads these.
+      if (ML_BUFS == 1) asm volatile("bar.sync 1, %0;" ::"n"(GROUPS * 128) : "memory");
+      tc_fence_before_sync();
     }
   }
   tc_fence_before_sync();
@@ -555,21 +683,8 @@ attention_tile_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return (EncodeTiledFn)p;
-  }();
-  return fn;
-}
+using tc_host::encode_fn;
+using tc_host::EncodeTiledFn;
 
 struct MapKey {
   const void* ptr;
@@ -586,8 +701,8 @@ struct MapKeyHash {
   }
 };
 
-// A bf16 tensor [d3][d2][d1][64] (64 contiguous) seen through boxes [1][b2][b1][64] (d3 = 0: three
-// dimensions, box [b2][b1][64]), 128-byte swizzle; elements outside read as zeros.
+// A bf16 tensor [d3][d2][d1][head size] (channels contiguous) seen through boxes [1][b2][b1][64]
+// (d3 = 0: three dimensions, box [b2][b1][64]), 128-byte swizzle; elements outside read as zeros.
 int tensor_map(const void* ptr, long long d1, long long d2, long long d3, int b1, int b2, CUtensorMap* out) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
@@ -603,7 +718,7 @@ int tensor_map(const void* ptr, long long d1, long long d2, long long d3, int b1
   const int rank = d3 > 0 ? 4 : 3;
   cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)d1, (cuuint64_t)d2, (cuuint64_t)(d3 > 0 ? d3 : 1)};
   cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)HD * 2 * d1, (cuuint64_t)HD * 2 * d1 * d2};
-  cuuint32_t box[4] = {(cuuint32_t)HD, (cuuint32_t)b1, (cuuint32_t)b2, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)b1, (cuuint32_t)b2, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUtensorMap m;
   CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -631,10 +746,10 @@ bool tile_tc_takes(const Params& p, int T, long long pages) {
 int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len, cudaStream_t stream) {
   CUtensorMap qm, km, vm;
   const int tokens_per_tile = QROWS / p.g;
-  // queries [T][Hq][64] through boxes [tokens_per_tile][g][64]
+  // queries [T][Hq][head size] through boxes [tokens_per_tile][g][64]
   int rc = tensor_map(p.q, p.Hq, T, 0, p.g, tokens_per_tile, &qm);
   if (rc) return rc;
-  // pools [pages][Hkv][page_size][64] through boxes [1][1][page_size][64]
+  // pools [pages][Hkv][page_size][head size] through boxes [1][1][page_size][64]
   rc = tensor_map(p.k_pool, p.page_size, p.Hkv, pages, p.page_size, 1, &km);
   if (rc) return rc;
   rc = tensor_map(p.v_pool, p.page_size, p.Hkv, pages, p.page_size, 1, &vm);
@@ -648,12 +763,7 @@ int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len
   const int q_tiles = (max_q_len + tokens_per_tile - 1) / tokens_per_tile;
   const long long total = (long long)q_tiles * p.Hkv * R;
   if (total > 0x7fffffff) return gb::fail(GB_UNSUPPORTED, "attention_tc: %lld pieces of work", total);
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  }
+  const int sms = tc_host::sm_count();
   dim3 grid((unsigned)(total < sms ? total : sms), 1, 1);
   return gb::check_pdl_launch(gb::launch_pdl(attention_tile_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream,
                                              dim3(1, 1, 1), qm, km, vm, p, q_tiles, (int)total),

@@ -214,6 +214,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 // distance between such groups along the contraction. The leading byte offset (between blocks of
 // 64 channels) is not used with 64 channels.
 __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr) { return smem_desc_sw128(smem_addr); }
+// With more than 64 channels: blocks of 64 channels lie `block_bytes` apart (the leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t block_bytes) {
+  uint64_t d = smem_desc_sw128(smem_addr);
+  d &= ~((uint64_t)0x3FFF << 16);
+  d |= (uint64_t)((block_bytes >> 4) & 0x3FFF) << 16;
+  return d;
+}
 
 // Instruction descriptor, kind::f16: D format f32 (1) in bits 4-5, A and B
 // format bf16 (1) in 7-9 and 10-12, both K-major (bits 15, 16 clear), N >> 3 in
@@ -252,6 +259,61 @@ __device__ __forceinline__ void mma_bf16_x4(uint32_t tmem_d, uint64_t desc_a, ui
       ::"r"(tmem_d), "l"(desc_a), "l"(a1), "l"(a2), "l"(a3), "l"(desc_b), "l"(b1), "l"(b2), "l"(b3), "r"(idesc)
       : "memory");
 }
+// The same with a choice for the first product: it overwrites the accumulator or adds to it.
+__device__ __forceinline__ void mma_bf16_x4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t step_a, uint32_t step_b, bool first_accumulates) {
+  const uint64_t a1 = desc_a + step_a, a2 = desc_a + 2 * step_a, a3 = desc_a + 3 * step_a;
+  const uint64_t b1 = desc_b + step_b, b2 = desc_b + 2 * step_b, b3 = desc_b + 3 * step_b;
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, %10, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %5, %9, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %6, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %7, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %9, p1;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(a1), "l"(a2), "l"(a3), "l"(desc_b), "l"(b1), "l"(b2), "l"(b3), "r"(idesc),
+        "r"((uint32_t)first_accumulates)
+      : "memory");
+}
+// Four products whose A operand lies in tensor memory: 128 lanes (rows), per product 8 columns of
+// 32 bits, each holding two consecutive elements of the contraction in bf16 (the lower index in the
+// lower half). B comes from shared memory as above.
+__device__ __forceinline__ void mma_bf16_ts_x4(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t step_b, bool first_accumulates) {
+  const uint64_t b1 = desc_b + step_b, b2 = desc_b + 2 * step_b, b3 = desc_b + 3 * step_b;
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, %10, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %5, %9, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %6, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %7, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %8, %9, p1;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(tmem_a + 8), "r"(tmem_a + 16), "r"(tmem_a + 24), "l"(desc_b), "l"(b1), "l"(b2),
+        "l"(b3), "r"(idesc), "r"((uint32_t)first_accumulates)
+      : "memory");
+}
+// The same for two products.
+__device__ __forceinline__ void mma_bf16_ts_x2(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t step_b, bool first_accumulates) {
+  const uint64_t b1 = desc_b + step_b;
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, %6, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %3, %5, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %4, %5, p1;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(tmem_a + 8), "l"(desc_b), "l"(b1), "r"(idesc), "r"((uint32_t)first_accumulates)
+      : "memory");
+}
+template <int STEPS>
+__device__ __forceinline__ void mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t step_b, bool first_accumulates) {
+  static_assert(STEPS == 2 || STEPS == 4, "two or four products");
+  if (STEPS == 2) mma_bf16_ts_x2(tmem_d, tmem_a, desc_b, idesc, step_b, first_accumulates);
+  else mma_bf16_ts_x4(tmem_d, tmem_a, desc_b, idesc, step_b, first_accumulates);
+}
 // Makes `bar` complete once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -281,6 +343,30 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// The other way: 32 registers into 32 consecutive columns of this thread's lane.
+__device__ __forceinline__ void tmem_st_32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// 16 registers into 16 consecutive columns.
+__device__ __forceinline__ void tmem_st_16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st_32(taddr, r); }
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st_16(taddr, r); }
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 }  // namespace tc

@@ -368,6 +368,10 @@ TCGEN05_ATTENTION_CASES = [
     (32, 4, 64, 32, [(900, 400)], 200),                        # a window shorter than the context
     (4, 1, 64, 8, [(500, 500), (129, 129)], 50),               # groups of 4, pages of 8, a short window
     (2, 1, 64, 128, [(3, 3), (131, 131), (256, 128)], 0),      # pages as long as a key tile
+    (8, 8, 128, 32, [(700, 700), (130, 130)], 0),              # heads of 128, each with its own kv head
+    (32, 8, 128, 64, [(1000, 300), (64, 1), (257, 257)], 0),   # heads of 128 in groups of 4; a portion; pages of 64
+    (16, 2, 128, 16, [(900, 500)], 150),                       # heads of 128 in groups of 8, a window
+    (4, 4, 128, 128, [(5, 5), (400, 272)], 0),                 # heads of 128, pages as long as a key tile
 ]
 
 
@@ -469,21 +473,30 @@ def test_attention_decode_with_tma_far_key(ops):
         close(out, ref, 1e-2, f"far key at {far}, decode by TMA")
 
 
-def test_attention_tcgen05_far_key(ops):
-    """One early key stands out for one late query row of a long portion."""
-    Hq, Hkv, hd, page = 8, 2, 64, 32
-    q, k, v, bt, cu, kvl, treq, _ = _attention_case(Hq, Hkv, hd, page, [(1100, 600)], 0, torch.bfloat16)
-    far, tok, head = 5, 577, 6                               # head 6 reads kv head 1
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("far", [5, 720, 1050])
+def test_attention_tcgen05_one_key_stands_out(ops, hd, far):
+    """One key stands out for one late query row of a long portion: an early one (its weight must
+    survive every later tile), or a late one after hundreds of ordinary keys (the running maximum
+    jumps, and what has been accumulated is rescaled), in either half of a key tile."""
+    Hq, Hkv, page = 8, 2, 32
+    q, k, v, bt, cu, kvl, treq, _ = _attention_case(Hq, Hkv, hd, page, [(1100, 600)], 0, torch.bfloat16, seed=far)
+    tok, head = 577, 6                                       # head 6 reads kv head 1; the token stands at position 1077
     pg = int(bt[0, far // page])
     k[pg, 1, far % page] = (q[tok, head].float() * 4).bfloat16()
     v[pg, 1, far % page] = 50.0
     ref = torch.zeros(600, Hq * hd)
     cpu.paged_attention(q.float(), k.float(), v.float(), bt, cu, kvl, treq, ref, hd ** -0.5, 0, page, 1, 0, 0)
     assert ref[tok, head * hd:(head + 1) * hd].mean() > 40
+    lib = ops.tc._attention_lib(hd)
+    lib.gb_attention_tc_tile_launches.restype = ctypes.c_longlong
+    before = lib.gb_attention_tc_tile_launches()
     out = torch.zeros(ref.shape, dtype=torch.bfloat16, device="cuda")
     ops.paged_attention(dev(q), dev(k), dev(v), dev(bt), dev(cu), dev(kvl), dev(treq), out, hd ** -0.5, 0, page, 1,
                         600, 1100, min_q_len=600)
-    close(out, ref, 1e-2, "far key, tcgen05")
+    ops.tc.check_errors()
+    assert lib.gb_attention_tc_tile_launches() == before + 1, "the tcgen05 kernel did not take the shape"
+    close(out, ref, 1e-2, f"key {far} stands out, tcgen05, head size {hd}")
 
 
 def test_attention_finds_one_far_key_among_hundreds(ops):
