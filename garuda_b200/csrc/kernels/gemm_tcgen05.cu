@@ -1032,11 +1032,22 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_m, const __gri
 // 256), which outweighs hiding a lone tile's epilogue under a second tile; for the same reason tiles
 // of 384 columns (a 256- and a 128-column product per step), tried for widths where 256-wide tiles
 // need a second, nearly empty round over the pairs, were slower than that second round.
+// BN = 320 (five heads of 64, for a query/key/value product whose 256-wide tiles would need a second,
+// nearly empty round): a product has at most 256 columns, so a step is a product of 256 and one of
+// 64 columns (two of 160 took longer: a product's time grows in steps with its width); each CTA
+// loads its half of either product's weight rows, so that the accumulator's columns stay in the
+// weights' order. 320 columns leave tensor memory for one accumulator stage only.
 template <int BN>
 struct PairGeometry {
-  static constexpr int STAGE_BYTES = BM * BK * 2 + (BN / 2) * BK * 2;      // per CTA: 32 KB or 24 KB
-  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;                // 6 or 8
+  static constexpr int PARTS = BN > 256 ? 2 : 1;                           // products per step
+  static constexpr int COLS0 = BN > 256 ? 256 : BN, COLS1 = BN - COLS0;    // their widths
+  static constexpr int BOX_ROWS = BN > 256 ? COLS1 / 2 : BN / 2;           // weight rows per TMA box
+  static constexpr int ACC_STAGES = 2 * BN <= 512 ? 2 : 1;
+  static constexpr int STAGE_BYTES = BM * BK * 2 + (BN / 2) * BK * 2;      // per CTA: 32 KB, 24 KB or 36 KB
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;                // 6, 8 or 5
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static_assert(STAGE_BYTES % 1024 == 0 && (BOX_ROWS * BK * 2) % 1024 == 0 && (COLS0 / 2) % BOX_ROWS == 0,
+                "operand tiles on swizzle boundaries, whole boxes");
 };
 
 template <int BN, int EPI, typename OT>
@@ -1046,7 +1057,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
                     const EpilogueArgs ra) {
   using PG = PairGeometry<BN>;
   constexpr int STAGES = PG::STAGES, PAIR_STAGE_BYTES = PG::STAGE_BYTES;
-  constexpr int TMEM_COLS = 2 * BN;               // two accumulator stages
+  constexpr int ACC = PG::ACC_STAGES;             // accumulator stages
+  constexpr int TMEM_COLS = ACC * BN <= 512 && ACC * BN > 256 ? 512 : ACC * BN;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -1097,7 +1109,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
       int s = 0, par = 1, issued = 0;
       for (int tile = pair; tile < total_tiles && !*aborted; tile += pairs) {
         const int m0 = (tile % tiles_m) * (2 * BM) + (int)rank * BM;
-        const int n0 = (tile / tiles_m) * BN + (int)rank * (BN / 2);
+        const int nt0 = (tile / tiles_m) * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&empty_bar[s]), par)) {
             gb_err::report(ERR_WAIT_EMPTY);
@@ -1108,7 +1120,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
           const uint32_t base = tiles + s * PAIR_STAGE_BYTES;
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[s]), 2 * PAIR_STAGE_BYTES);
           tma_load_2d_pair(base, &map_m, bar, kb * BK, m0);
-          tma_load_2d_pair(base + BM * BK * 2, &map_n, bar, kb * BK, n0);
+          // this CTA's half of the first product's weight rows, then of the second's, box by box
+#pragma unroll
+          for (int b = 0; b < BN / 2 / PG::BOX_ROWS; ++b) {
+            const int r0 = b * PG::BOX_ROWS;      // row within this CTA's BN / 2
+            const int feature = r0 < PG::COLS0 / 2 ? (int)rank * (PG::COLS0 / 2) + r0
+                                                   : PG::COLS0 + (int)rank * (PG::COLS1 / 2) + (r0 - PG::COLS0 / 2);
+            tma_load_2d_pair(base + BM * BK * 2 + r0 * BK * 2, &map_n, bar, kb * BK, nt0 + feature);
+          }
           ++issued;
           if (++s == STAGES) s = 0, par ^= 1;
         }
@@ -1123,12 +1142,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       // ------------------------------------------------------------ MMA issuer (even CTA)
-      constexpr uint32_t idesc = instr_desc_bf16(2 * BM, BN);
+      constexpr uint32_t idesc = instr_desc_bf16(2 * BM, PG::COLS0);
+      constexpr uint32_t idesc1 = instr_desc_bf16(2 * BM, PG::COLS1 > 0 ? PG::COLS1 : 16);
       const uint64_t da0 = smem_desc_sw128(tiles), db0 = smem_desc_sw128(tiles + BM * BK * 2);
       int s = 0, par = 0, t = 0;
       for (int tile = pair; tile < total_tiles && !*aborted; tile += pairs, ++t) {
-        const int as = t & 1;
-        if (!mbar_wait(smem_u32(&acc_empty[as]), ((t >> 1) & 1) ^ 1)) {   // both epilogues have drained this stage
+        const int as = ACC == 2 ? (t & 1) : 0;
+        if (!mbar_wait(smem_u32(&acc_empty[as]), ((ACC == 2 ? (t >> 1) : t) & 1) ^ 1)) {   // both epilogues have drained this stage
           gb_err::report(ERR_WAIT_ACCUM);
           *aborted = 1;
           break;
@@ -1144,7 +1164,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
           tc_fence_after_sync();
           const uint64_t da = da0 + (uint64_t)(s * (PAIR_STAGE_BYTES >> 4)), db = db0 + (uint64_t)(s * (PAIR_STAGE_BYTES >> 4));
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) mma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, kb > 0 || k > 0);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            mma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, kb > 0 || k > 0);
+            if (PG::PARTS == 2)
+              mma_bf16_pair(acc + PG::COLS0, da + 2 * k, db + (uint64_t)((PG::COLS0 / 2) * BK * 2 >> 4) + 2 * k, idesc1,
+                            kb > 0 || k > 0);
+          }
           mma_commit_pair(smem_u32(&empty_bar[s]), 3);      // the stage is free in both CTAs
           if (++s == STAGES) s = 0, par ^= 1;
         }
@@ -1159,12 +1184,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_cons
     const bool vec = (((uintptr_t)out) & 15) == 0 && ((size_t)ldo * sizeof(OT)) % 16 == 0;
     int t = 0;
     for (int tile = pair; tile < total_tiles; tile += pairs, ++t) {
-      const int as = t & 1;
+      const int as = ACC == 2 ? (t & 1) : 0;
       const int m0 = (tile % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (tile / tiles_m) * BN;
       float first[32];
       epilogue_prefetch<BN, EPI, OT>(first, m0 + quarter * 32 + lane, n0, out, ldo, rows_m, rows_n, c_begin);
       const float inv = epilogue_row_scale(ra, m0 + quarter * 32 + lane, rows_m);
-      bool have = mbar_wait(smem_u32(&acc_full[as]), (t >> 1) & 1);
+      bool have = mbar_wait(smem_u32(&acc_full[as]), (ACC == 2 ? (t >> 1) : t) & 1);
       if (!have && lane == 0) {
         gb_err::report(ERR_WAIT_ACCUM);
         *aborted = 1;
@@ -1531,6 +1556,16 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, int Mx, int K, void* 
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
   if (many_token_pairs(Mx, Nw)) {
+    // 320-wide tiles (two products a step, about 1.4 times a 256-wide tile's time) where they save a
+    // round over the pairs: 2,048 tokens times 2,560 features are 80 tiles of 256 columns for 74 pairs,
+    // but 64 of 320
+    const int most = sm_count() / 2, tiles_m = (Mx + 2 * BM - 1) / (2 * BM);
+    const int rounds256 = (tiles_m * ((Nw + 255) / 256) + most - 1) / most;
+    const int rounds320 = (tiles_m * ((Nw + 319) / 320) + most - 1) / most;
+    if (320 % head_dim == 0 && rounds320 * 14 < rounds256 * 10) {
+      if ((rc = tensor_map_2d(w, Nw, K, PairGeometry<320>::BOX_ROWS, &mn))) return rc;
+      return launch_pair<320, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Mx, Nw, Nw, K, stream, ra);
+    }
     if ((rc = tensor_map_2d(w, Nw, K, 128, &mn))) return rc;
     return launch_pair<256, EPI_ROPE, __nv_bfloat16>(mm, mn, none, 0, Mx, Nw, Nw, K, stream, ra);
   }
