@@ -365,13 +365,41 @@ def cpu_reference_seconds() -> dict:
 
 def run_one_phase(args, engine, cfg, rng, context) -> dict:
     """One phase only, for profiling: `--only prefill` runs a 2,048-token prompt `steps` times,
-    `--only decode` prefills `--batch` requests and runs `steps` decode steps. Prints times, not the
-    benchmark record."""
+    `--only decode` prefills `--batch` requests and runs `steps` decode steps, `--only attention` runs
+    the attention kernel alone on the last `--tokens` tokens of one request of `--context` (random
+    queries, keys and values in the engine's own cache layout). Prints times, not the benchmark
+    record."""
     import torch
     from garuda_b200 import StepEntry
     runner, V = engine.runner, cfg["vocab_size"]
     ev = lambda: torch.cuda.Event(enable_timing=True)
     times = []
+    if args.only == "attention":
+        T, ctx_len, page = args.tokens, max(args.context or args.tokens, args.tokens), 32
+        Hq, Hkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+        npages = (ctx_len + page - 1) // page
+        dev, ops = engine.device, engine.ops
+        k, v = (torch.randn(npages + 1, Hkv, page, hd, device=dev).bfloat16() for _ in range(2))
+        q = torch.randn(T, Hq, hd, device=dev).bfloat16()
+        out = torch.zeros(T, Hq * hd, device=dev, dtype=torch.bfloat16)
+        table = torch.arange(npages, dtype=torch.int32, device=dev).view(1, npages)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        kvl = torch.tensor([ctx_len], dtype=torch.int32, device=dev)
+        treq = torch.zeros(T, dtype=torch.int32, device=dev)
+        for i in range(args.warmup + args.steps):
+            s, e = ev(), ev()
+            torch.cuda.synchronize()
+            s.record()
+            ops.paged_attention(q, k, v, table, cu, kvl, treq, out, hd ** -0.5, 0, page, 1, T, ctx_len, min_q_len=T)
+            e.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times.append(s.elapsed_time(e))
+        ops.tc.check_errors()
+        ms = sorted(times)[len(times) // 2]
+        flops = 4.0 * Hq * hd * (T * (ctx_len - T) + T * (T + 1) / 2)
+        return {"only": "attention", "shape": args.shape, "tokens": T, "context": ctx_len, "heads": Hq, "kv_heads": Hkv,
+                "head_dim": hd, "us": round(ms * 1e3, 1), "tflops_causal": round(flops / ms / 1e9, 1)}
     if args.only == "prefill":
         toks = rng.integers(0, V, args.tokens).tolist()
         for i in range(args.warmup + args.steps):
@@ -414,10 +442,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="tinyllama", choices=sorted(SHAPES),
                     help="layer sizes: one of the reference's published configurations")
-    ap.add_argument("--only", choices=["prefill", "decode"], help="run one phase only (for profiling)")
+    ap.add_argument("--only", choices=["prefill", "decode", "attention"], help="run one phase only (for profiling)")
     ap.add_argument("--batch", type=int, default=8, help="requests of the timed decode steps")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="prompt tokens with --only prefill")
-    ap.add_argument("--context", type=int, default=0, help="context reached with --only decode (default: the shape's)")
+    ap.add_argument("--context", type=int, default=0, help="context reached with --only decode (default: the shape's); keys with --only attention")
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (reported beside the full number)")
     args = ap.parse_args()
