@@ -131,117 +131,48 @@ __device__ bool bisect(const float* p, int V, double* sh_d, int* sh_i, Pred pred
   return true;
 }
 
+// Called by the first warp: the bin of hist[0..255] that holds the `remaining`-th value from the top
+// goes to sh_i[0], its rank within that bin to sh_i[1]. Every lane sums eight bins, a suffix sum over
+// the lanes finds the lane, which then walks its own eight.
+__device__ __forceinline__ void pick_bin(const int* hist, int remaining, int* sh_i) {
+  const int lane = threadIdx.x;
+  int mine8 = 0;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) mine8 += hist[8 * lane + q];
+  int suffix = mine8;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_down_sync(0xffffffffu, suffix, o);
+    if (lane + o < 32) suffix += v;
+  }
+  int above = suffix - mine8;                      // in the bins of the lanes above this one
+  if (above < remaining && remaining <= suffix) {
+    int bin = 8 * lane + 7;
+    for (; bin > 8 * lane; --bin) {
+      if (above + hist[bin] >= remaining) break;
+      above += hist[bin];
+    }
+    sh_i[0] = bin;
+    sh_i[1] = remaining - above;
+  }
+}
+
 // top_k of at most LIST_MAX, the usual case: the k most likely tokens are picked out and sorted,
 // and top-p, the total mass and the walk to the drawn point run over that short list exactly as the
 // reference walks its sorted candidates (garuda/src/runtime/mod.rs:109-172), instead of one bisection
 // over the whole vocabulary for each of them.
 constexpr int LIST_MAX = 1024;
 
-// p: the row's probabilities. Ends with the chosen token in *out. Every thread of the block calls it.
-// must_reach: top-p has to be reached within these k (the caller has no top-k of its own and tries the k
-// most likely tokens first); if it is not, nothing is written and false returned, to every thread.
-__device__ bool sample_from_top_k(const float* p, int V, int k, float tp, float uniform_draw, int32_t* out,
-                                  int* sh_cnt, int* sh_i, bool must_reach) {
-  __shared__ unsigned long long keys[LIST_MAX];   // probability bits, then ~token id: descending = by probability, then by id
-  __shared__ int hist[257];                       // bin 256 takes what a pass does not count
-  const int kk = min(k, V);
-  // the kk-th largest probability by its bit pattern, a byte at a time from the top
-  uint32_t prefix = 0;
-  int remaining = kk;
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    const uint32_t mask = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
-    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
-    __syncthreads();
-    // Probabilities crowd into a few bins (most share their exponent), so the lanes of a warp that
-    // hit the same bin add to it once, together.
-    const int padded = (V + 31) & ~31;
-    for (int i = threadIdx.x; i < padded; i += blockDim.x) {
-      const uint32_t b = i < V ? __float_as_uint(p[i]) : 0u;
-      const int bin = (i < V && (b & mask) == (prefix & mask)) ? (int)((b >> shift) & 255u) : 256;
-      const unsigned peers = __match_any_sync(0xffffffffu, bin);
-      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
-    }
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      // the bin that holds the `remaining`-th from the top: every lane of the first warp sums eight bins,
-      // a suffix sum over the lanes finds the lane, which then walks its own eight
-      const int lane = threadIdx.x;
-      int mine8 = 0;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) mine8 += hist[8 * lane + q];
-      int suffix = mine8;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_down_sync(0xffffffffu, suffix, o);
-        if (lane + o < 32) suffix += v;
-      }
-      int above = suffix - mine8;                      // in the bins of the lanes above this one
-      if (above < remaining && remaining <= suffix) {
-        int bin = 8 * lane + 7;
-        for (; bin > 8 * lane; --bin) {
-          if (above + hist[bin] >= remaining) break;
-          above += hist[bin];
-        }
-        sh_i[0] = bin;
-        sh_i[1] = remaining - above;
-      }
-    }
-    __syncthreads();
-    prefix |= (uint32_t)sh_i[0] << shift;
-    remaining = sh_i[1];
-    __syncthreads();
-  }
-  const uint32_t tau_bits = prefix;   // the kk-th largest; `remaining` of those equal to it are wanted
-  const int gt = kk - remaining;
-  if (must_reach && kk < V) {
-    // Before the list is gathered, sorted and walked: does its mass reach top-p at all? (With a slack
-    // for the order of the additions: a list that only just reaches it is walked and decides itself.)
-    __shared__ double part[32];
-    double above = 0.0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float v = p[i];
-      if (__float_as_uint(v) > tau_bits) above += (double)v;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) above += __shfl_xor_sync(0xffffffffu, above, o);
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = above;
-    __syncthreads();
-    double mass = (double)remaining * (double)__uint_as_float(tau_bits);
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mass += part[w];
-    __syncthreads();
-    if (mass < (double)tp * (1.0 - 1e-6)) return false;
-  }
-  // gather: everything above tau in any order (the sort below orders it), and of those equal to tau
-  // the `remaining` lowest token ids. For these every warp takes a run of the vocabulary and walks it
-  // 32 tokens at a time, so that ranks among the ties follow the token ids.
-  if (threadIdx.x == 0) sh_i[2] = 0;
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int run = ((V + nw - 1) / nw + 31) & ~31;            // tokens per warp, whole walks of 32
-  const int lo = min(V, warp * run), hi = min(V, lo + run);
-  int ties = 0;
-  for (int base = lo; base < hi; base += 32) {
-    const int i = base + lane;
-    const uint32_t b = i < hi ? __float_as_uint(p[i]) : 0u;
-    if (i < hi && b > tau_bits) keys[atomicAdd(&sh_i[2], 1)] = ((unsigned long long)b << 32) | (0xffffffffu - (uint32_t)i);
-    ties += __popc(__ballot_sync(0xffffffffu, i < hi && b == tau_bits));
-  }
-  if (lane == 0) sh_cnt[warp] = ties;
-  __syncthreads();
-  int before = 0;                                            // ties in the runs of the warps in front
-  for (int w = 0; w < warp; ++w) before += sh_cnt[w];
-  for (int base = lo; base < hi && before < remaining; base += 32) {
-    const int i = base + lane;
-    const bool tie = i < hi && __float_as_uint(p[i]) == tau_bits;
-    const unsigned votes = __ballot_sync(0xffffffffu, tie);
-    const int rank = before + __popc(votes & ((1u << lane) - 1u));
-    if (tie && rank < remaining) keys[gt + rank] = ((unsigned long long)tau_bits << 32) | (0xffffffffu - (uint32_t)i);
-    before += __popc(votes);
-  }
+// keys[0 .. count): candidates as (probability bits, ~token id), among them the kk most likely ones
+// by (probability descending, token id ascending). Sorts them that way and walks the first kk as the
+// reference walks its sorted candidates. Every thread of the block calls it; see sample_from_top_k for
+// must_reach and the result.
+__device__ bool sort_and_walk(unsigned long long* keys, int count, int kk, int V, float tp, float uniform_draw,
+                              int32_t* out, int* sh_i, bool must_reach) {
   // sort descending (bitonic, padded with zeros to a power of two)
   int size = 1;
-  while (size < kk) size <<= 1;
-  for (int i = kk + threadIdx.x; i < size; i += blockDim.x) keys[i] = 0ull;
+  while (size < count) size <<= 1;
+  for (int i = count + threadIdx.x; i < size; i += blockDim.x) keys[i] = 0ull;
   __syncthreads();
   if (size <= 64) {
     // a short list is sorted by the first warp alone: no block-wide barriers
@@ -307,6 +238,128 @@ __device__ bool sample_from_top_k(const float* p, int V, int k, float tp, float 
   return done;
 }
 
+// p: the row's probabilities. Ends with the chosen token in *out. Every thread of the block calls it.
+// must_reach: top-p has to be reached within these k (the caller has no top-k of its own and tries the k
+// most likely tokens first); if it is not, nothing is written and false returned, to every thread.
+__device__ bool sample_from_top_k(const float* p, int V, int k, float tp, float uniform_draw, int32_t* out,
+                                  int* sh_cnt, int* sh_i, bool must_reach, unsigned long long* keys, int* hist) {
+  const int kk = min(k, V);
+  // the kk-th largest probability by its bit pattern, a byte at a time from the top
+  uint32_t prefix = 0;
+  int remaining = kk;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    const uint32_t mask = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
+    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
+    __syncthreads();
+    // Probabilities crowd into a few bins (most share their exponent), so the lanes of a warp that
+    // hit the same bin add to it once, together.
+    const int padded = (V + 31) & ~31;
+    for (int i = threadIdx.x; i < padded; i += blockDim.x) {
+      const uint32_t b = i < V ? __float_as_uint(p[i]) : 0u;
+      const int bin = (i < V && (b & mask) == (prefix & mask)) ? (int)((b >> shift) & 255u) : 256;
+      const unsigned peers = __match_any_sync(0xffffffffu, bin);
+      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) pick_bin(hist, remaining, sh_i);
+    __syncthreads();
+    prefix |= (uint32_t)sh_i[0] << shift;
+    remaining = sh_i[1];
+    __syncthreads();
+  }
+  const uint32_t tau_bits = prefix;   // the kk-th largest; `remaining` of those equal to it are wanted
+  const int gt = kk - remaining;
+  if (must_reach && kk < V) {
+    // Before the list is gathered, sorted and walked: does its mass reach top-p at all? (With a slack
+    // for the order of the additions: a list that only just reaches it is walked and decides itself.)
+    __shared__ double part[32];
+    double above = 0.0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = p[i];
+      if (__float_as_uint(v) > tau_bits) above += (double)v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) above += __shfl_xor_sync(0xffffffffu, above, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = above;
+    __syncthreads();
+    double mass = (double)remaining * (double)__uint_as_float(tau_bits);
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mass += part[w];
+    __syncthreads();
+    if (mass < (double)tp * (1.0 - 1e-6)) return false;
+  }
+  // gather: everything above tau in any order (the sort below orders it), and of those equal to tau
+  // the `remaining` lowest token ids. For these every warp takes a run of the vocabulary and walks it
+  // 32 tokens at a time, so that ranks among the ties follow the token ids.
+  if (threadIdx.x == 0) sh_i[2] = 0;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int run = ((V + nw - 1) / nw + 31) & ~31;            // tokens per warp, whole walks of 32
+  const int lo = min(V, warp * run), hi = min(V, lo + run);
+  int ties = 0;
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const uint32_t b = i < hi ? __float_as_uint(p[i]) : 0u;
+    if (i < hi && b > tau_bits) keys[atomicAdd(&sh_i[2], 1)] = ((unsigned long long)b << 32) | (0xffffffffu - (uint32_t)i);
+    ties += __popc(__ballot_sync(0xffffffffu, i < hi && b == tau_bits));
+  }
+  if (lane == 0) sh_cnt[warp] = ties;
+  __syncthreads();
+  int before = 0;                                            // ties in the runs of the warps in front
+  for (int w = 0; w < warp; ++w) before += sh_cnt[w];
+  for (int base = lo; base < hi && before < remaining; base += 32) {
+    const int i = base + lane;
+    const bool tie = i < hi && __float_as_uint(p[i]) == tau_bits;
+    const unsigned votes = __ballot_sync(0xffffffffu, tie);
+    const int rank = before + __popc(votes & ((1u << lane) - 1u));
+    if (tie && rank < remaining) keys[gt + rank] = ((unsigned long long)tau_bits << 32) | (0xffffffffu - (uint32_t)i);
+    before += __popc(votes);
+  }
+  return sort_and_walk(keys, kk, kk, V, tp, uniform_draw, out, sh_i, must_reach);
+}
+
+// top_k below the number of threads, the usual case of all: no pass over the vocabulary beyond one
+// that picks candidates out. Every thread knows the largest probability among its own tokens; the k-th
+// largest of these maxima is a lower bound of the k-th largest probability (each of the k threads above
+// it holds a token at least that likely), so every one of the k most likely tokens, and every token
+// tied with the last of them, is at least that likely. Those tokens, a few more than k, are sorted and
+// walked. e: the exponentials before their division by the sum (p = e * inv, as the full pass computes
+// it); thread_max: the largest of the thread's own p. False, to every thread, if the candidates do not
+// fit the list (many equal probabilities): the caller goes on the general way.
+__device__ bool sample_from_short_list(const float* e, int V, int k, float inv, float thread_max, float tp,
+                                       float uniform_draw, int32_t* out, int* sh_i, unsigned long long* keys, int* hist) {
+  // the k-th largest maximum, to its upper 16 bits: a lower bound still
+  uint32_t prefix = 0;
+  int remaining = k;
+  const uint32_t mine = __float_as_uint(thread_max);
+  for (int shift = 24; shift >= 16; shift -= 8) {
+    const uint32_t mask = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
+    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
+    __syncthreads();
+    if ((mine & mask) == (prefix & mask)) atomicAdd(&hist[(mine >> shift) & 255u], 1);
+    __syncthreads();
+    if (threadIdx.x < 32) pick_bin(hist, remaining, sh_i);
+    __syncthreads();
+    prefix |= (uint32_t)sh_i[0] << shift;
+    remaining = sh_i[1];
+    __syncthreads();
+  }
+  const uint32_t bound = prefix;
+  if (threadIdx.x == 0) sh_i[2] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const uint32_t b = __float_as_uint(e[i] * inv);
+    if (b >= bound) {
+      const int at = atomicAdd(&sh_i[2], 1);
+      if (at < LIST_MAX) keys[at] = ((unsigned long long)b << 32) | (0xffffffffu - (uint32_t)i);
+    }
+  }
+  __syncthreads();
+  const int count = sh_i[2];
+  __syncthreads();      // before sh_i is used again
+  if (count > LIST_MAX || count < k) return false;
+  return sort_and_walk(keys, count, k, V, tp, uniform_draw, out, sh_i, false);
+}
+
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
@@ -317,6 +370,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   __shared__ int sh_i[64];
   __shared__ float sh_f[32];
   __shared__ int sh_cnt[1024];
+  __shared__ unsigned long long keys[LIST_MAX];   // probability bits, then ~token id: descending = by probability, then by id
+  __shared__ int hist[257];                       // bin 256 takes what a pass does not count
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
   float* p = in_shared ? row_shared : scratch + (size_t)r * V;
@@ -339,10 +394,12 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   for (int w = 0; w < nw; ++w) m = fmaxf(m, sh_f[w]);
   const bool finite_max = (m - m) == 0.f;  // neither infinite nor NaN
   double sum = 0.0;
+  float largest = 0.f;       // of this thread's exponentials
   for_each_logit(row, V, [&](int i, float v) {
     const float e = finite_max ? expf(v / temp - m) : 1.0f;
     p[i] = e;
     sum += (double)e;
+    largest = fmaxf(largest, e);
   });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -354,16 +411,20 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   const bool good = finite_max && (fsum - fsum) == 0.f && fsum > 0.f;  // a NaN among the inputs fails here
   const float inv = good ? 1.0f / fsum : 0.f;
   const float uniform = 1.0f / (float)V;
+  if (good && top_k[r] > 0 && top_k[r] < (int)blockDim.x && top_k[r] < V && top_k[r] <= LIST_MAX) {
+    __syncthreads();          // the exponentials of all threads are in place
+    if (sample_from_short_list(p, V, top_k[r], inv, largest * inv, top_p[r], u[r], out + r, sh_i, keys, hist)) return;
+  }
   for (int i = threadIdx.x; i < V; i += blockDim.x) p[i] = good ? p[i] * inv : uniform;
   __syncthreads();
 
   if (top_k[r] > 0 && top_k[r] <= LIST_MAX) {
-    sample_from_top_k(p, V, top_k[r], top_p[r], u[r], out + r, sh_cnt, sh_i, false);
+    sample_from_top_k(p, V, top_k[r], top_p[r], u[r], out + r, sh_cnt, sh_i, false, keys, hist);
     return;
   }
   // top-p alone (or with a top-k beyond the list): nearly always it is reached within the LIST_MAX most
   // likely tokens, and then those are all that matter
-  if (top_p[r] < 1.0f && sample_from_top_k(p, V, LIST_MAX, top_p[r], u[r], out + r, sh_cnt, sh_i, true)) return;
+  if (top_p[r] < 1.0f && sample_from_top_k(p, V, LIST_MAX, top_p[r], u[r], out + r, sh_cnt, sh_i, true, keys, hist)) return;
 
   // n: how many candidates survive top-k (:144-158) and top-p (:161-172)
   int n = V;
