@@ -291,22 +291,34 @@ def run_ours(args) -> dict:
 
     # ---------------------------------------------------------------- end to end through Engine.generate
     prompts = [rng.integers(0, V, context - K - W - 1).tolist() for _ in range(batch)]
+
+    def steady_rate(stamps):
+        """Tokens a second while all requests decode together: from the moment the last request to
+        start has had its W warm-up tokens (with long prompts the first requests decode beside the
+        others' prompt portions for a while) to the moment the first request ends."""
+        per = {}
+        for i, when in stamps:
+            per.setdefault(i, []).append(when)
+        if len(per) < batch or min(len(v) for v in per.values()) <= W:
+            return 0.0
+        t0 = max(v[W - 1] for v in per.values())
+        t1 = min(v[-1] for v in per.values())
+        inside = sorted(when for _, when in stamps if t0 <= when <= t1)
+        return (len(inside) - 1) / (inside[-1] - inside[0]) if len(inside) > 1 and inside[-1] > inside[0] else 0.0
+
     stamps = []
     engine.warm_up()      # graphs of the smaller batches, which the run's last rounds use as requests end
-    engine.generate(prompts, SamplingParams.greedy(max_tokens=K + W), on_token=lambda i, t: stamps.append(time.perf_counter()))
+    engine.generate(prompts, SamplingParams.greedy(max_tokens=K + W), on_token=lambda i, t: stamps.append((i, time.perf_counter())))
     torch.cuda.synchronize()
-    # the first W rounds of tokens are warm-up (they also hold the prefill); the rest is timed
-    timed = stamps[batch * W - 1:]
-    e2e_value = (len(timed) - 1) / (timed[-1] - timed[0]) if len(timed) > 1 else 0.0
+    e2e_value = steady_rate(stamps)
     cap = runner.graphs.graphs.get(batch)
     h2d = int(cap.pinned.numel() * 4) if cap is not None else 0
     # the same with sampled requests (the reference's default temperature, top-k and top-p), as a point
     stamps_s = []
     engine.generate(prompts, SamplingParams(temperature=0.8, top_k=40, top_p=0.95, max_tokens=K + W, seed=1),
-                    on_token=lambda i, t: stamps_s.append(time.perf_counter()))
+                    on_token=lambda i, t: stamps_s.append((i, time.perf_counter())))
     torch.cuda.synchronize()
-    timed_s = stamps_s[batch * W - 1:]
-    points["e2e_sampled"] = round((len(timed_s) - 1) / (timed_s[-1] - timed_s[0]) if len(timed_s) > 1 else 0.0, 1)
+    points["e2e_sampled"] = round(steady_rate(stamps_s), 1)
     engine.check_errors()
 
     return {
