@@ -591,6 +591,39 @@ def test_sampling_among_equal_probabilities_goes_by_token_id(ops):
         assert abs(got[i] - want) <= 1 and (k == 0 or got[i] < k), (rows[i], got[i], want)    # a draw on a boundary may round either way
 
 
+def test_sampling_with_ties_at_the_last_place_of_top_k(ops):
+    """Several tokens share the k-th largest logit: the ones with the lowest ids are the candidates,
+    whichever thread met them. Few enough ties for the short list of candidates, and (second half of
+    the rows) so many that the kernel falls back on its passes over the whole vocabulary."""
+    from tests.helpers import assert_tokens_follow_the_plain_sampler
+    V, k = 32000, 6
+    g = torch.Generator().manual_seed(3)
+    base = torch.randn(V, generator=g)
+    top = torch.topk(base, 4).indices.tolist()                 # four clear leaders
+    rows, logits = [], []
+    for ties in ([31000, 17, 9000, 1024, 2047], list(range(3000, 3000 + 1500, 1))):     # all at one value below the leaders
+        row = base.clone()
+        row[row > 2.5] = 2.0
+        for i, t in enumerate(top):
+            row[t] = 6.0 - 0.5 * i
+        row[torch.tensor(ties)] = 3.0                           # places 5 and 6 go to the two lowest ids among these
+        for u in (0.0, 0.3, 0.6, 0.9, 0.97, 0.999):
+            rows.append((1.0, k, 1.0, u))
+            logits.append(row)
+    R = len(rows)
+    logits = torch.stack(logits)
+    out = torch.zeros(R, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(R * V, device="cuda")
+    f = lambda i, dt: dev(torch.tensor([r[i] for r in rows], dtype=dt))
+    ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32), out, scratch)
+    got = out.tolist()
+    assert_tokens_follow_the_plain_sampler(rows, logits, got)
+    seen = set(got)
+    for i in range(R):
+        assert got[i] in set(top) | ({17, 1024} if i < 6 else {3000, 3001}), (i, got[i])
+    assert {17, 1024} & seen and {3000, 3001} & seen, "the tied candidates are reached by the later draws"
+
+
 @pytest.mark.parametrize("V", [50, 331, 32000, 128256])
 def test_sampling_follows_the_plain_sampler(ops, V):
     """At 128,256 entries a row's probabilities no longer fit in shared memory: the kernel keeps
