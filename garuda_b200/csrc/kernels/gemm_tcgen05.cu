@@ -137,16 +137,33 @@ struct Geometry {
   static constexpr int TMEM_COLS = COLS_NEEDED <= 32 ? 32 : COLS_NEEDED <= 64 ? 64 : COLS_NEEDED <= 128 ? 128
                                    : COLS_NEEDED <= 256 ? 256 : 512;
   static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
-  // bytes one CTA of a cluster sends to the leader: its whole accumulator
-  static constexpr int PARTIAL_BYTES = ACCUMULATORS * BN * BM * 4;
+  // The CTAs of a cluster exchange partial sums in chunks of 16 columns (tokens): chunk c is summed
+  // and written out by rank c % owners, owners = min(cluster, chunks); every other rank sends it
+  // its 16 columns of that chunk. A rank thus receives (cluster - 1) x (its chunks) x 8 KB.
+  static constexpr int CHUNKS = ACCUMULATORS * BN / 16;
+  static constexpr int CHUNK_BYTES = 16 * BM * 4;
+  static constexpr int owners(int cluster) { return cluster < CHUNKS ? cluster : CHUNKS; }
+  static constexpr int owned_most(int cluster) { return (CHUNKS + owners(cluster) - 1) / owners(cluster); }
+  static constexpr int receive_bytes(int cluster) { return (cluster - 1) * owned_most(cluster) * CHUNK_BYTES; }
   // statically declared shared memory (barriers) comes out of the same limit; EXTRA bytes lie
   // between the pipeline and the partial sums
   static constexpr int STATIC_RESERVE = 2 * 1024;
-  static constexpr int MAX_CLUSTER_RAW = 1 + (SMEM_LIMIT - STATIC_RESERVE - 1024 - PIPE_BYTES - EXTRA) / PARTIAL_BYTES;
-  static constexpr int MAX_CLUSTER = !TRANS ? 1 : (MAX_CLUSTER_RAW < 1 ? 1 : MAX_CLUSTER_RAW < 8 ? MAX_CLUSTER_RAW : 8);
   // + slack to align the tiles to 1024 B
   static constexpr int smem_bytes(int cluster, int stages = STAGES) {
-    return stages * STAGE_BYTES + 1024 + EXTRA + (cluster - 1) * PARTIAL_BYTES;
+    return stages * STAGE_BYTES + 1024 + EXTRA + receive_bytes(cluster);
+  }
+  static constexpr int max_cluster() {
+    int best = 1;
+    for (int c = 2; c <= 8; ++c)
+      if (smem_bytes(c) + STATIC_RESERVE <= SMEM_LIMIT) best = c;
+    return best;
+  }
+  static constexpr int MAX_CLUSTER = !TRANS ? 1 : max_cluster();
+  static constexpr int most_smem() {      // over the cluster sizes that fit
+    int most = smem_bytes(1);
+    for (int c = 2; c <= 8; ++c)
+      if (smem_bytes(c) + STATIC_RESERVE <= SMEM_LIMIT && smem_bytes(c) > most) most = smem_bytes(c);
+    return most;
   }
   static_assert(PIPE_BYTES + 1024 + EXTRA + STATIC_RESERVE <= SMEM_LIMIT, "tile and tables too large for shared memory");
   static constexpr int SMEM_BYTES = smem_bytes(1);
@@ -194,9 +211,12 @@ constexpr int C_THREADS = 192;   // warp 0: producer, warp 1: MMA issuer, warps 
 
 // Few tokens. rows_m / rows_n: valid rows of the MMA-row operand (the weights: output features)
 // and of the MMA-column operand (the tokens). The output is written transposed: out[token][feature].
-// The CTAs of a cluster (gridDim.z of them, along z) split the K blocks, kb_per_rank each. Every
-// CTA but rank 0 sends its accumulator to rank 0's shared memory with st.async, counted on rank
-// 0's mbarrier; rank 0 adds them in rank order and writes the result.
+// The CTAs of a cluster (gridDim.z of them, along z) split the K blocks, kb_per_rank each. The
+// tile's columns (tokens) are shared out in chunks of 16 among the first ranks (with 16 tokens:
+// rank 0 alone): a rank sends every chunk that is not its own to the chunk's owner with st.async,
+// counted on the owner's mbarrier; the owner adds the ranks' sums in rank order and writes the
+// chunk out. With 32 or 64 tokens the exchange, the epilogue and the memory for what is received
+// are thus spread over up to four CTAs.
 template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(C_THREADS, 1)
 gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
@@ -230,10 +250,16 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
   const int kb_begin = rank * kb_per_rank;
   const int num_kb = max(min(total_kb, kb_begin + kb_per_rank) - kb_begin, 0);
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  // [rank - 1][ACC * BN columns][128 rows] floats: the threads of a warp (consecutive rows) write and
-  // read consecutive words, so neither the remote stores nor the leader's loads collide on a bank
+  // what a rank receives: [sender, in rank order without itself][its chunk][16 columns][128 rows]
+  // floats: the threads of a warp (consecutive rows) write and read consecutive words, so neither
+  // the remote stores nor the owner's loads collide on a bank
   const uint32_t pipe_bytes = (uint32_t)stages * G::STAGE_BYTES;
   const uint32_t partials = tiles + pipe_bytes + rope_table_bytes(EPI, BN);
+  // chunk c of 16 tokens belongs to rank c % owners; this rank's are rank, rank + owners, ...
+  constexpr int CHUNKS = G::CHUNKS;
+  const int owners = ranks < CHUNKS ? ranks : CHUNKS;
+  const int owned_most = (CHUNKS + owners - 1) / owners;
+  const int my_chunks = rank < owners ? (CHUNKS - rank + owners - 1) / owners : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -244,7 +270,8 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     mbar_init(smem_u32(&partial_bar), 1);
     abort_s = 0;
     fence_barrier_init();
-    if (rank == 0 && ranks > 1) mbar_arrive_expect_tx(smem_u32(&partial_bar), (uint32_t)(ranks - 1) * G::PARTIAL_BYTES);
+    if (my_chunks > 0 && ranks > 1)
+      mbar_arrive_expect_tx(smem_u32(&partial_bar), (uint32_t)((ranks - 1) * my_chunks * G::CHUNK_BYTES));
     fence_proxy_async();
     prefetch_tensormap(&map_m);
     prefetch_tensormap(&map_n);
@@ -356,7 +383,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     float (*rope_cs)[64] = reinterpret_cast<float (*)[64]>(smem_raw + (tiles - smem_u32(smem_raw)) + pipe_bytes);
     float (*rope_sn)[64] = rope_cs + BN;
     long long* rope_slot = reinterpret_cast<long long*>(rope_sn + BN);   // element offset of the token's row, head 0; -1: no page
-    if (ROPE_EARLY && rank == 0) {
+    if (ROPE_EARLY && my_chunks > 0) {
       const int t = (int)threadIdx.x - 64;
       const int half = ra.head_dim >> 1, lg = 31 - __clz(half);      // head_dim divides 128: a power of two
       for (int e = t; e < BN * half; e += 128) {
@@ -382,19 +409,24 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     }
     constexpr bool emit = EPI == EPI_ACCUMULATE_NORM;                    // the norm behind this product is folded in
     constexpr bool ADD = EPI == EPI_ACCUMULATE || emit;
-    float old[ADD ? BN : 1];
+    float old[ADD ? BN : 1];                 // of this rank's chunks, in their order
     // each epilogue warp's sum of squares per token, in the pipeline's memory (idle by then; static
     // shared memory is kept small, so that two CTAs still fit on an SM)
     float (*red_s)[BN] = reinterpret_cast<float (*)[BN]>(smem_raw + (tiles - smem_u32(smem_raw)));
     float w_row = 0.f;
-    if (rank == 0) {
+    if (my_chunks > 0) {
       if (emit && row < rows_m) w_row = ra.weight[row];                 // a model constant: no need to wait
       gb::pdl_wait();
       if (ADD) {
         // what is to be added to is fetched while the matrix product runs
 #pragma unroll
-        for (int j = 0; j < BN; ++j)
-          old[j] = (row < rows_m && n0 + j < rows_n) ? gb::to_float<OT>(out[(size_t)(n0 + j) * ldo + row]) : 0.f;
+        for (int q = 0; q < CHUNKS; ++q) {
+          const int c = (rank + q * owners) * 16;       // first column of this rank's q-th chunk
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            old[ADD ? q * 16 + j : 0] = (q < my_chunks && row < rows_m && n0 + c + j < rows_n)
+                                            ? gb::to_float<OT>(out[(size_t)(n0 + c + j) * ldo + row]) : 0.f;
+        }
       }
       if (ra.sums_in != nullptr) {
         // the norm in front of this product: 1/rms of every token, from the partial sums (in tile
@@ -429,22 +461,24 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
       }
     };
 
-    if (rank != 0) {
-      if (num_kb > 0) {
-        // this thread's row of the accumulator into rank 0's shared memory
-        const uint32_t mine = partials + (uint32_t)(rank - 1) * G::PARTIAL_BYTES + (uint32_t)row_in_tile * 4;
-        const uint32_t remote = map_to_rank(mine, 0);
-        const uint32_t remote_bar = map_to_rank(smem_u32(&partial_bar), 0);
+    if (ranks > 1 && num_kb > 0) {
+      // this thread's row of every chunk that another rank owns, into that rank's shared memory
+      const int slot_of_mine = rank;         // among the senders of an owner o: rank if rank < o, else rank - 1
 #pragma unroll 1
-        for (int c = 0; c < ACC * BN; c += 16) {
-          float v[16];
-          load16(c, v);
+      for (int ch = 0; ch < CHUNKS; ++ch) {
+        const int o = ch % owners;
+        if (o == rank) continue;
+        const int slot = slot_of_mine < o ? slot_of_mine : slot_of_mine - 1;
+        const uint32_t there = partials + (uint32_t)((slot * owned_most + ch / owners) * G::CHUNK_BYTES) + (uint32_t)row_in_tile * 4;
+        const uint32_t remote = map_to_rank(there, (uint32_t)o);
+        const uint32_t remote_bar = map_to_rank(smem_u32(&partial_bar), (uint32_t)o);
+        float v[16];
+        load16(ch * 16, v);
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            st_async_f32(remote + (uint32_t)(c + j) * (BM * 4), remote_bar, have ? v[j] : 0.f);
-        }
+        for (int j = 0; j < 16; ++j) st_async_f32(remote + (uint32_t)j * (BM * 4), remote_bar, have ? v[j] : 0.f);
       }
-    } else {
+    }
+    if (my_chunks > 0) {
       if (ranks > 1) {
         const bool got = mbar_wait(smem_u32(&partial_bar), 0);
         if (!got && lane == 0) gb_err::report(ERR_WAIT_ACCUM);
@@ -457,16 +491,35 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
         // features. The up half hands its values over through shared memory (the pipeline's, which
         // is idle by now).
         float* xch = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)));   // [16][64 or 128]
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-          float v[16];
-          load16(c, v);
-          // the other ranks' sums, in rank order (the same sum every time); sixteen independent
-          // loads per rank, so that they overlap
-          for (int p = 1; p < ranks; ++p) {
-            const float* src = partial + (size_t)(p - 1) * (G::PARTIAL_BYTES / 4) + c * BM;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] += src[j * BM];
+        for (int q = 0; q < CHUNKS; ++q) {
+          if (q >= my_chunks) break;
+          const int c = (rank + q * owners) * 16;       // first column of this rank's q-th chunk
+          float own[16], v[16];
+          load16(c, own);
+          // all ranks' sums in rank order (the same sum every time), this rank's own in its place;
+          // sixteen independent loads per rank, so that they overlap
+          if (CHUNKS == 1) {        // rank 0 owns the one chunk
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = own[j];
+            for (int pr = 1; pr < ranks; ++pr) {
+              const float* src = partial + (size_t)(pr - 1) * (G::CHUNK_BYTES / 4);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += src[j * BM];
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            for (int pr = 0; pr < ranks; ++pr) {
+              if (pr == rank) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += own[j];
+              } else {
+                const float* src = partial + (size_t)(((pr < rank ? pr : pr - 1) * owned_most + q) * (G::CHUNK_BYTES / 4));
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += src[j * BM];
+              }
+            }
           }
           if (ra.sums_in != nullptr) {
 #pragma unroll
@@ -529,7 +582,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               sq[j] = 0.f;
               if (row >= rows_m || col >= rows_n) continue;
               float x = v[j];
-              if (ADD) x += old[ADD ? c + j : 0];
+              if (ADD) x += old[ADD ? q * 16 + j : 0];
               store_value<OT>(out + (size_t)col * ldo + row, x);
               if (emit) {
                 ra.h_out[(size_t)col * ldo + row] = __float2bfloat16_rn(x * w_row);
@@ -546,7 +599,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
           // this tile's sum of squares for every token: the four warps' parts in a fixed order
           asm volatile("bar.sync 1, 128;" ::: "memory");
           const int t = (int)threadIdx.x - 64;
-          if (t < BN && n0 + t < rows_n)
+          if (t < BN && (t >> 4) % owners == rank && n0 + t < rows_n)      // the tokens of this rank's chunks
             ra.sums_out[(size_t)blockIdx.y * ra.sums_ld + n0 + t] = red_s[0][t] + red_s[1][t] + red_s[2][t] + red_s[3][t];
         }
       }
@@ -1283,7 +1336,7 @@ int launch_cluster(const CUtensorMap& mm, const CUtensorMap& mn, OT* out, int ld
   static gb::OncePerDevice configured;
   if (configured.needed()) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         G::smem_bytes(G::MAX_CLUSTER));
+                                         G::most_smem());
     if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
     configured.done();
   }
