@@ -12,10 +12,24 @@ __device__ __forceinline__ void for_each_logit(const float* __restrict__ row, in
   if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
     const int n4 = V >> 2;
     const float4* r4 = reinterpret_cast<const float4*>(row);
-#pragma unroll 8
-    for (int q = threadIdx.x; q < n4; q += blockDim.x) {
-      const float4 v = r4[q];
-      f(4 * q, v.x); f(4 * q + 1, v.y); f(4 * q + 2, v.z); f(4 * q + 3, v.w);
+    // eight loads are asked for before the first value is used: f may store (to memory that the
+    // compiler cannot tell from the row), and a load behind a store would wait for it
+    constexpr int BATCH = 8;
+    const int stride = (int)blockDim.x;
+    for (int q0 = threadIdx.x; q0 < n4; q0 += BATCH * stride) {
+      float4 v[BATCH];
+#pragma unroll
+      for (int b = 0; b < BATCH; ++b) {
+        const int q = q0 + b * stride;
+        v[b] = q < n4 ? r4[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int b = 0; b < BATCH; ++b) {
+        const int q = q0 + b * stride;
+        if (q < n4) {
+          f(4 * q, v[b].x); f(4 * q + 1, v[b].y); f(4 * q + 2, v[b].z); f(4 * q + 3, v[b].w);
+        }
+      }
     }
     tail = 4 * n4;
   }
@@ -346,13 +360,15 @@ __device__ bool sample_from_short_list(const float* e, int V, int k, float inv, 
   const uint32_t bound = prefix;
   if (threadIdx.x == 0) sh_i[2] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const uint32_t b = __float_as_uint(e[i] * inv);
+  // (several loads in flight: with a vocabulary too large for shared memory the exponentials lie in
+  // global memory, and a loop of single loads would wait out the latency of each)
+  for_each_logit(e, V, [&](int i, float v) {
+    const uint32_t b = __float_as_uint(v * inv);
     if (b >= bound) {
       const int at = atomicAdd(&sh_i[2], 1);
       if (at < LIST_MAX) keys[at] = ((unsigned long long)b << 32) | (0xffffffffu - (uint32_t)i);
     }
-  }
+  });
   __syncthreads();
   const int count = sh_i[2];
   __syncthreads();      // before sh_i is used again
@@ -386,12 +402,15 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   // softmax(logits / temperature), with the reference's uniform fallbacks
   // (garuda/src/simd/mod.rs:132-158)
   float m = -INFINITY;
-  for_each_logit(row, V, [&](int, float v) { m = fmaxf(m, v / temp); });
+  // (the largest quotient is the quotient of the largest logit: division by a positive number is
+  // monotonic, also after rounding; one division instead of one per token)
+  for_each_logit(row, V, [&](int, float v) { m = fmaxf(m, v); });
   m = gb::warp_max(m);
   if (lane == 0) sh_f[warp] = m;
   __syncthreads();
   m = -INFINITY;
   for (int w = 0; w < nw; ++w) m = fmaxf(m, sh_f[w]);
+  m = m / temp;
   const bool finite_max = (m - m) == 0.f;  // neither infinite nor NaN
   double sum = 0.0;
   float largest = 0.f;       // of this thread's exponentials
