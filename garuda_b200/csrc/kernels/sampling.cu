@@ -376,21 +376,29 @@ __device__ bool sample_from_short_list(const float* e, int V, int k, float inv, 
   return sort_and_walk(keys, count, k, V, tp, uniform_draw, out, sh_i, false);
 }
 
-__global__ void __launch_bounds__(1024)
-sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
-              const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
-              const float* __restrict__ u, int32_t* __restrict__ out, float* __restrict__ scratch, int V,
-              int in_shared) {
-  extern __shared__ float row_shared[];      // in_shared: the row's probabilities live here, not in scratch
-  __shared__ double sh_d[32];
-  __shared__ int sh_i[64];
-  __shared__ float sh_f[32];
-  __shared__ int sh_cnt[1024];
-  __shared__ unsigned long long keys[LIST_MAX];   // probability bits, then ~token id: descending = by probability, then by id
-  __shared__ int hist[257];                       // bin 256 takes what a pass does not count
-  const int r = blockIdx.x;
+// What the sampling kernels keep in shared memory beside a row's probabilities.
+struct SampleShared {
+  double sh_d[32];
+  int sh_i[64];
+  float sh_f[32];
+  int sh_cnt[1024];
+  unsigned long long keys[LIST_MAX];   // probability bits, then ~token id: descending = by probability, then by id
+  int hist[257];                       // bin 256 takes what a pass does not count
+};
+
+// One row by one CTA: every thread of the block calls it. p: room for the row's probabilities
+// (shared memory, or the caller's scratch).
+__device__ void sample_row(const float* __restrict__ logits, const float* __restrict__ temperature,
+                           const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
+                           const float* __restrict__ u, int32_t* __restrict__ out, float* p, int V, int r,
+                           SampleShared& sh) {
+  double* sh_d = sh.sh_d;
+  int* sh_i = sh.sh_i;
+  float* sh_f = sh.sh_f;
+  int* sh_cnt = sh.sh_cnt;
+  unsigned long long* keys = sh.keys;
+  int* hist = sh.hist;
   const float* row = logits + (size_t)r * V;
-  float* p = in_shared ? row_shared : scratch + (size_t)r * V;
   const float temp = temperature[r];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   if (temp == 0.f) {  // greedy (:99-107)
@@ -506,6 +514,164 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   }
 }
 
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ u, int32_t* __restrict__ out, float* __restrict__ scratch, int V,
+              int in_shared) {
+  extern __shared__ float row_shared[];      // in_shared: the row's probabilities live here, not in scratch
+  __shared__ SampleShared sh;
+  const int r = blockIdx.x;
+  sample_row(logits, temperature, top_k, top_p, u, out, in_shared ? row_shared : scratch + (size_t)r * V, V, r, sh);
+}
+
+
+// ------------------------------------------------------------------ a row by a cluster of CTAs
+// One CTA works through a row at the pace of one SM's arithmetic: a division, an exponential and a
+// handful of other instructions per token and pass (60 us at 128,256 tokens). With a small top_k
+// the passes over the vocabulary are all there is to do, so the eight CTAs of a cluster take an
+// eighth of the row each: the maximum and the sum are exchanged through the cluster's shared
+// memory, every CTA bounds the k-th largest probability from below within its own part (see
+// sample_from_short_list; the largest of the bounds holds for the whole row), and the candidates go
+// straight into the first CTA's list, which sorts and walks them. Rows it does not take (greedy, no
+// or a large top_k, a degenerate softmax, more candidates than the list holds) are done by the
+// first CTA alone, the general way, in the caller's scratch memory.
+constexpr int ROW_CTAS = 8;
+constexpr int SMALL_K = 64;
+
+__device__ __forceinline__ uint32_t shared_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t in_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__global__ void __cluster_dims__(ROW_CTAS, 1, 1) __launch_bounds__(1024)
+sample_cluster_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                      const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
+                      const float* __restrict__ u, int32_t* __restrict__ out, float* __restrict__ scratch, int V) {
+  extern __shared__ float part_e[];          // this CTA's part of the row: the exponentials
+  __shared__ SampleShared sh;
+  __shared__ float c_max[ROW_CTAS];
+  __shared__ double c_sum[ROW_CTAS];
+  __shared__ uint32_t c_bound[ROW_CTAS];
+  const int r = blockIdx.x / ROW_CTAS;
+  const uint32_t rank = cluster_rank();
+  const float temp = temperature[r];
+  const int k = top_k[r];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  // the same for every CTA of the cluster: either all go on, or the first one works alone
+  if (temp == 0.f || k <= 0 || k > SMALL_K || k >= V) {
+    if (rank == 0) sample_row(logits, temperature, top_k, top_p, u, out, scratch + (size_t)r * V, V, r, sh);
+    return;
+  }
+  const float* row = logits + (size_t)r * V;
+  const int per = (((V + ROW_CTAS - 1) / ROW_CTAS) + 3) & ~3;     // a multiple of four: parts start on 16 bytes if the row does
+  const int lo = min(V, (int)rank * per), n = min(V, lo + per) - lo;
+
+  // the row's maximum
+  float m = -INFINITY;
+  for_each_logit(row + lo, n, [&](int, float v) { m = fmaxf(m, v); });
+  m = gb::warp_max(m);
+  if (lane == 0) sh.sh_f[warp] = m;
+  if (threadIdx.x == 0) sh.sh_i[2] = 0;            // the first CTA's count of candidates
+  __syncthreads();
+  if (threadIdx.x < ROW_CTAS) {
+    float mine = -INFINITY;
+    for (int w = 0; w < nw; ++w) mine = fmaxf(mine, sh.sh_f[w]);
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(in_rank(shared_u32(&c_max[rank]), threadIdx.x)), "f"(mine) : "memory");
+  }
+  cluster_sync_all();
+  m = -INFINITY;
+  for (int c = 0; c < ROW_CTAS; ++c) m = fmaxf(m, c_max[c]);
+  m = m / temp;
+  const bool finite_max = (m - m) == 0.f;
+
+  // exponentials of this part, their sum, every thread's largest
+  double sum = 0.0;
+  float largest = 0.f;
+  for_each_logit(row + lo, n, [&](int i, float v) {
+    const float e = finite_max ? expf(v / temp - m) : 1.0f;
+    part_e[i] = e;
+    sum += (double)e;
+    largest = fmaxf(largest, e);
+  });
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) sh.sh_d[warp] = sum;
+  __syncthreads();
+  // the k-th largest of the threads' maxima, to its upper 16 bits: at least k tokens of this part are
+  // at least that likely
+  uint32_t prefix = 0;
+  {
+    int remaining = k;
+    const uint32_t mine = __float_as_uint(largest);
+    for (int shift = 24; shift >= 16; shift -= 8) {
+      const uint32_t mask = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
+      if (threadIdx.x < 256) sh.hist[threadIdx.x] = 0;
+      __syncthreads();
+      if ((mine & mask) == (prefix & mask)) atomicAdd(&sh.hist[(mine >> shift) & 255u], 1);
+      __syncthreads();
+      if (threadIdx.x < 32) pick_bin(sh.hist, remaining, sh.sh_i);
+      __syncthreads();
+      prefix |= (uint32_t)sh.sh_i[0] << shift;
+      remaining = sh.sh_i[1];
+      __syncthreads();
+    }
+  }
+  if (threadIdx.x < ROW_CTAS) {
+    double mine = 0.0;
+    for (int w = 0; w < nw; ++w) mine += sh.sh_d[w];
+    asm volatile("st.shared::cluster.f64 [%0], %1;" ::"r"(in_rank(shared_u32(&c_sum[rank]), threadIdx.x)), "d"(mine) : "memory");
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(in_rank(shared_u32(&c_bound[rank]), threadIdx.x)), "r"(prefix) : "memory");
+  }
+  cluster_sync_all();
+  double total = 0.0;
+  uint32_t bound_e = 0;
+  for (int c = 0; c < ROW_CTAS; ++c) {
+    total += c_sum[c];
+    bound_e = max(bound_e, c_bound[c]);
+  }
+  const float fsum = (float)total;
+  const bool good = finite_max && (fsum - fsum) == 0.f && fsum > 0.f;
+  if (!good) {          // the same verdict in every CTA
+    if (rank == 0) sample_row(logits, temperature, top_k, top_p, u, out, scratch + (size_t)r * V, V, r, sh);
+    return;
+  }
+  const float inv = 1.0f / fsum;
+  // e >= bound implies e * inv >= bound * inv (rounding keeps the order)
+  const uint32_t bound = __float_as_uint(__uint_as_float(bound_e) * inv);
+  const uint32_t count_at = in_rank(shared_u32(&sh.sh_i[2]), 0), keys_at = in_rank(shared_u32(&sh.keys[0]), 0);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint32_t b = __float_as_uint(part_e[i] * inv);
+    if (b >= bound) {
+      uint32_t at;
+      asm volatile("atom.shared::cluster.add.u32 %0, [%1], 1;" : "=r"(at) : "r"(count_at) : "memory");
+      if (at < (uint32_t)LIST_MAX) {
+        const unsigned long long key = ((unsigned long long)b << 32) | (0xffffffffu - (uint32_t)(lo + i));
+        asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(keys_at + at * 8u), "l"(key) : "memory");
+      }
+    }
+  }
+  cluster_sync_all();
+  if (rank != 0) return;
+  const int count = sh.sh_i[2];
+  __syncthreads();      // before sh_i is used again
+  if (count > LIST_MAX || count < k) {       // many equal probabilities: the general way
+    sample_row(logits, temperature, top_k, top_p, u, out, scratch + (size_t)r * V, V, r, sh);
+    return;
+  }
+  sort_and_walk(sh.keys, count, k, V, top_p[r], u[r], out + r, sh.sh_i, false);
+}
+
 }  // namespace
 
 
@@ -535,6 +701,34 @@ int launch_sample(const float* logits, const float* temperature, const int32_t* 
   return gb::check_launch("sample");
 }
 }  // namespace
+
+// The same where every row is greedy or has a top_k of at most 64: eight CTAs share a row's passes
+// over the vocabulary (other rows are still right, only slower than through gb_sample).
+GB_EXPORT int gb_sample_small_k(const float* logits, const float* temperature, const int32_t* top_k,
+                                const float* top_p, const float* u, int32_t* out, float* scratch, int R, int V,
+                                cudaStream_t stream) {
+  if (R <= 0) return GB_OK;
+  if (V <= 0) return gb::fail(GB_BAD_ARGUMENT, "cannot sample from empty logits");
+  const int per = (((V + ROW_CTAS - 1) / ROW_CTAS) + 3) & ~3;
+  const size_t bytes = (size_t)per * sizeof(float);
+  // more rows than the SMs hold clusters of: one CTA per row is as fast (measured: 64 rows)
+  static int sms = [] {
+    int dev = 0, v = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v;
+  }();
+  if (bytes > 160 * 1024 || R * ROW_CTAS > sms)
+    return launch_sample(logits, temperature, top_k, top_p, u, out, scratch, R, V, stream);
+  static gb::OncePerDevice configured;
+  if (configured.needed()) {
+    cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "sample: %s", cudaGetErrorString(e));
+    configured.done();
+  }
+  sample_cluster_kernel<<<R * ROW_CTAS, 1024, bytes, stream>>>(logits, temperature, top_k, top_p, u, out, scratch, V);
+  return gb::check_launch("sample (clusters)");
+}
 
 // One token per row of logits [R, V]. Rows with temperature 0 are greedy.
 // scratch: R * V floats of work space (the probabilities, where a row does not fit in shared memory).

@@ -131,6 +131,8 @@ class CudaOps:
             "gb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
             "gb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                           c_void_p],
+            "gb_sample_small_k": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                  c_void_p],
         }
         for name, argtypes in sig.items():
             fn = getattr(L, name)
@@ -413,15 +415,21 @@ class CudaOps:
         self._check(self.core, self.core.gb_argmax(logits.data_ptr(), out.data_ptr(), R, V, self._stream()),
                     "argmax")
 
-    def sample(self, logits, temperature, top_k, top_p, u, out, scratch):
+    #: ``small_top_k`` may be said of rows that are greedy or have a top_k of 1 to this
+    SMALL_TOP_K = 64
+
+    def sample(self, logits, temperature, top_k, top_p, u, out, scratch, small_top_k: bool = False):
         """One token per row. ``temperature`` 0 is greedy; ``u`` is the row's uniform
-        draw. ``scratch``: float32 ``[R, V]`` work space."""
+        draw. ``scratch``: float32 ``[R, V]`` work space. ``small_top_k``: the caller knows
+        that every row is greedy or has a top_k of 1 to ``SMALL_TOP_K`` (eight CTAs then share a
+        row; the tokens are the same either way)."""
         self._on_device(logits, temperature, top_k, top_p, u, out, scratch)
         R, V = logits.shape
         _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: float32 logits")
         _need(temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and u.dtype == torch.float32
               and top_k.dtype == torch.int32 and out.dtype == torch.int32, "sample: parameter dtypes")
         _need(scratch.dtype == torch.float32 and scratch.numel() >= R * V, "sample: scratch too small")
-        self._check(self.core, self.core.gb_sample(
+        fn = self.core.gb_sample_small_k if small_top_k else self.core.gb_sample
+        self._check(self.core, fn(
             logits.data_ptr(), temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), u.data_ptr(),
             out.data_ptr(), scratch.data_ptr(), R, V, self._stream()), "sample")

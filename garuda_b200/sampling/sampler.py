@@ -92,5 +92,10 @@ class Sampler:
             params = torch.from_numpy(host)
         if self._scratch is None or self._scratch.numel() < R * V:
             self._scratch = torch.empty(R * V, dtype=torch.float32, device=self.device)
-        self.ops.sample(logits, params[0], params[3].view(torch.int32), params[1], params[2], out,
-                        self._scratch)
+        small = all(t == 0.0 or 0 < k <= getattr(self.ops, "SMALL_TOP_K", 0) for t, k in zip(temperature, top_k))
+        if small:
+            self.ops.sample(logits, params[0], params[3].view(torch.int32), params[1], params[2], out,
+                            self._scratch, small_top_k=True)
+        else:
+            self.ops.sample(logits, params[0], params[3].view(torch.int32), params[1], params[2], out,
+                            self._scratch)

@@ -618,6 +618,10 @@ def test_sampling_with_ties_at_the_last_place_of_top_k(ops):
     ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32), out, scratch)
     got = out.tolist()
     assert_tokens_follow_the_plain_sampler(rows, logits, got)
+    shared = torch.full((R,), -1, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32), shared, scratch,
+               small_top_k=True)
+    assert_tokens_follow_the_plain_sampler(rows, logits, shared.tolist())
     seen = set(got)
     for i in range(R):
         assert got[i] in set(top) | ({17, 1024} if i < 6 else {3000, 3001}), (i, got[i])
@@ -640,3 +644,10 @@ def test_sampling_follows_the_plain_sampler(ops, V):
     ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32),
                out, scratch)
     assert_tokens_follow_the_plain_sampler(rows, logits, out.tolist())
+    # the kernel in which eight CTAs share a row (meant for rows with a small top_k; it does the others the
+    # general way): the same tokens
+    shared = torch.full((R,), -1, dtype=torch.int32, device="cuda")
+    scratch.fill_(float("nan"))
+    ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32),
+               shared, scratch, small_top_k=True)
+    assert_tokens_follow_the_plain_sampler(rows, logits, shared.tolist())
