@@ -386,15 +386,21 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
     if (ROPE_EARLY && my_chunks > 0) {
       const int t = (int)threadIdx.x - 64;
       const int half = ra.head_dim >> 1, lg = 31 - __clz(half);      // head_dim divides 128: a power of two
-      for (int e = t; e < BN * half; e += 128) {
-        const int j = e >> lg, fi = e & (half - 1);
-        float sn = 0.f, cs = 1.f;
-        if (ra.cs != nullptr && n0 + j < rows_n) {
-          const float2 v = ra.cs[(size_t)(n0 + j) * half + fi];
-          cs = v.x, sn = v.y;
+      // only the tokens of this rank's chunks (with 64 tokens and heads of 128 the whole table is
+      // 4,096 entries, 32 loads in a row for every thread, and took longer than the product)
+      for (int q = 0; q < my_chunks; ++q) {
+        const int c = (rank + q * owners) * 16;
+#pragma unroll 4
+        for (int e = t; e < 16 * half; e += 128) {
+          const int j = c + (e >> lg), fi = e & (half - 1);
+          float sn = 0.f, cs = 1.f;
+          if (ra.cs != nullptr && n0 + j < rows_n) {
+            const float2 v = ra.cs[(size_t)(n0 + j) * half + fi];
+            cs = v.x, sn = v.y;
+          }
+          rope_cs[j][fi] = cs;
+          rope_sn[j][fi] = sn;
         }
-        rope_cs[j][fi] = cs;
-        rope_sn[j][fi] = sn;
       }
       if (t < BN) {
         long long slot = -1;
