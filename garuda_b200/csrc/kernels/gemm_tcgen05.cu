@@ -50,7 +50,10 @@ constexpr int BK = 64;    // bf16 per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int SMEM_LIMIT = 227 * 1024;          // most dynamic shared memory a CTA can have
 constexpr int SMEM_BUDGET_LARGE = 200 * 1024;   // many tokens: one CTA per SM, all of it pipeline
-constexpr int SMEM_BUDGET_SMALL = 110 * 1024;   // few tokens: pipeline depth that the stream of weights needs
+constexpr int SMEM_BUDGET_SMALL = 110 * 1024;   // up to 16 tokens: pipeline depth that the stream of weights needs
+// 32 or 64 tokens: a CTA has 20 or 24 KB per step of K in flight, and what is in flight bounds what
+// it takes in (four stages of 24 KB against 2 us of latency are 48 GB/s): as deep as fits
+constexpr int SMEM_BUDGET_MID = 192 * 1024;
 constexpr int SMEM_BUDGET_DUAL = 140 * 1024;    // few tokens, gate and up together
 
 // EPI_ACCUMULATE_NORM: accumulate, and fold in the first half of the norm that follows (EpilogueArgs::h_out);
@@ -130,7 +133,8 @@ struct Geometry {
   static constexpr int STAGE_BYTES = NUM_M * A_BYTES + NUM_N * B_BYTES;
   // shared memory for the operand pipeline; the swapped orientation leaves room for the partial sums
   // that the other CTAs of a cluster send, and (without them) for a second CTA on the SM
-  static constexpr int PIPE_BUDGET = !TRANS ? SMEM_BUDGET_LARGE : (DUAL_M ? SMEM_BUDGET_DUAL : SMEM_BUDGET_SMALL);
+  static constexpr int PIPE_BUDGET = !TRANS ? SMEM_BUDGET_LARGE
+                                     : DUAL_M ? SMEM_BUDGET_DUAL : BN >= 32 ? SMEM_BUDGET_MID : SMEM_BUDGET_SMALL;
   static constexpr int STAGES = (PIPE_BUDGET / STAGE_BYTES) < 8 ? (PIPE_BUDGET / STAGE_BYTES) : 8;
   static constexpr int ACCUMULATORS = NUM_M * NUM_N;
   static constexpr int COLS_NEEDED = ACCUMULATORS * BN;
@@ -152,20 +156,26 @@ struct Geometry {
   static constexpr int smem_bytes(int cluster, int stages = STAGES) {
     return stages * STAGE_BYTES + 1024 + EXTRA + receive_bytes(cluster);
   }
+  // the most stages (at most STAGES) with which a cluster of this size fits; 0: it does not fit
+  static constexpr int stages_that_fit(int cluster) {
+    int st = STAGES;
+    while (st >= 2 && smem_bytes(cluster, st) + STATIC_RESERVE > SMEM_LIMIT) --st;
+    return st >= 2 ? st : 0;
+  }
   static constexpr int max_cluster() {
     int best = 1;
     for (int c = 2; c <= 8; ++c)
-      if (smem_bytes(c) + STATIC_RESERVE <= SMEM_LIMIT) best = c;
+      if (stages_that_fit(c) >= (STAGES < 4 ? STAGES : 4)) best = c;
     return best;
   }
   static constexpr int MAX_CLUSTER = !TRANS ? 1 : max_cluster();
   static constexpr int most_smem() {      // over the cluster sizes that fit
-    int most = smem_bytes(1);
+    int most = smem_bytes(1, stages_that_fit(1));
     for (int c = 2; c <= 8; ++c)
-      if (smem_bytes(c) + STATIC_RESERVE <= SMEM_LIMIT && smem_bytes(c) > most) most = smem_bytes(c);
+      if (stages_that_fit(c) > 0 && smem_bytes(c, stages_that_fit(c)) > most) most = smem_bytes(c, stages_that_fit(c));
     return most;
   }
-  static_assert(PIPE_BYTES + 1024 + EXTRA + STATIC_RESERVE <= SMEM_LIMIT, "tile and tables too large for shared memory");
+  static_assert(2 * STAGE_BYTES + 1024 + EXTRA + STATIC_RESERVE <= SMEM_LIMIT, "tile and tables too large for shared memory");
   static constexpr int SMEM_BYTES = smem_bytes(1);
   static_assert(STAGES >= 2, "tile too large for shared memory");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
@@ -1295,11 +1305,13 @@ ClusterPlan pick_cluster_plan(Kernel kernel, int* active, int tiles, int total_k
   double best_cost = 1e30;
   const int sms = sm_count();
   for (int s = 1; s <= G::MAX_CLUSTER && s <= 6 && s <= total_kb; ++s) {
+    const int st1 = G::stages_that_fit(s);       // one CTA per SM: as deep a pipeline as fits
+    if (st1 < 2) continue;
     if (active[s] == 0) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(1, 148, s);
       cfg.blockDim = dim3(C_THREADS);
-      cfg.dynamicSmemBytes = G::smem_bytes(s);
+      cfg.dynamicSmemBytes = G::smem_bytes(s, st1);
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
       attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = s;
@@ -1315,10 +1327,12 @@ ClusterPlan pick_cluster_plan(Kernel kernel, int* active, int tiles, int total_k
     if (active[s] < 1) continue;
     const int per = (total_kb + s - 1) / s;
     const int ctas = tiles * s;
-    // one CTA per SM
+    // one CTA per SM; whole clusters must find room in one GPC, so fewer may be resident than
+    // the SMs would hold CTAs
     {
-      const double cost = (double)((ctas + sms - 1) / sms) * (per + 13.5);
-      if (cost < best_cost) { best_cost = cost; best = ClusterPlan{s, G::STAGES}; }
+      const int rounds = (tiles + active[s] - 1) / active[s];
+      const double cost = (double)rounds * (per + 13.5);
+      if (cost < best_cost) { best_cost = cost; best = ClusterPlan{s, st1}; }
     }
     // two per SM: the most stages that let two CTAs (and their 1 KB each of reserve) share 227 KB
     int st2 = G::STAGES;
