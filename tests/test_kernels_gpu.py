@@ -629,6 +629,28 @@ def test_sampling_with_ties_at_the_last_place_of_top_k(ops):
 
 
 @pytest.mark.parametrize("V", [50, 331, 32000, 128256])
+def test_sampling_rows_shared_by_clusters(ops, V):
+    """Few enough rows for a cluster of eight CTAs each: rows with a small top_k go the shared way
+    (each CTA an eighth of the vocabulary, also where an eighth is less than top_k), the others
+    (greedy, top-p alone, a large top_k) are done by the cluster's first CTA alone."""
+    from tests.helpers import assert_tokens_follow_the_plain_sampler
+    settings = [(0.8, 40, 0.95), (1.0, 64, 1.0), (0.5, 5, 1.0), (0.0, 40, 0.95), (0.8, 1, 0.95), (2.0, 30, 0.5),
+                (1.3, 0, 0.7), (1.5, 100, 0.9)]
+    for u in (0.0, 0.37, 0.999):
+        rows = [(t, k, p, u) for t, k, p in settings]
+        R = len(rows)
+        g = torch.Generator().manual_seed(V + int(u * 100))
+        logits = torch.randn(R, V, generator=g) * 2
+        logits[1, 5] = logits[1, V - 2] = logits[1].max() + 1          # ties among the most likely, in two CTAs' parts
+        out = torch.full((R,), -1, dtype=torch.int32, device="cuda")
+        scratch = torch.full((R * V,), float("nan"), device="cuda")
+        f = lambda i, dt: dev(torch.tensor([r[i] for r in rows], dtype=dt))
+        ops.sample(dev(logits), f(0, torch.float32), f(1, torch.int32), f(2, torch.float32), f(3, torch.float32),
+                   out, scratch, small_top_k=True)
+        assert_tokens_follow_the_plain_sampler(rows, logits, out.tolist())
+
+
+@pytest.mark.parametrize("V", [50, 331, 32000, 128256])
 def test_sampling_follows_the_plain_sampler(ops, V):
     """At 128,256 entries a row's probabilities no longer fit in shared memory: the kernel keeps
     them in the caller's scratch instead (another branch of it, and the one a Llama-3 vocabulary takes)."""
