@@ -20,8 +20,8 @@ struct Params {
   float scale_log2;              // scale * log2(e)
 };
 
-// True if the tcgen05 kernel takes this shape (head size 64, a power-of-two group, pages of a
-// multiple of 8 keys that divide 128).
+// True if the tcgen05 kernel takes this shape (head size 64 or 128, a power-of-two group, pages of
+// a multiple of 8 keys that divide 128).
 bool tile_tc_takes(const Params& p, int T, long long pages);
 // Launches it for every request with more than ROWS_DECODE rows. Returns a GbStatus.
 int launch_tile_tc(const Params& p, int T, long long pages, int R, int max_q_len, cudaStream_t stream);
