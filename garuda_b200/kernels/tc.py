@@ -196,8 +196,8 @@ class TensorCoreKernels:
 
         The kernel that copies pages by TMA (head sizes 64 and 128). A few requests: a cluster per
         (request, kv head), as many CTAs as the SMs take one each, every CTA with at least 8 tiles
-        of 32 keys, clusters above four only while the whole grid stays within 64 CTAs (larger ones
-        are placed late). When that would leave clusters of under four (many requests, or many kv
+        of 32 keys, clusters of eight for up to 12 (request, kv head) pairs, of six for up to 20
+        (more of them than that do not fit the GPU at once and run in two rounds). When that would leave clusters of under four (many requests, or many kv
         heads): independent CTAs that merge through scratch memory, about 256 in all, each with at
         least 16 tiles, at most 16 per request.
 
@@ -209,7 +209,11 @@ class TensorCoreKernels:
         if head_dim in (64, 128):
             tiles = max((max_kv_len + 31) // 32, 1)
             c = min(148 // pairs, tiles // 8, 8 if head_dim == 64 else 4)
-            if c > 4 and pairs * c > 64:
+            # whole clusters have to find room in one GPC: the GPU holds 12 clusters of eight and 20
+            # of six at once (16 and 24 ran in two rounds); clusters of four it holds 32 of
+            if c > 6 and pairs > 12:
+                c = 6
+            if c > 4 and pairs > 20:
                 c = 4
             independent = max(1, min(256 // pairs, tiles // 16, 16))
             # clusters, unless they would be under four CTAs or independent CTAs would put twice as many

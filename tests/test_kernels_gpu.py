@@ -410,7 +410,7 @@ DECODE_TMA_CASES = [
 ]
 
 
-@pytest.mark.parametrize("ranks,cluster", [(1, 0), (2, 0), (3, 0), (4, 0), (8, 0), (16, 0), (2, 1), (3, 1), (4, 1), (8, 1)])
+@pytest.mark.parametrize("ranks,cluster", [(1, 0), (2, 0), (3, 0), (4, 0), (8, 0), (16, 0), (2, 1), (3, 1), (4, 1), (6, 1), (8, 1)])
 @pytest.mark.parametrize("Hq,Hkv,hd,page,reqs,window", DECODE_TMA_CASES)
 def test_attention_decode_with_tma_page_copies(ops, Hq, Hkv, hd, page, reqs, window, ranks, cluster):
     """The decode kernel that fetches pages by TMA, with every way of splitting a request's keys
