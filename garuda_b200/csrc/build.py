@@ -35,7 +35,7 @@ KERNEL_LIBS: Dict[str, List[str]] = {
     "garuda_core": ["elementwise.cu", "gemm_simple.cu", "attention_simple.cu", "sampling.cu"],
     "garuda_tc": ["gemm_tcgen05.cu"],
 }
-HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "bindings.cpp"]
+HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "step_batch.cpp", "bindings.cpp"]
 
 
 class BuildError(RuntimeError):

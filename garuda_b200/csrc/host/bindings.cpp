@@ -1,13 +1,48 @@
-// Python bindings of the host runtime: cache manager, scheduler, generator.
+// Python bindings of the host runtime: cache manager, step batches, scheduler, generator.
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
 #include "cache_manager.hpp"
 #include "scheduler.hpp"
+#include "step_batch.hpp"
 
 namespace py = pybind11;
 using namespace garuda;
+
+namespace {
+
+// A batch from Python, converted once for the check and for the arrays: any sequence of objects
+// with `request`, `tokens` and `want`.
+struct StepRequests {
+  std::vector<StepRequest> items;
+};
+
+StepRequests step_requests(const py::sequence& entries) {
+  StepRequests out;
+  out.items.reserve(py::len(entries));
+  try {
+    for (const py::handle& e : entries) {
+      StepRequest r;
+      r.request = e.attr("request").cast<int64_t>();
+      for (const py::handle& t : e.attr("tokens")) r.tokens.push_back(t.cast<int64_t>());
+      for (const py::handle& w : e.attr("want")) r.want.push_back(w.cast<int64_t>());
+      out.items.push_back(std::move(r));
+    }
+  } catch (const py::cast_error&) {
+    throw StepError("a step's request ids, tokens and wanted places must be integers");
+  }
+  return out;
+}
+
+int32_t* words_of(py::array_t<int32_t, py::array::c_style>& buffer, int needed) {
+  if (buffer.ndim() != 1 || buffer.shape(0) < needed)
+    throw StepError("the batch's buffer holds " + std::to_string(buffer.size()) + " words, the batch needs " +
+                    std::to_string(needed));
+  return buffer.mutable_data();
+}
+
+}  // namespace
 
 PYBIND11_MODULE(_garuda_host, m) {
   m.doc() = "garuda_b200 host runtime: paged-cache bookkeeping, scheduler, splitmix64";
@@ -73,6 +108,59 @@ PYBIND11_MODULE(_garuda_host, m) {
       .def("check_invariants", &CacheManager::check_invariants)
       .def_property_readonly("pages_handed_out", &CacheManager::pages_handed_out)
       .def_property_readonly("pages_reused", &CacheManager::pages_reused);
+
+  py::register_exception<StepError>(m, "StepError", PyExc_ValueError);
+
+  py::class_<StepRequests>(m, "StepRequests")
+      .def(py::init(&step_requests), py::arg("entries"))
+      .def("__len__", [](const StepRequests& v) { return v.items.size(); })
+      .def_property_readonly("requests", [](const StepRequests& v) {
+        std::vector<int64_t> ids;
+        for (const StepRequest& r : v.items) ids.push_back(r.request);
+        return ids;
+      });
+
+  py::class_<BatchLayout>(m, "BatchLayout")
+      .def_readonly("token_ids", &BatchLayout::token_ids)
+      .def_readonly("positions", &BatchLayout::positions)
+      .def_readonly("token_req", &BatchLayout::token_req)
+      .def_readonly("cu_q", &BatchLayout::cu_q)
+      .def_readonly("kv_lens", &BatchLayout::kv_lens)
+      .def_readonly("slots", &BatchLayout::slots)
+      .def_readonly("logit_rows", &BatchLayout::logit_rows)
+      .def_readonly("tables", &BatchLayout::tables)
+      .def_readonly("words", &BatchLayout::words)
+      .def_readonly("tokens", &BatchLayout::tokens)
+      .def_readonly("rows", &BatchLayout::rows)
+      .def_readonly("wanted", &BatchLayout::wanted)
+      .def_readonly("groups", &BatchLayout::groups)
+      .def_readonly("table_width", &BatchLayout::table_width)
+      .def_readonly("max_q", &BatchLayout::max_q)
+      .def_readonly("max_kv", &BatchLayout::max_kv)
+      .def_readonly("min_q", &BatchLayout::min_q);
+
+  py::class_<Reserved>(m, "Reserved")
+      .def_readonly("new_lens", &Reserved::new_lens)
+      .def_readonly("starting_slots", &Reserved::starting_slots);
+
+  py::class_<StepBuilder>(m, "StepBuilder")
+      .def(py::init<CacheManager*, int>(), py::arg("cache"), py::arg("vocab"), py::keep_alive<1, 2>())
+      .def("check_and_reserve", [](StepBuilder& b, const StepRequests& entries) { return b.check_and_reserve(entries.items); })
+      .def("commit", &StepBuilder::commit)
+      .def("layout", [](const StepBuilder& b, const StepRequests& entries) { return b.layout(entries.items); })
+      .def("decode_layout", &StepBuilder::decode_layout)
+      .def("fill",
+           [](const StepBuilder& b, const StepRequests& entries,
+              const std::vector<std::pair<int64_t, int>>& new_lens, BatchLayout& layout,
+              py::array_t<int32_t, py::array::c_style> buffer) {
+             b.fill(entries.items, new_lens, layout, words_of(buffer, layout.words));
+           })
+      .def("fill_decode",
+           [](const StepBuilder& b, const StepRequests& entries,
+              const std::vector<std::pair<int64_t, int>>& new_lens, const BatchLayout& layout,
+              py::array_t<int32_t, py::array::c_style> buffer) {
+             b.fill_decode(entries.items, new_lens, layout, words_of(buffer, layout.words));
+           });
 
   py::class_<Rng>(m, "Rng")
       .def(py::init<uint64_t>(), py::arg("seed") = 0)

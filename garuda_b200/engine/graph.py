@@ -11,9 +11,8 @@ page, which the kernels skip.
 from __future__ import annotations
 
 import gc
-from typing import Dict, List, Sequence
+from typing import Dict
 
-import numpy as np
 import torch
 
 from .batch import StepBatch, StepContext, Workspace
@@ -27,8 +26,8 @@ def _bucket(n: int) -> int:
 
 
 class _Captured:
-    def __init__(self, graph, logits, host, dev, offs):
-        self.graph, self.logits, self.host, self.dev, self.offs = graph, logits, host, dev, offs
+    def __init__(self, graph, logits, host, dev, layout):
+        self.graph, self.logits, self.host, self.dev, self.layout = graph, logits, host, dev, layout
 
 
 class DecodeGraphs:
@@ -43,66 +42,28 @@ class DecodeGraphs:
         return (self.runner.model.graph_safe and len(entries) <= self.max_bucket
                 and all(len(e.tokens) == 1 for e in entries))
 
-    # ------------------------------------------------------------------ layout
-    def _layout(self, B: int):
-        mgr = self.runner.cache.manager
-        G, width = mgr.num_groups, self.runner.cache.table_width
-        offs, cursor = {}, 0
-        for name, n in (("token_ids", B), ("positions", B), ("token_req", B), ("cu_q", B + 1),
-                        ("kv_lens", B), ("slots", B), ("logit_rows", B), ("tables", G * B * width)):
-            offs[name] = (cursor, n)
-            cursor += (n + 3) // 4 * 4
-        return offs, cursor
-
-    def _fill(self, cap: _Captured, B: int, entries, new_lens) -> None:
-        mgr = self.runner.cache.manager
-        G, width = mgr.num_groups, self.runner.cache.table_width
-        h = cap.host
-
-        def view(name):
-            o, n = cap.offs[name]
-            return h[o:o + n]
-
-        R = len(entries)
-        token_ids, positions = view("token_ids"), view("positions")
-        kv_lens, slots = view("kv_lens"), view("slots")
-        token_ids[:] = 0
-        positions[:] = 0
-        kv_lens[:] = 1
-        slots[:] = -1          # padding rows have no state slot
-        view("token_req")[:] = np.arange(B, dtype=np.int32)
-        view("cu_q")[:] = np.arange(B + 1, dtype=np.int32)
-        view("logit_rows")[:] = np.arange(B, dtype=np.int32)
-        tables = view("tables").reshape(G, B, width) if G else None
-        if G:
-            tables[:] = -1
-        for i, (e, (_, new_len)) in enumerate(zip(entries, new_lens)):
-            token_ids[i] = int(e.tokens[0])
-            positions[i] = new_len - 1
-            kv_lens[i] = new_len
-            slots[i] = mgr.slot(e.request)
-        if G and R:
-            mgr.fill_block_tables([e.request for e in entries], tables)
-
+    # ------------------------------------------------------------------ arrays
     def _batch(self, cap: _Captured, B: int) -> StepBatch:
         mgr = self.runner.cache.manager
-        G, width = mgr.num_groups, self.runner.cache.table_width
+        lay = cap.layout
+        G, width = lay.groups, lay.table_width
 
-        def dview(name):
-            o, n = cap.offs[name]
-            return cap.dev[o:o + n]
+        def dview(at, n):
+            return cap.dev[at:at + n]
 
-        tables = [dview("tables").view(G, B, width)[g] for g in range(G)] if G else []
-        return StepBatch(num_tokens=B, num_requests=B, token_ids=dview("token_ids"),
-                         positions=dview("positions"), token_req=dview("token_req"), cu_q=dview("cu_q"),
-                         kv_lens=dview("kv_lens"), slots=dview("slots"), block_tables=tables,
-                         logit_rows=dview("logit_rows"), num_logit_rows=B, max_q_len=1,
-                         max_kv_len=mgr.max_positions, host={})
+        tables = [dview(lay.tables, G * B * width).view(G, B, width)[g] for g in range(G)] if G else []
+        return StepBatch(num_tokens=B, num_requests=B, token_ids=dview(lay.token_ids, B),
+                         positions=dview(lay.positions, B), token_req=dview(lay.token_req, B),
+                         cu_q=dview(lay.cu_q, B + 1), kv_lens=dview(lay.kv_lens, B), slots=dview(lay.slots, B),
+                         block_tables=tables, logit_rows=dview(lay.logit_rows, B), num_logit_rows=B,
+                         max_q_len=1, max_kv_len=mgr.max_positions, host={})
 
     # ------------------------------------------------------------------ capture
     def _capture(self, B: int) -> _Captured:
         r = self.runner
-        offs, size = self._layout(B)
+        # the arrays of a step of B single tokens, as the C++ step builder lays them out and fills them
+        layout = r.builder.decode_layout(B)
+        size = layout.words
         # Two pinned staging buffers in turn, each with an event that tells when its copy to the device
         # has run: a caller that does not read a step's logits (a prompt's unwanted tokens, a timing
         # loop) comes back before the copy of the step in front has happened, and must not overwrite
@@ -110,10 +71,10 @@ class DecodeGraphs:
         staging = [torch.empty(size, dtype=torch.int32).pin_memory() for _ in range(2)]
         host = staging[0]
         dev = torch.zeros(size, dtype=torch.int32, device=r.device)
-        cap = _Captured(None, None, host.numpy(), dev, offs)
+        cap = _Captured(None, None, host.numpy(), dev, layout)
         cap.pinned = host
         cap.staging, cap.copied, cap.turn = staging, [None, None], 0
-        self._fill(cap, B, [], [])
+        r.builder.fill_decode(r.host.StepRequests([]), [], layout, cap.host)
         dev.copy_(host, non_blocking=True)
         batch = self._batch(cap, B)
         ws = Workspace(r.device)
@@ -168,9 +129,10 @@ class DecodeGraphs:
         return cap.launches if cap is not None else 0
 
     # ------------------------------------------------------------------ run
-    def run(self, entries, new_lens, device_tokens=None) -> torch.Tensor:
-        """``device_tokens``: int32 on the device, the entries' tokens in their order, for a step
-        whose tokens the host does not know yet (they come from the step in front)."""
+    def run(self, entries, requests, new_lens, device_tokens=None) -> torch.Tensor:
+        """``requests``: the entries as the step builder holds them. ``device_tokens``: int32 on the
+        device, the entries' tokens in their order, for a step whose tokens the host does not know
+        yet (they come from the step in front)."""
         B = _bucket(len(entries))
         cap = self.graphs.get(B)
         if cap is None:
@@ -180,13 +142,13 @@ class DecodeGraphs:
         cap.host = cap.pinned.numpy()
         if cap.copied[cap.turn] is not None:
             cap.copied[cap.turn].synchronize()      # the copy that last read this buffer has run
-        self._fill(cap, B, entries, new_lens)
+        self.runner.builder.fill_decode(requests, new_lens, cap.layout, cap.host)
         cap.dev.copy_(cap.pinned, non_blocking=True)
         if cap.copied[cap.turn] is None:
             cap.copied[cap.turn] = torch.cuda.Event()
         cap.copied[cap.turn].record()
         if device_tokens is not None:
-            o, _ = cap.offs["token_ids"]
+            o = cap.layout.token_ids
             cap.dev[o:o + len(entries)].copy_(device_tokens[:len(entries)])
         cap.graph.replay()
         self.replays += 1

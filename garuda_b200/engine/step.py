@@ -34,16 +34,18 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=tuple)   # places among them whose logits are wanted
 
 
-def _align(n: int, a: int = 4) -> int:
-    return (n + a - 1) // a * a
-
-
 class StepRunner:
+    """Runs steps. Its host half is the C++ ``StepBuilder`` (``csrc/host/step_batch.hpp``): it checks
+    a batch, reserves its pages and writes the arrays that the kernels read into one pinned buffer,
+    which goes to the device in one copy."""
+
     def __init__(self, model, cache: PagedCache, ops, dtype: torch.dtype, device):
         self.model, self.cache, self.ops, self.dtype = model, cache, ops, dtype
         self.device = torch.device(device)
         self.ws = Workspace(self.device)
         self.vocab = model.spec.vocab_size
+        self.host = cache.host_module
+        self.builder = self.host.StepBuilder(cache.manager, self.vocab)
         self.steps = 0
         self.tokens_run = 0
         self.graphs = None        # DecodeGraphs, when decode steps are replayed from CUDA graphs
@@ -56,127 +58,49 @@ class StepRunner:
 
     # ------------------------------------------------------------------ checks
     def _validate_and_reserve(self, entries: Sequence[StepEntry]):
-        mgr = self.cache.manager
-        if not entries:
-            raise StepError("a step needs at least one entry")
-        seen = set()
-        wants = []
-        fresh = []
-        starting = []          # requests whose first token this step runs
-        for e in entries:
-            if e.request in seen:
-                raise StepError(f"request {e.request} appears twice in one step")
-            seen.add(e.request)
-            n = len(e.tokens)
-            if n == 0:
-                raise StepError(f"request {e.request} brings no tokens")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab:
-                    raise StepError(f"token {t} of request {e.request} is outside the vocabulary of {self.vocab}")
-            for w in e.want:
-                if not 0 <= int(w) < n:
-                    raise StepError(f"request {e.request} wants logits at place {w} of {n} tokens")
-            known = mgr.known(e.request)
-            old = mgr.length(e.request) if known else 0
-            if old + n > mgr.max_positions:
-                raise StepError(f"{n} tokens do not fit the {mgr.max_positions}-position context "
-                                f"({old} used) of request {e.request}")
-            if not known:
-                fresh.append(e.request)
-            if old == 0:
-                starting.append(e.request)
-            wants.append((e.request, old + n))
-        if len(fresh) > mgr.free_slots:
-            raise StepError(f"{len(fresh)} new requests but only {mgr.free_slots} request slots are free")
-        for r in fresh:
-            self.cache.acquire(r)
+        """The batch for the C++ side and what it reserved: ``(requests, new_lens)``, ``new_lens``
+        a list of (request, its length after the step). Raises with nothing changed."""
         try:
-            if not mgr.can_reserve(wants):
-                need = [mgr.pages_needed(r, n) for r, n in wants]
-                total = [sum(x[g] for x in need) for g in range(mgr.num_groups)]
-                free = [mgr.free_pages(g) for g in range(mgr.num_groups)]
-                raise self.cache.host_module.OutOfPages(
-                    f"the step needs {total} pages per group but only {free} are free")
-            for r, n in wants:
-                mgr.reserve(r, n)
-        except Exception:
-            for r in fresh:
-                mgr.release(r)
-            raise
+            requests = self.host.StepRequests(entries)
+            reserved = self.builder.check_and_reserve(requests)
+        except self.host.StepError as e:
+            raise StepError(str(e)) from None
         # A request that starts at position 0 starts from zeroed fixed-size state, whoever took its
-        # slot (this runner just now, or a scheduler that admitted it, or readmitted it after it
+        # slot (this step just now, or a scheduler that admitted it, or readmitted it after it
         # had been preempted) and whoever held the slot before.
-        if starting and self.cache.states:
-            self.cache.reset_states([mgr.slot(r) for r in starting])
-        return wants
+        if reserved.starting_slots and self.cache.states:
+            self.cache.reset_states(reserved.starting_slots)
+        return requests, reserved.new_lens
 
     # ------------------------------------------------------------------ batch
-    def build_batch(self, entries: Sequence[StepEntry], new_lens) -> StepBatch:
-        mgr = self.cache.manager
-        R = len(entries)
-        T = sum(len(e.tokens) for e in entries)
-        W = sum(len(e.want) for e in entries)
-        G, width = mgr.num_groups, self.cache.table_width
-        offs = {}
-        cursor = 0
-        for name, n in (("token_ids", T), ("positions", T), ("token_req", T), ("cu_q", R + 1),
-                        ("kv_lens", R), ("slots", R), ("logit_rows", max(W, 1)),
-                        ("tables", G * R * width)):
-            offs[name] = (cursor, n)
-            cursor += _align(n)
-        pinned = self._stage(cursor)
-        host = pinned.numpy()[:cursor] if pinned is not None else np.empty(cursor, dtype=np.int32)
-
-        def view(name):
-            o, n = offs[name]
-            return host[o:o + n]
-
-        token_ids, positions, token_req = view("token_ids"), view("positions"), view("token_req")
-        cu_q, kv_lens, slots, logit_rows = view("cu_q"), view("kv_lens"), view("slots"), view("logit_rows")
-        logit_rows[:] = 0
-        t = w = 0
-        cu_q[0] = 0
-        max_q = max_kv = 0
-        min_q = 1 << 30
-        for i, (e, (_, new_len)) in enumerate(zip(entries, new_lens)):
-            n = len(e.tokens)
-            start = new_len - n
-            token_ids[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
-            positions[t:t + n] = np.arange(start, new_len, dtype=np.int32)
-            token_req[t:t + n] = i
-            for place in e.want:
-                logit_rows[w] = t + int(place)
-                w += 1
-            t += n
-            cu_q[i + 1] = t
-            kv_lens[i] = new_len
-            slots[i] = mgr.slot(e.request)
-            max_q, max_kv, min_q = max(max_q, n), max(max_kv, new_len), min(min_q, n)
-        tables = view("tables").reshape(G, R, width) if G else None
-        if G:
-            mgr.fill_block_tables([e.request for e in entries], tables)
-
+    def build_batch(self, requests, new_lens) -> StepBatch:
+        lay = self.builder.layout(requests)
+        pinned = self._stage(lay.words)
+        host = pinned.numpy() if pinned is not None else np.empty(lay.words, dtype=np.int32)
+        self.builder.fill(requests, new_lens, lay, host)
         if pinned is not None:
-            dev = pinned[:cursor].to(self.device, non_blocking=True)
+            dev = pinned[:lay.words].to(self.device, non_blocking=True)
             if self._staged[self._turn] is None:
                 self._staged[self._turn] = torch.cuda.Event()
             self._staged[self._turn].record()
         else:
             dev = torch.from_numpy(host).clone()
+        T, R, W, G, width = lay.tokens, lay.rows, lay.wanted, lay.groups, lay.table_width
 
-        def dview(name):
-            o, n = offs[name]
-            return dev[o:o + n]
+        def both(at, n):
+            return dev[at:at + n], host[at:at + n]
 
-        dtables = [dview("tables").view(G, R, width)[g] for g in range(G)] if G else []
+        (token_ids, h_ids), (positions, h_pos), (token_req, h_req) = both(lay.token_ids, T), both(lay.positions, T), both(lay.token_req, T)
+        (cu_q, h_cu), (kv_lens, h_kv), (slots, h_slots) = both(lay.cu_q, R + 1), both(lay.kv_lens, R), both(lay.slots, R)
+        logit_rows, h_rows = both(lay.logit_rows, W)
+        tables = dev[lay.tables:lay.tables + G * R * width].view(G, R, width) if G else None
         return StepBatch(
-            num_tokens=T, num_requests=R, token_ids=dview("token_ids"), positions=dview("positions"),
-            token_req=dview("token_req"), cu_q=dview("cu_q"), kv_lens=dview("kv_lens"),
-            slots=dview("slots"), block_tables=dtables, logit_rows=dview("logit_rows")[:W],
-            num_logit_rows=W, max_q_len=max_q, max_kv_len=max_kv, min_q_len=min_q,
-            host={"token_ids": token_ids, "positions": positions, "token_req": token_req, "cu_q": cu_q,
-                  "kv_lens": kv_lens, "slots": slots, "logit_rows": logit_rows[:W],
-                  "requests": [e.request for e in entries]},
+            num_tokens=T, num_requests=R, token_ids=token_ids, positions=positions, token_req=token_req,
+            cu_q=cu_q, kv_lens=kv_lens, slots=slots, block_tables=[tables[g] for g in range(G)],
+            logit_rows=logit_rows, num_logit_rows=W, max_q_len=lay.max_q, max_kv_len=lay.max_kv,
+            min_q_len=lay.min_q,
+            host={"token_ids": h_ids, "positions": h_pos, "token_req": h_req, "cu_q": h_cu, "kv_lens": h_kv,
+                  "slots": h_slots, "logit_rows": h_rows, "requests": requests.requests},
         )
 
     def _stage(self, n: int):
@@ -205,21 +129,19 @@ class StepRunner:
         tokens are placeholders then). Only decode steps replayed from graphs take it."""
         if device_tokens is not None and not (self.graphs is not None and self.graphs.eligible(entries)):
             raise StepError("tokens on the device are taken by graph-replayed decode steps only")
-        new_lens = self._validate_and_reserve(entries)
+        requests, new_lens = self._validate_and_reserve(entries)
         if self.graphs is not None and self.graphs.eligible(entries):
-            logits = self.graphs.run(entries, new_lens, device_tokens)
+            logits = self.graphs.run(entries, requests, new_lens, device_tokens)
             tokens = len(entries)
         else:
-            batch = self.build_batch(entries, new_lens)
+            batch = self.build_batch(requests, new_lens)
             ctx = StepContext(batch=batch, ws=self.ws, ops=self.ops, dtype=self.dtype)
             caches = self.cache.layer_caches(batch.block_tables)
             hold = getattr(self.ops, "on_current_stream", None)
             with (hold() if hold is not None else contextlib.nullcontext()):
                 logits = self.model.forward(ctx, caches)
             tokens = batch.num_tokens
-        mgr = self.cache.manager
-        for r, n in new_lens:
-            mgr.commit(r, n)
+        self.builder.commit(new_lens)
         self.steps += 1
         self.tokens_run += tokens
         return logits
