@@ -1449,9 +1449,23 @@ constexpr int few_token_limit() { return 256; }
 // More than 64 tokens: whether CTA pairs take the product, and the tile width over the weight's rows.
 // Pairs pay from about a thousand tokens (768: 3.9 ms a step with pairs, 3.4 without; 1,024: 4.4 against 4.5):
 // below that their 256 x 256 tiles are too few for the 74 pairs.
-bool many_token_pairs(int tokens, int weight_rows) { return tokens >= 8 * BM && weight_rows >= 256; }
-int many_token_width(int tokens, int weight_rows) {
-  return many_token_pairs(tokens, weight_rows) ? 256 : pick_tile_width(tokens, weight_rows);
+bool many_token_pairs(int tokens, int weight_rows, int epi = -1) {
+  if (weight_rows < 256) return false;
+  if (tokens >= 8 * BM) return true;
+  // The gate/up product has the most tiles by far, and below a thousand tokens still pays where the
+  // pairs' 256 x 256 tiles need fewer rounds: a round of pairs costs a CTA as much as a round of 128-wide
+  // tiles (1 MB of operands for each), so 512 tokens times 11,264 packed rows are two rounds of pairs
+  // against three (a step of 512 tokens 3.35 to 3.1 ms). The other products have one round either way.
+  if (epi != EPI_SWIGLU || tokens <= few_token_limit()) return false;
+  const int sms = sm_count(), pairs = sms / 2;
+  const int pair_tiles = ((tokens + 2 * BM - 1) / (2 * BM)) * ((weight_rows + 255) / 256);
+  const int pair_cost = ((pair_tiles + pairs - 1) / pairs) * 128;
+  const int tiles_m = (tokens + BM - 1) / BM;
+  auto cost = [&](int bn) { return ((tiles_m * ((weight_rows + bn - 1) / bn) + sms - 1) / sms) * bn; };
+  return pair_cost < (cost(256) < cost(128) ? cost(256) : cost(128));
+}
+int many_token_width(int tokens, int weight_rows, int epi = -1) {
+  return many_token_pairs(tokens, weight_rows, epi) ? 256 : pick_tile_width(tokens, weight_rows);
 }
 
 }  // namespace
@@ -1569,8 +1583,8 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
     return dispatch_cluster<64>(epi, out_dtype, mm, mn, out, Nw, weight_rows, Nw, Mx, K, stream, ra);
   }
   if ((rc = tensor_map_2d(x, Mx, K, BM, &mm))) return rc;
-  const bool pairs = many_token_pairs(Mx, weight_rows);
-  const int width = many_token_width(Mx, weight_rows);
+  const bool pairs = many_token_pairs(Mx, weight_rows, epi);
+  const int width = many_token_width(Mx, weight_rows, epi);
   // CTA pairs: each CTA of a pair loads half of the weight tile's rows
   if ((rc = tensor_map_2d(w, weight_rows, K, pairs ? 128 : width, &mn))) return rc;
 #define GB_MANY(LAUNCH, BN_)                                                                                          \

@@ -124,8 +124,9 @@ def test_few_token_products_at_layer_sizes_give_the_same_bits_every_time(ops, M,
     ops.tc.check_errors()
 
 
-@pytest.mark.parametrize("M", [1, 9, 33, 64, 100, 257])
-@pytest.mark.parametrize("F,K", [(176, 64), (200, 72), (1000, 256)])
+# the last case: so many packed rows that CTA pairs take the product below a thousand tokens
+@pytest.mark.parametrize("M,F,K", [(M, F, K) for F, K in [(176, 64), (200, 72), (1000, 256)]
+                                   for M in [1, 9, 33, 64, 100, 257]] + [(520, 5632, 64)])
 def test_tensor_core_gate_up(ops, M, F, K):
     h = (torch.randn(M, K) * 0.5).bfloat16()
     w = (torch.randn(2 * F, K) * 0.2).bfloat16()
