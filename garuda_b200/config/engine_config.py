@@ -7,7 +7,8 @@ refuses what cannot be honoured instead of ignoring it (:283-347); sizes are
 written ``"512MB"``, ``"8 GiB"`` (:232-269). Keys that the reference has keep
 their names and meanings (``model.path``, ``model.context``,
 ``model.sliding_window``, ``model.gpu``, ``server.max_concurrent``,
-``server.queue_capacity``, ``sampling.*``); the others are this engine's own.
+``server.queue_capacity``, ``server.request_timeout_secs``, ``sampling.*``); the others are this
+engine's own.
 """
 from __future__ import annotations
 
@@ -82,6 +83,7 @@ class RuntimeSection:
 class ServerSection:
     max_concurrent: int = 4       # requests running at once
     queue_capacity: int = 256     # requests waiting before submissions are refused
+    request_timeout_secs: int = 120   # a request ends with "timeout" this long after it was submitted
 
 
 @dataclass
@@ -178,6 +180,8 @@ class EngineConfig:
             raise ConfigError("server.max_concurrent must be at least 1")
         if self.server.queue_capacity < 1:
             raise ConfigError("server.queue_capacity must be at least 1")
+        if self.server.request_timeout_secs < 1:           # garuda/src/config/mod.rs:327-330
+            raise ConfigError("server.request_timeout_secs must be at least 1")
         from ..sampling.params import SamplingParams
         SamplingParams(temperature=self.sampling.temperature, top_p=self.sampling.top_p,
                        top_k=self.sampling.top_k, max_tokens=self.sampling.max_tokens).validate()

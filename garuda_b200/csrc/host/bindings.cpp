@@ -239,6 +239,7 @@ PYBIND11_MODULE(_garuda_host, m) {
       .def_readonly("submitted", &SchedulerStats::submitted)
       .def_readonly("completed", &SchedulerStats::completed)
       .def_readonly("cancelled", &SchedulerStats::cancelled)
+      .def_readonly("timed_out", &SchedulerStats::timed_out)
       .def_readonly("failed", &SchedulerStats::failed)
       .def_readonly("rejected_busy", &SchedulerStats::rejected_busy)
       .def_readonly("preemptions", &SchedulerStats::preemptions)
@@ -251,7 +252,10 @@ PYBIND11_MODULE(_garuda_host, m) {
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init<SchedulerConfig, CacheManager*>(), py::arg("config"), py::arg("cache"),
            py::keep_alive<1, 3>())
-      .def("submit", &Scheduler::submit, py::arg("prompt"), py::arg("params"), py::arg("priority") = 0)
+      .def("submit", &Scheduler::submit, py::arg("prompt"), py::arg("params"), py::arg("priority") = 0,
+           py::arg("timeout") = 0.0)
+      .def("now", &Scheduler::now)
+      .def("set_time", &Scheduler::set_time)
       .def("cancel", &Scheduler::cancel)
       .def("plan", &Scheduler::plan)
       .def("peek_uniform", &Scheduler::peek_uniform)

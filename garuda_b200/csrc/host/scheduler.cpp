@@ -27,9 +27,15 @@ Scheduler::Scheduler(SchedulerConfig config, CacheManager* cache) : config_(conf
     throw SchedulerError("max_concurrent exceeds the cache's request slots");
 }
 
-int64_t Scheduler::submit(std::vector<int32_t> prompt, SamplingParams params, int priority) {
+double Scheduler::now() const {
+  if (manual_time_ >= 0.0) return manual_time_;
+  return std::chrono::duration<double>(std::chrono::steady_clock::now() - started_).count();
+}
+
+int64_t Scheduler::submit(std::vector<int32_t> prompt, SamplingParams params, int priority, double timeout_seconds) {
   const std::string bad = params.problem();
   if (!bad.empty()) throw SchedulerError(bad);
+  if (!(timeout_seconds >= 0.0)) throw SchedulerError("a timeout must not be negative");
   if (prompt.empty()) throw SchedulerError("prompt is empty");
   if (static_cast<int>(prompt.size()) >= config_.max_context)
     throw SchedulerError("prompt of " + std::to_string(prompt.size()) + " tokens does not fit the " +
@@ -51,6 +57,7 @@ int64_t Scheduler::submit(std::vector<int32_t> prompt, SamplingParams params, in
   r.params = params;
   r.rng = Rng(params.has_seed ? params.seed : static_cast<uint64_t>(r.id));
   r.priority = priority;
+  if (timeout_seconds > 0.0) r.deadline = now() + timeout_seconds;
   r.arrival = arrivals_++;
   auto pos = std::find_if(queue_.begin(), queue_.end(), [&](const Request& q) {
     return !q.requeued && q.priority < r.priority;
@@ -77,6 +84,7 @@ void Scheduler::finish(Request& r, std::vector<Event>* events, EventKind kind, c
   events->push_back(e);
   if (kind == EventKind::Done) ++stats_.completed;
   else if (detail == "cancelled") ++stats_.cancelled;
+  else if (detail == "timeout") ++stats_.timed_out;
   else ++stats_.failed;
   const int64_t id = r.id;
   running_.erase(std::remove_if(running_.begin(), running_.end(),
@@ -113,15 +121,18 @@ int Scheduler::largest_reservable(const Request& r, int want) const {
 
 StepPlan Scheduler::plan() {
   StepPlan plan;
-  // requests that were cancelled since the last step (garuda/src/scheduler/mod.rs:554-573, :607-633)
+  // requests that were cancelled since the last step, or whose time has run out
+  // (garuda/src/scheduler/mod.rs:554-573, :607-633): waiting or running, they end here, between steps
+  const double t = now();
   for (auto it = queue_.begin(); it != queue_.end();) {
-    if (it->cancelled) {
+    if (it->cancelled || t >= it->deadline) {
       Event e;
       e.id = it->id;
       e.kind = EventKind::Error;
-      e.detail = "cancelled";
+      e.detail = it->cancelled ? "cancelled" : "timeout";
       plan.events.push_back(e);
-      ++stats_.cancelled;
+      ++(it->cancelled ? stats_.cancelled : stats_.timed_out);
+      if (cache_->known(it->id)) cache_->release(it->id);
       it = queue_.erase(it);
     } else {
       ++it;
@@ -129,6 +140,7 @@ StepPlan Scheduler::plan() {
   }
   for (size_t i = 0; i < running_.size();) {
     if (running_[i].cancelled) finish(running_[i], &plan.events, EventKind::Error, "cancelled");
+    else if (t >= running_[i].deadline) finish(running_[i], &plan.events, EventKind::Error, "timeout");
     else ++i;
   }
 

@@ -15,8 +15,10 @@
 // what it had generated; a request that cannot fit even alone ends with an error.
 #pragma once
 
+#include <chrono>
 #include <cstdint>
 #include <deque>
+#include <limits>
 #include <string>
 #include <vector>
 
@@ -90,7 +92,7 @@ struct Event {
   int64_t id = 0;
   EventKind kind = EventKind::Token;
   int32_t token = -1;
-  std::string detail;  // Done: "length" | "context_full" | "eos"; Error: the message
+  std::string detail;  // Done: "length" | "context_full" | "eos"; Error: the message ("cancelled", "timeout", ...)
 };
 
 struct StepPlan {
@@ -105,7 +107,7 @@ struct StepPlan {
 };
 
 struct SchedulerStats {  // garuda/src/scheduler/mod.rs:188-197, and what a page pool adds
-  uint64_t submitted = 0, completed = 0, cancelled = 0, failed = 0, rejected_busy = 0;
+  uint64_t submitted = 0, completed = 0, cancelled = 0, timed_out = 0, failed = 0, rejected_busy = 0;
   uint64_t preemptions = 0, steps = 0, tokens_fed = 0, tokens_generated = 0;
   int running = 0, queued = 0;
 };
@@ -115,10 +117,17 @@ class Scheduler {
   Scheduler(SchedulerConfig config, CacheManager* cache);
 
   // Validates (garuda/src/runtime/mod.rs:578-589) and queues. priority: higher first, FIFO within.
-  int64_t submit(std::vector<int32_t> prompt, SamplingParams params, int priority = 0);
+  // timeout_seconds: the request ends with the error "timeout" at the first plan made that long
+  // after it was submitted, waiting or running (the deadline is submission time + timeout and is
+  // checked between steps: garuda/src/scheduler/mod.rs:520, :566-573, :623-631); 0: no limit.
+  int64_t submit(std::vector<int32_t> prompt, SamplingParams params, int priority = 0, double timeout_seconds = 0.0);
   void cancel(int64_t id);
   // Decide the next step. Reserves the pages its entries need.
   StepPlan plan();
+  // Seconds on the scheduler's clock: a steady clock that starts with the scheduler, or, once
+  // set_time was called, the time given last (for tests and for replaying a schedule).
+  double now() const;
+  void set_time(double seconds) { manual_time_ = seconds; }
   // The uniform draw that the next plan will give a running request's sampling entry (its
   // generator is not advanced): for a decode step that is launched before that plan is made.
   float peek_uniform(int64_t id) const;
@@ -144,6 +153,7 @@ class Scheduler {
     uint64_t admitted = 0;        // order of admission; larger is more recent
     bool cancelled = false;
     bool requeued = false;        // preempted: goes before every fresh request
+    double deadline = std::numeric_limits<double>::infinity();   // on the scheduler's clock
   };
 
   void finish(Request& r, std::vector<Event>* events, EventKind kind, const std::string& detail);
@@ -157,6 +167,8 @@ class Scheduler {
   int64_t next_id_ = 1;
   uint64_t arrivals_ = 0, admissions_ = 0;
   SchedulerStats stats_;
+  std::chrono::steady_clock::time_point started_ = std::chrono::steady_clock::now();
+  double manual_time_ = -1.0;          // negative: the steady clock
 };
 
 }  // namespace garuda

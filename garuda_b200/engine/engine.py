@@ -34,7 +34,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 class GenerationResult:
     tokens: List[int] = field(default_factory=list)
     finish_reason: str = ""          # "length" | "context_full" | "eos" | "error"
-    error: Optional[str] = None
+    error: Optional[str] = None      # with "error": the message ("cancelled", "timeout", a failed step's, ...)
 
 
 class Engine:
@@ -43,11 +43,17 @@ class Engine:
                  kv_cache_bytes: Optional[int] = None, max_concurrent: int = 4,
                  queue_capacity: int = 256, max_batch_tokens: int = 2048, prefill_chunk: int = 2048,
                  cuda_graphs: bool = True, lookahead: bool = True, device: int = 0, ignore_eos: bool = False,
-                 eos_token_id: Union[None, int, Sequence[int]] = None, ops=None):
+                 eos_token_id: Union[None, int, Sequence[int]] = None,
+                 request_timeout: Optional[float] = None, ops=None):
+        """``request_timeout``: seconds from its submission after which a request, waiting or
+        running, ends with the error "timeout" (garuda/src/scheduler/mod.rs:520); None: no limit."""
         if dtype not in _DTYPES:
             raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
         self.dtype = _DTYPES[dtype]
         self.model_dir = model_dir
+        if request_timeout is not None and not request_timeout > 0:
+            raise ConfigError(f"request_timeout must be positive, got {request_timeout!r}")
+        self.request_timeout = None if request_timeout is None else float(request_timeout)
         config_dict = read_config_json(model_dir)
         if sliding_window:
             config_dict = dict(config_dict, sliding_window=int(sliding_window))
@@ -121,7 +127,7 @@ class Engine:
             kv_cache_bytes=kv_bytes or None, max_concurrent=cfg.server.max_concurrent,
             queue_capacity=cfg.server.queue_capacity, max_batch_tokens=cfg.runtime.max_batch_tokens,
             prefill_chunk=cfg.runtime.prefill_chunk, cuda_graphs=cfg.runtime.cuda_graphs,
-            lookahead=cfg.runtime.lookahead,
+            lookahead=cfg.runtime.lookahead, request_timeout=cfg.server.request_timeout_secs,
             device=cfg.runtime.device)
         kwargs.update(overrides)
         return cls(cfg.model.path, **kwargs)
@@ -164,10 +170,16 @@ class Engine:
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None,
-                 on_token=None) -> List[GenerationResult]:
+                 on_token=None, timeout: Optional[float] = None) -> List[GenerationResult]:
         """Generate for every prompt (lists of token ids), batching them
         continuously. ``sampling``: one ``SamplingParams`` for all, or one per
-        prompt. ``on_token(index, token)`` is called as tokens arrive."""
+        prompt. ``on_token(index, token)`` is called as tokens arrive. ``timeout``: seconds
+        after its submission at which a request ends with the error "timeout", checked between
+        steps (default: the engine's ``request_timeout``)."""
+        if timeout is None:
+            timeout = self.request_timeout
+        elif not timeout > 0:
+            raise ConfigError(f"timeout must be positive, got {timeout!r}")
         if sampling is None:
             sampling = SamplingParams()
         if isinstance(sampling, SamplingParams):
@@ -203,7 +215,8 @@ class Engine:
             while pending:
                 i = pending[0]
                 try:
-                    rid = sched.submit(list(map(int, prompts[i])), self._host_params(sampling[i]))
+                    rid = sched.submit(list(map(int, prompts[i])), self._host_params(sampling[i]), 0,
+                                       float(timeout or 0.0))
                 except self._host.Busy:
                     break      # the queue is full: run steps, then submit the rest
                 except (self._host.SchedulerError, ConfigError) as e:
@@ -308,7 +321,7 @@ class Engine:
     def stats(self) -> dict:
         s = self.scheduler.stats()
         m = self.cache.manager
-        out = {k: getattr(s, k) for k in ("submitted", "completed", "cancelled", "failed", "rejected_busy",
+        out = {k: getattr(s, k) for k in ("submitted", "completed", "cancelled", "timed_out", "failed", "rejected_busy",
                                           "preemptions", "steps", "tokens_fed", "tokens_generated",
                                           "running", "queued")}
         out["pages_free"] = [m.free_pages(g) for g in range(m.num_groups)]

@@ -82,6 +82,7 @@ def test_engine_config_toml(tmp_path):
     c = EngineConfig.load(str(p))
     assert c.model.path == "/m" and c.model.dtype == "float32" and c.model.context == 512
     assert c.server.max_concurrent == 2 and c.server.queue_capacity == 256      # default filled in
+    assert c.server.request_timeout_secs == 120
     assert c.sampling.temperature == 0.0 and c.sampling.top_k == 40
     assert EngineConfig.load_or_default(str(tmp_path / "absent.toml")).model.context == 4096
 
@@ -92,6 +93,7 @@ def test_engine_config_toml(tmp_path):
     ("[model]\ngpu = false\n", "gpu"),
     ("[model]\ncontext = 8\nsliding_window = 9\n", "sliding_window"),
     ("[server]\nmax_concurrent = 0\n", "max_concurrent"),
+    ("[server]\nrequest_timeout_secs = 0\n", "request_timeout_secs"),
     ("[sampling]\ntop_p = 0.0\n", "top_p"),
     ("[sampling]\ntemperature = -1.0\n", "temperature"),
     ("[memory]\nkv_cache = \"12XB\"\n", "unit"),

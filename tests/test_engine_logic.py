@@ -170,3 +170,27 @@ def test_eos_and_errors_in_generate():
     assert res[0].finish_reason == "error" and "empty" in res[0].error
     assert res[1].finish_reason == "error" and "vocabulary" in res[1].error
     assert res[2].finish_reason == "length" and len(res[2].tokens) == 2
+
+
+def test_generation_with_a_timeout_ends_the_request_and_frees_what_it_held():
+    e = engine("A", max_concurrent=2)
+    prompts = [random_tokens("A", 9, 1), random_tokens("A", 5, 2)]
+    e.scheduler.set_time(10.0)
+    seen = []
+
+    def on_token(i, tok):
+        seen.append(i)
+        if len(seen) == 6:                       # three tokens each: now the clock jumps past the deadline
+            e.scheduler.set_time(20.0)
+
+    res = e.generate(prompts, SamplingParams.greedy(max_tokens=40), on_token=on_token, timeout=5.0)
+    assert [r.finish_reason for r in res] == ["error", "error"] and [r.error for r in res] == ["timeout", "timeout"]
+    assert [len(r.tokens) for r in res] == [3, 3]
+    st = e.stats()
+    assert st["timed_out"] == 2 and st["running"] == 0 and st["pages_free"] == st["pages_total"]
+    # the tokens that came before the deadline are those of an unlimited run
+    e.scheduler.set_time(30.0)
+    free = e.generate(prompts, SamplingParams.greedy(max_tokens=3))
+    assert [r.tokens for r in free] == [r.tokens for r in res] and all(r.finish_reason == "length" for r in free)
+    with pytest.raises(Exception):
+        e.generate(prompts, timeout=0)

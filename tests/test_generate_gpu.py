@@ -141,6 +141,37 @@ def test_steps_launched_ahead_change_nothing(dtype):
             assert any(r.finish_reason != "length" for r in want)
 
 
+def test_a_timeout_between_steps_launched_ahead():
+    """A request whose time runs out while a step for it is already in flight (launched ahead)
+    ends with the error, the other goes on to the tokens of a run without limits, and nothing
+    stays behind in the cache."""
+    from garuda_b200 import Engine, SamplingParams
+    prompts = [random_tokens("A", 9, 1), random_tokens("A", 5, 2), random_tokens("A", 7, 3)]
+    params = [SamplingParams.greedy(max_tokens=m) for m in (40, 6, 40)]
+    e = Engine(model_dir("A"), dtype="bfloat16", page_size=16, max_concurrent=3)
+    free = e.generate(prompts, params)
+    e.scheduler.set_time(10.0)
+    count = [0]
+
+    def on_token(i, tok):
+        count[0] += 1
+        if count[0] == 30:                       # ten tokens each, the second request long finished
+            e.scheduler.set_time(20.0)
+
+    res = e.generate(prompts, params, on_token=on_token, timeout=5.0)
+    assert [r.finish_reason for r in res] == ["error", "length", "error"]
+    assert res[0].error == res[2].error == "timeout" and res[1].tokens == free[1].tokens
+    for got, want in zip(res, free):
+        assert 0 < len(got.tokens) <= len(want.tokens) and got.tokens == want.tokens[:len(got.tokens)]
+    st = e.stats()
+    assert st["timed_out"] == 2 and st["running"] == 0 and st["pages_free"] == st["pages_total"]
+    e.scheduler.set_time(30.0)
+    again = e.generate(prompts, params)          # the engine goes on as before
+    assert [r.tokens for r in again] == [r.tokens for r in free]
+    e.cache.manager.check_invariants()
+    e.check_errors()
+
+
 def test_missing_extension_fails_loudly(monkeypatch):
     from garuda_b200.csrc import build
     from garuda_b200.kernels import ops as ops_mod

@@ -298,3 +298,46 @@ def test_any_of_several_end_tokens_finishes_a_request():
     ev = s.complete(plan, [90])
     assert [(e.id, e.detail) for e in ev if e.kind == Done] == [(ids[1], "eos")]
     assert s.idle() and cache.free_pages(0) == 64
+
+
+def test_a_request_that_outruns_its_timeout_is_stopped_between_steps():
+    # garuda/src/scheduler/mod.rs:1032-1049; here on a clock that the test sets
+    s, cache = make(max_concurrent=2, pages=16)
+    s.set_time(100.0)
+    a = s.submit([1, 2, 3], greedy(max_tokens=50), 0, 5.0)     # running when its time runs out
+    b = s.submit([4, 5], greedy(max_tokens=50))                 # no limit
+    c = s.submit([6, 7], greedy(max_tokens=50), 0, 2.0)        # still waiting when its time runs out
+    with pytest.raises(host.SchedulerError):
+        s.submit([1], greedy(), 0, -1.0)
+    plan, _ = run_step(s, cache)
+    assert sorted(e.id for e in plan.entries) == [a, b] and s.stats().queued == 1
+    s.set_time(101.9)
+    plan, _ = run_step(s, cache)
+    assert not plan.events and s.stats().queued == 1
+    s.set_time(102.0)                                           # c's deadline: submission + 2 s
+    plan, _ = run_step(s, cache)
+    assert [(e.id, e.kind, e.detail) for e in plan.events] == [(c, Error, "timeout")]
+    assert sorted(e.id for e in plan.entries) == [a, b]
+    held = cache.free_pages(0)
+    s.set_time(105.0)
+    plan, _ = run_step(s, cache)
+    assert [(e.id, e.kind, e.detail) for e in plan.events] == [(a, Error, "timeout")]
+    assert [e.id for e in plan.entries] == [b]
+    assert not cache.known(a) and cache.free_pages(0) > held    # what it held went back
+    st = s.stats()
+    assert (st.timed_out, st.cancelled, st.failed, st.running, st.queued) == (2, 0, 0, 1, 0)
+    s.set_time(1e9)                                             # b has no deadline
+    plan, _ = run_step(s, cache)
+    assert [e.id for e in plan.entries] == [b] and not plan.events
+    cache.check_invariants()
+
+
+def test_the_scheduler_clock_runs_by_itself_unless_it_is_set():
+    s, _ = make()
+    t0 = s.now()
+    assert 0.0 <= t0 < 5.0
+    import time
+    time.sleep(0.02)
+    assert s.now() >= t0 + 0.015
+    s.set_time(42.0)
+    assert s.now() == 42.0
