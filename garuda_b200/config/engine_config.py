@@ -16,7 +16,6 @@ import math
 import os
 import tomllib
 from dataclasses import dataclass, field, fields
-from typing import Optional
 
 from .model_config import ConfigError
 

@@ -21,7 +21,7 @@ import argparse
 import json
 import os
 import sys
-from typing import Iterable, Optional
+from typing import Iterable
 
 
 def replay(engine, lines: Iterable[str], out_dir: str, report=None) -> int:

@@ -14,7 +14,7 @@ from __future__ import annotations
 import contextlib
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Sequence
 
 import numpy as np
 import torch

@@ -10,7 +10,7 @@ architecture is a function from its configuration to a ``ModelSpec``
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
 import torch

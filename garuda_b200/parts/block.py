@@ -8,7 +8,7 @@ last matrix product); if it returns a tensor instead, the block adds it.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Optional
+from typing import Optional
 
 from .base import PartSpec, build_part, register_block
 

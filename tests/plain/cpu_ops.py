@@ -12,7 +12,6 @@ Written from the reference's formulas (cited per function); shares no code with
 """
 from __future__ import annotations
 
-import math
 
 import numpy as np
 import torch

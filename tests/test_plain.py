@@ -2,7 +2,6 @@
 (the reference tests the same ones: garuda/src/simd/mod.rs:251-298,
 garuda/src/attention/mod.rs:161-238, garuda/src/runtime/mod.rs:1112-1224)."""
 import numpy as np
-import pytest
 
 from tests.plain import llama_plain as P
 from tests.plain.sampling_plain import Rng, sample, candidates
