@@ -341,3 +341,117 @@ def test_the_scheduler_clock_runs_by_itself_unless_it_is_set():
     assert s.now() >= t0 + 0.015
     s.set_time(42.0)
     assert s.now() == 42.0
+
+
+def _next_token(history, vocab):
+    """A stand-in for the model: the next token as a function of everything before it."""
+    h = 0
+    for t in history:
+        h = (h * 131 + t + 7) % 1000003
+    return h % vocab
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_keep_every_promise(seed):
+    """Random arrivals, lengths, priorities, cancellations and limits of time in a pool so small
+    that requests are sent back and recomputed. Every step keeps the budget and the portion size,
+    feeds each request exactly the positions it has not fed, and loses no page; every request that
+    ends normally has the tokens of a run alone, whatever happened to it on the way."""
+    import random
+    rng = random.Random(seed)
+    vocab, eos = 50, 49
+    page_size = rng.choice([2, 4, 8])
+    max_context = 48
+    pages = rng.randint(max_context // page_size + 1, 3 * max_context // page_size)
+    max_concurrent = rng.randint(2, 4)
+    budget = rng.randint(6, 24)
+    chunk = rng.choice([0, 3, 8, 16])
+    s, cache = make(pages=pages, page_size=page_size, max_concurrent=max_concurrent, max_batch_tokens=budget,
+                    prefill_chunk=chunk, max_context=max_context, queue_capacity=6, eos=eos, vocab=vocab)
+    clock = 0.0
+    s.set_time(clock)
+    prompts, limits, deadline, emitted, ended, fed_history = {}, {}, {}, {}, {}, {}
+    cancelled = set()
+    to_submit = 25
+    for _ in range(4000):
+        if to_submit and rng.random() < 0.3:
+            prompt = [rng.randrange(vocab - 1) for _ in range(rng.randint(1, 30))]
+            limit = rng.randint(1, 25)
+            timeout = rng.choice([0.0, 0.0, 0.0, rng.uniform(1.0, 40.0)])
+            try:
+                rid = s.submit(prompt, greedy(max_tokens=limit), rng.randint(0, 2), timeout)
+            except host.Busy:
+                pass
+            else:
+                to_submit -= 1
+                prompts[rid], limits[rid], emitted[rid], fed_history[rid] = prompt, limit, [], []
+                deadline[rid] = clock + timeout if timeout else None
+        live = [r for r in prompts if r not in ended]
+        if live and rng.random() < 0.03:
+            victim = rng.choice(live)
+            s.cancel(victim)
+            cancelled.add(victim)
+        if s.idle():
+            if not to_submit:
+                break
+            continue
+        clock += rng.uniform(0.0, 0.5)
+        s.set_time(clock)
+        plan = s.plan()
+        for ev in plan.events:
+            assert ev.kind == Error and ev.id not in ended
+            ended[ev.id] = ev.detail
+            if ev.detail == "timeout":
+                assert deadline[ev.id] is not None and clock >= deadline[ev.id]
+            if ev.detail == "cancelled":
+                assert ev.id in cancelled
+        for rid in plan.preempted:
+            fed_history[rid] = []                         # it will be fed again from its first token
+        assert plan.num_tokens <= budget and len(plan.entries) <= max_concurrent
+        assert len({e.id for e in plan.entries}) == len(plan.entries)
+        sampled = []
+        for e in plan.entries:
+            assert e.id not in ended
+            assert deadline[e.id] is None or clock < deadline[e.id]
+            assert e.start == len(fed_history[e.id])       # exactly the positions not fed yet
+            assert 1 <= len(e.tokens) <= (chunk or budget) or len(e.tokens) == 1
+            assert cache.reserved_length(e.id) >= e.start + len(e.tokens) and cache.slot(e.id) == e.slot
+            fed_history[e.id] += e.tokens
+            whole = prompts[e.id] + emitted[e.id]
+            assert fed_history[e.id] == whole[:len(fed_history[e.id])]
+            assert e.sample == (len(fed_history[e.id]) == len(whole))
+            if e.sample:
+                sampled.append(_next_token(fed_history[e.id], vocab))
+        for ev in s.complete(plan, sampled):
+            assert ev.id not in ended
+            if ev.kind == Token:
+                emitted[ev.id].append(ev.token)
+            else:
+                ended[ev.id] = ev.detail
+        cache.check_invariants()
+        assert s.stats().running <= max_concurrent
+    assert s.idle() and not to_submit and set(ended) == set(prompts)
+    assert cache.live_requests == 0 and all(cache.free_pages(g) == pages for g in range(cache.num_groups))
+    reasons = set(ended.values())
+    for rid, prompt in prompts.items():
+        # alone: token by token until the limit, the end token or a full context
+        seq, want, why = list(prompt), [], None
+        while why is None:
+            t = _next_token(seq, vocab)
+            seq.append(t)
+            if t == eos:
+                why = "eos"
+                break
+            want.append(t)
+            if len(want) >= limits[rid]:
+                why = "length"
+            elif len(seq) >= max_context:
+                why = "context_full"
+        if ended[rid] in ("length", "eos", "context_full"):
+            assert (emitted[rid], ended[rid]) == (want, why), rid
+        else:
+            assert ended[rid] in ("cancelled", "timeout") or "more pages" in ended[rid], ended[rid]
+            assert emitted[rid] == want[:len(emitted[rid])]
+    st = s.stats()
+    assert st.submitted == 25 and st.completed + st.cancelled + st.timed_out + st.failed == 25
+    assert reasons & {"length", "eos", "context_full"}
