@@ -194,3 +194,39 @@ def test_generation_with_a_timeout_ends_the_request_and_frees_what_it_held():
     assert [r.tokens for r in free] == [r.tokens for r in res] and all(r.finish_reason == "length" for r in free)
     with pytest.raises(Exception):
         e.generate(prompts, timeout=0)
+
+
+def test_trace_replay_loop_writes_the_plain_models_logits(tmp_path):
+    """The loop behind bin/trace_run, `garuda replay` and Engine.replay, over the reference kernels:
+    requests named by strings or numbers, one left out of a step and going on later, blank lines, a
+    step that only ends requests, an unknown name in `end`, pages used again."""
+    import json
+    from garuda_b200.engine.replay import replay
+    e = engine("B", kv_tokens=96, max_concurrent=3)           # 12 pages of 8 for 40 + 30 + 33 tokens in turn
+    a, b, c = (random_tokens("B", n, 60 + n) for n in (40, 30, 33))
+    refs = {k: plain_logits("B", torch.float32, t) for k, t in (("a", a), ("b", b), ("c", c))}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:17], "want": [0, 16]}, {"id": 7, "tokens": b[:2], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[17:39], "want": [21]}], "end": []},          # 7 sits this one out
+        {"step": 2, "entries": [{"id": 7, "tokens": b[2:], "want": [0, 27]}, {"id": "a", "tokens": a[39:], "want": [0]}], "end": ["a", "nobody"]},
+        {"step": 3, "entries": [], "end": [7]},
+        {"step": 5, "entries": [{"id": "c", "tokens": c, "want": [32]}], "end": ["c"]},
+    ]
+    lines = [json.dumps(s) for s in steps]
+    lines.insert(2, "   ")
+    seen = []
+    n = replay(e, lines, str(tmp_path / "out"), report=seen.append)
+    assert n == 5 and seen == [0, 1, 2, 3, 5]
+    vocab = refs["a"].shape[1]
+
+    def got(step):
+        return np.fromfile(tmp_path / "out" / f"{step}.f32", dtype="<f4").reshape(-1, vocab)
+
+    assert_close(got(0), refs["a"][[0, 16]], "float32", "step 0")
+    assert_close(got(1), refs["a"][[38]], "float32", "step 1")
+    assert_close(got(2), np.concatenate([refs["b"][[2, 29]], refs["a"][[39]]]), "float32", "step 2")
+    assert not (tmp_path / "out" / "3.f32").exists()
+    assert_close(got(5), refs["c"][[32]], "float32", "step 5")
+    m = e.cache.manager
+    assert m.live_requests == 0 and m.pages_reused > 0
+    m.check_invariants()
