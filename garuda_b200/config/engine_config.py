@@ -75,6 +75,7 @@ class RuntimeSection:
     prefill_chunk: int = 2048
     cuda_graphs: bool = True      # replay decode steps from captured graphs
     lookahead: bool = True        # launch the next greedy decode step while this one's tokens travel to the host
+    paced_prefill: bool = False   # while something decodes, prompt portions sized to cost about one decode step
     device: int = 0
 
 

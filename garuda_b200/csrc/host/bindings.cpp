@@ -205,13 +205,20 @@ PYBIND11_MODULE(_garuda_host, m) {
                       if (id >= 0) c.eos_token_ids.push_back(id);
                     })
       .def_readwrite("vocab_size", &SchedulerConfig::vocab_size)
-      .def_readwrite("ignore_eos", &SchedulerConfig::ignore_eos);
+      .def_readwrite("ignore_eos", &SchedulerConfig::ignore_eos)
+      .def_readwrite("paced_prefill", &SchedulerConfig::paced_prefill);
+
+  py::class_<Pacing>(m, "Pacing")
+      .def_readonly("decode_step", &Pacing::decode_step)
+      .def_readonly("prefill_token", &Pacing::prefill_token)
+      .def_property_readonly("chunk", &Pacing::chunk);
 
   py::class_<PlanEntry>(m, "PlanEntry")
       .def_readonly("id", &PlanEntry::id)
       .def_readonly("slot", &PlanEntry::slot)
       .def_readonly("start", &PlanEntry::start)
       .def_readonly("tokens", &PlanEntry::tokens)
+      .def_readonly("decode", &PlanEntry::decode)
       .def_readonly("sample", &PlanEntry::sample)
       .def_readonly("temperature", &PlanEntry::temperature)
       .def_readonly("top_p", &PlanEntry::top_p)
@@ -259,7 +266,8 @@ PYBIND11_MODULE(_garuda_host, m) {
       .def("cancel", &Scheduler::cancel)
       .def("plan", &Scheduler::plan)
       .def("peek_uniform", &Scheduler::peek_uniform)
-      .def("complete", &Scheduler::complete)
+      .def("complete", &Scheduler::complete, py::arg("plan"), py::arg("sampled"), py::arg("elapsed") = -1.0)
+      .def_property_readonly("pacing", [](const Scheduler& s) { return s.pacing(); })
       .def("fail", &Scheduler::fail)
       .def("idle", &Scheduler::idle)
       .def("stats", &Scheduler::stats);

@@ -145,9 +145,10 @@ StepPlan Scheduler::plan() {
   }
 
   const int chunk_cap = config_.prefill_chunk > 0 ? config_.prefill_chunk : config_.max_batch_tokens;
-  auto add_entry = [&](Request& r, int count) {
+  auto add_entry = [&](Request& r, int count, bool decode = false) {
     PlanEntry e;
     e.id = r.id;
+    e.decode = decode;
     e.slot = cache_->slot(r.id);
     e.start = r.fed;
     e.tokens.assign(r.tokens.begin() + r.fed, r.tokens.begin() + r.fed + count);
@@ -180,17 +181,20 @@ StepPlan Scheduler::plan() {
         again = true;
         break;
       }
-      add_entry(r, 1);
+      add_entry(r, 1, true);
       budget -= 1;
     }
     if (again) continue;
+    // while something is decoding, a prompt's portion costs about one decode step
+    const int portion_cap = config_.paced_prefill && !plan.entries.empty() ? std::min(chunk_cap, pacing_.chunk())
+                                                                          : chunk_cap;
 
     // portions of the prompts that are still going in, in order of admission
     for (size_t i = 0; i < running_.size() && budget > 0; ++i) {
       Request& r = running_[i];
       const int remaining = static_cast<int>(r.tokens.size()) - r.fed;
       if (remaining <= 1) continue;
-      const int want = std::min({remaining, budget, chunk_cap});
+      const int want = std::min({remaining, budget, portion_cap});
       const int got = largest_reservable(r, want);
       if (got <= 0) continue;
       cache_->reserve(r.id, r.fed + got);
@@ -205,7 +209,7 @@ StepPlan Scheduler::plan() {
     while (plan.preempted.empty() && static_cast<int>(running_.size()) < config_.max_concurrent &&
            !queue_.empty() && budget > 0 && cache_->free_slots() > 0) {
       Request& q = queue_.front();
-      const int want = std::min({static_cast<int>(q.tokens.size()), budget, chunk_cap});
+      const int want = std::min({static_cast<int>(q.tokens.size()), budget, portion_cap});
       cache_->acquire(q.id);
       int got = largest_reservable(q, want);
       if (q.requeued && !running_.empty() &&
@@ -268,8 +272,17 @@ float Scheduler::peek_uniform(int64_t id) const {
   throw SchedulerError("request " + std::to_string(id) + " is not running");
 }
 
-std::vector<Event> Scheduler::complete(const StepPlan& plan, const std::vector<int32_t>& sampled) {
+std::vector<Event> Scheduler::complete(const StepPlan& plan, const std::vector<int32_t>& sampled,
+                                       double elapsed_seconds) {
   std::vector<Event> events;
+  if (elapsed_seconds >= 0.0) {
+    int decoded = 0, prompt = 0;
+    for (const auto& e : plan.entries) (e.decode ? decoded : prompt) += static_cast<int>(e.tokens.size());
+    if (prompt == 0 && decoded > 0) pacing_.observe_decode(elapsed_seconds);
+    else if (decoded == 0) pacing_.observe_prefill(elapsed_seconds, prompt);
+    else if (pacing_.decode_step >= 0.0 && elapsed_seconds > pacing_.decode_step)
+      pacing_.observe_prefill(elapsed_seconds - pacing_.decode_step, prompt);
+  }
   size_t wanted = 0;
   for (const auto& e : plan.entries) wanted += e.sample ? 1 : 0;
   if (sampled.size() != wanted)

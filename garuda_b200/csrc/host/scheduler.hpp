@@ -66,6 +66,31 @@ struct SchedulerConfig {
   std::vector<int32_t> eos_token_ids;  // generation ends on any of them; empty: none
   int vocab_size = 0;           // prompts are checked against it at submit; 0: unchecked
   bool ignore_eos = false;
+  // While something is decoding, a prompt goes in by portions that cost about one decode step, from
+  // running estimates of both costs (garuda/src/scheduler/mod.rs:305-370); off: prefill_chunk alone.
+  bool paced_prefill = false;
+};
+
+// Running estimates of what a decode step and a prompt token cost (exponential moving averages,
+// weight 0.25 on the newest sample), and the portion that balances them: decode step / prompt
+// token, held to [1, 512]; 32 until both are known (garuda/src/scheduler/mod.rs:319-370).
+struct Pacing {
+  static constexpr double kAlpha = 0.25;
+  static constexpr int kInitial = 32, kMin = 1, kMax = 512;
+  double decode_step = -1.0;    // seconds; negative: not known yet
+  double prefill_token = -1.0;  // seconds per token
+  static void blend(double* slot, double sample) {
+    *slot = *slot < 0.0 ? sample : *slot * (1.0 - kAlpha) + sample * kAlpha;
+  }
+  void observe_decode(double seconds) { blend(&decode_step, seconds); }
+  void observe_prefill(double seconds, int tokens) {
+    if (tokens > 0) blend(&prefill_token, seconds / tokens);
+  }
+  int chunk() const {
+    if (decode_step < 0.0 || !(prefill_token > 0.0)) return kInitial;
+    const double c = decode_step / prefill_token;
+    return c < kMin ? kMin : c > kMax ? kMax : static_cast<int>(c);
+  }
 };
 
 struct SchedulerError : std::runtime_error {
@@ -80,6 +105,7 @@ struct PlanEntry {
   int slot = 0;
   int start = 0;                 // position of the first token
   std::vector<int32_t> tokens;   // the tokens this step feeds
+  bool decode = false;           // the request is decoding: this is its one next token
   bool sample = false;           // logits of the last token are wanted and a token is drawn
   float temperature = 0.f, top_p = 1.f;
   int top_k = 0;
@@ -132,7 +158,13 @@ class Scheduler {
   // generator is not advanced): for a decode step that is launched before that plan is made.
   float peek_uniform(int64_t id) const;
   // The step ran; `sampled` holds one token per entry with sample == true, in order.
-  std::vector<Event> complete(const StepPlan& plan, const std::vector<int32_t>& sampled);
+  // elapsed_seconds: what the step took, for the pacing of prompt portions (negative: not measured).
+  // A step of decode tokens only is a sample of the decode step's cost; a step of prompt tokens
+  // only, of a prompt token's; a mixed step's time beyond the decode step's estimate is its prompt
+  // tokens' (the reference times its two calls apart: garuda/src/scheduler/mod.rs:481-491).
+  std::vector<Event> complete(const StepPlan& plan, const std::vector<int32_t>& sampled,
+                              double elapsed_seconds = -1.0);
+  const Pacing& pacing() const { return pacing_; }
   // The step failed: every request of the plan ends with this error.
   std::vector<Event> fail(const StepPlan& plan, const std::string& message);
   bool idle() const { return running_.empty() && queue_.empty(); }
@@ -167,6 +199,7 @@ class Scheduler {
   int64_t next_id_ = 1;
   uint64_t arrivals_ = 0, admissions_ = 0;
   SchedulerStats stats_;
+  Pacing pacing_;
   std::chrono::steady_clock::time_point started_ = std::chrono::steady_clock::now();
   double manual_time_ = -1.0;          // negative: the steady clock
 };

@@ -44,9 +44,11 @@ class Engine:
                  queue_capacity: int = 256, max_batch_tokens: int = 2048, prefill_chunk: int = 2048,
                  cuda_graphs: bool = True, lookahead: bool = True, device: int = 0, ignore_eos: bool = False,
                  eos_token_id: Union[None, int, Sequence[int]] = None,
-                 request_timeout: Optional[float] = None, ops=None):
+                 request_timeout: Optional[float] = None, paced_prefill: bool = False, ops=None):
         """``request_timeout``: seconds from its submission after which a request, waiting or
-        running, ends with the error "timeout" (garuda/src/scheduler/mod.rs:520); None: no limit."""
+        running, ends with the error "timeout" (garuda/src/scheduler/mod.rs:520); None: no limit.
+        ``paced_prefill``: while something is decoding, prompts go in by portions that cost about
+        one decode step, sized from the measured times of the steps (garuda/src/scheduler/mod.rs:305-370)."""
         if dtype not in _DTYPES:
             raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
         self.dtype = _DTYPES[dtype]
@@ -110,6 +112,8 @@ class Engine:
             eos = tuple(int(t) for t in eos_token_id)
         sc.eos_token_ids = list(eos)
         sc.ignore_eos = bool(ignore_eos)
+        sc.paced_prefill = bool(paced_prefill)
+        self.paced_prefill = bool(paced_prefill)
         self.scheduler = host.Scheduler(sc, self.cache.manager)
         self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda"
         # launch the next greedy decode step before this step's tokens have reached the host
@@ -127,7 +131,8 @@ class Engine:
             kv_cache_bytes=kv_bytes or None, max_concurrent=cfg.server.max_concurrent,
             queue_capacity=cfg.server.queue_capacity, max_batch_tokens=cfg.runtime.max_batch_tokens,
             prefill_chunk=cfg.runtime.prefill_chunk, cuda_graphs=cfg.runtime.cuda_graphs,
-            lookahead=cfg.runtime.lookahead, request_timeout=cfg.server.request_timeout_secs,
+            lookahead=cfg.runtime.lookahead, paced_prefill=cfg.runtime.paced_prefill,
+            request_timeout=cfg.server.request_timeout_secs,
             device=cfg.runtime.device)
         kwargs.update(overrides)
         return cls(cfg.model.path, **kwargs)
@@ -233,6 +238,7 @@ class Engine:
             if not plan.entries:
                 ahead = None
                 continue
+            started = time.perf_counter()
             try:
                 collect, ahead = self._run_plan(plan, ahead)
                 tokens = collect()
@@ -240,7 +246,10 @@ class Engine:
                 ahead = None
                 handle(sched.fail(plan, f"{type(exc).__name__}: {exc}"))
                 continue
-            handle(sched.complete(plan, tokens))
+            # what the step took, for the pacing of prompt portions (with steps launched ahead: the
+            # wait for this step's tokens, about one step in the steady state)
+            elapsed = time.perf_counter() - started if self.paced_prefill else -1.0
+            handle(sched.complete(plan, tokens, elapsed))
         return results
 
     def _run_plan(self, plan, ahead):

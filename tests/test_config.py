@@ -82,7 +82,7 @@ def test_engine_config_toml(tmp_path):
     c = EngineConfig.load(str(p))
     assert c.model.path == "/m" and c.model.dtype == "float32" and c.model.context == 512
     assert c.server.max_concurrent == 2 and c.server.queue_capacity == 256      # default filled in
-    assert c.server.request_timeout_secs == 120
+    assert c.server.request_timeout_secs == 120 and c.runtime.paced_prefill is False
     assert c.sampling.temperature == 0.0 and c.sampling.top_k == 40
     assert EngineConfig.load_or_default(str(tmp_path / "absent.toml")).model.context == 4096
 

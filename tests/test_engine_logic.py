@@ -230,3 +230,19 @@ def test_trace_replay_loop_writes_the_plain_models_logits(tmp_path):
     m = e.cache.manager
     assert m.live_requests == 0 and m.pages_reused > 0
     m.check_invariants()
+
+
+def test_paced_prompt_portions_change_the_steps_and_not_the_tokens():
+    cfg = TINY["A"][0]
+    prompts = [random_tokens("A", n, 90 + n) for n in (3, 60, 45, 2, 70)]
+    plain = engine("A", max_concurrent=3).generate(prompts, SamplingParams.greedy(max_tokens=10))
+    paced = engine("A", max_concurrent=3, paced_prefill=True)
+    res = paced.generate(prompts, SamplingParams.greedy(max_tokens=10))
+    assert [r.tokens for r in res] == [r.tokens for r in plain]
+    p = paced.scheduler.pacing
+    assert p.decode_step > 0 and p.prefill_token > 0 and 1 <= p.chunk <= 512      # both costs were measured
+    unpaced = engine("A", max_concurrent=3)
+    unpaced.generate(prompts, SamplingParams.greedy(max_tokens=10))
+    assert unpaced.scheduler.pacing.decode_step == -1.0                             # nothing is timed without it
+    w = folder_weights(model_dir("A"))
+    assert res[1].tokens == llama_plain.greedy_generate(cfg, w, prompts[1], 10)

@@ -10,11 +10,12 @@ Token, Done, Error = host.EventKind.Token, host.EventKind.Done, host.EventKind.E
 
 
 def make(pages=64, page_size=4, max_concurrent=4, max_batch_tokens=32, prefill_chunk=16, max_context=64,
-         queue_capacity=8, eos=-1, windows=(0,), vocab=100):
+         queue_capacity=8, eos=-1, windows=(0,), vocab=100, paced=False):
     cache = host.CacheManager([host.GroupConfig(pages, w) for w in windows], page_size, max_concurrent, max_context)
     c = host.SchedulerConfig()
     c.max_concurrent, c.queue_capacity, c.max_batch_tokens = max_concurrent, queue_capacity, max_batch_tokens
     c.prefill_chunk, c.max_context, c.eos_token_id, c.vocab_size = prefill_chunk, max_context, eos, vocab
+    c.paced_prefill = paced
     return host.Scheduler(c, cache), cache
 
 
@@ -455,3 +456,60 @@ def test_random_workloads_keep_every_promise(seed):
     st = s.stats()
     assert st.submitted == 25 and st.completed + st.cancelled + st.timed_out + st.failed == 25
     assert reasons & {"length", "eos", "context_full"}
+
+
+def test_paced_prompt_portions_cost_about_one_decode_step():
+    """garuda/src/scheduler/mod.rs:305-370 and :473-491: nothing decoding, a prompt goes in as fast as
+    the budget lets it; beside decoding requests it goes in by portions of decode step / prompt token
+    tokens (32 until both are measured), moving averages with weight 0.25 on the newest sample."""
+    s, cache = make(pages=600, page_size=4, max_batch_tokens=700, prefill_chunk=600, max_context=1000, paced=True)
+    p = s.pacing
+    assert (p.decode_step, p.prefill_token, p.chunk) == (-1.0, -1.0, 32)
+    a = s.submit(list(range(50)), greedy(max_tokens=100))
+    plan = s.plan()
+    assert [(e.id, len(e.tokens), e.decode) for e in plan.entries] == [(a, 50, False)]    # nobody to stall
+    s.complete(plan, [1], 0.050)                            # 1 ms a prompt token
+    assert s.pacing.prefill_token == pytest.approx(0.001) and s.pacing.chunk == 32         # no decode step seen yet
+    b = s.submit([3] * 99, greedy(max_tokens=100))
+    plan = s.plan()
+    assert [(e.id, len(e.tokens), e.decode) for e in plan.entries] == [(a, 1, True), (b, 32, False)]
+    s.complete(plan, [1], 0.040)                            # a mixed step before any decode step was timed: no sample
+    assert s.pacing.decode_step == -1.0 and s.pacing.prefill_token == pytest.approx(0.001)
+    s.cancel(b)
+    plan = s.plan()
+    assert [(e.id, e.decode) for e in plan.entries] == [(a, True)]
+    s.complete(plan, [1], 0.010)                            # a decode step: 10 ms
+    assert s.pacing.decode_step == pytest.approx(0.010) and s.pacing.chunk == 10
+    plan = s.plan()
+    s.complete(plan, [1], 0.020)
+    assert s.pacing.decode_step == pytest.approx(0.0125) and s.pacing.chunk == 12          # 0.75 * 10 + 0.25 * 20
+    c = s.submit([5] * 100, greedy(max_tokens=100))
+    plan = s.plan()
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(a, 1), (c, 12)]
+    s.complete(plan, [1], 0.0125 + 12 * 0.003)              # the time beyond a decode step is the prompt tokens'
+    assert s.pacing.prefill_token == pytest.approx(0.75 * 0.001 + 0.25 * 0.003)
+    assert s.pacing.chunk == 8                              # 12.5 ms / 1.5 ms
+    plan = s.plan()
+    assert [(e.id, e.start, len(e.tokens)) for e in plan.entries] == [(a, 54, 1), (c, 12, 8)]
+    # the estimate is held to [1, 512], and to the configured portion
+    s.complete(plan, [1], 100.0)
+    assert s.pacing.chunk == 1
+    for _ in range(40):
+        plan = s.plan()
+        if len(plan.entries) == 1:
+            break
+        assert len(plan.entries[1].tokens) == 1
+        s.complete(plan, [1] * sum(e.sample for e in plan.entries))
+    s2, _ = make(pages=600, page_size=4, max_batch_tokens=700, prefill_chunk=20, max_context=1000, paced=True)
+    x = s2.submit([1, 2], greedy(max_tokens=100))
+    s2.complete(s2.plan(), [1], 0.001)
+    s2.complete(s2.plan(), [1], 1.0)                        # a decode step of a second
+    y = s2.submit([7] * 300, greedy())
+    plan = s2.plan()
+    assert s2.pacing.chunk == 512 and [(e.id, len(e.tokens)) for e in plan.entries] == [(x, 1), (y, 20)]
+    # without pacing the portion is the configured one
+    s3, _ = make(pages=600, page_size=4, max_batch_tokens=700, prefill_chunk=600, max_context=1000)
+    x = s3.submit([1, 2], greedy(max_tokens=100))
+    s3.complete(s3.plan(), [1], 0.5)
+    y = s3.submit([7] * 300, greedy())
+    assert [(e.id, len(e.tokens)) for e in s3.plan().entries] == [(x, 1), (y, 300)]
