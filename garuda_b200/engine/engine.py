@@ -178,7 +178,8 @@ class Engine:
                  on_token=None, timeout: Optional[float] = None) -> List[GenerationResult]:
         """Generate for every prompt (lists of token ids), batching them
         continuously. ``sampling``: one ``SamplingParams`` for all, or one per
-        prompt. ``on_token(index, token)`` is called as tokens arrive. ``timeout``: seconds
+        prompt. ``on_token(index, token)`` is called as tokens arrive; if it returns False, that
+        request is cancelled (it ends with the error "cancelled" before the next step). ``timeout``: seconds
         after its submission at which a request ends with the error "timeout", checked between
         steps (default: the engine's ``request_timeout``)."""
         if timeout is None:
@@ -205,8 +206,10 @@ class Engine:
                     continue
                 if ev.kind == self._host.EventKind.Token:
                     results[i].tokens.append(ev.token)
-                    if on_token is not None:
-                        on_token(i, ev.token)
+                    # a callback that answers False has gone: its request is cancelled between steps, as
+                    # a closed stream is in the reference (garuda/src/scheduler/mod.rs:616-621)
+                    if on_token is not None and on_token(i, ev.token) is False:
+                        sched.cancel(ev.id)
                 elif ev.kind == self._host.EventKind.Done:
                     results[i].finish_reason = ev.detail
                     live -= 1

@@ -246,3 +246,20 @@ def test_paced_prompt_portions_change_the_steps_and_not_the_tokens():
     assert unpaced.scheduler.pacing.decode_step == -1.0                             # nothing is timed without it
     w = folder_weights(model_dir("A"))
     assert res[1].tokens == llama_plain.greedy_generate(cfg, w, prompts[1], 10)
+
+
+def test_a_callback_that_answers_false_cancels_its_request():
+    prompts = [random_tokens("A", 9, 1), random_tokens("A", 5, 2)]
+    free = engine("A").generate(prompts, SamplingParams.greedy(max_tokens=8))
+    e = engine("A")
+    got = {0: 0, 1: 0}
+
+    def on_token(i, tok):
+        got[i] += 1
+        return not (i == 0 and got[0] == 3)          # the first request's reader leaves after three tokens
+
+    res = e.generate(prompts, SamplingParams.greedy(max_tokens=8), on_token=on_token)
+    assert (res[0].finish_reason, res[0].error, res[0].tokens) == ("error", "cancelled", free[0].tokens[:3])
+    assert (res[1].finish_reason, res[1].tokens) == ("length", free[1].tokens)
+    st = e.stats()
+    assert st["cancelled"] == 1 and st["completed"] == 1 and st["pages_free"] == st["pages_total"]
