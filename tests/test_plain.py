@@ -2,6 +2,7 @@
 (the reference tests the same ones: garuda/src/simd/mod.rs:251-298,
 garuda/src/attention/mod.rs:161-238, garuda/src/runtime/mod.rs:1112-1224)."""
 import numpy as np
+import pytest
 
 from tests.plain import llama_plain as P
 from tests.plain.sampling_plain import Rng, sample, candidates
@@ -86,3 +87,26 @@ def test_generator_matches_the_host_runtime():
         for _ in range(5):
             assert a.next_u64() == b.next_u64()
         assert float(a.next_f32()) == b.next_f32()
+
+
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_the_two_restatements_agree(name):
+    """The numpy restatement (whole sequences, numpy's sums) and the scalar C++ one (token by token
+    over a growing cache, every sum in the reference's order), written apart from the same lines of
+    the reference, give the same logits to 32-bit rounding, in every tiny configuration: both
+    pairings of the rotation, windows, tied and untied heads, groups of one, two and three. Each is
+    as far from the 64-bit result as the other."""
+    from tests.plain import llama_scalar
+    cfg = TINY[name][0]
+    w = folder_weights(model_dir(name))
+    toks = random_tokens(name, min(cfg["max_position_embeddings"], 200), 17)     # beyond every window
+    a = P.forward(cfg, w, toks, np.float32)
+    b = llama_scalar.forward(cfg, w, toks)
+    exact = P.forward(cfg, w, toks, np.float64)
+    top = np.abs(exact).max()
+    assert np.abs(a - b).max() <= 5e-6 * top
+    assert np.abs(a - exact).max() <= 5e-6 * top and np.abs(b - exact).max() <= 5e-6 * top
+    # the same first maximum at every position: greedy decoding agrees token for token
+    assert [P.argmax_first(r) for r in a] == [P.argmax_first(r) for r in b]
+    with pytest.raises(ValueError):
+        llama_scalar.forward(cfg, w, [0, cfg["vocab_size"]])
