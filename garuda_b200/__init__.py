@@ -9,9 +9,9 @@ from .config import LlamaConfig, ConfigError, register_architecture, registered_
 from .config.engine_config import EngineConfig, parse_size
 from .sampling import SamplingParams
 from . import parts, models
-from .engine import Engine, GenerationResult, StepEntry, StepRunner, StepError
+from .engine import Engine, GenerationResult, StreamEvent, StepEntry, StepRunner, StepError
 from .weights import write_random_model, WeightError
 
-__all__ = ["Engine", "EngineConfig", "SamplingParams", "GenerationResult", "StepEntry", "StepRunner",
+__all__ = ["Engine", "EngineConfig", "SamplingParams", "GenerationResult", "StreamEvent", "StepEntry", "StepRunner",
            "StepError", "LlamaConfig", "ConfigError", "WeightError", "write_random_model",
            "register_architecture", "registered_architectures", "parse_size", "parts", "models"]

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import time
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Union
+from typing import Dict, Iterator, List, Optional, Sequence, Union
 
 import torch
 
@@ -35,6 +35,16 @@ class GenerationResult:
     tokens: List[int] = field(default_factory=list)
     finish_reason: str = ""          # "length" | "context_full" | "eos" | "error"
     error: Optional[str] = None      # with "error": the message ("cancelled", "timeout", a failed step's, ...)
+
+
+@dataclass
+class StreamEvent:
+    """One event of a request's output (garuda/src/scheduler/mod.rs:67-71)."""
+    index: int                       # which prompt of the call
+    kind: str                        # "token" | "done" | "error"
+    token: Optional[int] = None
+    detail: Optional[str] = None     # done: "length" | "context_full" | "eos"; error: the message
+    request: int = -1                # the scheduler's id of the request (``Engine.scheduler.cancel``)
 
 
 class Engine:
@@ -182,6 +192,28 @@ class Engine:
         request is cancelled (it ends with the error "cancelled" before the next step). ``timeout``: seconds
         after its submission at which a request ends with the error "timeout", checked between
         steps (default: the engine's ``request_timeout``)."""
+        results = [GenerationResult() for _ in prompts]
+        for ev in self.stream(prompts, sampling, timeout=timeout):
+            r = results[ev.index]
+            if ev.kind == "token":
+                r.tokens.append(ev.token)
+                # a callback that answers False has gone: its request is cancelled between steps, as
+                # a closed stream is in the reference (garuda/src/scheduler/mod.rs:616-621)
+                if on_token is not None and on_token(ev.index, ev.token) is False:
+                    self.scheduler.cancel(ev.request)
+            elif ev.kind == "done":
+                r.finish_reason = ev.detail
+            else:
+                r.finish_reason, r.error = "error", ev.detail
+        return results
+
+    def stream(self, prompts: Sequence[Sequence[int]],
+               sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None,
+               timeout: Optional[float] = None) -> Iterator[StreamEvent]:
+        """The events of ``generate`` as they happen, in the reference's manner
+        (garuda/src/scheduler/mod.rs:67-71): for every prompt its tokens, then one ``done`` (with
+        the reason) or ``error`` (with the message). Closing the iterator before its end, or
+        dropping it, cancels what is still running (a dropped handle cancels: :92-109)."""
         if timeout is None:
             timeout = self.request_timeout
         elif not timeout > 0:
@@ -192,68 +224,67 @@ class Engine:
             sampling = [sampling] * len(prompts)
         if len(sampling) != len(prompts):
             raise ConfigError(f"{len(sampling)} sampling settings for {len(prompts)} prompts")
-        results = [GenerationResult() for _ in prompts]
+        return self._events(prompts, sampling, float(timeout or 0.0))
+
+    def _events(self, prompts, sampling, timeout: float):
         index_of: Dict[int, int] = {}
         pending = list(range(len(prompts)))
         sched = self.scheduler
-        live = 0
+        kinds = self._host.EventKind
 
-        def handle(events):
-            nonlocal live
+        def told(events):
             for ev in events:
                 i = index_of.get(ev.id)
                 if i is None:
                     continue
-                if ev.kind == self._host.EventKind.Token:
-                    results[i].tokens.append(ev.token)
-                    # a callback that answers False has gone: its request is cancelled between steps, as
-                    # a closed stream is in the reference (garuda/src/scheduler/mod.rs:616-621)
-                    if on_token is not None and on_token(i, ev.token) is False:
-                        sched.cancel(ev.id)
-                elif ev.kind == self._host.EventKind.Done:
-                    results[i].finish_reason = ev.detail
-                    live -= 1
+                if ev.kind == kinds.Token:
+                    yield StreamEvent(i, "token", token=ev.token, request=ev.id)
                 else:
-                    results[i].finish_reason = "error"
-                    results[i].error = ev.detail
-                    live -= 1
+                    del index_of[ev.id]
+                    yield StreamEvent(i, "done" if ev.kind == kinds.Done else "error", detail=ev.detail,
+                                      request=ev.id)
 
         ahead = None      # (ids, Pending): a decode step launched before its plan was made
-        while pending or live:
-            while pending:
-                i = pending[0]
-                try:
-                    rid = sched.submit(list(map(int, prompts[i])), self._host_params(sampling[i]), 0,
-                                       float(timeout or 0.0))
-                except self._host.Busy:
-                    break      # the queue is full: run steps, then submit the rest
-                except (self._host.SchedulerError, ConfigError) as e:
-                    results[i].finish_reason, results[i].error = "error", str(e)
+        try:
+            while pending or index_of:
+                while pending:
+                    i = pending[0]
+                    try:
+                        rid = sched.submit(list(map(int, prompts[i])), self._host_params(sampling[i]), 0, timeout)
+                    except self._host.Busy:
+                        break      # the queue is full: run steps, then submit the rest
+                    except (self._host.SchedulerError, ConfigError) as e:
+                        pending.pop(0)
+                        yield StreamEvent(i, "error", detail=str(e))
+                        continue
+                    index_of[rid] = i
                     pending.pop(0)
+                if not index_of:
                     continue
-                index_of[rid] = i
-                live += 1
-                pending.pop(0)
-            if not live:
-                continue
-            plan = sched.plan()
-            handle(plan.events)
-            if not plan.entries:
-                ahead = None
-                continue
-            started = time.perf_counter()
-            try:
-                collect, ahead = self._run_plan(plan, ahead)
-                tokens = collect()
-            except Exception as exc:     # the step failed as a whole: its requests end with the error
-                ahead = None
-                handle(sched.fail(plan, f"{type(exc).__name__}: {exc}"))
-                continue
-            # what the step took, for the pacing of prompt portions (with steps launched ahead: the
-            # wait for this step's tokens, about one step in the steady state)
-            elapsed = time.perf_counter() - started if self.paced_prefill else -1.0
-            handle(sched.complete(plan, tokens, elapsed))
-        return results
+                plan = sched.plan()
+                yield from told(plan.events)
+                if not plan.entries:
+                    ahead = None
+                    continue
+                started = time.perf_counter()
+                try:
+                    collect, ahead = self._run_plan(plan, ahead)
+                    tokens = collect()
+                except Exception as exc:     # the step failed as a whole: its requests end with the error
+                    ahead = None
+                    yield from told(sched.fail(plan, f"{type(exc).__name__}: {exc}"))
+                    continue
+                # what the step took, for the pacing of prompt portions (with steps launched ahead: the
+                # wait for this step's tokens, about one step in the steady state)
+                elapsed = time.perf_counter() - started if self.paced_prefill else -1.0
+                yield from told(sched.complete(plan, tokens, elapsed))
+        finally:
+            # left before the end: nobody reads what is still running, so it is cancelled, and the
+            # scheduler gives back what it held (the next plan does that; it runs no step)
+            if index_of:
+                for rid in index_of:
+                    sched.cancel(rid)
+                sched.plan()
 
     def _run_plan(self, plan, ahead):
         """Runs a plan's entries and starts drawing their tokens. Returns ``(collect,

@@ -263,3 +263,33 @@ def test_a_callback_that_answers_false_cancels_its_request():
     assert (res[1].finish_reason, res[1].tokens) == ("length", free[1].tokens)
     st = e.stats()
     assert st["cancelled"] == 1 and st["completed"] == 1 and st["pages_free"] == st["pages_total"]
+
+
+def test_events_stream_as_they_happen_and_leaving_early_cancels():
+    """garuda/src/scheduler/mod.rs:67-71 (tokens, then one Done or Error per request) and :92-109 (a
+    dropped handle cancels)."""
+    prompts = [random_tokens("A", 9, 1), random_tokens("A", 5, 2), []]
+    free = engine("A").generate(prompts[:2], SamplingParams.greedy(max_tokens=6))
+    e = engine("A")
+    events = list(e.stream(prompts, SamplingParams.greedy(max_tokens=6)))
+    assert (events[0].index, events[0].kind) == (2, "error") and "empty" in events[0].detail     # refused at once
+    for i in (0, 1):
+        mine = [ev for ev in events if ev.index == i]
+        assert [ev.kind for ev in mine] == ["token"] * 6 + ["done"] and mine[-1].detail == "length"
+        assert [ev.token for ev in mine[:-1]] == free[i].tokens
+        assert len({ev.request for ev in mine}) == 1
+    # the two requests run together: their tokens alternate
+    assert [ev.index for ev in events[1:5]] == [0, 1, 0, 1]
+    # leaving after a few events cancels what is running, and everything goes back
+    it = e.stream(prompts[:2], SamplingParams.greedy(max_tokens=50))
+    seen = [next(it) for _ in range(5)]
+    assert all(ev.kind == "token" for ev in seen)
+    it.close()
+    st = e.stats()
+    assert st["running"] == 0 and st["queued"] == 0 and st["cancelled"] == 2
+    assert st["pages_free"] == st["pages_total"]
+    e.cache.manager.check_invariants()
+    again = e.generate(prompts[:2], SamplingParams.greedy(max_tokens=6))          # and the engine goes on
+    assert [r.tokens for r in again] == [r.tokens for r in free]
+    with pytest.raises(Exception):
+        e.stream(prompts[:2], [SamplingParams.greedy()])                          # refused when called, not later
