@@ -185,15 +185,18 @@ class Engine:
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None,
-                 on_token=None, timeout: Optional[float] = None) -> List[GenerationResult]:
+                 on_token=None, timeout: Optional[float] = None,
+                 priority: Union[int, Sequence[int]] = 0) -> List[GenerationResult]:
         """Generate for every prompt (lists of token ids), batching them
         continuously. ``sampling``: one ``SamplingParams`` for all, or one per
         prompt. ``on_token(index, token)`` is called as tokens arrive; if it returns False, that
         request is cancelled (it ends with the error "cancelled" before the next step). ``timeout``: seconds
         after its submission at which a request ends with the error "timeout", checked between
-        steps (default: the engine's ``request_timeout``)."""
+        steps (default: the engine's ``request_timeout``). ``priority``: one for all or one per
+        prompt; among waiting requests the higher goes first, equal ones in order of arrival
+        (garuda/src/scheduler/mod.rs:138-148)."""
         results = [GenerationResult() for _ in prompts]
-        for ev in self.stream(prompts, sampling, timeout=timeout):
+        for ev in self.stream(prompts, sampling, timeout=timeout, priority=priority):
             r = results[ev.index]
             if ev.kind == "token":
                 r.tokens.append(ev.token)
@@ -209,7 +212,7 @@ class Engine:
 
     def stream(self, prompts: Sequence[Sequence[int]],
                sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None,
-               timeout: Optional[float] = None) -> Iterator[StreamEvent]:
+               timeout: Optional[float] = None, priority: Union[int, Sequence[int]] = 0) -> Iterator[StreamEvent]:
         """The events of ``generate`` as they happen, in the reference's manner
         (garuda/src/scheduler/mod.rs:67-71): for every prompt its tokens, then one ``done`` (with
         the reason) or ``error`` (with the message). Closing the iterator before its end, or
@@ -224,9 +227,12 @@ class Engine:
             sampling = [sampling] * len(prompts)
         if len(sampling) != len(prompts):
             raise ConfigError(f"{len(sampling)} sampling settings for {len(prompts)} prompts")
-        return self._events(prompts, sampling, float(timeout or 0.0))
+        priorities = [int(priority)] * len(prompts) if isinstance(priority, int) else [int(p) for p in priority]
+        if len(priorities) != len(prompts):
+            raise ConfigError(f"{len(priorities)} priorities for {len(prompts)} prompts")
+        return self._events(prompts, sampling, float(timeout or 0.0), priorities)
 
-    def _events(self, prompts, sampling, timeout: float):
+    def _events(self, prompts, sampling, timeout: float, priorities):
         index_of: Dict[int, int] = {}
         pending = list(range(len(prompts)))
         sched = self.scheduler
@@ -250,7 +256,8 @@ class Engine:
                 while pending:
                     i = pending[0]
                     try:
-                        rid = sched.submit(list(map(int, prompts[i])), self._host_params(sampling[i]), 0, timeout)
+                        rid = sched.submit(list(map(int, prompts[i])), self._host_params(sampling[i]),
+                                           priorities[i], timeout)
                     except self._host.Busy:
                         break      # the queue is full: run steps, then submit the rest
                     except (self._host.SchedulerError, ConfigError) as e:

@@ -293,3 +293,20 @@ def test_events_stream_as_they_happen_and_leaving_early_cancels():
     assert [r.tokens for r in again] == [r.tokens for r in free]
     with pytest.raises(Exception):
         e.stream(prompts[:2], [SamplingParams.greedy()])                          # refused when called, not later
+
+
+def test_priorities_decide_who_waits():
+    # one request runs at a time and all four wait when the first plan is made: the higher priority goes
+    # first, equal ones keep their order (garuda/src/scheduler/mod.rs:138-148, :1052-1112)
+    prompts = [random_tokens("A", 4, i) for i in range(4)]
+    e = engine("A", max_concurrent=1)
+    order = []
+    for ev in e.stream(prompts, SamplingParams.greedy(max_tokens=2), priority=[0, 0, 5, 0]):
+        if ev.kind == "done":
+            order.append(ev.index)
+    assert order == [2, 0, 1, 3]
+    solo = engine("A").generate(prompts, SamplingParams.greedy(max_tokens=2))
+    res = e.generate(prompts, SamplingParams.greedy(max_tokens=2), priority=[0, 1, 2, 3])
+    assert [r.tokens for r in res] == [r.tokens for r in solo]
+    with pytest.raises(Exception):
+        e.generate(prompts, priority=[1, 2])
