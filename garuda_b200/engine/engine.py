@@ -227,7 +227,7 @@ class Engine:
             sampling = [sampling] * len(prompts)
         if len(sampling) != len(prompts):
             raise ConfigError(f"{len(sampling)} sampling settings for {len(prompts)} prompts")
-        priorities = [int(priority)] * len(prompts) if isinstance(priority, int) else [int(p) for p in priority]
+        priorities = [int(p) for p in priority] if hasattr(priority, "__iter__") else [int(priority)] * len(prompts)
         if len(priorities) != len(prompts):
             raise ConfigError(f"{len(priorities)} priorities for {len(prompts)} prompts")
         return self._events(prompts, sampling, float(timeout or 0.0), priorities)
